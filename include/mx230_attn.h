@@ -1,0 +1,263 @@
+/*
+ * mx230_attn.h -- C ABI of the B200 (sm_100a) attention library.
+ *
+ * Drop-in boundary for the attention path of glaucomaa/mx230.  The reference has
+ * no FFI layer: its Rust host looks CUDA kernels up by C symbol name in embedded
+ * PTX and launches them with cudarc.  Each entry point below therefore replaces
+ * one reference kernel symbol (plus its Rust launch wrapper) and keeps that
+ * kernel's argument list, in order, after two leading arguments:
+ *
+ *     handle  per-device library state (workspace, status words); replaces the
+ *             CudaFunction handle tables (02-flash-attention/src/main.rs:24-28,
+ *             92-98, 392-415; 03-llm-engine/src/gpu.rs:982-1098)
+ *     stream  the caller's CUstream / cudaStream_t, as void*; replaces
+ *             `stream.launch_builder(..)` (02-flash-attention/src/main.rs:47-64)
+ *
+ * Conventions
+ *  - every pointer argument is a DEVICE pointer unless named `*_host`;
+ *  - all work is enqueued on `stream`; no entry point synchronises, allocates or
+ *    frees on the launch path (mx230_create / mx230_reserve / mx230_destroy /
+ *    mx230_check_status are the only calls that do), so the decode step stays
+ *    capturable in a CUDA graph as in 03-llm-engine/src/gpu.rs:4024-4054;
+ *  - the caller owns every buffer it passes; head_dim must be 64;
+ *  - return value: MX230_OK or an MX230_ERR_* code; mx230_last_error() returns a
+ *    message for the calling thread.  The reference panics on a failed launch
+ *    (02-flash-attention/src/main.rs:50,87); a binding should `.expect()` the code.
+ *  - one handle is used by one host thread at a time; one handle per device.
+ */
+#ifndef MX230_ATTN_H
+#define MX230_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MX230_ABI_VERSION 1
+
+enum {
+    MX230_OK = 0,
+    MX230_ERR_INVALID_ARG = 1,   /* null pointer, negative size, misalignment */
+    MX230_ERR_UNSUPPORTED = 2,   /* e.g. head_dim != 64, n_head % n_kv_head != 0 */
+    MX230_ERR_WORKSPACE = 3,     /* workspace too small: call mx230_reserve first */
+    MX230_ERR_CUDA = 4,          /* a CUDA runtime/driver call failed */
+    MX230_ERR_DEVICE_STATUS = 5, /* a kernel reported a bounded-wait timeout */
+    MX230_ERR_NO_DEVICE = 6      /* no usable sm_100 device */
+};
+
+/* int8 KV score arithmetic of the decode/prefill kernels over an int8 cache */
+enum {
+    MX230_Q8_SCORE_REF = 0,  /* q quantised per head to int8 and integer dots, exactly the
+                                reference kernel's arithmetic (llm.cu:1349-1386) */
+    MX230_Q8_SCORE_EXACT = 1 /* fp32 q against dequantised K (scale*code + beta) */
+};
+
+enum {
+    MX230_OPT_Q8_SCORE_MODE = 1, /* MX230_Q8_SCORE_* (default REF) */
+    MX230_OPT_DECODE_CHUNK = 2   /* keys per decode CTA; 0 = automatic */
+};
+
+typedef struct mx230_handle mx230_handle;
+
+/* ---- library / handle ------------------------------------------------------ */
+int mx230_abi_version(void);
+const char *mx230_last_error(void);
+const char *mx230_status_string(int code);
+
+/* Creates the per-device state and a workspace of `workspace_bytes` on `device`.
+ * Replaces CudaContext::new + load_ptx (common/src/lib.rs:11-18). */
+int mx230_create(mx230_handle **out, int device, size_t workspace_bytes);
+int mx230_destroy(mx230_handle *h);
+/* Grows the workspace to at least `bytes` (synchronises the device; not for the launch path). */
+int mx230_reserve(mx230_handle *h, size_t bytes);
+int mx230_set_option(mx230_handle *h, int option, int value);
+/* Workspace needed by the fp32-in/fp32-out flash entry points (bf16 operand staging). */
+size_t mx230_flash_workspace_bytes(int batch_heads, int n, int with_backward);
+/* Workspace needed by decode (split-KV partial triples). */
+size_t mx230_decode_workspace_bytes(int n_seq, int n_head, int max_splits);
+/* Synchronises `stream`, reads and clears the device status words. */
+int mx230_check_status(mx230_handle *h, void *stream);
+/* Number of kernels launched through this handle so far. */
+long long mx230_launch_count(const mx230_handle *h);
+
+/* ---- 02-flash-attention ----------------------------------------------------
+ * Tensors are `batch_heads` independent heads laid out [batch_heads][n][64] fp32,
+ * contiguous; batch_heads = 1 is exactly the reference call.  Scale = 1/sqrt(64).
+ * Operands are rounded to bf16, products accumulate in fp32 on the tensor cores. */
+
+/* attn_flash(Q,K,V,O,N,causal): 02-flash-attention/kernels/attention_flash.cu:91-94,
+ * run_flash 02-flash-attention/src/main.rs:68-88 */
+int mx230_attn_flash(mx230_handle *h, void *stream, const float *Q, const float *K,
+                     const float *V, float *O, int batch_heads, int n, int causal);
+/* attn_flash_lse(Q,K,V,O,L,N,causal): attention_flash.cu:97-100, run_flash_lse
+ * main.rs:102-123.  L[i] = m_i + ln(l_i) (natural log of the scaled scores). */
+int mx230_attn_flash_lse(mx230_handle *h, void *stream, const float *Q, const float *K,
+                         const float *V, float *O, float *L, int batch_heads, int n, int causal);
+/* attn_bwd_preprocess(dO,O,Delta,N): attention_bwd.cu:32-44, run_preprocess main.rs:126-143 */
+int mx230_attn_bwd_preprocess(mx230_handle *h, void *stream, const float *dO, const float *O,
+                              float *Delta, int batch_heads, int n);
+/* attn_bwd_dq(Q,K,V,dO,L,Delta,dQ,N,causal): attention_bwd.cu:96-158 */
+int mx230_attn_bwd_dq(mx230_handle *h, void *stream, const float *Q, const float *K,
+                      const float *V, const float *dO, const float *L, const float *Delta,
+                      float *dQ, int batch_heads, int n, int causal);
+/* attn_bwd_dkv(Q,K,V,dO,L,Delta,dK,dV,N,causal): attention_bwd.cu:165-243 */
+int mx230_attn_bwd_dkv(mx230_handle *h, void *stream, const float *Q, const float *K,
+                       const float *V, const float *dO, const float *L, const float *Delta,
+                       float *dK, float *dV, int batch_heads, int n, int causal);
+/* run_bwd_flash (main.rs:179-210): the dQ pass then the dK/dV pass, one operand staging. */
+int mx230_attn_bwd_flash(mx230_handle *h, void *stream, const float *Q, const float *K,
+                         const float *V, const float *dO, const float *L, const float *Delta,
+                         float *dQ, float *dK, float *dV, int batch_heads, int n, int causal);
+
+/* bf16-resident forms (no counterpart in the reference, whose tensors are fp32):
+ * operands already rounded to bf16 [batch_heads][n][64]; outputs stay fp32. */
+int mx230_cast_bf16(mx230_handle *h, void *stream, const float *src, void *dst_bf16, size_t count);
+int mx230_attn_flash_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb,
+                          const void *Vb, float *O, float *L_or_null, int batch_heads, int n,
+                          int causal);
+int mx230_attn_bwd_flash_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb,
+                              const void *Vb, const void *dOb, const float *L, const float *Delta,
+                              float *dQ, float *dK, float *dV, int batch_heads, int n, int causal);
+
+/* ---- 03-llm-engine: per-layer attention step (RoPE -> KV write -> attention) --
+ * qkv row layout: [n_head*64 Q | n_kv_head*64 K | n_kv_head*64 V] fp32
+ * (03-llm-engine/src/model.rs:95-103).  Cache layouts as the reference:
+ * fp32  k,v   [slot][n_kv_head*64]
+ * int8  kq,vq [slot][n_kv_head*64] codes; ks,vs,kb,vb [slot][n_kv_head] fp32
+ * (03-llm-engine/src/gpu.rs:188-205).  kb == vb == NULL selects the symmetric
+ * absmax/127 format (scale only) instead of the reference's affine (scale, beta).
+ * Paged variants translate position t to row bt[t/bs]*bs + t%bs (llm.cu:959-963). */
+
+/* rope / rope_dyn / rope_batch / rope_seqpos: llm.cu:1072-1117,1513-1530 */
+int mx230_rope(mx230_handle *h, void *stream, float *qkv, int pos, int n_head, int n_kv_head,
+               int head_dim, float theta);
+int mx230_rope_dyn(mx230_handle *h, void *stream, float *qkv, const int *pos_ptr, int n_head,
+                   int n_kv_head, int head_dim, float theta);
+int mx230_rope_batch(mx230_handle *h, void *stream, float *qkv, int pos0, int n_tok, int n_head,
+                     int n_kv_head, int head_dim, int stride, float theta);
+int mx230_rope_seqpos(mx230_handle *h, void *stream, float *qkv, const int *pos, int n_seq,
+                      int n_head, int n_kv_head, int head_dim, int stride, float theta);
+
+/* fp32 KV write: copy_kv_dyn / copy_kv_paged_dyn (llm.cu:965-986), copy_kv_batch /
+ * copy_kv_batch_paged (llm.cu:3635-3655), copy_kv_seqpos (llm.cu:1491-1501);
+ * mx230_copy_kv replaces the two memcpy_dtod of 03-llm-engine/src/gpu.rs:2594-2605. */
+int mx230_copy_kv(mx230_handle *h, void *stream, float *kcache, float *vcache, const float *qkv,
+                  int pos, int q_dim, int kv_dim);
+int mx230_copy_kv_dyn(mx230_handle *h, void *stream, float *kcache, float *vcache,
+                      const float *qkv, const int *pos_ptr, int q_dim, int kv_dim);
+int mx230_copy_kv_paged_dyn(mx230_handle *h, void *stream, float *kcache, float *vcache,
+                            const float *qkv, const int *pos_ptr, int q_dim, int kv_dim,
+                            const int *bt, int bs);
+int mx230_copy_kv_batch(mx230_handle *h, void *stream, float *kcache, float *vcache,
+                        const float *qkv, int pos0, int n_tok, int q_dim, int kv_dim, int stride);
+int mx230_copy_kv_batch_paged(mx230_handle *h, void *stream, float *kcache, float *vcache,
+                              const float *qkv, int pos0, int n_tok, int q_dim, int kv_dim,
+                              int stride, const int *bt, int bs);
+int mx230_copy_kv_seqpos(mx230_handle *h, void *stream, float *kcache, float *vcache,
+                         const float *qkv, const int *pos, int n_seq, int q_dim, int kv_dim,
+                         int qkv_stride, const int *tables, int block_size, int n_log);
+
+/* int8 quantize-on-write, bit-exact with quant_affine (llm.cu:1137-1149):
+ * quantize_kv / _dyn / _paged_dyn (llm.cu:1176-1203), _batch / _batch_paged
+ * (llm.cu:1205-1240), _seqpos (llm.cu:1503-1510).  n_tok / n_seq are the grid.y
+ * of the reference launches (gpu.rs:3292-3296,3585-3589). */
+int mx230_quantize_kv(mx230_handle *h, void *stream, int8_t *kq, int8_t *vq, float *ks, float *vs,
+                      float *kb, float *vb, const float *qkv, int pos, int q_dim, int n_kv_head,
+                      int head_dim);
+int mx230_quantize_kv_dyn(mx230_handle *h, void *stream, int8_t *kq, int8_t *vq, float *ks,
+                          float *vs, float *kb, float *vb, const float *qkv, const int *pos_ptr,
+                          int q_dim, int n_kv_head, int head_dim);
+int mx230_quantize_kv_paged_dyn(mx230_handle *h, void *stream, int8_t *kq, int8_t *vq, float *ks,
+                                float *vs, float *kb, float *vb, const float *qkv,
+                                const int *pos_ptr, int q_dim, int n_kv_head, int head_dim,
+                                const int *bt, int bs);
+int mx230_quantize_kv_batch(mx230_handle *h, void *stream, int8_t *kq, int8_t *vq, float *ks,
+                            float *vs, float *kb, float *vb, const float *qkv, int pos0, int n_tok,
+                            int q_dim, int n_kv_head, int head_dim, int stride);
+int mx230_quantize_kv_batch_paged(mx230_handle *h, void *stream, int8_t *kq, int8_t *vq, float *ks,
+                                  float *vs, float *kb, float *vb, const float *qkv, int pos0,
+                                  int n_tok, int q_dim, int n_kv_head, int head_dim, int stride,
+                                  const int *bt, int bs);
+int mx230_quantize_kv_seqpos(mx230_handle *h, void *stream, int8_t *kq, int8_t *vq, float *ks,
+                             float *vs, float *kb, float *vb, const float *qkv, const int *pos,
+                             int n_seq, int q_dim, int n_kv_head, int head_dim, int qkv_stride,
+                             const int *tables, int block_size, int n_log);
+
+/* decode attention over an fp32 cache, keys 0..=t_cur: attn_decode / _dyn / _paged /
+ * _paged_dyn (llm.cu:1296-1325), attn_decode_batched (llm.cu:1468-1476).
+ * Unlike the reference (shared s[2048], llm.cu:1251) the context is unbounded. */
+int mx230_attn_decode(mx230_handle *h, void *stream, float *out, const float *qkv,
+                      const float *kcache, const float *vcache, int t_cur, int n_head,
+                      int n_kv_head, int head_dim);
+int mx230_attn_decode_dyn(mx230_handle *h, void *stream, float *out, const float *qkv,
+                          const float *kcache, const float *vcache, const int *pos_ptr,
+                          int n_head, int n_kv_head, int head_dim);
+int mx230_attn_decode_paged(mx230_handle *h, void *stream, float *out, const float *qkv,
+                            const float *kcache, const float *vcache, int t_cur, int n_head,
+                            int n_kv_head, int head_dim, const int *bt, int bs);
+int mx230_attn_decode_paged_dyn(mx230_handle *h, void *stream, float *out, const float *qkv,
+                                const float *kcache, const float *vcache, const int *pos_ptr,
+                                int n_head, int n_kv_head, int head_dim, const int *bt, int bs);
+int mx230_attn_decode_batched(mx230_handle *h, void *stream, float *out, const float *qkv,
+                              const float *kcache, const float *vcache, const int *pos, int n_seq,
+                              int n_head, int n_kv_head, int head_dim, const int *tables,
+                              int block_size, int n_log, int qkv_stride, int out_stride);
+
+/* the same over an int8 cache: attn_decode_q8 / _dyn / _paged / _paged_dyn
+ * (llm.cu:1420-1458), attn_decode_q8_batched (llm.cu:1478-1487) */
+int mx230_attn_decode_q8(mx230_handle *h, void *stream, float *out, const float *qkv,
+                         const int8_t *kq, const int8_t *vq, const float *ks, const float *vs,
+                         const float *kb, const float *vb, int t_cur, int n_head, int n_kv_head,
+                         int head_dim);
+int mx230_attn_decode_q8_dyn(mx230_handle *h, void *stream, float *out, const float *qkv,
+                             const int8_t *kq, const int8_t *vq, const float *ks, const float *vs,
+                             const float *kb, const float *vb, const int *pos_ptr, int n_head,
+                             int n_kv_head, int head_dim);
+int mx230_attn_decode_q8_paged(mx230_handle *h, void *stream, float *out, const float *qkv,
+                               const int8_t *kq, const int8_t *vq, const float *ks,
+                               const float *vs, const float *kb, const float *vb, int t_cur,
+                               int n_head, int n_kv_head, int head_dim, const int *bt, int bs);
+int mx230_attn_decode_q8_paged_dyn(mx230_handle *h, void *stream, float *out, const float *qkv,
+                                   const int8_t *kq, const int8_t *vq, const float *ks,
+                                   const float *vs, const float *kb, const float *vb,
+                                   const int *pos_ptr, int n_head, int n_kv_head, int head_dim,
+                                   const int *bt, int bs);
+int mx230_attn_decode_q8_batched(mx230_handle *h, void *stream, float *out, const float *qkv,
+                                 const int8_t *kq, const int8_t *vq, const float *ks,
+                                 const float *vs, const float *kb, const float *vb, const int *pos,
+                                 int n_seq, int n_head, int n_kv_head, int head_dim,
+                                 const int *tables, int block_size, int n_log, int qkv_stride,
+                                 int out_stride);
+
+/* Batched decode over per-sequence contiguous cache slabs (no counterpart in the
+ * reference, which batches only through block tables): sequence s reads cache
+ * rows [s*seq_rows, s*seq_rows + pos[s]].  fp32 cache when kq == NULL. */
+int mx230_attn_decode_slab(mx230_handle *h, void *stream, float *out, const float *qkv,
+                           const float *kcache, const float *vcache, const int8_t *kq,
+                           const int8_t *vq, const float *ks, const float *vs, const float *kb,
+                           const float *vb, const int *pos, int n_seq, int n_head, int n_kv_head,
+                           int head_dim, long long seq_rows, int qkv_stride, int out_stride);
+
+/* Split-KV decode across GPUs (no counterpart in the reference, which is single
+ * device): each rank attends its own key range [t0, t1) of every sequence slab
+ * and emits the unnormalised triple per (sequence, query head):
+ *   part_m [n_seq][n_head], part_l [n_seq][n_head], part_acc [n_seq][n_head][64]
+ * with acc = sum_j exp(s_j - m) v_j.  After an all-gather of the triples,
+ * mx230_merge_partials combines `parts` of them by log-sum-exp:
+ *   m = max m_r, l = sum l_r e^(m_r-m), out = sum acc_r e^(m_r-m) / l.
+ * Gathered layout: m,l [parts][rows]; acc [parts][rows][64]; out [rows][64]. */
+int mx230_attn_decode_partial(mx230_handle *h, void *stream, float *part_m, float *part_l,
+                              float *part_acc, const float *qkv, const float *kcache,
+                              const float *vcache, const int8_t *kq, const int8_t *vq,
+                              const float *ks, const float *vs, const float *kb, const float *vb,
+                              int t0, int t1, int n_seq, int n_head, int n_kv_head, int head_dim,
+                              long long seq_rows, int qkv_stride);
+int mx230_merge_partials(mx230_handle *h, void *stream, float *out, const float *m,
+                         const float *l, const float *acc, int parts, int rows, int head_dim);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MX230_ATTN_H */

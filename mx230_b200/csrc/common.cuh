@@ -1,0 +1,313 @@
+// Shared declarations for the mx230 attention library (sm_100a only).
+//
+// Host side: status codes, the per-device handle, error plumbing.
+// Device side: thin inline-PTX wrappers for mbarrier, TMA (cp.async.bulk.tensor,
+// plain per-CTA loads only), tensor memory (tcgen05.alloc/ld/st) and the 5th-gen
+// tensor-core MMA (tcgen05.mma + tcgen05.commit).
+//
+// Every device-side wait is bounded: a waiter polls for at most WAIT_LIMIT_NS
+// and then records an error in the handle's status word and abandons the tile,
+// so a protocol bug shows up as a status code, never as a hung GPU.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/mx230_attn.h"
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+typedef CUresult (*mx230_encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                          const cuuint64_t *, const cuuint64_t *,
+                                          const cuuint32_t *, const cuuint32_t *,
+                                          CUtensorMapInterleave, CUtensorMapSwizzle,
+                                          CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct mx230_handle {
+    int device;
+    int sm_count;
+    void *ws;              // workspace: bf16 operand staging / split-KV partials
+    size_t ws_bytes;
+    int *status_dev;       // [4] device status words (0 = ok)
+    unsigned *counters;    // split-KV arrival counters (self-resetting)
+    size_t n_counters;
+    int q8_score_mode;     // MX230_Q8_SCORE_*
+    int decode_chunk;      // keys per decode CTA (0 = automatic)
+    long long launches;    // kernels launched through this handle
+    mx230_encode_tiled_fn encode_tiled;
+};
+
+void mx230_set_error(const char *fmt, ...);
+int mx230_fail(int code, const char *fmt, ...);
+
+#define MX_CHECK_CUDA(expr)                                                                  \
+    do {                                                                                     \
+        cudaError_t _e = (expr);                                                             \
+        if (_e != cudaSuccess)                                                               \
+            return mx230_fail(MX230_ERR_CUDA, "%s: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                              __FILE__, __LINE__);                                           \
+    } while (0)
+
+#define MX_REQUIRE(cond, code, ...)                        \
+    do {                                                   \
+        if (!(cond)) return mx230_fail(code, __VA_ARGS__); \
+    } while (0)
+
+// Checks the launch and counts it on the handle.
+#define MX_LAUNCHED(h)                                                                      \
+    do {                                                                                    \
+        cudaError_t _e = cudaGetLastError();                                                \
+        if (_e != cudaSuccess)                                                              \
+            return mx230_fail(MX230_ERR_CUDA, "kernel launch: %s (%s:%d)",                  \
+                              cudaGetErrorString(_e), __FILE__, __LINE__);                  \
+        (h)->launches++;                                                                    \
+    } while (0)
+
+// RAII-free "make this handle's device current" used at the top of every entry point.
+struct mx230_device_guard {
+    int prev;
+    bool switched;
+    explicit mx230_device_guard(int dev) : prev(-1), switched(false) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) {
+            cudaSetDevice(dev);
+            switched = true;
+        }
+    }
+    ~mx230_device_guard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+// 2-D/3-D bf16 tensor map over [outer][rows][64] with a {64, box_rows, 1} box and
+// 128-byte swizzle (one 64-element bf16 row is exactly one 128-byte swizzle span).
+int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
+                         uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes,
+                         uint32_t box_rows);
+
+// fp32 -> bf16 staging of up to four equally sized tensors in one launch (flash_fwd.cu).
+int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src, void *const *dst,
+                      int n_tensors, size_t count);
+
+// ---------------------------------------------------------------------------
+// device
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+namespace mx {
+
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
+constexpr int STATUS_WAIT_TIMEOUT = 1;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// ---- mbarrier ----
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  `abort_flag` is a CTA-shared word: once any role of the CTA gave
+// up, everybody else leaves its waits at the next poll.  Returns false on abort.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          int *status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = globaltimer_ns();
+    unsigned polls = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++polls & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicExch(status, STATUS_WAIT_TIMEOUT);
+                return false;
+            }
+        }
+    }
+}
+
+// ---- TMA: plain (per-CTA) tiled loads into this CTA's shared memory ----
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *tmap, uint32_t bar,
+                                            int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// ---- proxy / tcgen05 fences ----
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// ---- tensor memory ----
+// Whole-warp calls.  `slot` is a shared-memory word that receives the base address.
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+
+// 32 lanes x 32 columns of 32-bit: thread i of the warp gets lane (base_lane + i).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+          "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+          "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+          "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+          "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// ---- MMA descriptors ----
+// Shared-memory operand descriptor, 128-byte swizzle, tile rows of 64 bf16 (128 B),
+// 8-row groups 1024 B apart.  The same bytes serve as a K-major operand (contraction
+// over the 64-element row) and as an MN-major operand (contraction over the rows).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                     // leading-dim byte offset (unused here)
+    d |= (uint64_t)(1024 >> 4) << 32;           // stride between 8-row groups
+    d |= (uint64_t)1 << 46;                     // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                     // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulation.
+// b_mn_major: B operand is contraction-strided (rows are the contraction index).
+__host__ __device__ constexpr uint32_t mma_idesc_bf16(int m, int n, bool a_mn_major,
+                                                      bool b_mn_major) {
+    return (1u << 4)                      // D = f32
+           | (1u << 7)                    // A = bf16
+           | (1u << 10)                   // B = bf16
+           | ((a_mn_major ? 1u : 0u) << 15)
+           | ((b_mn_major ? 1u : 0u) << 16)
+           | ((uint32_t)(n >> 3) << 17)
+           | ((uint32_t)(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on `bar` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+}  // namespace mx
+#endif  // __CUDACC__

@@ -1,0 +1,948 @@
+// Per-layer attention step, part 2: decode attention (one query row per sequence)
+// over the fp32 or int8 KV cache, grouped-query aware, split over the key axis.
+//
+// Reference semantics: attn_decode_impl / attn_decode_q8_impl and their wrappers,
+// 03-llm-engine/kernels/llm.cu:1246-1487 -- one block per QUERY head, three phases
+// (scores+max, exp+sum, PV), whole score row in shared s[2048].
+//
+// This design: one CTA per (key split, kv head, sequence) serves ALL query heads of
+// the kv head's group, so every cache byte leaves HBM once.  The key range is
+// walked in chunks; per chunk the same three phases run, K and V tiles stream
+// through a cp.async shared-memory ring (memory parallelism independent of
+// register pressure), and chunks are chained by an online-softmax rescale, so the
+// context length is unbounded.  Split CTAs leave (m, l, acc) partials in the
+// workspace; the last CTA to arrive for a (sequence, kv head) merges them by
+// log-sum-exp.  HBM-bound: no tensor cores, int8 codes dequantised in registers.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int DEC_THREADS = 128;
+constexpr int TILE_KEYS = 128;  // keys per ring stage (int8: 128 x 64 B = 8 KB)
+constexpr int RING = 4;         // cp.async stages
+constexpr int CHUNK_KEYS = 1024;
+
+struct DecodeParams {
+    float *out;               // [n_seq][out_stride]; head h at h*64 (null in partial mode)
+    int out_stride;
+    float *fin_m, *fin_l, *fin_acc;  // partial mode outputs [n_seq][n_head](x64), else null
+    float *ws_m, *ws_l, *ws_acc;     // split partials [n_seq][n_head][n_splits](x64)
+    unsigned *counters;
+    const float *qkv;
+    int qkv_stride;
+    const float *kcache, *vcache;    // fp32 cache
+    const int8_t *kq, *vq;           // int8 cache
+    const float *ks, *vs, *kb, *vb;
+    // key range of sequence s: [t0, t1) when range_mode, else [0, pos(s)+1)
+    int range_mode, t0, t1;
+    int pos_kind;  // 0 host scalar `pos`, 1 *pos_dev, 2 pos_dev[s]
+    int pos;
+    const int *pos_dev;
+    const int *tables;  // block tables; kind 2: row s of n_log entries; null = linear
+    int bs, n_log;
+    long long seq_rows;  // linear batched slabs: sequence s starts at row s*seq_rows
+    int n_head, n_kv_head, group, head_groups;
+    int score_mode;
+};
+
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ size_t cache_row(const DecodeParams &P, const int *table, long long base,
+                                            int t) {
+    if (table) return (size_t)(table[t / P.bs] * P.bs + t % P.bs);
+    return (size_t)(base + t);
+}
+
+__device__ __forceinline__ void key_range(const DecodeParams &P, int s, int &kbeg, int &kend) {
+    if (P.range_mode) {
+        kbeg = P.t0;
+        kend = P.t1;
+    } else {
+        int p = P.pos_kind == 0 ? P.pos : (P.pos_kind == 1 ? *P.pos_dev : P.pos_dev[s]);
+        kbeg = 0;
+        kend = p + 1;
+    }
+}
+
+// Split c of n covers a 32-aligned slice of [kbeg, kend).
+__device__ __forceinline__ void split_range(int kbeg, int kend, int c, int n, int &a, int &b) {
+    int len = kend - kbeg;
+    int per = (len + n - 1) / n;
+    per = (per + 31) & ~31;
+    a = kbeg + c * per;
+    b = min(kend, a + per);
+    if (a > kend) a = kend;
+    if (b < a) b = a;
+}
+
+// Byte offset of 16-byte piece `p` of key row `k` inside a ring stage: the XOR keeps
+// eight consecutive keys reading the same piece index on distinct banks.
+__device__ __forceinline__ int stage_off(int k, int p) { return k * 64 + ((p ^ ((k >> 1) & 3)) << 4); }
+
+// Final or partial write of one (sequence, kv head) group from merged values held
+// by the first threads of the CTA.
+template <int G>
+__device__ void merge_and_store(const DecodeParams &P, int s, int head0, int gc, int n_splits) {
+    // thread t handles (g = t / 16, 4 consecutive dims at (t % 16) * 4) and loops g by 8
+    for (int g = threadIdx.x / 16; g < gc; g += DEC_THREADS / 16) {
+        int d4 = (threadIdx.x % 16) * 4;
+        int h = head0 + g;
+        size_t pbase = ((size_t)s * P.n_head + h) * n_splits;
+        float mm = -CUDART_INF_F;
+        for (int c = 0; c < n_splits; ++c) mm = fmaxf(mm, P.ws_m[pbase + c]);
+        float ll = 0.0f;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = 0; c < n_splits; ++c) {
+            float mc = P.ws_m[pbase + c];
+            float w = (mc == -CUDART_INF_F) ? 0.0f : __expf(mc - mm);
+            ll += P.ws_l[pbase + c] * w;
+            float4 v = *(const float4 *)(P.ws_acc + (pbase + c) * 64 + d4);
+            a.x += v.x * w, a.y += v.y * w, a.z += v.z * w, a.w += v.w * w;
+        }
+        if (P.fin_acc) {
+            size_t o = (size_t)s * P.n_head + h;
+            *(float4 *)(P.fin_acc + o * 64 + d4) = a;
+            if (d4 == 0) {
+                P.fin_m[o] = mm;
+                P.fin_l[o] = ll;
+            }
+        } else {
+            float inv = 1.0f / ll;
+            *(float4 *)(P.out + (size_t)s * P.out_stride + h * 64 + d4) =
+                make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// int8 cache
+// ---------------------------------------------------------------------------
+template <int G>
+__global__ void __launch_bounds__(DEC_THREADS)
+decode_q8_kernel(const DecodeParams P) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    unsigned char *ring = smem_raw;                                  // RING x 8 KB
+    float *sc = (float *)(smem_raw + RING * TILE_KEYS * 64);         // [CHUNK_KEYS][G]
+    float *qf = sc + CHUNK_KEYS * G;                                 // [G][64]
+    int *qq = (int *)(qf + G * 64);                                  // [G][16]
+    float *red = (float *)(qq + G * 16);                             // [4][G] scratch
+    float *hv = red + 4 * G;                                         // [4][G]: qs, qsum, m_new, alpha
+    __shared__ int is_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int s = blockIdx.z;
+    const int kvh = blockIdx.y / P.head_groups;
+    const int hg = blockIdx.y - kvh * P.head_groups;
+    const int head0 = kvh * P.group + hg * 8;
+    const int gc = min(G, P.group - hg * 8);  // heads served by this CTA
+    const int n_splits = gridDim.x;
+    const int nkv = P.n_kv_head, kvd = nkv * 64;
+
+    int kbeg, kend, ka, kb_;
+    key_range(P, s, kbeg, kend);
+    split_range(kbeg, kend, blockIdx.x, n_splits, ka, kb_);
+    const int *table = P.tables ? P.tables + (P.pos_kind == 2 ? (size_t)s * P.n_log : 0) : nullptr;
+    const long long base = P.tables ? 0 : (long long)s * P.seq_rows;
+    const bool affine = P.kb != nullptr;
+    const float scale = 0.125f;  // 1/sqrt(64)
+
+    // ---- q: fp32 copy, and (reference score mode) per-head int8 codes ----
+    const float *qrow = P.qkv + (size_t)s * P.qkv_stride + head0 * 64;
+    for (int i = tid; i < G * 64; i += DEC_THREADS) qf[i] = (i / 64 < gc) ? qrow[i] : 0.0f;
+    __syncthreads();
+    if (warp < 4) {
+        // one warp per head, heads warp, warp+4
+        for (int g = warp; g < G; g += 4) {
+            float a = qf[g * 64 + lane], b = qf[g * 64 + 32 + lane];
+            if (P.score_mode == MX230_Q8_SCORE_REF) {
+                float qmax = warp_max_f(fmaxf(fabsf(a), fabsf(b)));
+                float qid = qmax > 0.0f ? __fdiv_rn(127.0f, qmax) : 0.0f;
+                int ca = max(-127, min(127, __float2int_rn(a * qid)));
+                int cb = max(-127, min(127, __float2int_rn(b * qid)));
+                int8_t *qb = (int8_t *)(qq + g * 16);
+                qb[lane] = (int8_t)ca;
+                qb[32 + lane] = (int8_t)cb;
+                float qsum = warp_sum_f((float)(ca + cb));  // exact: small integers
+                if (lane == 0) {
+                    hv[0 * G + g] = (qmax > 0.0f ? __fdiv_rn(qmax, 127.0f) : 0.0f) * scale;
+                    hv[1 * G + g] = qsum;
+                }
+            } else {
+                float qsum = warp_sum_f(a + b);
+                if (lane == 0) {
+                    hv[0 * G + g] = scale;
+                    hv[1 * G + g] = qsum;
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    float m_run[G], l_thr[G], b_thr[G];
+    float acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m_run[g] = -CUDART_INF_F;
+        l_thr[g] = 0.0f;
+        b_thr[g] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+    }
+
+    const int n_keys = kb_ - ka;
+    const int n_chunks = (n_keys + CHUNK_KEYS - 1) / CHUNK_KEYS;
+    // tile sequence: per chunk, its K tiles then its V tiles
+    auto tiles_in_chunk = [&](int c) {
+        int len = min(CHUNK_KEYS, n_keys - c * CHUNK_KEYS);
+        return (len + TILE_KEYS - 1) / TILE_KEYS;
+    };
+    int total_tiles = 0;
+    for (int c = 0; c < n_chunks; ++c) total_tiles += 2 * tiles_in_chunk(c);
+
+    // producer state: next tile to issue
+    int pc = 0, pt = 0, issued = 0;  // chunk, tile-in-chunk (0..2T-1), count
+    auto issue_next = [&]() {
+        if (issued < total_tiles) {
+            int T = tiles_in_chunk(pc);
+            bool isv = pt >= T;
+            int tile = isv ? pt - T : pt;
+            int key0 = ka + pc * CHUNK_KEYS + tile * TILE_KEYS;
+            const int8_t *src = isv ? P.vq : P.kq;
+            uint32_t dst = mx::smem_u32(ring + (issued % RING) * (TILE_KEYS * 64));
+#pragma unroll
+            for (int it = 0; it < (TILE_KEYS * 4) / DEC_THREADS; ++it) {
+                int piece = it * DEC_THREADS + tid;
+                int k = piece >> 2, p = piece & 3;
+                int t = key0 + k;
+                bool ok = t < kb_;
+                size_t row = cache_row(P, table, base, ok ? t : ka);
+                cp_async16(dst + stage_off(k, p), src + row * kvd + kvh * 64 + p * 16, ok ? 16 : 0);
+            }
+            ++issued;
+            if (++pt == 2 * T) {
+                pt = 0;
+                ++pc;
+            }
+        }
+        cp_async_commit();
+    };
+
+    for (int i = 0; i < RING - 1; ++i) issue_next();
+
+    int consumed = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+        const int T = tiles_in_chunk(c);
+        const int clen = min(CHUNK_KEYS, n_keys - c * CHUNK_KEYS);
+        const int ck0 = ka + c * CHUNK_KEYS;
+        float tmax[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) tmax[g] = -CUDART_INF_F;
+
+        // ---- phase 1: scores of this chunk, one key per thread per tile ----
+        for (int tile = 0; tile < T; ++tile, ++consumed) {
+            int t = ck0 + tile * TILE_KEYS + tid;
+            bool ok = t < kb_;
+            size_t row = cache_row(P, table, base, ok ? t : ka);
+            float ksc = P.ks[row * nkv + kvh];
+            float kbe = affine ? P.kb[row * nkv + kvh] : 0.0f;
+            cp_async_wait<RING - 2>();
+            __syncthreads();
+            issue_next();
+            const unsigned char *st = ring + (consumed % RING) * (TILE_KEYS * 64);
+            float sco[G];
+            if (P.score_mode == MX230_Q8_SCORE_REF) {
+                int dot[G];
+#pragma unroll
+                for (int g = 0; g < G; ++g) dot[g] = 0;
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    int4 kw = *(const int4 *)(st + stage_off(tid, p));
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        int4 qw = *(const int4 *)(qq + g * 16 + p * 4);
+                        dot[g] = __dp4a(kw.x, qw.x, dot[g]);
+                        dot[g] = __dp4a(kw.y, qw.y, dot[g]);
+                        dot[g] = __dp4a(kw.z, qw.z, dot[g]);
+                        dot[g] = __dp4a(kw.w, qw.w, dot[g]);
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+                    sco[g] = hv[0 * G + g] * (ksc * (float)dot[g] + kbe * hv[1 * G + g]);
+            } else {
+                float dot[G];
+#pragma unroll
+                for (int g = 0; g < G; ++g) dot[g] = 0.0f;
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    int4 kw = *(const int4 *)(st + stage_off(tid, p));
+                    const int w4[4] = {kw.x, kw.y, kw.z, kw.w};
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        float c0 = (float)(int8_t)(w4[w] & 0xFF);
+                        float c1 = (float)(int8_t)((w4[w] >> 8) & 0xFF);
+                        float c2 = (float)(int8_t)((w4[w] >> 16) & 0xFF);
+                        float c3 = (float)(int8_t)((w4[w] >> 24) & 0xFF);
+#pragma unroll
+                        for (int g = 0; g < G; ++g) {
+                            float4 qv = *(const float4 *)(qf + g * 64 + p * 16 + w * 4);
+                            dot[g] += qv.x * c0 + qv.y * c1 + qv.z * c2 + qv.w * c3;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+                    sco[g] = scale * (ksc * dot[g] + kbe * hv[1 * G + g]);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float v = ok ? sco[g] : -CUDART_INF_F;
+                sc[(tile * TILE_KEYS + tid) * G + g] = v;
+                tmax[g] = fmaxf(tmax[g], v);
+            }
+        }
+
+        // ---- chunk max per head, running max, rescale factor ----
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float v = warp_max_f(tmax[g]);
+            if (lane == 0) red[warp * G + g] = v;
+        }
+        __syncthreads();
+        if (tid < G) {
+            float v = fmaxf(fmaxf(red[tid], red[G + tid]), fmaxf(red[2 * G + tid], red[3 * G + tid]));
+            hv[2 * G + tid] = v;
+        }
+        __syncthreads();
+        float m_new[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            m_new[g] = fmaxf(m_run[g], hv[2 * G + g]);
+            float alpha = (m_run[g] == -CUDART_INF_F) ? 0.0f : __expf(m_run[g] - m_new[g]);
+            l_thr[g] *= alpha;
+            b_thr[g] *= alpha;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[g][j] *= alpha;
+            m_run[g] = m_new[g];
+        }
+
+        // ---- phase 2a: p = exp(s - m); weights w = p * vs written back in place ----
+        for (int k = tid; k < clen; k += DEC_THREADS) {
+            size_t row = cache_row(P, table, base, ck0 + k);
+            float vsc = P.vs[row * nkv + kvh];
+            float vbe = affine ? P.vb[row * nkv + kvh] : 0.0f;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float p = __expf(sc[k * G + g] - m_new[g]);
+                l_thr[g] += p;
+                b_thr[g] += p * vbe;
+                sc[k * G + g] = p * vsc;
+            }
+        }
+        // keys of the last tile beyond the chunk get weight 0
+        for (int k = clen + tid; k < T * TILE_KEYS; k += DEC_THREADS) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) sc[k * G + g] = 0.0f;
+        }
+
+        // ---- phase 2b: acc += w * V; thread = (key lane kl, 8-byte slice dsl) ----
+        const int kl = tid >> 3, dsl = tid & 7;
+        for (int tile = 0; tile < T; ++tile, ++consumed) {
+            cp_async_wait<RING - 2>();
+            __syncthreads();  // also orders the weight writes above before their use
+            issue_next();
+            const unsigned char *st = ring + (consumed % RING) * (TILE_KEYS * 64);
+#pragma unroll 4
+            for (int step = 0; step < TILE_KEYS / 16; ++step) {
+                int k = step * 16 + kl;
+                int2 vw = *(const int2 *)(st + stage_off(k, dsl >> 1) + (dsl & 1) * 8);
+                float v[8];
+                v[0] = (float)(int8_t)(vw.x & 0xFF);
+                v[1] = (float)(int8_t)((vw.x >> 8) & 0xFF);
+                v[2] = (float)(int8_t)((vw.x >> 16) & 0xFF);
+                v[3] = (float)(int8_t)((vw.x >> 24) & 0xFF);
+                v[4] = (float)(int8_t)(vw.y & 0xFF);
+                v[5] = (float)(int8_t)((vw.y >> 8) & 0xFF);
+                v[6] = (float)(int8_t)((vw.y >> 16) & 0xFF);
+                v[7] = (float)(int8_t)((vw.y >> 24) & 0xFF);
+                const float *wk = sc + (tile * TILE_KEYS + k) * G;
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float w = wk[g];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(w, v[j], acc[g][j]);
+                }
+            }
+        }
+        __syncthreads();  // sc is rewritten by the next chunk's phase 1
+    }
+    cp_async_wait<0>();
+
+    // ---- CTA reduction: l, beta sum, acc over the 16 key lanes ----
+    float l_tot[G], b_tot[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float lv = warp_sum_f(l_thr[g]), bv = warp_sum_f(b_thr[g]);
+        if (lane == 0) {
+            red[warp * G + g] = lv;
+            hv[2 * G + g] = 0.0f;
+        }
+        __syncthreads();
+        lv = red[g] + red[G + g] + red[2 * G + g] + red[3 * G + g];
+        __syncthreads();
+        if (lane == 0) red[warp * G + g] = bv;
+        __syncthreads();
+        bv = red[g] + red[G + g] + red[2 * G + g] + red[3 * G + g];
+        __syncthreads();
+        l_tot[g] = lv;
+        b_tot[g] = bv;
+    }
+    // key lanes inside a warp differ in lane bits 3,4
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float v = acc[g][j];
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 8);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 16);
+            acc[g][j] = v;
+        }
+    float *accs = sc;  // [4 warps][G][64]
+    if (lane < 8) {
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) accs[(warp * G + g) * 64 + lane * 8 + j] = acc[g][j];
+    }
+    __syncthreads();
+
+    const bool direct = (n_splits == 1) && (P.fin_acc == nullptr);
+    for (int i = tid; i < gc * 64; i += DEC_THREADS) {
+        int g = i >> 6, d = i & 63;
+        float a = accs[(0 * G + g) * 64 + d] + accs[(1 * G + g) * 64 + d] +
+                  accs[(2 * G + g) * 64 + d] + accs[(3 * G + g) * 64 + d];
+        // pick this head's totals without dynamic register indexing
+        float lt = 0.0f, bt = 0.0f, mt = 0.0f;
+#pragma unroll
+        for (int gg = 0; gg < G; ++gg)
+            if (gg == g) {
+                lt = l_tot[gg];
+                bt = b_tot[gg];
+                mt = m_run[gg];
+            }
+        a += bt;  // V's affine offset: sum_j p_j * vb_j, the same for every dim
+        int h = head0 + g;
+        if (direct) {
+            P.out[(size_t)s * P.out_stride + h * 64 + d] = a / lt;
+        } else {
+            size_t pi = ((size_t)s * P.n_head + h) * n_splits + blockIdx.x;
+            P.ws_acc[pi * 64 + d] = a;
+            if (d == 0) {
+                P.ws_m[pi] = mt;
+                P.ws_l[pi] = lt;
+            }
+        }
+    }
+    if (direct) return;
+
+    // ---- last CTA of this (sequence, kv head group) merges the splits ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned prev = atomicInc(&P.counters[(size_t)s * gridDim.y + blockIdx.y], n_splits - 1);
+        is_last = (prev == (unsigned)(n_splits - 1));
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    merge_and_store<G>(P, s, head0, gc, n_splits);
+}
+
+// ---------------------------------------------------------------------------
+// fp32 cache (control path): direct 128-bit global loads, 4 lanes per key
+// ---------------------------------------------------------------------------
+template <int G>
+__global__ void __launch_bounds__(DEC_THREADS)
+decode_f32_kernel(const DecodeParams P) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float *sc = (float *)smem_raw;          // [CHUNK_KEYS][G]
+    float *qf = sc + CHUNK_KEYS * G;        // [G][64]
+    float *red = qf + G * 64;               // [4][G]
+    float *hv = red + 4 * G;                // [G] chunk max
+    __shared__ int is_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int s = blockIdx.z;
+    const int kvh = blockIdx.y / P.head_groups;
+    const int hg = blockIdx.y - kvh * P.head_groups;
+    const int head0 = kvh * P.group + hg * 8;
+    const int gc = min(G, P.group - hg * 8);
+    const int n_splits = gridDim.x;
+    const int nkv = P.n_kv_head, kvd = nkv * 64;
+
+    int kbeg, kend, ka, kb_;
+    key_range(P, s, kbeg, kend);
+    split_range(kbeg, kend, blockIdx.x, n_splits, ka, kb_);
+    const int *table = P.tables ? P.tables + (P.pos_kind == 2 ? (size_t)s * P.n_log : 0) : nullptr;
+    const long long base = P.tables ? 0 : (long long)s * P.seq_rows;
+    const float scale = 0.125f;
+
+    const float *qrow = P.qkv + (size_t)s * P.qkv_stride + head0 * 64;
+    for (int i = tid; i < G * 64; i += DEC_THREADS) qf[i] = (i / 64 < gc) ? qrow[i] : 0.0f;
+    __syncthreads();
+
+    float m_run[G], l_thr[G];
+    float acc[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m_run[g] = -CUDART_INF_F;
+        l_thr[g] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[g][j] = 0.0f;
+    }
+
+    const int n_keys = kb_ - ka;
+    const int kq4 = tid >> 2, part = tid & 3;  // phase 1: key lane (0..31), 16-float slice
+    const int kl = tid >> 4, dsl = tid & 15;   // phase 2: key lane (0..7), 4-float slice
+    for (int c0 = 0; c0 < n_keys; c0 += CHUNK_KEYS) {
+        const int clen = min(CHUNK_KEYS, n_keys - c0);
+        const int ck0 = ka + c0;
+        float tmax[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) tmax[g] = -CUDART_INF_F;
+        for (int k = kq4; k < ((clen + 31) & ~31); k += 32) {
+            bool ok = k < clen;
+            size_t row = cache_row(P, table, base, ck0 + (ok ? k : 0));
+            const float4 *kp = (const float4 *)(P.kcache + row * kvd + kvh * 64 + part * 16);
+            float4 k0 = kp[0], k1 = kp[1], k2 = kp[2], k3 = kp[3];
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float4 *qp = (const float4 *)(qf + g * 64 + part * 16);
+                float4 q0 = qp[0], q1 = qp[1], q2 = qp[2], q3 = qp[3];
+                float d = q0.x * k0.x + q0.y * k0.y + q0.z * k0.z + q0.w * k0.w;
+                d += q1.x * k1.x + q1.y * k1.y + q1.z * k1.z + q1.w * k1.w;
+                d += q2.x * k2.x + q2.y * k2.y + q2.z * k2.z + q2.w * k2.w;
+                d += q3.x * k3.x + q3.y * k3.y + q3.z * k3.z + q3.w * k3.w;
+                d += __shfl_xor_sync(0xFFFFFFFFu, d, 1);
+                d += __shfl_xor_sync(0xFFFFFFFFu, d, 2);
+                float v = ok ? d * scale : -CUDART_INF_F;
+                if (part == 0 && ok) sc[k * G + g] = v;
+                tmax[g] = fmaxf(tmax[g], v);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float v = warp_max_f(tmax[g]);
+            if (lane == 0) red[warp * G + g] = v;
+        }
+        __syncthreads();
+        if (tid < G)
+            hv[tid] = fmaxf(fmaxf(red[tid], red[G + tid]), fmaxf(red[2 * G + tid], red[3 * G + tid]));
+        __syncthreads();
+        float m_new[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            m_new[g] = fmaxf(m_run[g], hv[g]);
+            float alpha = (m_run[g] == -CUDART_INF_F) ? 0.0f : __expf(m_run[g] - m_new[g]);
+            l_thr[g] *= alpha;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[g][j] *= alpha;
+            m_run[g] = m_new[g];
+        }
+        for (int k = tid; k < clen; k += DEC_THREADS) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float p = __expf(sc[k * G + g] - m_new[g]);
+                l_thr[g] += p;
+                sc[k * G + g] = p;
+            }
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int k = kl; k < clen; k += 8) {
+            size_t row = cache_row(P, table, base, ck0 + k);
+            float4 v = *(const float4 *)(P.vcache + row * kvd + kvh * 64 + dsl * 4);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float w = sc[k * G + g];
+                acc[g][0] = fmaf(w, v.x, acc[g][0]);
+                acc[g][1] = fmaf(w, v.y, acc[g][1]);
+                acc[g][2] = fmaf(w, v.z, acc[g][2]);
+                acc[g][3] = fmaf(w, v.w, acc[g][3]);
+            }
+        }
+        __syncthreads();
+    }
+
+    float l_tot[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float lv = warp_sum_f(l_thr[g]);
+        if (lane == 0) red[warp * G + g] = lv;
+        __syncthreads();
+        l_tot[g] = red[g] + red[G + g] + red[2 * G + g] + red[3 * G + g];
+        __syncthreads();
+    }
+    // key lanes inside a warp differ in lane bit 4
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[g][j] += __shfl_xor_sync(0xFFFFFFFFu, acc[g][j], 16);
+    float *accs = sc;  // [4][G][64]
+    if (lane < 16) {
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) accs[(warp * G + g) * 64 + lane * 4 + j] = acc[g][j];
+    }
+    __syncthreads();
+    const bool direct = (n_splits == 1) && (P.fin_acc == nullptr);
+    for (int i = tid; i < gc * 64; i += DEC_THREADS) {
+        int g = i >> 6, d = i & 63;
+        float a = accs[(0 * G + g) * 64 + d] + accs[(1 * G + g) * 64 + d] +
+                  accs[(2 * G + g) * 64 + d] + accs[(3 * G + g) * 64 + d];
+        float lt = 0.0f, mt = 0.0f;
+#pragma unroll
+        for (int gg = 0; gg < G; ++gg)
+            if (gg == g) {
+                lt = l_tot[gg];
+                mt = m_run[gg];
+            }
+        int h = head0 + g;
+        if (direct) {
+            P.out[(size_t)s * P.out_stride + h * 64 + d] = a / lt;
+        } else {
+            size_t pi = ((size_t)s * P.n_head + h) * n_splits + blockIdx.x;
+            P.ws_acc[pi * 64 + d] = a;
+            if (d == 0) {
+                P.ws_m[pi] = mt;
+                P.ws_l[pi] = lt;
+            }
+        }
+    }
+    if (direct) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned prev = atomicInc(&P.counters[(size_t)s * gridDim.y + blockIdx.y], n_splits - 1);
+        is_last = (prev == (unsigned)(n_splits - 1));
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    merge_and_store<G>(P, s, head0, gc, n_splits);
+}
+
+// Log-sum-exp merge of gathered partial triples: one thread per (row, 4 dims).
+__global__ void merge_partials_kernel(float *out, const float *m, const float *l, const float *acc,
+                                      int parts, int rows) {
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * 16) return;
+    int r = idx >> 4, d4 = (idx & 15) * 4;
+    float mm = -CUDART_INF_F;
+    for (int p = 0; p < parts; ++p) mm = fmaxf(mm, m[(size_t)p * rows + r]);
+    float ll = 0.0f;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < parts; ++p) {
+        float mp = m[(size_t)p * rows + r];
+        float w = (mp == -CUDART_INF_F) ? 0.0f : __expf(mp - mm);
+        ll += l[(size_t)p * rows + r] * w;
+        float4 v = *(const float4 *)(acc + ((size_t)p * rows + r) * 64 + d4);
+        a.x += v.x * w, a.y += v.y * w, a.z += v.z * w, a.w += v.w * w;
+    }
+    float inv = 1.0f / ll;
+    *(float4 *)(out + (size_t)r * 64 + d4) = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+}
+
+size_t q8_smem_bytes(int G) {
+    return (size_t)RING * TILE_KEYS * 64 + sizeof(float) * ((size_t)CHUNK_KEYS * G + G * 64 + 4 * G + 4 * G) +
+           sizeof(int) * (size_t)G * 16;
+}
+size_t f32_smem_bytes(int G) {
+    return sizeof(float) * ((size_t)CHUNK_KEYS * G + G * 64 + 4 * G + G);
+}
+
+template <int G>
+int launch_g(mx230_handle *h, cudaStream_t st, const DecodeParams &P, dim3 grid, bool q8) {
+    if (q8) {
+        size_t sm = q8_smem_bytes(G);
+        MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_kernel<G>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+        decode_q8_kernel<G><<<grid, DEC_THREADS, sm, st>>>(P);
+    } else {
+        size_t sm = f32_smem_bytes(G);
+        MX_CHECK_CUDA(cudaFuncSetAttribute(decode_f32_kernel<G>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+        decode_f32_kernel<G><<<grid, DEC_THREADS, sm, st>>>(P);
+    }
+    MX_LAUNCHED(h);
+    return MX230_OK;
+}
+
+// `known_keys`: host-known upper bound of keys per sequence (<= 0 when the position
+// lives on the device); only steers how many key splits are launched.
+int launch_decode(mx230_handle *h, void *stream, DecodeParams P, int n_seq, int head_dim,
+                  long long known_keys) {
+    MX_REQUIRE(h && P.qkv, MX230_ERR_INVALID_ARG, "attn_decode: null argument");
+    MX_REQUIRE(head_dim == 64, MX230_ERR_UNSUPPORTED, "attn_decode: head_dim %d unsupported (must be 64)",
+               head_dim);
+    MX_REQUIRE(P.n_head > 0 && P.n_kv_head > 0 && P.n_head % P.n_kv_head == 0, MX230_ERR_UNSUPPORTED,
+               "attn_decode: n_head %d must be a positive multiple of n_kv_head %d", P.n_head,
+               P.n_kv_head);
+    const bool q8 = P.kq != nullptr;
+    if (q8)
+        MX_REQUIRE(P.vq && P.ks && P.vs && ((P.kb == nullptr) == (P.vb == nullptr)),
+                   MX230_ERR_INVALID_ARG, "attn_decode_q8: missing cache array");
+    else
+        MX_REQUIRE(P.kcache && P.vcache, MX230_ERR_INVALID_ARG, "attn_decode: null cache");
+    MX_REQUIRE(P.fin_acc || P.out, MX230_ERR_INVALID_ARG, "attn_decode: null output");
+    MX_REQUIRE(P.tables == nullptr || P.bs > 0, MX230_ERR_INVALID_ARG, "attn_decode: block size %d",
+               P.bs);
+    MX_REQUIRE((((uintptr_t)P.qkv | (uintptr_t)P.out | (uintptr_t)P.kcache | (uintptr_t)P.vcache |
+                 (uintptr_t)P.kq | (uintptr_t)P.vq) & 15) == 0 && P.qkv_stride % 4 == 0 &&
+                   P.out_stride % 4 == 0,
+               MX230_ERR_INVALID_ARG, "attn_decode: buffers must be 16-byte aligned");
+    if (P.range_mode) MX_REQUIRE(P.t0 >= 0 && P.t1 > P.t0, MX230_ERR_INVALID_ARG,
+                                 "attn_decode_partial: empty key range [%d, %d)", P.t0, P.t1);
+    if (!P.range_mode && P.pos_kind == 0)
+        MX_REQUIRE(P.pos >= 0, MX230_ERR_INVALID_ARG, "attn_decode: negative position %d", P.pos);
+    if (n_seq <= 0) return n_seq == 0 ? MX230_OK
+                                      : mx230_fail(MX230_ERR_INVALID_ARG, "attn_decode: negative n_seq");
+
+    P.group = P.n_head / P.n_kv_head;
+    P.head_groups = (P.group + 7) / 8;
+    P.score_mode = h->q8_score_mode;
+    int gy = P.n_kv_head * P.head_groups;
+    MX_REQUIRE((size_t)n_seq * gy <= h->n_counters, MX230_ERR_UNSUPPORTED,
+               "attn_decode: n_seq*n_kv_head %lld exceeds %zu", (long long)n_seq * gy, h->n_counters);
+
+    // how many key splits: fill the machine (~3 CTAs per SM) but keep >= 256 keys each
+    long long base_ctas = (long long)n_seq * gy;
+    int want = (int)((3LL * h->sm_count + base_ctas - 1) / base_ctas);
+    int n_splits;
+    if (h->decode_chunk > 0 && known_keys > 0) {
+        n_splits = (int)((known_keys + h->decode_chunk - 1) / h->decode_chunk);
+    } else {
+        long long keys = known_keys > 0 ? known_keys : 4096;
+        int max_by_len = (int)((keys + 255) / 256);
+        n_splits = want < 1 ? 1 : want;
+        if (n_splits > max_by_len) n_splits = max_by_len;
+    }
+    if (n_splits < 1) n_splits = 1;
+    if (n_splits > 256) n_splits = 256;
+    if (n_splits > 1 || P.fin_acc) {
+        size_t need = (size_t)n_seq * P.n_head * n_splits * 66 * sizeof(float);
+        MX_REQUIRE(h->ws && need <= h->ws_bytes, MX230_ERR_WORKSPACE,
+                   "attn_decode: workspace %zu B < %zu B needed for %d key splits", h->ws_bytes, need,
+                   n_splits);
+        size_t rows = (size_t)n_seq * P.n_head * n_splits;
+        P.ws_acc = (float *)h->ws;
+        P.ws_m = P.ws_acc + rows * 64;
+        P.ws_l = P.ws_m + rows;
+    }
+    P.counters = h->counters;
+
+    mx230_device_guard guard(h->device);
+    dim3 grid(n_splits, gy, n_seq);
+    cudaStream_t st = (cudaStream_t)stream;
+    int g = P.group > 8 ? 8 : P.group;
+    if (g == 1) return launch_g<1>(h, st, P, grid, q8);
+    if (g == 2) return launch_g<2>(h, st, P, grid, q8);
+    if (g <= 4) return launch_g<4>(h, st, P, grid, q8);
+    return launch_g<8>(h, st, P, grid, q8);
+}
+
+DecodeParams base_params(float *out, int out_stride, const float *qkv, int qkv_stride, int n_head,
+                         int n_kv_head) {
+    DecodeParams P;
+    memset(&P, 0, sizeof(P));
+    P.out = out;
+    P.out_stride = out_stride;
+    P.qkv = qkv;
+    P.qkv_stride = qkv_stride;
+    P.n_head = n_head;
+    P.n_kv_head = n_kv_head;
+    return P;
+}
+
+}  // namespace
+
+// ---- fp32 cache ----
+extern "C" int mx230_attn_decode(mx230_handle *h, void *stream, float *out, const float *qkv,
+                                 const float *kcache, const float *vcache, int t_cur, int n_head,
+                                 int n_kv_head, int head_dim) {
+    DecodeParams P = base_params(out, n_head * 64, qkv, 0, n_head, n_kv_head);
+    P.kcache = kcache, P.vcache = vcache, P.pos_kind = 0, P.pos = t_cur;
+    return launch_decode(h, stream, P, 1, head_dim, (long long)t_cur + 1);
+}
+extern "C" int mx230_attn_decode_dyn(mx230_handle *h, void *stream, float *out, const float *qkv,
+                                     const float *kcache, const float *vcache, const int *pos_ptr,
+                                     int n_head, int n_kv_head, int head_dim) {
+    MX_REQUIRE(pos_ptr, MX230_ERR_INVALID_ARG, "attn_decode_dyn: null pos_ptr");
+    DecodeParams P = base_params(out, n_head * 64, qkv, 0, n_head, n_kv_head);
+    P.kcache = kcache, P.vcache = vcache, P.pos_kind = 1, P.pos_dev = pos_ptr;
+    return launch_decode(h, stream, P, 1, head_dim, 0);
+}
+extern "C" int mx230_attn_decode_paged(mx230_handle *h, void *stream, float *out, const float *qkv,
+                                       const float *kcache, const float *vcache, int t_cur,
+                                       int n_head, int n_kv_head, int head_dim, const int *bt,
+                                       int bs) {
+    MX_REQUIRE(bt, MX230_ERR_INVALID_ARG, "attn_decode_paged: null block table");
+    DecodeParams P = base_params(out, n_head * 64, qkv, 0, n_head, n_kv_head);
+    P.kcache = kcache, P.vcache = vcache, P.pos_kind = 0, P.pos = t_cur, P.tables = bt, P.bs = bs;
+    return launch_decode(h, stream, P, 1, head_dim, (long long)t_cur + 1);
+}
+extern "C" int mx230_attn_decode_paged_dyn(mx230_handle *h, void *stream, float *out,
+                                           const float *qkv, const float *kcache,
+                                           const float *vcache, const int *pos_ptr, int n_head,
+                                           int n_kv_head, int head_dim, const int *bt, int bs) {
+    MX_REQUIRE(pos_ptr && bt, MX230_ERR_INVALID_ARG, "attn_decode_paged_dyn: null argument");
+    DecodeParams P = base_params(out, n_head * 64, qkv, 0, n_head, n_kv_head);
+    P.kcache = kcache, P.vcache = vcache, P.pos_kind = 1, P.pos_dev = pos_ptr, P.tables = bt, P.bs = bs;
+    return launch_decode(h, stream, P, 1, head_dim, 0);
+}
+extern "C" int mx230_attn_decode_batched(mx230_handle *h, void *stream, float *out,
+                                         const float *qkv, const float *kcache,
+                                         const float *vcache, const int *pos, int n_seq,
+                                         int n_head, int n_kv_head, int head_dim,
+                                         const int *tables, int block_size, int n_log,
+                                         int qkv_stride, int out_stride) {
+    MX_REQUIRE(pos && tables, MX230_ERR_INVALID_ARG, "attn_decode_batched: null argument");
+    DecodeParams P = base_params(out, out_stride, qkv, qkv_stride, n_head, n_kv_head);
+    P.kcache = kcache, P.vcache = vcache, P.pos_kind = 2, P.pos_dev = pos;
+    P.tables = tables, P.bs = block_size, P.n_log = n_log;
+    return launch_decode(h, stream, P, n_seq, head_dim, (long long)n_log * block_size);
+}
+
+// ---- int8 cache ----
+#define Q8_ARGS kq, vq, ks, vs, kb, vb
+static void set_q8(DecodeParams &P, const int8_t *kq, const int8_t *vq, const float *ks,
+                   const float *vs, const float *kb, const float *vb) {
+    P.kq = kq, P.vq = vq, P.ks = ks, P.vs = vs, P.kb = kb, P.vb = vb;
+}
+extern "C" int mx230_attn_decode_q8(mx230_handle *h, void *stream, float *out, const float *qkv,
+                                    const int8_t *kq, const int8_t *vq, const float *ks,
+                                    const float *vs, const float *kb, const float *vb, int t_cur,
+                                    int n_head, int n_kv_head, int head_dim) {
+    MX_REQUIRE(kq, MX230_ERR_INVALID_ARG, "attn_decode_q8: null kq");
+    DecodeParams P = base_params(out, n_head * 64, qkv, 0, n_head, n_kv_head);
+    set_q8(P, Q8_ARGS);
+    P.pos_kind = 0, P.pos = t_cur;
+    return launch_decode(h, stream, P, 1, head_dim, (long long)t_cur + 1);
+}
+extern "C" int mx230_attn_decode_q8_dyn(mx230_handle *h, void *stream, float *out,
+                                        const float *qkv, const int8_t *kq, const int8_t *vq,
+                                        const float *ks, const float *vs, const float *kb,
+                                        const float *vb, const int *pos_ptr, int n_head,
+                                        int n_kv_head, int head_dim) {
+    MX_REQUIRE(kq && pos_ptr, MX230_ERR_INVALID_ARG, "attn_decode_q8_dyn: null argument");
+    DecodeParams P = base_params(out, n_head * 64, qkv, 0, n_head, n_kv_head);
+    set_q8(P, Q8_ARGS);
+    P.pos_kind = 1, P.pos_dev = pos_ptr;
+    return launch_decode(h, stream, P, 1, head_dim, 0);
+}
+extern "C" int mx230_attn_decode_q8_paged(mx230_handle *h, void *stream, float *out,
+                                          const float *qkv, const int8_t *kq, const int8_t *vq,
+                                          const float *ks, const float *vs, const float *kb,
+                                          const float *vb, int t_cur, int n_head, int n_kv_head,
+                                          int head_dim, const int *bt, int bs) {
+    MX_REQUIRE(kq && bt, MX230_ERR_INVALID_ARG, "attn_decode_q8_paged: null argument");
+    DecodeParams P = base_params(out, n_head * 64, qkv, 0, n_head, n_kv_head);
+    set_q8(P, Q8_ARGS);
+    P.pos_kind = 0, P.pos = t_cur, P.tables = bt, P.bs = bs;
+    return launch_decode(h, stream, P, 1, head_dim, (long long)t_cur + 1);
+}
+extern "C" int mx230_attn_decode_q8_paged_dyn(mx230_handle *h, void *stream, float *out,
+                                              const float *qkv, const int8_t *kq,
+                                              const int8_t *vq, const float *ks, const float *vs,
+                                              const float *kb, const float *vb, const int *pos_ptr,
+                                              int n_head, int n_kv_head, int head_dim,
+                                              const int *bt, int bs) {
+    MX_REQUIRE(kq && pos_ptr && bt, MX230_ERR_INVALID_ARG, "attn_decode_q8_paged_dyn: null argument");
+    DecodeParams P = base_params(out, n_head * 64, qkv, 0, n_head, n_kv_head);
+    set_q8(P, Q8_ARGS);
+    P.pos_kind = 1, P.pos_dev = pos_ptr, P.tables = bt, P.bs = bs;
+    return launch_decode(h, stream, P, 1, head_dim, 0);
+}
+extern "C" int mx230_attn_decode_q8_batched(mx230_handle *h, void *stream, float *out,
+                                            const float *qkv, const int8_t *kq, const int8_t *vq,
+                                            const float *ks, const float *vs, const float *kb,
+                                            const float *vb, const int *pos, int n_seq, int n_head,
+                                            int n_kv_head, int head_dim, const int *tables,
+                                            int block_size, int n_log, int qkv_stride,
+                                            int out_stride) {
+    MX_REQUIRE(kq && pos && tables, MX230_ERR_INVALID_ARG, "attn_decode_q8_batched: null argument");
+    DecodeParams P = base_params(out, out_stride, qkv, qkv_stride, n_head, n_kv_head);
+    set_q8(P, Q8_ARGS);
+    P.pos_kind = 2, P.pos_dev = pos, P.tables = tables, P.bs = block_size, P.n_log = n_log;
+    return launch_decode(h, stream, P, n_seq, head_dim, (long long)n_log * block_size);
+}
+
+// ---- contiguous per-sequence slabs, and split-KV partials ----
+extern "C" int mx230_attn_decode_slab(mx230_handle *h, void *stream, float *out, const float *qkv,
+                                      const float *kcache, const float *vcache, const int8_t *kq,
+                                      const int8_t *vq, const float *ks, const float *vs,
+                                      const float *kb, const float *vb, const int *pos, int n_seq,
+                                      int n_head, int n_kv_head, int head_dim, long long seq_rows,
+                                      int qkv_stride, int out_stride) {
+    MX_REQUIRE(pos && seq_rows > 0, MX230_ERR_INVALID_ARG, "attn_decode_slab: null pos or bad seq_rows");
+    DecodeParams P = base_params(out, out_stride, qkv, qkv_stride, n_head, n_kv_head);
+    P.kcache = kcache, P.vcache = vcache;
+    set_q8(P, Q8_ARGS);
+    P.pos_kind = 2, P.pos_dev = pos, P.seq_rows = seq_rows;
+    return launch_decode(h, stream, P, n_seq, head_dim, seq_rows);
+}
+
+extern "C" int mx230_attn_decode_partial(mx230_handle *h, void *stream, float *part_m,
+                                         float *part_l, float *part_acc, const float *qkv,
+                                         const float *kcache, const float *vcache,
+                                         const int8_t *kq, const int8_t *vq, const float *ks,
+                                         const float *vs, const float *kb, const float *vb, int t0,
+                                         int t1, int n_seq, int n_head, int n_kv_head, int head_dim,
+                                         long long seq_rows, int qkv_stride) {
+    MX_REQUIRE(part_m && part_l && part_acc, MX230_ERR_INVALID_ARG,
+               "attn_decode_partial: null partial output");
+    MX_REQUIRE(seq_rows > 0 || n_seq == 1, MX230_ERR_INVALID_ARG, "attn_decode_partial: bad seq_rows");
+    DecodeParams P = base_params(nullptr, 0, qkv, qkv_stride, n_head, n_kv_head);
+    P.kcache = kcache, P.vcache = vcache;
+    set_q8(P, Q8_ARGS);
+    P.fin_m = part_m, P.fin_l = part_l, P.fin_acc = part_acc;
+    P.range_mode = 1, P.t0 = t0, P.t1 = t1, P.seq_rows = seq_rows;
+    return launch_decode(h, stream, P, n_seq, head_dim, (long long)t1 - t0);
+}
+
+extern "C" int mx230_merge_partials(mx230_handle *h, void *stream, float *out, const float *m,
+                                    const float *l, const float *acc, int parts, int rows,
+                                    int head_dim) {
+    MX_REQUIRE(h && out && m && l && acc, MX230_ERR_INVALID_ARG, "merge_partials: null argument");
+    MX_REQUIRE(head_dim == 64, MX230_ERR_UNSUPPORTED, "merge_partials: head_dim must be 64");
+    MX_REQUIRE(parts > 0 && rows >= 0, MX230_ERR_INVALID_ARG, "merge_partials: bad sizes");
+    if (rows == 0) return MX230_OK;
+    mx230_device_guard guard(h->device);
+    merge_partials_kernel<<<(rows * 16 + 127) / 128, 128, 0, (cudaStream_t)stream>>>(out, m, l, acc,
+                                                                                   parts, rows);
+    MX_LAUNCHED(h);
+    return MX230_OK;
+}

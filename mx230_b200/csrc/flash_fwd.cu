@@ -1,0 +1,442 @@
+// Flash-attention forward for sm_100a: O = softmax(scale * Q K^T [+ causal]) V and
+// the per-row log-sum-exp L = m + ln(l), never materialising the N x N scores.
+//
+// Reference semantics: flash_fwd / attn_flash / attn_flash_lse,
+// 02-flash-attention/kernels/attention_flash.cu:17-100 (fp32 SIMT, one thread per
+// query row).  This kernel keeps those semantics (scale 1/sqrt(64), key j <= query i
+// when causal, any N, natural-log L) and maps the two contractions onto the 5th-gen
+// tensor cores:
+//
+//   * one CTA owns 256 query rows of one head as two 128-row tiles;
+//   * warp 8 streams Q once and K/V tiles (128 keys) through a 4-stage shared-memory
+//     ring with plain per-CTA TMA tile loads (128-byte swizzle);
+//   * warp 9 issues tcgen05.mma: S_t = Q_t K^T into tensor memory (128 fp32 columns per
+//     tile) and O_t += P_t V with P_t read back from tensor memory as bf16;
+//   * warps 0-3 / 4-7 are the softmax groups of tile 0 / 1, one thread per query row:
+//     row max, exp2, row sum, bf16 P written over S, O rescaled in tensor memory.
+//   The two tiles ping-pong, so the tensor core works on one tile while the other
+//   tile's softmax runs on the CUDA cores.
+//
+// Operands are bf16 (rounded once by the cast pre-pass), accumulation is fp32.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;        // query rows per tile
+constexpr int QT = 2;          // query tiles per CTA
+constexpr int BN = 128;        // keys per K/V tile
+constexpr int HD = 64;
+constexpr int KV_STAGES = 4;
+constexpr int TILE_BYTES = BN * HD * 2;  // 16 KB
+constexpr int FWD_THREADS = 320;
+
+constexpr int SMEM_Q = 0;
+constexpr int SMEM_K = SMEM_Q + QT * TILE_BYTES;
+constexpr int SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;
+constexpr int SMEM_BAR = SMEM_V + KV_STAGES * TILE_BYTES;
+constexpr int SMEM_TOTAL = SMEM_BAR + 256;
+constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;  // slack for 1024-byte alignment
+
+// barrier slots (8 bytes each) inside SMEM_BAR
+constexpr int BAR_Q_FULL = 0;
+constexpr int BAR_K_FULL = 1;                    // [KV_STAGES]
+constexpr int BAR_K_EMPTY = BAR_K_FULL + KV_STAGES;
+constexpr int BAR_V_FULL = BAR_K_EMPTY + KV_STAGES;
+constexpr int BAR_V_EMPTY = BAR_V_FULL + KV_STAGES;
+constexpr int BAR_S_FULL = BAR_V_EMPTY + KV_STAGES;  // [QT]
+constexpr int BAR_P_READY = BAR_S_FULL + QT;         // [QT]
+constexpr int BAR_O_DONE = BAR_P_READY + QT;         // [QT]
+constexpr int N_BARS = BAR_O_DONE + QT;              // 23
+
+// tensor-memory columns
+constexpr int TM_S = 0;     // S_t at TM_S + t*128 (P_t overlays its first 64 columns)
+constexpr int TM_O = 256;   // O_t at TM_O + t*64
+constexpr int TM_COLS = 512;
+
+struct FwdParams {
+    float *O;        // [BH][N][64]
+    float *L;        // [BH][N] or null
+    int n;
+    int causal;
+    int *status;
+};
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FwdParams P) {
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t smem_base = (mx::smem_u32(smem_dyn) + 1023u) & ~1023u;
+    unsigned char *smem = smem_dyn + (smem_base - mx::smem_u32(smem_dyn));
+    const uint32_t bar0 = smem_base + SMEM_BAR;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    volatile uint32_t *tmem_slot = (volatile uint32_t *)(smem + SMEM_BAR + 8 * N_BARS);
+    volatile int *abort_flag = (volatile int *)(smem + SMEM_BAR + 8 * N_BARS + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int N = P.n;
+    const int bh = blockIdx.y;
+    // heaviest (latest) causal blocks first
+    const int qb = P.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    const int q0 = qb * (QT * BM);
+    const int n_kv_total = (N + BN - 1) / BN;
+    int n_it[QT];
+#pragma unroll
+    for (int t = 0; t < QT; ++t) {
+        int r0 = q0 + t * BM;
+        if (r0 >= N) n_it[t] = 0;
+        else n_it[t] = P.causal ? min(n_kv_total, r0 / BN + 1) : n_kv_total;
+    }
+    const int n_max = max(n_it[0], n_it[1]);
+
+    if (tid == 0) {
+        mx::mbar_init(bar(BAR_Q_FULL), 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mx::mbar_init(bar(BAR_K_FULL + s), 1);
+            mx::mbar_init(bar(BAR_K_EMPTY + s), 1);
+            mx::mbar_init(bar(BAR_V_FULL + s), 1);
+            mx::mbar_init(bar(BAR_V_EMPTY + s), 1);
+        }
+        for (int t = 0; t < QT; ++t) {
+            mx::mbar_init(bar(BAR_S_FULL + t), 1);
+            mx::mbar_init(bar(BAR_P_READY + t), BM);
+            mx::mbar_init(bar(BAR_O_DONE + t), 1);
+        }
+        *abort_flag = 0;
+        mx::mbar_fence_init();
+    }
+    if (warp == 9) mx::tmem_alloc(mx::smem_u32((const void *)tmem_slot), TM_COLS);
+    mx::tc_fence_before();
+    __syncthreads();
+    mx::tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 8) {
+        // ------------------------- TMA producer -------------------------
+        if (lane == 0) {
+            mx::tma_prefetch_desc(&tmQ);
+            mx::tma_prefetch_desc(&tmK);
+            mx::tma_prefetch_desc(&tmV);
+            int nq = (n_it[1] > 0) ? 2 : 1;
+            mx::mbar_expect_tx(bar(BAR_Q_FULL), nq * TILE_BYTES);
+            for (int t = 0; t < nq; ++t)
+                mx::tma_load_3d(smem_base + SMEM_Q + t * TILE_BYTES, &tmQ, bar(BAR_Q_FULL), 0,
+                                q0 + t * BM, bh);
+            bool ok = true;
+            for (int j = 0; j < n_max && ok; ++j) {
+                int s = j % KV_STAGES, r = j / KV_STAGES;
+                if (r > 0) ok = mx::mbar_wait(bar(BAR_K_EMPTY + s), (r - 1) & 1, abort_flag, P.status);
+                if (!ok) break;
+                mx::mbar_expect_tx(bar(BAR_K_FULL + s), TILE_BYTES);
+                mx::tma_load_3d(smem_base + SMEM_K + s * TILE_BYTES, &tmK, bar(BAR_K_FULL + s), 0,
+                                j * BN, bh);
+                if (r > 0) ok = mx::mbar_wait(bar(BAR_V_EMPTY + s), (r - 1) & 1, abort_flag, P.status);
+                if (!ok) break;
+                mx::mbar_expect_tx(bar(BAR_V_FULL + s), TILE_BYTES);
+                mx::tma_load_3d(smem_base + SMEM_V + s * TILE_BYTES, &tmV, bar(BAR_V_FULL + s), 0,
+                                j * BN, bh);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 9) {
+        // ------------------------- MMA issuer ---------------------------
+        if (lane == 0) {
+            constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BM, BN, false, false);
+            constexpr uint32_t IDESC_O = mx::mma_idesc_bf16(BM, HD, false, true);
+            bool ok = mx::mbar_wait(bar(BAR_Q_FULL), 0, abort_flag, P.status);
+            auto issue_s = [&](int t, int stage) {
+                uint64_t a = mx::smem_desc_sw128(smem_base + SMEM_Q + t * TILE_BYTES);
+                uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_K + stage * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k)  // 32 bytes per 16-element step inside the swizzle span
+                    mx::mma_ss(tmem + TM_S + t * BN, a + 2 * k, b + 2 * k, IDESC_S, k > 0);
+                mx::mma_commit(bar(BAR_S_FULL + t));
+            };
+            if (ok && n_max > 0) ok = mx::mbar_wait(bar(BAR_K_FULL + 0), 0, abort_flag, P.status);
+            if (ok && n_max > 0) {
+                mx::tc_fence_after();
+                for (int t = 0; t < QT; ++t)
+                    if (n_it[t] > 0) issue_s(t, 0);
+                mx::mma_commit(bar(BAR_K_EMPTY + 0));
+            }
+            for (int j = 0; j < n_max && ok; ++j) {
+                int s = j % KV_STAGES, r = j / KV_STAGES;
+                int s1 = (j + 1) % KV_STAGES, r1 = (j + 1) / KV_STAGES;
+                ok = mx::mbar_wait(bar(BAR_V_FULL + s), r & 1, abort_flag, P.status);
+                if (ok && j + 1 < n_max)
+                    ok = mx::mbar_wait(bar(BAR_K_FULL + s1), r1 & 1, abort_flag, P.status);
+                if (!ok) break;
+                for (int t = 0; t < QT && ok; ++t) {
+                    if (j >= n_it[t]) continue;
+                    ok = mx::mbar_wait(bar(BAR_P_READY + t), j & 1, abort_flag, P.status);
+                    if (!ok) break;
+                    mx::tc_fence_after();
+                    uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_V + s * TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BN / 16; ++k)  // 16 keys: 8 packed columns of P, 2048 bytes of V
+                        mx::mma_ts(tmem + TM_O + t * HD, tmem + TM_S + t * BN + 8 * k, b + 128 * k,
+                                   IDESC_O, (j > 0 || k > 0));
+                    mx::mma_commit(bar(BAR_O_DONE + t));
+                    if (j + 1 < n_it[t]) issue_s(t, s1);
+                }
+                if (!ok) break;
+                mx::mma_commit(bar(BAR_V_EMPTY + s));
+                if (j + 1 < n_max) mx::mma_commit(bar(BAR_K_EMPTY + s1));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------- softmax groups -----------------------
+        const int t = warp >> 2;             // query tile of this group
+        const int row_in_tile = tid & 127;
+        const int row = q0 + t * BM + row_in_tile;
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tm_s = tmem + lane_off + TM_S + t * BN;
+        const uint32_t tm_o = tmem + lane_off + TM_O + t * HD;
+        const float c = 0.125f * 1.4426950408889634f;  // scale * log2(e)
+        const int n_t = n_it[t];
+        float m = -CUDART_INF_F, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_t; ++j) {
+            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), j & 1, abort_flag, P.status));
+            if (!ok) break;
+            mx::tc_fence_after();
+            const int key0 = j * BN;
+            const bool need_mask = (key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM);
+            // pass 1: row max
+            float mx_ = m;
+#pragma unroll
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t v[32];
+                mx::tmem_ld32(tm_s + cc * 32, v);
+                mx::tmem_wait_ld();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        int key = key0 + cc * 32 + i;
+                        bool valid = key < N && (!P.causal || key <= row);
+                        mx_ = valid ? fmaxf(mx_, __uint_as_float(v[i])) : mx_;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx_ = fmaxf(mx_, __uint_as_float(v[i]));
+                }
+            }
+            const float m_new = mx_;
+            const float mc = m_new * c;
+            const float alpha = mx::ex2(m * c - mc);  // 0 on the first tile (m = -inf)
+            // pass 2: p = exp2(s*c - m*c), packed to bf16 over the S columns
+            float rs = 0.0f;
+#pragma unroll
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t v[32];
+                mx::tmem_ld32(tm_s + cc * 32, v);
+                mx::tmem_wait_ld();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = mx::ex2(fmaf(__uint_as_float(v[i]), c, -mc));
+                    float p1 = mx::ex2(fmaf(__uint_as_float(v[i + 1]), c, -mc));
+                    if (need_mask) {
+                        int key = key0 + cc * 32 + i;
+                        if (!(key < N && (!P.causal || key <= row))) p0 = 0.0f;
+                        if (!(key + 1 < N && (!P.causal || key + 1 <= row))) p1 = 0.0f;
+                    }
+                    rs += p0 + p1;
+                    pk[i >> 1] = mx::pack_bf16(p0, p1);
+                }
+                mx::tmem_st16(tm_s + cc * 16, pk);
+            }
+            l = l * alpha + rs;
+            m = m_new;
+            // rescale O once the previous P V has landed
+            if (j > 0) {
+                ok = __all_sync(0xFFFFFFFFu,
+                                mx::mbar_wait(bar(BAR_O_DONE + t), (j - 1) & 1, abort_flag, P.status));
+                if (!ok) break;
+                mx::tc_fence_after();
+                if (__any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
+#pragma unroll
+                    for (int cc = 0; cc < HD / 32; ++cc) {
+                        uint32_t v[32];
+                        mx::tmem_ld32(tm_o + cc * 32, v);
+                        mx::tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        mx::tmem_st32(tm_o + cc * 32, v);
+                    }
+                }
+            }
+            mx::tmem_wait_st();
+            mx::tc_fence_before();
+            mx::mbar_arrive(bar(BAR_P_READY + t));
+        }
+        // epilogue: O / l and the log-sum-exp
+        if (ok && n_t > 0) {
+            ok = __all_sync(0xFFFFFFFFu,
+                            mx::mbar_wait(bar(BAR_O_DONE + t), (n_t - 1) & 1, abort_flag, P.status));
+            if (ok) {
+                mx::tc_fence_after();
+                const float inv = 1.0f / l;
+                float *orow = P.O + ((size_t)bh * N + row) * HD;
+#pragma unroll
+                for (int cc = 0; cc < HD / 32; ++cc) {
+                    uint32_t v[32];
+                    mx::tmem_ld32(tm_o + cc * 32, v);
+                    mx::tmem_wait_ld();
+                    if (row < N) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            float4 o4 = make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
+                                                    __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+                            *(float4 *)(orow + cc * 32 + i) = o4;
+                        }
+                    }
+                }
+                if (P.L != nullptr && row < N) P.L[(size_t)bh * N + row] = m * 0.125f + __logf(l);
+            }
+        }
+    }
+
+    // ------------------------- teardown ---------------------------------
+    mx::tc_fence_before();
+    __syncthreads();
+    mx::tc_fence_after();
+    if (warp == 9) mx::tmem_dealloc(tmem, TM_COLS);
+}
+
+// fp32 -> bf16 (round to nearest even) for up to four equally sized tensors.
+struct CastParams {
+    const float *src[4];
+    __nv_bfloat16 *dst[4];
+    size_t count;  // elements per tensor, multiple of 8
+};
+
+__global__ void cast_bf16_kernel(const CastParams P) {
+    const float *src = P.src[blockIdx.y];
+    __nv_bfloat16 *dst = P.dst[blockIdx.y];
+    size_t n8 = P.count / 8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+         i += (size_t)gridDim.x * blockDim.x) {
+        float4 a = ((const float4 *)src)[2 * i], b = ((const float4 *)src)[2 * i + 1];
+        uint4 o;
+        o.x = mx::pack_bf16(a.x, a.y);
+        o.y = mx::pack_bf16(a.z, a.w);
+        o.z = mx::pack_bf16(b.x, b.y);
+        o.w = mx::pack_bf16(b.z, b.w);
+        ((uint4 *)dst)[i] = o;
+    }
+}
+
+}  // namespace
+
+int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src, void *const *dst,
+                      int n_tensors, size_t count) {
+    MX_REQUIRE(count % 8 == 0, MX230_ERR_INVALID_ARG, "cast: element count must be a multiple of 8");
+    if (count == 0 || n_tensors == 0) return MX230_OK;
+    CastParams P;
+    for (int i = 0; i < 4; ++i) {
+        P.src[i] = src[i < n_tensors ? i : 0];
+        P.dst[i] = (__nv_bfloat16 *)dst[i < n_tensors ? i : 0];
+        MX_REQUIRE((((uintptr_t)P.src[i] | (uintptr_t)P.dst[i]) & 15) == 0, MX230_ERR_INVALID_ARG,
+                   "cast: buffers must be 16-byte aligned");
+    }
+    P.count = count;
+    size_t n8 = count / 8;
+    unsigned bx = (unsigned)((n8 + 255) / 256);
+    unsigned cap = (unsigned)h->sm_count * 8;
+    if (bx > cap) bx = cap;
+    cast_bf16_kernel<<<dim3(bx, n_tensors), 256, 0, st>>>(P);
+    MX_LAUNCHED(h);
+    return MX230_OK;
+}
+
+int mx230_launch_flash_fwd(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
+                           const void *Vb, float *O, float *L, int batch_heads, int n, int causal) {
+    CUtensorMap tq, tk, tv;
+    uint64_t rs = HD * 2, os = (uint64_t)n * HD * 2;
+    int rc;
+    if ((rc = mx230_make_tmap_bf16(h, &tq, Qb, n, batch_heads, rs, os, BM))) return rc;
+    if ((rc = mx230_make_tmap_bf16(h, &tk, Kb, n, batch_heads, rs, os, BN))) return rc;
+    if ((rc = mx230_make_tmap_bf16(h, &tv, Vb, n, batch_heads, rs, os, BN))) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+        MX_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SMEM_ALLOC));
+        attr_set = true;
+    }
+    FwdParams P;
+    P.O = O;
+    P.L = L;
+    P.n = n;
+    P.causal = causal ? 1 : 0;
+    P.status = h->status_dev;
+    dim3 grid((n + QT * BM - 1) / (QT * BM), batch_heads);
+    flash_fwd_kernel<<<grid, FWD_THREADS, SMEM_ALLOC, st>>>(tq, tk, tv, P);
+    MX_LAUNCHED(h);
+    return MX230_OK;
+}
+
+static int check_flash_args(const char *who, mx230_handle *h, int batch_heads, int n) {
+    MX_REQUIRE(h != nullptr, MX230_ERR_INVALID_ARG, "%s: null handle", who);
+    MX_REQUIRE(batch_heads >= 0 && n >= 0, MX230_ERR_INVALID_ARG, "%s: negative size", who);
+    MX_REQUIRE(batch_heads <= 65535, MX230_ERR_UNSUPPORTED, "%s: batch_heads %d > 65535", who,
+               batch_heads);
+    return MX230_OK;
+}
+
+extern "C" int mx230_cast_bf16(mx230_handle *h, void *stream, const float *src, void *dst_bf16,
+                               size_t count) {
+    MX_REQUIRE(h && (count == 0 || (src && dst_bf16)), MX230_ERR_INVALID_ARG, "cast_bf16: null argument");
+    mx230_device_guard guard(h->device);
+    const float *s[1] = {src};
+    void *d[1] = {dst_bf16};
+    return mx230_launch_cast(h, (cudaStream_t)stream, s, d, 1, count);
+}
+
+extern "C" int mx230_attn_flash_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb,
+                                     const void *Vb, float *O, float *L_or_null, int batch_heads,
+                                     int n, int causal) {
+    int rc = check_flash_args("attn_flash_bf16", h, batch_heads, n);
+    if (rc) return rc;
+    if (batch_heads == 0 || n == 0) return MX230_OK;
+    MX_REQUIRE(Qb && Kb && Vb && O, MX230_ERR_INVALID_ARG, "attn_flash_bf16: null tensor");
+    MX_REQUIRE((((uintptr_t)O) & 15) == 0, MX230_ERR_INVALID_ARG, "attn_flash_bf16: O must be 16-byte aligned");
+    mx230_device_guard guard(h->device);
+    return mx230_launch_flash_fwd(h, (cudaStream_t)stream, Qb, Kb, Vb, O, L_or_null, batch_heads, n,
+                                  causal);
+}
+
+static int flash_fp32(mx230_handle *h, void *stream, const float *Q, const float *K, const float *V,
+                      float *O, float *L, int batch_heads, int n, int causal, const char *who) {
+    int rc = check_flash_args(who, h, batch_heads, n);
+    if (rc) return rc;
+    if (batch_heads == 0 || n == 0) return MX230_OK;
+    MX_REQUIRE(Q && K && V && O, MX230_ERR_INVALID_ARG, "%s: null tensor", who);
+    size_t need = mx230_flash_workspace_bytes(batch_heads, n, 0);
+    MX_REQUIRE(h->ws && need <= h->ws_bytes, MX230_ERR_WORKSPACE,
+               "%s: workspace %zu B < %zu B needed (call mx230_reserve)", who, h->ws_bytes, need);
+    mx230_device_guard guard(h->device);
+    size_t one = need / 3;
+    size_t count = (size_t)batch_heads * n * HD;
+    void *qb = h->ws, *kb = (char *)h->ws + one, *vb = (char *)h->ws + 2 * one;
+    const float *src[3] = {Q, K, V};
+    void *dst[3] = {qb, kb, vb};
+    rc = mx230_launch_cast(h, (cudaStream_t)stream, src, dst, 3, count);
+    if (rc) return rc;
+    return mx230_launch_flash_fwd(h, (cudaStream_t)stream, qb, kb, vb, O, L, batch_heads, n, causal);
+}
+
+extern "C" int mx230_attn_flash(mx230_handle *h, void *stream, const float *Q, const float *K,
+                                const float *V, float *O, int batch_heads, int n, int causal) {
+    return flash_fp32(h, stream, Q, K, V, O, nullptr, batch_heads, n, causal, "attn_flash");
+}
+
+extern "C" int mx230_attn_flash_lse(mx230_handle *h, void *stream, const float *Q, const float *K,
+                                    const float *V, float *O, float *L, int batch_heads, int n,
+                                    int causal) {
+    MX_REQUIRE(L != nullptr || batch_heads == 0 || n == 0, MX230_ERR_INVALID_ARG,
+               "attn_flash_lse: null L");
+    return flash_fp32(h, stream, Q, K, V, O, L, batch_heads, n, causal, "attn_flash_lse");
+}

@@ -1,0 +1,192 @@
+// Library state: per-device handle, workspace, status words, error strings and
+// TMA tensor-map construction.  Replaces the reference's context / module plumbing
+// (common/src/lib.rs:11-18, 02-flash-attention/src/main.rs:392-415).
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+static thread_local char g_err[512] = "";
+
+void mx230_set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int mx230_fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+extern "C" int mx230_abi_version(void) { return MX230_ABI_VERSION; }
+
+extern "C" const char *mx230_last_error(void) { return g_err; }
+
+extern "C" const char *mx230_status_string(int code) {
+    switch (code) {
+        case MX230_OK: return "ok";
+        case MX230_ERR_INVALID_ARG: return "invalid argument";
+        case MX230_ERR_UNSUPPORTED: return "unsupported shape or option";
+        case MX230_ERR_WORKSPACE: return "workspace too small";
+        case MX230_ERR_CUDA: return "CUDA call failed";
+        case MX230_ERR_DEVICE_STATUS: return "device-side bounded wait timed out";
+        case MX230_ERR_NO_DEVICE: return "no sm_100 device";
+        default: return "unknown status";
+    }
+}
+
+static const size_t N_COUNTERS = 1 << 16;
+
+extern "C" int mx230_create(mx230_handle **out, int device, size_t workspace_bytes) {
+    MX_REQUIRE(out != nullptr, MX230_ERR_INVALID_ARG, "mx230_create: out is null");
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return mx230_fail(MX230_ERR_NO_DEVICE, "mx230_create: no CUDA device visible");
+    }
+    MX_REQUIRE(device >= 0 && device < count, MX230_ERR_INVALID_ARG,
+               "mx230_create: device %d out of range (0..%d)", device, count - 1);
+    cudaDeviceProp prop;
+    MX_CHECK_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return mx230_fail(MX230_ERR_NO_DEVICE,
+                          "mx230_create: device %d is sm_%d%d; this library is built for sm_100a only",
+                          device, prop.major, prop.minor);
+    mx230_device_guard guard(device);
+    MX_CHECK_CUDA(cudaSetDevice(device));
+
+    mx230_handle *h = new mx230_handle();
+    memset(h, 0, sizeof(*h));
+    h->device = device;
+    h->sm_count = prop.multiProcessorCount;
+    h->q8_score_mode = MX230_Q8_SCORE_REF;
+    h->n_counters = N_COUNTERS;
+
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess) {
+        delete h;
+        return mx230_fail(MX230_ERR_CUDA, "mx230_create: cuTensorMapEncodeTiled unavailable");
+    }
+    h->encode_tiled = (mx230_encode_tiled_fn)fn;
+
+    if (cudaMalloc(&h->status_dev, 4 * sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&h->counters, N_COUNTERS * sizeof(unsigned)) != cudaSuccess) {
+        delete h;
+        return mx230_fail(MX230_ERR_CUDA, "mx230_create: cudaMalloc of status words failed");
+    }
+    cudaMemset(h->status_dev, 0, 4 * sizeof(int));
+    cudaMemset(h->counters, 0, N_COUNTERS * sizeof(unsigned));
+    if (workspace_bytes > 0) {
+        if (cudaMalloc(&h->ws, workspace_bytes) != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(h->status_dev);
+            cudaFree(h->counters);
+            delete h;
+            return mx230_fail(MX230_ERR_CUDA, "mx230_create: cudaMalloc(%zu) for the workspace failed",
+                              workspace_bytes);
+        }
+        h->ws_bytes = workspace_bytes;
+    }
+    MX_CHECK_CUDA(cudaDeviceSynchronize());
+    *out = h;
+    return MX230_OK;
+}
+
+extern "C" int mx230_destroy(mx230_handle *h) {
+    if (h == nullptr) return MX230_OK;
+    mx230_device_guard guard(h->device);
+    cudaDeviceSynchronize();
+    if (h->ws) cudaFree(h->ws);
+    if (h->status_dev) cudaFree(h->status_dev);
+    if (h->counters) cudaFree(h->counters);
+    delete h;
+    return MX230_OK;
+}
+
+extern "C" int mx230_reserve(mx230_handle *h, size_t bytes) {
+    MX_REQUIRE(h != nullptr, MX230_ERR_INVALID_ARG, "mx230_reserve: null handle");
+    if (bytes <= h->ws_bytes) return MX230_OK;
+    mx230_device_guard guard(h->device);
+    MX_CHECK_CUDA(cudaDeviceSynchronize());
+    if (h->ws) cudaFree(h->ws);
+    h->ws = nullptr;
+    h->ws_bytes = 0;
+    MX_CHECK_CUDA(cudaMalloc(&h->ws, bytes));
+    h->ws_bytes = bytes;
+    return MX230_OK;
+}
+
+extern "C" int mx230_set_option(mx230_handle *h, int option, int value) {
+    MX_REQUIRE(h != nullptr, MX230_ERR_INVALID_ARG, "mx230_set_option: null handle");
+    switch (option) {
+        case MX230_OPT_Q8_SCORE_MODE:
+            MX_REQUIRE(value == MX230_Q8_SCORE_REF || value == MX230_Q8_SCORE_EXACT,
+                       MX230_ERR_INVALID_ARG, "mx230_set_option: bad q8 score mode %d", value);
+            h->q8_score_mode = value;
+            return MX230_OK;
+        case MX230_OPT_DECODE_CHUNK:
+            MX_REQUIRE(value >= 0 && value <= 2048 && value % 128 == 0, MX230_ERR_INVALID_ARG,
+                       "mx230_set_option: decode chunk must be 0 or a multiple of 128 up to 2048");
+            h->decode_chunk = value;
+            return MX230_OK;
+        default:
+            return mx230_fail(MX230_ERR_INVALID_ARG, "mx230_set_option: unknown option %d", option);
+    }
+}
+
+extern "C" size_t mx230_flash_workspace_bytes(int batch_heads, int n, int with_backward) {
+    if (batch_heads <= 0 || n <= 0) return 0;
+    size_t one = (size_t)batch_heads * (size_t)n * 64 * sizeof(__nv_bfloat16);
+    one = (one + 1023) & ~(size_t)1023;
+    return one * (with_backward ? 4 : 3);
+}
+
+extern "C" size_t mx230_decode_workspace_bytes(int n_seq, int n_head, int max_splits) {
+    if (n_seq <= 0 || n_head <= 0 || max_splits <= 0) return 0;
+    return (size_t)n_seq * n_head * max_splits * 66 * sizeof(float);
+}
+
+extern "C" int mx230_check_status(mx230_handle *h, void *stream) {
+    MX_REQUIRE(h != nullptr, MX230_ERR_INVALID_ARG, "mx230_check_status: null handle");
+    mx230_device_guard guard(h->device);
+    MX_CHECK_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    int st[4] = {0, 0, 0, 0};
+    MX_CHECK_CUDA(cudaMemcpy(st, h->status_dev, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st[0] != 0 || st[1] != 0) {
+        cudaMemset(h->status_dev, 0, sizeof(st));
+        return mx230_fail(MX230_ERR_DEVICE_STATUS,
+                          "device status %d (1 = bounded wait timed out), detail %d", st[0], st[1]);
+    }
+    return MX230_OK;
+}
+
+extern "C" long long mx230_launch_count(const mx230_handle *h) { return h ? h->launches : 0; }
+
+int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
+                         uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes,
+                         uint32_t box_rows) {
+    MX_REQUIRE(((uintptr_t)base & 15) == 0, MX230_ERR_INVALID_ARG,
+               "tensor map base %p is not 16-byte aligned", base);
+    MX_REQUIRE(row_stride_bytes % 16 == 0 && outer_stride_bytes % 16 == 0, MX230_ERR_INVALID_ARG,
+               "tensor map strides must be multiples of 16 bytes");
+    cuuint64_t dims[3] = {64, rows, outer};
+    cuuint64_t strides[2] = {row_stride_bytes, outer_stride_bytes};
+    cuuint32_t box[3] = {64, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = h->encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base),
+                                 dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return mx230_fail(MX230_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return MX230_OK;
+}

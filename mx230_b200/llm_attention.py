@@ -1,0 +1,284 @@
+"""Host mirror of the reference engine's per-layer attention step
+(03-llm-engine/src/gpu.rs:2570-2672 decode, :2808-2918 graph decode, :3204-3347 prefill
+write path, :3530-3628 batched decode): RoPE -> KV write -> attention, with the kernel
+chosen by (cache format, paging).  One Python function per reference kernel symbol,
+same argument order; `KvCache` and `Paging` mirror gpu.rs:188-205 and :381-539.
+Tensors are torch CUDA tensors; nothing here synchronises or allocates on the step path.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import check, lib, ptr
+from .common import Handle, stream_ptr
+
+KV_BLOCK = 16  # 03-llm-engine/src/gpu.rs:209
+
+
+class KvCache:
+    """One layer's KV cache: fp32 `[slots][n_kv_head*64]`, or int8 codes of that shape
+    plus per-(slot, kv head) fp32 scale (and beta when `affine`), gpu.rs:188-205."""
+
+    def __init__(self, slots: int, n_kv_head: int, head_dim: int = 64, quant: bool = False,
+                 affine: bool = True, device="cuda"):
+        self.slots, self.n_kv_head, self.head_dim = slots, n_kv_head, head_dim
+        self.quant, self.affine = quant, affine
+        kvd = n_kv_head * head_dim
+        if quant:
+            self.k = torch.zeros(slots, kvd, dtype=torch.int8, device=device)
+            self.v = torch.zeros(slots, kvd, dtype=torch.int8, device=device)
+            self.ks = torch.zeros(slots, n_kv_head, dtype=torch.float32, device=device)
+            self.vs = torch.zeros(slots, n_kv_head, dtype=torch.float32, device=device)
+            self.kb = torch.zeros(slots, n_kv_head, dtype=torch.float32, device=device) if affine else None
+            self.vb = torch.zeros(slots, n_kv_head, dtype=torch.float32, device=device) if affine else None
+        else:
+            self.k = torch.zeros(slots, kvd, dtype=torch.float32, device=device)
+            self.v = torch.zeros(slots, kvd, dtype=torch.float32, device=device)
+
+    def q8_args(self):
+        return (ptr(self.k), ptr(self.v), ptr(self.ks), ptr(self.vs), ptr(self.kb), ptr(self.vb))
+
+    def nbytes(self) -> int:
+        n = self.k.numel() * self.k.element_size() * 2
+        if self.quant:
+            n += self.ks.numel() * 4 * (4 if self.affine else 2)
+        return n
+
+
+class Paging:
+    """Logical position -> physical row through a block table (gpu.rs:381-539):
+    row = table[t // block_size] * block_size + t % block_size."""
+
+    def __init__(self, table, block_size: int = KV_BLOCK):
+        self.table_dev = table  # int32 CUDA tensor [n_log] or [n_seq][n_log]
+        self.block_size = block_size
+        self.n_log = table.shape[-1]
+
+    def phys_row(self, host_table, pos: int) -> int:
+        return int(host_table[pos // self.block_size]) * self.block_size + pos % self.block_size
+
+
+# ---------------------------------------------------------------- rope
+def rope(h: Handle, qkv, pos: int, n_head, n_kv_head, head_dim, theta, stream=None):
+    check(lib().mx230_rope(h._h, stream_ptr(stream), ptr(qkv), pos, n_head, n_kv_head, head_dim, theta))
+
+
+def rope_dyn(h: Handle, qkv, pos_ptr, n_head, n_kv_head, head_dim, theta, stream=None):
+    check(lib().mx230_rope_dyn(h._h, stream_ptr(stream), ptr(qkv), ptr(pos_ptr), n_head, n_kv_head,
+                               head_dim, theta))
+
+
+def rope_batch(h: Handle, qkv, pos0, n_tok, n_head, n_kv_head, head_dim, stride, theta, stream=None):
+    check(lib().mx230_rope_batch(h._h, stream_ptr(stream), ptr(qkv), pos0, n_tok, n_head, n_kv_head,
+                                 head_dim, stride, theta))
+
+
+def rope_seqpos(h: Handle, qkv, pos, n_seq, n_head, n_kv_head, head_dim, stride, theta, stream=None):
+    check(lib().mx230_rope_seqpos(h._h, stream_ptr(stream), ptr(qkv), ptr(pos), n_seq, n_head,
+                                  n_kv_head, head_dim, stride, theta))
+
+
+# ---------------------------------------------------------------- fp32 KV write
+def copy_kv(h: Handle, c: KvCache, qkv, pos: int, q_dim, kv_dim, stream=None):
+    check(lib().mx230_copy_kv(h._h, stream_ptr(stream), ptr(c.k), ptr(c.v), ptr(qkv), pos, q_dim, kv_dim))
+
+
+def copy_kv_dyn(h: Handle, c: KvCache, qkv, pos_ptr, q_dim, kv_dim, stream=None):
+    check(lib().mx230_copy_kv_dyn(h._h, stream_ptr(stream), ptr(c.k), ptr(c.v), ptr(qkv),
+                                  ptr(pos_ptr), q_dim, kv_dim))
+
+
+def copy_kv_paged_dyn(h: Handle, c: KvCache, qkv, pos_ptr, q_dim, kv_dim, pg: Paging, stream=None):
+    check(lib().mx230_copy_kv_paged_dyn(h._h, stream_ptr(stream), ptr(c.k), ptr(c.v), ptr(qkv),
+                                        ptr(pos_ptr), q_dim, kv_dim, ptr(pg.table_dev), pg.block_size))
+
+
+def copy_kv_batch(h: Handle, c: KvCache, qkv, pos0, n_tok, q_dim, kv_dim, stride, pg: Paging | None = None,
+                  stream=None):
+    if pg is None:
+        check(lib().mx230_copy_kv_batch(h._h, stream_ptr(stream), ptr(c.k), ptr(c.v), ptr(qkv), pos0,
+                                        n_tok, q_dim, kv_dim, stride))
+    else:
+        check(lib().mx230_copy_kv_batch_paged(h._h, stream_ptr(stream), ptr(c.k), ptr(c.v), ptr(qkv),
+                                              pos0, n_tok, q_dim, kv_dim, stride, ptr(pg.table_dev),
+                                              pg.block_size))
+
+
+def copy_kv_seqpos(h: Handle, c: KvCache, qkv, pos, n_seq, q_dim, kv_dim, qkv_stride, pg: Paging,
+                   stream=None):
+    check(lib().mx230_copy_kv_seqpos(h._h, stream_ptr(stream), ptr(c.k), ptr(c.v), ptr(qkv), ptr(pos),
+                                     n_seq, q_dim, kv_dim, qkv_stride, ptr(pg.table_dev),
+                                     pg.block_size, pg.n_log))
+
+
+# ---------------------------------------------------------------- int8 quantize-on-write
+def quantize_kv(h: Handle, c: KvCache, qkv, pos: int, q_dim, n_kv_head, head_dim, stream=None):
+    check(lib().mx230_quantize_kv(h._h, stream_ptr(stream), *c.q8_args(), ptr(qkv), pos, q_dim,
+                                  n_kv_head, head_dim))
+
+
+def quantize_kv_dyn(h: Handle, c: KvCache, qkv, pos_ptr, q_dim, n_kv_head, head_dim, stream=None):
+    check(lib().mx230_quantize_kv_dyn(h._h, stream_ptr(stream), *c.q8_args(), ptr(qkv), ptr(pos_ptr),
+                                      q_dim, n_kv_head, head_dim))
+
+
+def quantize_kv_paged_dyn(h: Handle, c: KvCache, qkv, pos_ptr, q_dim, n_kv_head, head_dim, pg: Paging,
+                          stream=None):
+    check(lib().mx230_quantize_kv_paged_dyn(h._h, stream_ptr(stream), *c.q8_args(), ptr(qkv),
+                                            ptr(pos_ptr), q_dim, n_kv_head, head_dim,
+                                            ptr(pg.table_dev), pg.block_size))
+
+
+def quantize_kv_batch(h: Handle, c: KvCache, qkv, pos0, n_tok, q_dim, n_kv_head, head_dim, stride,
+                      pg: Paging | None = None, stream=None):
+    if pg is None:
+        check(lib().mx230_quantize_kv_batch(h._h, stream_ptr(stream), *c.q8_args(), ptr(qkv), pos0,
+                                            n_tok, q_dim, n_kv_head, head_dim, stride))
+    else:
+        check(lib().mx230_quantize_kv_batch_paged(h._h, stream_ptr(stream), *c.q8_args(), ptr(qkv),
+                                                  pos0, n_tok, q_dim, n_kv_head, head_dim, stride,
+                                                  ptr(pg.table_dev), pg.block_size))
+
+
+def quantize_kv_seqpos(h: Handle, c: KvCache, qkv, pos, n_seq, q_dim, n_kv_head, head_dim, qkv_stride,
+                       pg: Paging, stream=None):
+    check(lib().mx230_quantize_kv_seqpos(h._h, stream_ptr(stream), *c.q8_args(), ptr(qkv), ptr(pos),
+                                         n_seq, q_dim, n_kv_head, head_dim, qkv_stride,
+                                         ptr(pg.table_dev), pg.block_size, pg.n_log))
+
+
+# ---------------------------------------------------------------- decode attention
+def attn_decode(h: Handle, out, qkv, c: KvCache, t_cur: int, n_head, n_kv_head, head_dim,
+                pg: Paging | None = None, stream=None):
+    """attn_decode / attn_decode_paged / attn_decode_q8 / attn_decode_q8_paged, chosen by
+    (cache format, paging) as gpu.rs:2607-2670."""
+    s = stream_ptr(stream)
+    L = lib()
+    if c.quant:
+        if pg is None:
+            check(L.mx230_attn_decode_q8(h._h, s, ptr(out), ptr(qkv), *c.q8_args(), t_cur, n_head,
+                                         n_kv_head, head_dim))
+        else:
+            check(L.mx230_attn_decode_q8_paged(h._h, s, ptr(out), ptr(qkv), *c.q8_args(), t_cur, n_head,
+                                               n_kv_head, head_dim, ptr(pg.table_dev), pg.block_size))
+    else:
+        if pg is None:
+            check(L.mx230_attn_decode(h._h, s, ptr(out), ptr(qkv), ptr(c.k), ptr(c.v), t_cur, n_head,
+                                      n_kv_head, head_dim))
+        else:
+            check(L.mx230_attn_decode_paged(h._h, s, ptr(out), ptr(qkv), ptr(c.k), ptr(c.v), t_cur,
+                                            n_head, n_kv_head, head_dim, ptr(pg.table_dev),
+                                            pg.block_size))
+
+
+def attn_decode_dyn(h: Handle, out, qkv, c: KvCache, pos_ptr, n_head, n_kv_head, head_dim,
+                    pg: Paging | None = None, stream=None):
+    """The `_dyn` forms of gpu.rs:2808-2918: position read from device memory."""
+    s = stream_ptr(stream)
+    L = lib()
+    if c.quant:
+        if pg is None:
+            check(L.mx230_attn_decode_q8_dyn(h._h, s, ptr(out), ptr(qkv), *c.q8_args(), ptr(pos_ptr),
+                                             n_head, n_kv_head, head_dim))
+        else:
+            check(L.mx230_attn_decode_q8_paged_dyn(h._h, s, ptr(out), ptr(qkv), *c.q8_args(),
+                                                   ptr(pos_ptr), n_head, n_kv_head, head_dim,
+                                                   ptr(pg.table_dev), pg.block_size))
+    else:
+        if pg is None:
+            check(L.mx230_attn_decode_dyn(h._h, s, ptr(out), ptr(qkv), ptr(c.k), ptr(c.v), ptr(pos_ptr),
+                                          n_head, n_kv_head, head_dim))
+        else:
+            check(L.mx230_attn_decode_paged_dyn(h._h, s, ptr(out), ptr(qkv), ptr(c.k), ptr(c.v),
+                                                ptr(pos_ptr), n_head, n_kv_head, head_dim,
+                                                ptr(pg.table_dev), pg.block_size))
+
+
+def attn_decode_batched(h: Handle, out, qkv, c: KvCache, pos, n_seq, n_head, n_kv_head, head_dim,
+                        pg: Paging, qkv_stride, out_stride, stream=None):
+    """attn_decode_batched / attn_decode_q8_batched, gpu.rs:3530-3628."""
+    s = stream_ptr(stream)
+    if c.quant:
+        check(lib().mx230_attn_decode_q8_batched(h._h, s, ptr(out), ptr(qkv), *c.q8_args(), ptr(pos),
+                                                 n_seq, n_head, n_kv_head, head_dim, ptr(pg.table_dev),
+                                                 pg.block_size, pg.n_log, qkv_stride, out_stride))
+    else:
+        check(lib().mx230_attn_decode_batched(h._h, s, ptr(out), ptr(qkv), ptr(c.k), ptr(c.v), ptr(pos),
+                                              n_seq, n_head, n_kv_head, head_dim, ptr(pg.table_dev),
+                                              pg.block_size, pg.n_log, qkv_stride, out_stride))
+
+
+def _cache_args(c: KvCache):
+    if c.quant:
+        return (None, None) + c.q8_args()
+    return (ptr(c.k), ptr(c.v), None, None, None, None, None, None)
+
+
+def attn_decode_slab(h: Handle, out, qkv, c: KvCache, pos, n_seq, n_head, n_kv_head, head_dim,
+                     seq_rows, qkv_stride, out_stride, stream=None):
+    """Batched decode over contiguous per-sequence cache slabs of `seq_rows` rows."""
+    check(lib().mx230_attn_decode_slab(h._h, stream_ptr(stream), ptr(out), ptr(qkv), *_cache_args(c),
+                                       ptr(pos), n_seq, n_head, n_kv_head, head_dim, seq_rows,
+                                       qkv_stride, out_stride))
+
+
+def attn_decode_partial(h: Handle, part_m, part_l, part_acc, qkv, c: KvCache, t0, t1, n_seq, n_head,
+                        n_kv_head, head_dim, seq_rows, qkv_stride, stream=None):
+    """Unnormalised (m, l, acc) of keys [t0, t1) per (sequence, query head)."""
+    check(lib().mx230_attn_decode_partial(h._h, stream_ptr(stream), ptr(part_m), ptr(part_l),
+                                          ptr(part_acc), ptr(qkv), *_cache_args(c), t0, t1, n_seq,
+                                          n_head, n_kv_head, head_dim, seq_rows, qkv_stride))
+
+
+def merge_partials(h: Handle, out, m, l, acc, parts, rows, head_dim=64, stream=None):
+    check(lib().mx230_merge_partials(h._h, stream_ptr(stream), ptr(out), ptr(m), ptr(l), ptr(acc),
+                                     parts, rows, head_dim))
+
+
+# ---------------------------------------------------------------- the step
+def decode_step(h: Handle, out, qkv, c: KvCache, pos: int, n_head, n_kv_head, head_dim, theta,
+                pg: Paging | None = None, host_table=None, use_rope=True, stream=None):
+    """One token of one sequence, as forward_layers does per layer (gpu.rs:2570-2672):
+    RoPE, KV write at the host-resolved physical row, then attention over 0..=pos."""
+    q_dim, kv_dim = n_head * head_dim, n_kv_head * head_dim
+    if use_rope:
+        rope(h, qkv, pos, n_head, n_kv_head, head_dim, theta, stream)
+    phys = pos if pg is None else pg.phys_row(host_table, pos)
+    if c.quant:
+        quantize_kv(h, c, qkv, phys, q_dim, n_kv_head, head_dim, stream)
+    else:
+        copy_kv(h, c, qkv, phys, q_dim, kv_dim, stream)
+    attn_decode(h, out, qkv, c, pos, n_head, n_kv_head, head_dim, pg, stream)
+
+
+def decode_step_dyn(h: Handle, out, qkv, c: KvCache, pos_ptr, n_head, n_kv_head, head_dim, theta,
+                    pg: Paging | None = None, use_rope=True, stream=None):
+    """The graph-capturable step of forward_body_dyn (gpu.rs:2808-2918)."""
+    q_dim, kv_dim = n_head * head_dim, n_kv_head * head_dim
+    if use_rope:
+        rope_dyn(h, qkv, pos_ptr, n_head, n_kv_head, head_dim, theta, stream)
+    if c.quant:
+        if pg is None:
+            quantize_kv_dyn(h, c, qkv, pos_ptr, q_dim, n_kv_head, head_dim, stream)
+        else:
+            quantize_kv_paged_dyn(h, c, qkv, pos_ptr, q_dim, n_kv_head, head_dim, pg, stream)
+    else:
+        if pg is None:
+            copy_kv_dyn(h, c, qkv, pos_ptr, q_dim, kv_dim, stream)
+        else:
+            copy_kv_paged_dyn(h, c, qkv, pos_ptr, q_dim, kv_dim, pg, stream)
+    attn_decode_dyn(h, out, qkv, c, pos_ptr, n_head, n_kv_head, head_dim, pg, stream)
+
+
+def batched_step(h: Handle, out, qkv, c: KvCache, pos, n_seq, n_head, n_kv_head, head_dim, theta,
+                 pg: Paging, qkv_stride, out_stride, use_rope=True, stream=None):
+    """One token for each of n_seq sequences, as forward_batched (gpu.rs:3530-3628)."""
+    q_dim, kv_dim = n_head * head_dim, n_kv_head * head_dim
+    if use_rope:
+        rope_seqpos(h, qkv, pos, n_seq, n_head, n_kv_head, head_dim, qkv_stride, theta, stream)
+    if c.quant:
+        quantize_kv_seqpos(h, c, qkv, pos, n_seq, q_dim, n_kv_head, head_dim, qkv_stride, pg, stream)
+    else:
+        copy_kv_seqpos(h, c, qkv, pos, n_seq, q_dim, kv_dim, qkv_stride, pg, stream)
+    attn_decode_batched(h, out, qkv, c, pos, n_seq, n_head, n_kv_head, head_dim, pg, qkv_stride,
+                        out_stride, stream)

@@ -1,0 +1,55 @@
+"""The C-ABI library loads without a GPU and exports every symbol the header declares."""
+import ctypes as C
+import os
+import subprocess
+
+import pytest
+
+from mx230_b200 import _lib, build
+
+
+def test_library_builds_and_loads(lib_built):
+    assert os.path.exists(lib_built)
+    L = _lib.lib()
+    assert L.mx230_abi_version() == 1
+
+
+def test_every_declared_symbol_is_exported(lib_built):
+    protos = _lib.declared_functions()
+    assert len(protos) >= 45, sorted(protos)
+    raw = C.CDLL(lib_built)
+    missing = [n for n in protos if not hasattr(raw, n)]
+    assert not missing, missing
+    # and nothing is exported that the header does not declare
+    out = subprocess.run(["nm", "-D", "--defined-only", lib_built], capture_output=True, text=True).stdout
+    exported = {ln.split()[-1] for ln in out.splitlines() if " T mx230_" in ln}
+    extra = {e for e in exported if e.startswith("mx230_") and "launch" not in e
+             and e not in protos and not e.startswith("mx230_set_error") and e != "mx230_fail"
+             and e != "mx230_make_tmap_bf16"}
+    assert not extra, extra
+
+
+def test_status_strings_and_errors(lib_built):
+    L = _lib.lib()
+    assert L.mx230_status_string(0) == b"ok"
+    assert b"workspace" in L.mx230_status_string(_lib.ERR_WORKSPACE)
+    # null out-pointer is rejected before any CUDA call
+    assert L.mx230_create(None, 0, 0) == _lib.ERR_INVALID_ARG
+    assert b"null" in L.mx230_last_error()
+    assert L.mx230_flash_workspace_bytes(48, 4096, 1) == 4 * 48 * 4096 * 64 * 2
+    assert L.mx230_flash_workspace_bytes(0, 4096, 1) == 0
+
+
+def test_create_without_device_fails_loudly(lib_built):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from mx230_b200.common import Handle
+    with pytest.raises(_lib.Mx230Error) as e:
+        Handle(0, 0)
+    assert e.value.code in (_lib.ERR_NO_DEVICE, _lib.ERR_CUDA)
+
+
+def test_sources_are_sm100a_only():
+    assert build.ARCH_FLAGS == ["-gencode", "arch=compute_100a,code=sm_100a"]
+    assert len(build.sources()) >= 5

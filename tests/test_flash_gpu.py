@@ -1,0 +1,183 @@
+"""Flash-attention forward / backward through the C ABI vs the oracle.
+
+Parity bar for floating point (bf16 operands, fp32 accumulation): max-abs error 2e-2 and
+norm-wise mean relative error sum|got-want| / sum|want| <= 5e-3 against the oracle's
+fp32 result, for O, L, dQ, dK, dV.  Inputs: the reference's own test inputs (uniform
+xorshift, N=512, seeds 1,2,3 / 11..14: 02-flash-attention/src/main.rs:419-499) and
+N(0,1) data at odd sizes.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from mx230_b200 import _lib
+from mx230_b200 import flash_attention as fa
+from tests.conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def nan_like(shape):
+    return torch.full(shape, float("nan"), device="cuda")
+
+
+def run_fwd(handle, q, k, v, causal):
+    n = q.shape[-2]
+    o = nan_like(q.shape)
+    l = nan_like(q.shape[:-1])
+    fa.run_flash_lse(handle, dev(q), dev(k), dev(v), o, l, n, causal)
+    handle.check_status()
+    return o.cpu().numpy(), l.cpu().numpy()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_forward_reference_inputs(handle, causal):
+    """run_verify: N=512, seeds 1,2,3 (02-flash-attention/src/main.rs:419-453)."""
+    n = 512
+    q, k, v = (oracle.pseudo_rand(n * 64, s).reshape(n, 64) for s in (1, 2, 3))
+    o, l = run_fwd(handle, q, k, v, causal)
+    wo, wl = oracle.attn_fwd(q, k, v, causal)
+    assert_close(o, wo, "O")
+    assert_close(l, wl, "L")
+    # run_flash (no L) gives the same O
+    o2 = nan_like((n, 64))
+    fa.run_flash(handle, dev(q), dev(k), dev(v), o2, n, causal)
+    assert np.array_equal(o2.cpu().numpy(), o)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("n", [1, 2, 63, 64, 65, 127, 128, 129, 255, 256, 257, 384, 1000])
+def test_forward_odd_sizes(handle, n, causal):
+    q, k, v = (oracle.normal((n, 64), 100 + n, i) for i in range(3))
+    o, l = run_fwd(handle, q, k, v, causal)
+    wo, wl = oracle.attn_fwd(q, k, v, causal)
+    assert_close(o, wo, f"O n={n}")
+    assert_close(l, wl, f"L n={n}")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_forward_batched_heads(handle, causal):
+    b, h, n = 2, 3, 600
+    q, k, v = (oracle.normal((b, h, n, 64), 7, i) for i in range(3))
+    o, l = run_fwd(handle, q, k, v, causal)
+    wo, wl = oracle.attn_fwd(q, k, v, causal)
+    assert_close(o, wo, "O")
+    assert_close(l, wl, "L")
+    # every head equals the same head run alone (heads are independent units)
+    o1, l1 = run_fwd(handle, q[1, 2], k[1, 2], v[1, 2], causal)
+    assert np.array_equal(o1, o[1, 2]) and np.array_equal(l1, l[1, 2])
+
+
+def test_forward_is_deterministic_and_bf16_entry_agrees(handle):
+    n = 777
+    q, k, v = (oracle.normal((4, n, 64), 8, i) for i in range(3))
+    a, la_ = run_fwd(handle, q, k, v, True)
+    b, lb = run_fwd(handle, q, k, v, True)
+    assert np.array_equal(a, b) and np.array_equal(la_, lb)
+    qb, kb, vb = (torch.empty(4, n, 64, dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    for src, dst in ((q, qb), (k, kb), (v, vb)):
+        fa.cast_bf16(handle, dev(src), dst)
+    assert torch.equal(qb, dev(q).to(torch.bfloat16))  # round-to-nearest-even cast
+    o = nan_like((4, n, 64))
+    l = nan_like((4, n))
+    fa.run_flash_bf16(handle, qb, kb, vb, o, l, n, True)
+    handle.check_status()
+    assert np.array_equal(o.cpu().numpy(), a) and np.array_equal(l.cpu().numpy(), la_)
+
+
+def run_bwd(handle, q, k, v, do, causal):
+    n = q.shape[-2]
+    dq_, dk_, dv_, ddo = dev(q), dev(k), dev(v), dev(do)
+    o = nan_like(q.shape)
+    l = nan_like(q.shape[:-1])
+    fa.run_flash_lse(handle, dq_, dk_, dv_, o, l, n, causal)
+    delta = nan_like(q.shape[:-1])
+    fa.run_preprocess(handle, ddo, o, delta, n)
+    gq, gk, gv = nan_like(q.shape), nan_like(q.shape), nan_like(q.shape)
+    fa.run_bwd_flash(handle, dq_, dk_, dv_, ddo, l, delta, gq, gk, gv, n, causal)
+    handle.check_status()
+    return o.cpu().numpy(), delta.cpu().numpy(), gq.cpu().numpy(), gk.cpu().numpy(), gv.cpu().numpy()
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_backward_reference_inputs(handle, causal):
+    """run_verify_bwd: N=512, seeds 11..14 (02-flash-attention/src/main.rs:457-499)."""
+    n = 512
+    q, k, v, do = (oracle.pseudo_rand(n * 64, s).reshape(n, 64) for s in (11, 12, 13, 14))
+    o, delta, gq, gk, gv = run_bwd(handle, q, k, v, do, causal)
+    wq, wk, wv = oracle.attn_bwd(q, k, v, do, causal)
+    assert_close(delta, oracle.bwd_preprocess(do, o), "Delta", max_abs=1e-5, mean_rel=1e-5)
+    assert_close(gq, wq, "dQ")
+    assert_close(gk, wk, "dK")
+    assert_close(gv, wv, "dV")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("n", [1, 63, 64, 65, 128, 129, 191, 256, 257, 1000])
+def test_backward_odd_sizes(handle, n, causal):
+    q, k, v, do = (oracle.normal((n, 64), 200 + n, i) for i in range(4))
+    _, _, gq, gk, gv = run_bwd(handle, q, k, v, do, causal)
+    wq, wk, wv = oracle.attn_bwd(q, k, v, do, causal)
+    assert_close(gq, wq, f"dQ n={n}")
+    assert_close(gk, wk, f"dK n={n}")
+    assert_close(gv, wv, f"dV n={n}")
+
+
+def test_backward_batched_split_passes_and_determinism(handle):
+    b, h, n = 2, 2, 520
+    q, k, v, do = (oracle.normal((b, h, n, 64), 9, i) for i in range(4))
+    _, _, gq, gk, gv = run_bwd(handle, q, k, v, do, True)
+    wq, wk, wv = oracle.attn_bwd(q, k, v, do, True)
+    assert_close(gq, wq, "dQ")
+    assert_close(gk, wk, "dK")
+    assert_close(gv, wv, "dV")
+    _, _, gq2, gk2, gv2 = run_bwd(handle, q, k, v, do, True)
+    assert np.array_equal(gq, gq2) and np.array_equal(gk, gk2) and np.array_equal(gv, gv2)
+    # the two passes are also callable on their own (attn_bwd_dq / attn_bwd_dkv)
+    dq_, dk_, dv_, ddo = dev(q), dev(k), dev(v), dev(do)
+    o, l, delta = nan_like(q.shape), nan_like(q.shape[:-1]), nan_like(q.shape[:-1])
+    fa.run_flash_lse(handle, dq_, dk_, dv_, o, l, n, True)
+    fa.run_preprocess(handle, ddo, o, delta, n)
+    a, bb, c = nan_like(q.shape), nan_like(q.shape), nan_like(q.shape)
+    fa.run_bwd_dq(handle, dq_, dk_, dv_, ddo, l, delta, a, n, True)
+    fa.run_bwd_dkv(handle, dq_, dk_, dv_, ddo, l, delta, bb, c, n, True)
+    handle.check_status()
+    assert np.array_equal(a.cpu().numpy(), gq) and np.array_equal(bb.cpu().numpy(), gk)
+    assert np.array_equal(c.cpu().numpy(), gv)
+
+
+def test_linearity_in_v_and_do_at_full_length(handle):
+    """Size-independent properties at N=4096 (the benchmark's sequence length), where the
+    oracle would take minutes: O is linear in V; dV is linear in dO; row sums of softmax
+    weights are 1 (V = ones gives O = ones)."""
+    n, bh = 4096, 2
+    q, k, v = (oracle.normal((bh, n, 64), 11, i) for i in range(3))
+    ones = np.ones_like(v)
+    o1, _ = run_fwd(handle, q, k, ones, True)
+    assert np.abs(o1 - 1.0).max() < 2e-2
+    oa, l = run_fwd(handle, q, k, v, True)
+    ob, _ = run_fwd(handle, q, k, 2.0 * v, True)
+    assert np.array_equal(ob, 2.0 * oa)  # scaling by 2 is exact in bf16 and fp32
+    # a sampled row against the oracle's per-row arithmetic
+    rows = oracle.attn_fwd_rows(q, k, v, True, 5, 997)
+    assert_close(oa[:, 5::997], rows, "sampled rows")
+
+
+def test_zero_sizes_and_bad_arguments(handle):
+    z = torch.zeros(0, 64, device="cuda")
+    fa.run_flash(handle, z, z, z, z, 0, True)  # N = 0 is a no-op
+    from mx230_b200.common import Handle
+    small = Handle(0, 1024)
+    q = torch.zeros(512, 64, device="cuda")
+    with pytest.raises(_lib.Mx230Error) as e:
+        fa.run_flash(small, q, q, q, q, 512, False)
+    assert e.value.code == _lib.ERR_WORKSPACE
+    small.reserve(fa.workspace_bytes(1, 512, False))
+    fa.run_flash(small, q, q, q, torch.zeros_like(q), 512, False)
+    small.check_status()
+    small.close()
