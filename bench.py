@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path: causal flash-attention forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (one "step"): the causal forward + backward of B=4, H=12, N=4096, d=64 through
+the fp32-in / fp32-out C-ABI entry points -- attn_flash_lse, attn_bwd_preprocess,
+attn_bwd_flash -- on seeded synthetic N(0,1) tensors.  Operands are rounded to bf16 by
+the library's own staging kernel inside the timed region; accumulation is fp32.
+Algorithmic work per step: forward 2*B*H*N^2*d = 103.08 GFLOP, backward 2.5x = 257.70 GFLOP
+(the two recomputed matmuls of the atomic-free split are not counted).
+
+`value`   whole-job TFLOP/s with the inputs resident in HBM, CUDA-event timed, max over ranks.
+`e2e`     the same metric with the inputs in pinned HOST memory: every step copies Q, K, V, dO
+          host->device and O, L, dQ, dK, dV device->host inside the timed region.
+`roofline` per-launch achieved TFLOP/s of the dominant kernel, from event pairs the library
+          records around each launch during the timed steps, against the measured dense
+          bf16 peak of MEASURED_PEAKS.json.
+`cpu_baseline` the CPU restatement of the reference's attention (oracle/) on a bounded sample.
+`decode`  HBM GB/s of the int8-KV GQA decode step (14q/2kv, ctx 2048, batch 64) and of its
+          fp32-KV control, caches rotated through > L2 worth of copies.
+
+With N > 1 GPUs (torchrun) every rank runs the same per-GPU workload on its own (batch, head)
+units -- no data-path collective -- and the job value is N * units / max-over-ranks time
+(weak scaling).  `--impl reference` times the CPU oracle with all host threads instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+B, H, N, D = 4, 12, 4096, 64
+BH = B * H
+FWD_FLOP = 2.0 * BH * N * N * D          # causal forward
+BWD_FLOP = 2.5 * FWD_FLOP                # five matmuls of the same size
+STEP_FLOP = FWD_FLOP + BWD_FLOP
+# share of the backward's algorithmic work attributed to each pass: dQ owns 1 matmul, dK/dV own
+# 2, and the two shared ones (S, dP) are split evenly
+DQ_FLOP = BWD_FLOP * 2.0 / 5.0
+DKV_FLOP = BWD_FLOP * 3.0 / 5.0
+WORKLOAD = "causal flash-attention fwd+bwd, B=4 H=12 N=4096 d=64 (BASELINE.json configs[1])"
+NOMINAL_BF16_TFLOPS = 2250.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"bf16_tflops": p.get("bf16_tflops"), "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                "hbm_gbs": p.get("hbm_gbs"), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                mhz.append(float(r[0]))
+                mx = float(r[1])
+                for nm, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nm)
+            except Exception:
+                pass
+        mhz.sort()
+        # clocks under load: the upper half of the samples (idle samples pull the median down)
+        load = mhz[len(mhz) // 2:] if mhz else []
+        return {"sm_mhz": (load[len(load) // 2] if load else None), "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_sample(heads: int, threads: int):
+    """Forward + backward of `heads` heads of the workload on the CPU oracle; returns seconds."""
+    import oracle
+    q, k, v, do = (oracle.normal((heads, N, D), 1234, i) for i in range(4))
+    t0 = time.perf_counter()
+    oracle.attn_fwd(q, k, v, True, threads=threads)
+    oracle.attn_bwd(q, k, v, do, True, threads=threads)
+    return time.perf_counter() - t0
+
+
+def run_reference(args):
+    """The reference's CPU attention path (C restatement: the Rust sources cannot be built
+    here) with all host threads, each step a bounded sample of the workload."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    import oracle
+    threads = oracle.max_threads()
+    heads = threads  # one head of B*H per thread and step
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_sample(min(heads, 2), threads)
+    times = [cpu_sample(heads, threads) for _ in range(args.steps)]
+    sec = sum(times) / len(times)
+    tflops = STEP_FLOP * heads / BH / sec / 1e12
+    line = {
+        "impl": "reference", "metric": "attn_fwd_bwd_tflops", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": f"{heads} of {BH} (batch, head) units per step"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"{heads} of {BH} heads, N={N}, forward+backward, {threads} OpenMP threads"},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def decode_bench(h, torch, la, n_seq=64, nh=14, nkv=2, ctx=2048, iters=40):
+    """int8-KV GQA decode (and fp32 control): GB/s of algorithmic bytes, caches rotated so that
+    consecutive launches never hit L2-resident data."""
+    out = {}
+    qd, kvd = nh * 64, nkv * 64
+    for quant in (True, False):
+        per_seq = ctx * kvd * 2 * (1 if quant else 4) + (ctx * nkv * 16 if quant else 0) + qd * 8
+        nbytes = n_seq * per_seq
+        copies = max(2, int(4 * 126e6 / nbytes) + 1)
+        caches = []
+        for _ in range(copies):
+            c = la.KvCache(n_seq * ctx, nkv, 64, quant)
+            if quant:
+                c.k.random_(-128, 128), c.v.random_(-128, 128)
+                c.ks.uniform_(0.01, 0.03), c.vs.uniform_(0.01, 0.03), c.kb.normal_(), c.vb.normal_()
+            else:
+                c.k.normal_(), c.v.normal_()
+            caches.append(c)
+        q = torch.randn(n_seq, qd, device="cuda")
+        o = torch.empty(n_seq, qd, device="cuda")
+        pos = torch.full((n_seq,), ctx - 1, dtype=torch.int32, device="cuda")
+        for i in range(copies):
+            la.attn_decode_slab(h, o, q, caches[i], pos, n_seq, nh, nkv, 64, ctx, qd, qd)
+        torch.cuda.synchronize()
+        h.profile_reset()
+        h.profile_enable(True)
+        for i in range(iters):
+            la.attn_decode_slab(h, o, q, caches[i % copies], pos, n_seq, nh, nkv, 64, ctx, qd, qd)
+        h.profile_enable(False)
+        prof = h.profile_read()
+        name = "decode_q8_kernel" if quant else "decode_f32_kernel"
+        cnt, ms = prof[name]
+        out["int8_kv" if quant else "fp32_kv"] = {
+            "gbs": nbytes / (ms / cnt) / 1e6, "us_per_launch": 1e3 * ms / cnt, "bytes_per_launch": nbytes,
+            "batch": n_seq, "ctx": ctx, "heads": f"{nh}q/{nkv}kv", "cache_copies_rotated": copies}
+        del caches
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from mx230_b200 import flash_attention as fa
+    from mx230_b200 import llm_attention as la
+    from mx230_b200.common import Handle
+
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the CUDA library is the only implementation")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    h = Handle(local, fa.workspace_bytes(BH, N, True))
+    gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    q, k, v, do = (torch.randn(B, H, N, D, device="cuda", generator=gen) for _ in range(4))
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, N, device="cuda")
+    delta = torch.empty_like(lse)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        fa.run_flash_lse(h, q, k, v, o, lse, N, True)
+        fa.run_preprocess(h, do, o, delta, N)
+        fa.run_bwd_flash(h, q, k, v, do, lse, delta, dq, dk, dv, N, True)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    h.check_status()
+    barrier()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    l0 = h.launches
+    h.profile_reset()
+    h.profile_enable(True)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    h.profile_enable(False)
+    launches = h.launches - l0
+    prof = h.profile_read()
+    h.check_status()
+
+    # ---- end to end: pinned host tensors in, results out, every step ----
+    hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, do))
+    ho, hl, hdq, hdk, hdv = (torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (o, lse, dq, dk, dv))
+
+    def e2e_step():
+        for dst, src in ((q, hq), (k, hk), (v, hv), (do, hdo)):
+            dst.copy_(src, non_blocking=True)
+        step()
+        for dst, src in ((ho, o), (hl, lse), (hdq, dq), (hdk, dk), (hdv, dv)):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    f1.record(stream)
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None
+    h2d = sum(t.numel() * 4 for t in (hq, hk, hv, hdo))
+    d2h = sum(t.numel() * 4 for t in (ho, hl, hdq, hdk, hdv))
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+
+    dec = decode_bench(h, torch, la) if rank == 0 else None
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_step = ms / args.steps
+        value = world * STEP_FLOP / (ms_step * 1e-3) / 1e12
+        e2e_val = world * STEP_FLOP / (e2e_ms / e2e_steps * 1e-3) / 1e12
+        kern = {}
+        for name, flop in (("flash_fwd_kernel", FWD_FLOP), ("bwd_dq_kernel", DQ_FLOP), ("bwd_dkv_kernel", DKV_FLOP)):
+            if name in prof:
+                cnt, tot = prof[name]
+                kern[name] = {"launches": cnt, "ms_per_launch": tot / cnt,
+                              "achieved_tflops": flop / (tot / cnt * 1e-3) / 1e12, "flop_per_launch": flop}
+        for name in ("cast_bf16_kernel", "bwd_preprocess_kernel"):
+            if name in prof:
+                cnt, tot = prof[name]
+                kern[name] = {"launches": cnt, "ms_per_launch": tot / cnt}
+        # dominant kernel = the one with the largest share of device time
+        dom = max((n for n in kern if "achieved_tflops" in kern[n]), key=lambda n: kern[n]["ms_per_launch"] * kern[n]["launches"])
+        peak = peaks["bf16_tflops"]
+        roofline = {"bound": "tensor", "kernel": dom, "achieved": kern[dom]["achieved_tflops"], "peak": peak,
+                    "unit": "TFLOP/s", "frac": kern[dom]["achieved_tflops"] / peak, "traffic": None,
+                    "peak_source": f"{peaks['source']} dense bf16 burst (MEASURED_PEAKS.json)",
+                    "frac_of_nominal": kern[dom]["achieved_tflops"] / NOMINAL_BF16_TFLOPS,
+                    "per_kernel": kern}
+        import oracle
+        cores = oracle.max_threads()
+        heads = max(1, min(cores, 8))
+        sec = cpu_sample(heads, cores)
+        cpu = {"value": STEP_FLOP * heads / BH / sec / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+               "sample": f"{heads} of {BH} heads, N={N}, forward+backward, {cores} OpenMP threads, {sec:.1f} s"}
+        if dec:
+            for kk in dec:
+                dec[kk]["frac_of_measured_hbm"] = dec[kk]["gbs"] / peaks["hbm_gbs"]
+        line = {
+            "metric": "attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu_units": f"{BH} (batch, head) units",
+                       "l2": "inputs larger than L2 (4 x 50 MB fp32 operands per step)",
+                       "entry_points": "mx230_attn_flash_lse + mx230_attn_bwd_preprocess + mx230_attn_bwd_flash"},
+            "fwd_tflops": world * FWD_FLOP / (kern["flash_fwd_kernel"]["ms_per_launch"] * 1e-3) / 1e12,
+            "bwd_tflops": world * BWD_FLOP / ((kern["bwd_dq_kernel"]["ms_per_launch"] +
+                                               kern["bwd_dkv_kernel"]["ms_per_launch"]) * 1e-3) / 1e12,
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": launches, "clocks": clocks, "decode": dec,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    h.close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -59,6 +59,23 @@ enum {
     MX230_OPT_DECODE_CHUNK = 2   /* keys per decode CTA; 0 = automatic */
 };
 
+/* kernel ids of the profiling interface */
+enum {
+    MX230_K_CAST = 0,
+    MX230_K_FLASH_FWD = 1,
+    MX230_K_BWD_PREPROCESS = 2,
+    MX230_K_BWD_DQ = 3,
+    MX230_K_BWD_DKV = 4,
+    MX230_K_ROPE = 5,
+    MX230_K_COPY_KV = 6,
+    MX230_K_QUANTIZE_KV = 7,
+    MX230_K_DECODE_F32 = 8,
+    MX230_K_DECODE_Q8 = 9,
+    MX230_K_MERGE = 10,
+    MX230_K_PREFILL = 11,
+    MX230_K_COUNT = 12
+};
+
 typedef struct mx230_handle mx230_handle;
 
 /* ---- library / handle ------------------------------------------------------ */
@@ -81,6 +98,16 @@ size_t mx230_decode_workspace_bytes(int n_seq, int n_head, int max_splits);
 int mx230_check_status(mx230_handle *h, void *stream);
 /* Number of kernels launched through this handle so far. */
 long long mx230_launch_count(const mx230_handle *h);
+
+/* Per-kernel device timing (the role of the reference's opt-in prof_attn_us attribution,
+ * 03-llm-engine/src/gpu.rs:1922-1928): while enabled, every launch is bracketed by a CUDA
+ * event pair on the caller's stream.  mx230_profile_read synchronises the recorded events
+ * and returns, for kernel id `kernel` (MX230_K_*), the launch count and the summed device
+ * milliseconds since the last mx230_profile_reset. */
+int mx230_profile_enable(mx230_handle *h, int on);
+int mx230_profile_reset(mx230_handle *h);
+int mx230_profile_read(mx230_handle *h, int kernel, long long *launches, double *total_ms);
+const char *mx230_kernel_name(int kernel);
 
 /* ---- 02-flash-attention ----------------------------------------------------
  * Tensors are `batch_heads` independent heads laid out [batch_heads][n][64] fp32,

@@ -29,6 +29,23 @@ class Handle:
     def check_status(self, stream=None) -> None:
         check(lib().mx230_check_status(self._h, stream_ptr(stream)))
 
+    # per-kernel device timing (the reference's opt-in prof_*_us attribution, gpu.rs:1922-1928)
+    def profile_enable(self, on: bool = True) -> None:
+        check(lib().mx230_profile_enable(self._h, int(on)))
+
+    def profile_reset(self) -> None:
+        check(lib().mx230_profile_reset(self._h))
+
+    def profile_read(self) -> dict:
+        """kernel name -> (launches, total device ms) since the last reset."""
+        out = {}
+        for k in range(_lib.K_COUNT):
+            n, ms = C.c_longlong(), C.c_double()
+            check(lib().mx230_profile_read(self._h, k, C.byref(n), C.byref(ms)))
+            if n.value:
+                out[lib().mx230_kernel_name(k).decode()] = (int(n.value), float(ms.value))
+        return out
+
     @property
     def launches(self) -> int:
         return int(lib().mx230_launch_count(self._h))

@@ -38,7 +38,27 @@ struct mx230_handle {
     int decode_chunk;      // keys per decode CTA (0 = automatic)
     long long launches;    // kernels launched through this handle
     mx230_encode_tiled_fn encode_tiled;
+    // per-kernel timing: event pairs recorded around launches while enabled
+    int prof_on;
+    int prof_used;                 // event pairs in flight
+    cudaEvent_t *prof_ev;          // [2 * PROF_CAP]
+    int *prof_kid;                 // [PROF_CAP]
+    long long prof_count[MX230_K_COUNT];
+    double prof_ms[MX230_K_COUNT];
 };
+
+constexpr int MX230_PROF_CAP = 8192;
+int mx230_prof_begin(mx230_handle *h, cudaStream_t st, int kid);  // returns slot or -1
+void mx230_prof_end(mx230_handle *h, cudaStream_t st, int slot);
+
+// Brackets one kernel launch: optional event pair, launch check, launch count.
+#define MX_LAUNCH(h, st, kid, ...)                                                          \
+    do {                                                                                    \
+        int _slot = (h)->prof_on ? mx230_prof_begin((h), (st), (kid)) : -1;                 \
+        __VA_ARGS__;                                                                        \
+        if (_slot >= 0) mx230_prof_end((h), (st), _slot);                                   \
+        MX_LAUNCHED(h);                                                                     \
+    } while (0)
 
 void mx230_set_error(const char *fmt, ...);
 int mx230_fail(int code, const char *fmt, ...);

@@ -690,14 +690,13 @@ int launch_g(mx230_handle *h, cudaStream_t st, const DecodeParams &P, dim3 grid,
         size_t sm = q8_smem_bytes(G);
         MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_kernel<G>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        decode_q8_kernel<G><<<grid, DEC_THREADS, sm, st>>>(P);
+        MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_kernel<G><<<grid, DEC_THREADS, sm, st>>>(P)));
     } else {
         size_t sm = f32_smem_bytes(G);
         MX_CHECK_CUDA(cudaFuncSetAttribute(decode_f32_kernel<G>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        decode_f32_kernel<G><<<grid, DEC_THREADS, sm, st>>>(P);
+        MX_LAUNCH(h, st, MX230_K_DECODE_F32, (decode_f32_kernel<G><<<grid, DEC_THREADS, sm, st>>>(P)));
     }
-    MX_LAUNCHED(h);
     return MX230_OK;
 }
 
@@ -941,8 +940,8 @@ extern "C" int mx230_merge_partials(mx230_handle *h, void *stream, float *out, c
     MX_REQUIRE(parts > 0 && rows >= 0, MX230_ERR_INVALID_ARG, "merge_partials: bad sizes");
     if (rows == 0) return MX230_OK;
     mx230_device_guard guard(h->device);
-    merge_partials_kernel<<<(rows * 16 + 127) / 128, 128, 0, (cudaStream_t)stream>>>(out, m, l, acc,
-                                                                                   parts, rows);
-    MX_LAUNCHED(h);
+    cudaStream_t st = (cudaStream_t)stream;
+    MX_LAUNCH(h, st, MX230_K_MERGE,
+              (merge_partials_kernel<<<(rows * 16 + 127) / 128, 128, 0, st>>>(out, m, l, acc, parts, rows)));
     return MX230_OK;
 }

@@ -536,8 +536,9 @@ int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, c
               int batch_heads, int n, int causal) {
     BwdParams P{L, Delta, dQ, nullptr, n, causal ? 1 : 0, h->status_dev};
     dim3 grid((n + NT * BT - 1) / (NT * BT), batch_heads);
-    bwd_dq_kernel<<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.own128[0], m.own128[3], m.str64[1], m.str64[2], P);
-    MX_LAUNCHED(h);
+    MX_LAUNCH(h, st, MX230_K_BWD_DQ,
+              (bwd_dq_kernel<<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.own128[0], m.own128[3], m.str64[1],
+                                                                  m.str64[2], P)));
     return MX230_OK;
 }
 
@@ -545,8 +546,9 @@ int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, 
                float *dV, int batch_heads, int n, int causal) {
     BwdParams P{L, Delta, dK, dV, n, causal ? 1 : 0, h->status_dev};
     dim3 grid((n + NT * BT - 1) / (NT * BT), batch_heads);
-    bwd_dkv_kernel<<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.own128[1], m.own128[2], m.str64[0], m.str64[3], P);
-    MX_LAUNCHED(h);
+    MX_LAUNCH(h, st, MX230_K_BWD_DKV,
+              (bwd_dkv_kernel<<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.own128[1], m.own128[2], m.str64[0],
+                                                                   m.str64[3], P)));
     return MX230_OK;
 }
 
@@ -610,8 +612,9 @@ extern "C" int mx230_attn_bwd_preprocess(mx230_handle *h, void *stream, const fl
                "attn_bwd_preprocess: inputs must be 16-byte aligned");
     mx230_device_guard guard(h->device);
     size_t threads = rows * 16;
-    bwd_preprocess_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(dO, O, Delta, rows);
-    MX_LAUNCHED(h);
+    cudaStream_t st = (cudaStream_t)stream;
+    MX_LAUNCH(h, st, MX230_K_BWD_PREPROCESS,
+              (bwd_preprocess_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(dO, O, Delta, rows)));
     return MX230_OK;
 }
 

@@ -347,8 +347,7 @@ int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src,
     unsigned bx = (unsigned)((n8 + 255) / 256);
     unsigned cap = (unsigned)h->sm_count * 8;
     if (bx > cap) bx = cap;
-    cast_bf16_kernel<<<dim3(bx, n_tensors), 256, 0, st>>>(P);
-    MX_LAUNCHED(h);
+    MX_LAUNCH(h, st, MX230_K_CAST, (cast_bf16_kernel<<<dim3(bx, n_tensors), 256, 0, st>>>(P)));
     return MX230_OK;
 }
 
@@ -373,8 +372,8 @@ int mx230_launch_flash_fwd(mx230_handle *h, cudaStream_t st, const void *Qb, con
     P.causal = causal ? 1 : 0;
     P.status = h->status_dev;
     dim3 grid((n + QT * BM - 1) / (QT * BM), batch_heads);
-    flash_fwd_kernel<<<grid, FWD_THREADS, SMEM_ALLOC, st>>>(tq, tk, tv, P);
-    MX_LAUNCHED(h);
+    MX_LAUNCH(h, st, MX230_K_FLASH_FWD,
+              (flash_fwd_kernel<<<grid, FWD_THREADS, SMEM_ALLOC, st>>>(tq, tk, tv, P)));
     return MX230_OK;
 }
 

@@ -108,6 +108,12 @@ extern "C" int mx230_destroy(mx230_handle *h) {
     if (h->ws) cudaFree(h->ws);
     if (h->status_dev) cudaFree(h->status_dev);
     if (h->counters) cudaFree(h->counters);
+    if (h->prof_ev) {
+        for (int i = 0; i < 2 * MX230_PROF_CAP; ++i)
+            if (h->prof_ev[i]) cudaEventDestroy(h->prof_ev[i]);
+        delete[] h->prof_ev;
+        delete[] h->prof_kid;
+    }
     delete h;
     return MX230_OK;
 }
@@ -167,6 +173,83 @@ extern "C" int mx230_check_status(mx230_handle *h, void *stream) {
                           "device status %d (1 = bounded wait timed out), detail %d", st[0], st[1]);
     }
     return MX230_OK;
+}
+
+int mx230_prof_begin(mx230_handle *h, cudaStream_t st, int kid) {
+    if (h->prof_used >= MX230_PROF_CAP) return -1;
+    if (h->prof_ev == nullptr) {
+        h->prof_ev = new cudaEvent_t[2 * MX230_PROF_CAP];
+        h->prof_kid = new int[MX230_PROF_CAP];
+        for (int i = 0; i < 2 * MX230_PROF_CAP; ++i) h->prof_ev[i] = nullptr;
+    }
+    int slot = h->prof_used;
+    for (int j = 0; j < 2; ++j)
+        if (h->prof_ev[2 * slot + j] == nullptr && cudaEventCreate(&h->prof_ev[2 * slot + j]) != cudaSuccess)
+            return -1;
+    h->prof_used++;
+    h->prof_kid[slot] = kid;
+    cudaEventRecord(h->prof_ev[2 * slot], st);
+    return slot;
+}
+
+void mx230_prof_end(mx230_handle *h, cudaStream_t st, int slot) {
+    cudaEventRecord(h->prof_ev[2 * slot + 1], st);
+}
+
+// Folds the recorded event pairs into the per-kernel totals (synchronises on them).
+static int prof_drain(mx230_handle *h) {
+    for (int i = 0; i < h->prof_used; ++i) {
+        MX_CHECK_CUDA(cudaEventSynchronize(h->prof_ev[2 * i + 1]));
+        float ms = 0.0f;
+        MX_CHECK_CUDA(cudaEventElapsedTime(&ms, h->prof_ev[2 * i], h->prof_ev[2 * i + 1]));
+        h->prof_ms[h->prof_kid[i]] += ms;
+        h->prof_count[h->prof_kid[i]]++;
+    }
+    h->prof_used = 0;
+    return MX230_OK;
+}
+
+extern "C" int mx230_profile_enable(mx230_handle *h, int on) {
+    MX_REQUIRE(h != nullptr, MX230_ERR_INVALID_ARG, "mx230_profile_enable: null handle");
+    mx230_device_guard guard(h->device);
+    if (!on && h->prof_on) {
+        int rc = prof_drain(h);
+        if (rc) return rc;
+    }
+    h->prof_on = on ? 1 : 0;
+    return MX230_OK;
+}
+
+extern "C" int mx230_profile_reset(mx230_handle *h) {
+    MX_REQUIRE(h != nullptr, MX230_ERR_INVALID_ARG, "mx230_profile_reset: null handle");
+    mx230_device_guard guard(h->device);
+    int rc = prof_drain(h);
+    if (rc) return rc;
+    for (int k = 0; k < MX230_K_COUNT; ++k) {
+        h->prof_count[k] = 0;
+        h->prof_ms[k] = 0.0;
+    }
+    return MX230_OK;
+}
+
+extern "C" int mx230_profile_read(mx230_handle *h, int kernel, long long *launches, double *total_ms) {
+    MX_REQUIRE(h != nullptr && launches && total_ms, MX230_ERR_INVALID_ARG, "mx230_profile_read: null argument");
+    MX_REQUIRE(kernel >= 0 && kernel < MX230_K_COUNT, MX230_ERR_INVALID_ARG,
+               "mx230_profile_read: kernel id %d out of range", kernel);
+    mx230_device_guard guard(h->device);
+    int rc = prof_drain(h);
+    if (rc) return rc;
+    *launches = h->prof_count[kernel];
+    *total_ms = h->prof_ms[kernel];
+    return MX230_OK;
+}
+
+extern "C" const char *mx230_kernel_name(int kernel) {
+    static const char *names[MX230_K_COUNT] = {
+        "cast_bf16_kernel", "flash_fwd_kernel", "bwd_preprocess_kernel", "bwd_dq_kernel",
+        "bwd_dkv_kernel", "rope_kernel", "copy_kv_kernel", "quantize_kv_kernel",
+        "decode_f32_kernel", "decode_q8_kernel", "merge_partials_kernel", "prefill_kernel"};
+    return (kernel >= 0 && kernel < MX230_K_COUNT) ? names[kernel] : "?";
 }
 
 extern "C" long long mx230_launch_count(const mx230_handle *h) { return h ? h->launches : 0; }

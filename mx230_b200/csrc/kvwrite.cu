@@ -135,9 +135,9 @@ int launch_rope(mx230_handle *h, void *stream, float *qkv, RowPos rp, int n_rows
     long long total = (long long)n_rows * (n_head + n_kv_head) * (head_dim / 2);
     if (total == 0) return MX230_OK;
     mx230_device_guard guard(h->device);
-    rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        qkv, rp, n_rows, n_head, n_kv_head, head_dim, stride, theta);
-    MX_LAUNCHED(h);
+    cudaStream_t st = (cudaStream_t)stream;
+    MX_LAUNCH(h, st, MX230_K_ROPE, (rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+        qkv, rp, n_rows, n_head, n_kv_head, head_dim, stride, theta)));
     return MX230_OK;
 }
 
@@ -152,9 +152,9 @@ int launch_copy(mx230_handle *h, void *stream, float *kcache, float *vcache, con
                                         : mx230_fail(MX230_ERR_INVALID_ARG, "copy_kv: negative rows");
     mx230_device_guard guard(h->device);
     dim3 grid((kv_dim / 4 + 127) / 128, n_rows);
-    copy_kv_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(kcache, vcache, qkv, rp, q_dim, kv_dim,
-                                                          stride);
-    MX_LAUNCHED(h);
+    cudaStream_t st = (cudaStream_t)stream;
+    MX_LAUNCH(h, st, MX230_K_COPY_KV,
+              (copy_kv_kernel<<<grid, 128, 0, st>>>(kcache, vcache, qkv, rp, q_dim, kv_dim, stride)));
     return MX230_OK;
 }
 
@@ -174,9 +174,10 @@ int launch_quant(mx230_handle *h, void *stream, int8_t *kq, int8_t *vq, float *k
                                         : mx230_fail(MX230_ERR_INVALID_ARG, "quantize_kv: negative rows");
     mx230_device_guard guard(h->device);
     long long warps = (long long)n_rows * n_kv_head * 2;
-    quantize_kv_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, (cudaStream_t)stream>>>(
-        kq, vq, ks, vs, kb, vb, qkv, rp, n_rows, q_dim, n_kv_head, stride);
-    MX_LAUNCHED(h);
+    cudaStream_t st = (cudaStream_t)stream;
+    MX_LAUNCH(h, st, MX230_K_QUANTIZE_KV,
+              (quantize_kv_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(
+                  kq, vq, ks, vs, kb, vb, qkv, rp, n_rows, q_dim, n_kv_head, stride)));
     return MX230_OK;
 }
 

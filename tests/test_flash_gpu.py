@@ -123,8 +123,11 @@ def test_backward_odd_sizes(handle, n, causal):
     q, k, v, do = (oracle.normal((n, 64), 200 + n, i) for i in range(4))
     _, _, gq, gk, gv = run_bwd(handle, q, k, v, do, causal)
     wq, wk, wv = oracle.attn_bwd(q, k, v, do, causal)
-    assert_close(gq, wq, f"dQ n={n}")
-    assert_close(gk, wk, f"dK n={n}")
+    # with a single visible key the softmax is constant, so dQ and dK are exactly zero and a
+    # relative error is undefined: only the absolute gate applies there
+    rel = 5e-3 if n > 1 else float("inf")
+    assert_close(gq, wq, f"dQ n={n}", mean_rel=rel)
+    assert_close(gk, wk, f"dK n={n}", mean_rel=rel)
     assert_close(gv, wv, f"dV n={n}")
 
 
