@@ -11,11 +11,13 @@
 //   * warp 8 streams Q once and K/V tiles (128 keys) through a 4-stage shared-memory
 //     ring with plain per-CTA TMA tile loads (128-byte swizzle);
 //   * warp 9 issues tcgen05.mma: S_t = Q_t K^T into tensor memory (128 fp32 columns per
-//     tile) and O_t += P_t V with P_t read back from tensor memory as bf16;
-//   * warps 0-3 / 4-7 are the softmax groups of tile 0 / 1, one thread per query row:
-//     row max, exp2, row sum, bf16 P written over S, O rescaled in tensor memory.
-//   The two tiles ping-pong, so the tensor core works on one tile while the other
-//   tile's softmax runs on the CUDA cores.
+//     tile) and O_t += P_t V with P_t read from tensor memory as bf16;
+//   * warps 0-3 / 4-7 are the softmax groups of tile 0 / 1, one thread per query row: the
+//     score row is pulled into registers in one round trip (which frees S_t for the next
+//     QK^T at once), then row max, exp2, row sum, bf16 P into its own tensor-memory
+//     columns; O_t is rescaled in tensor memory only when the row max grows by > 2^8.
+//   The two tiles ping-pong and S, P, O never alias, so the tensor core computes the next
+//   scores and the other tile's P V while a tile's softmax runs on the CUDA cores.
 //
 // Operands are bf16 (rounded once by the cast pre-pass), accumulation is fp32.
 #include <math_constants.h>
@@ -30,7 +32,7 @@ constexpr int BN = 128;        // keys per K/V tile
 constexpr int HD = 64;
 constexpr int KV_STAGES = 4;
 constexpr int TILE_BYTES = BN * HD * 2;  // 16 KB
-constexpr int FWD_THREADS = 320;
+constexpr int FWD_THREADS = 384;        // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
 
 constexpr int SMEM_Q = 0;
 constexpr int SMEM_K = SMEM_Q + QT * TILE_BYTES;
@@ -45,15 +47,22 @@ constexpr int BAR_K_FULL = 1;                    // [KV_STAGES]
 constexpr int BAR_K_EMPTY = BAR_K_FULL + KV_STAGES;
 constexpr int BAR_V_FULL = BAR_K_EMPTY + KV_STAGES;
 constexpr int BAR_V_EMPTY = BAR_V_FULL + KV_STAGES;
-constexpr int BAR_S_FULL = BAR_V_EMPTY + KV_STAGES;  // [QT]
-constexpr int BAR_P_READY = BAR_S_FULL + QT;         // [QT]
-constexpr int BAR_O_DONE = BAR_P_READY + QT;         // [QT]
-constexpr int N_BARS = BAR_O_DONE + QT;              // 23
+constexpr int BAR_S_FULL = BAR_V_EMPTY + KV_STAGES;  // [QT] MMA -> softmax: S_t written
+constexpr int BAR_S_FREE = BAR_S_FULL + QT;          // [QT] softmax -> MMA: S_t copied to registers
+constexpr int BAR_P_FULL = BAR_S_FREE + QT;          // [QT] softmax -> MMA: P_t written
+constexpr int BAR_O_DONE = BAR_P_FULL + QT;          // [QT] MMA -> softmax: O_t += P_t V complete
+constexpr int N_BARS = BAR_O_DONE + QT;              // 25
 
-// tensor-memory columns
-constexpr int TM_S = 0;     // S_t at TM_S + t*128 (P_t overlays its first 64 columns)
-constexpr int TM_O = 256;   // O_t at TM_O + t*64
+// tensor-memory columns: nothing aliases, so S_t(j+1) can be produced while P_t(j) is consumed
+constexpr int TM_S = 0;     // S_t at TM_S + t*128, fp32
+constexpr int TM_P = 256;   // P_t at TM_P + t*64, bf16 pairs
+constexpr int TM_O = 384;   // O_t at TM_O + t*64, fp32
 constexpr int TM_COLS = 512;
+
+// The running row max is only raised when it would grow by more than 2^RESCALE_LOG2 in the
+// exponent; until then probabilities are taken against the stale max (they stay below
+// 2^RESCALE_LOG2, harmless in bf16/fp32) and O needs no rescale.
+constexpr float RESCALE_LOG2 = 8.0f;
 
 struct FwdParams {
     float *O;        // [BH][N][64]
@@ -62,6 +71,32 @@ struct FwdParams {
     int causal;
     int *status;
 };
+
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long r, float &a, float &b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
+}
+// (a.x*b.x + c.x, a.y*b.y + c.y) in one issue slot
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b,
+                                                    unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -76,9 +111,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int N = P.n;
-    const int bh = blockIdx.y;
-    // heaviest (latest) causal blocks first
-    const int qb = P.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    // heads vary fastest in launch order and, when causal, the latest (heaviest) query
+    // blocks of every head are dispatched first
+    const int bh = blockIdx.x;
+    const int qb = P.causal ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
     const int q0 = qb * (QT * BM);
     const int n_kv_total = (N + BN - 1) / BN;
     int n_it[QT];
@@ -100,7 +136,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         for (int t = 0; t < QT; ++t) {
             mx::mbar_init(bar(BAR_S_FULL + t), 1);
-            mx::mbar_init(bar(BAR_P_READY + t), BM);
+            mx::mbar_init(bar(BAR_S_FREE + t), BM);
+            mx::mbar_init(bar(BAR_P_FULL + t), BM);
             mx::mbar_init(bar(BAR_O_DONE + t), 1);
         }
         *abort_flag = 0;
@@ -112,7 +149,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mx::tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 8) {
+    // register budget: the softmax warpgroups hold a 128-value score row per thread, the
+    // third warpgroup (TMA, MMA, two idle warps) needs few
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        if (warp == 8) {
         // ------------------------- TMA producer -------------------------
         if (lane == 0) {
             mx::tma_prefetch_desc(&tmQ);
@@ -139,7 +180,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
         }
         __syncwarp();
-    } else if (warp == 9) {
+        } else if (warp == 9) {
         // ------------------------- MMA issuer ---------------------------
         if (lane == 0) {
             constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BM, BN, false, false);
@@ -161,40 +202,52 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 mx::mma_commit(bar(BAR_K_EMPTY + 0));
             }
             for (int j = 0; j < n_max && ok; ++j) {
-                int s = j % KV_STAGES, r = j / KV_STAGES;
-                int s1 = (j + 1) % KV_STAGES, r1 = (j + 1) / KV_STAGES;
-                ok = mx::mbar_wait(bar(BAR_V_FULL + s), r & 1, abort_flag, P.status);
-                if (ok && j + 1 < n_max)
+                const int s = j % KV_STAGES, r = j / KV_STAGES;
+                const int s1 = (j + 1) % KV_STAGES, r1 = (j + 1) / KV_STAGES;
+                // next scores as soon as the softmax groups hold the current ones in registers
+                if (j + 1 < n_max) {
                     ok = mx::mbar_wait(bar(BAR_K_FULL + s1), r1 & 1, abort_flag, P.status);
-                if (!ok) break;
+                    for (int t = 0; t < QT && ok; ++t) {
+                        if (j + 1 >= n_it[t]) continue;
+                        ok = mx::mbar_wait(bar(BAR_S_FREE + t), j & 1, abort_flag, P.status);
+                        if (!ok) break;
+                        mx::tc_fence_after();
+                        issue_s(t, s1);
+                    }
+                    if (!ok) break;
+                    mx::mma_commit(bar(BAR_K_EMPTY + s1));
+                }
+                ok = mx::mbar_wait(bar(BAR_V_FULL + s), r & 1, abort_flag, P.status);
                 for (int t = 0; t < QT && ok; ++t) {
                     if (j >= n_it[t]) continue;
-                    ok = mx::mbar_wait(bar(BAR_P_READY + t), j & 1, abort_flag, P.status);
+                    ok = mx::mbar_wait(bar(BAR_P_FULL + t), j & 1, abort_flag, P.status);
                     if (!ok) break;
                     mx::tc_fence_after();
                     uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_V + s * TILE_BYTES);
 #pragma unroll
                     for (int k = 0; k < BN / 16; ++k)  // 16 keys: 8 packed columns of P, 2048 bytes of V
-                        mx::mma_ts(tmem + TM_O + t * HD, tmem + TM_S + t * BN + 8 * k, b + 128 * k,
+                        mx::mma_ts(tmem + TM_O + t * HD, tmem + TM_P + t * (BN / 2) + 8 * k, b + 128 * k,
                                    IDESC_O, (j > 0 || k > 0));
                     mx::mma_commit(bar(BAR_O_DONE + t));
-                    if (j + 1 < n_it[t]) issue_s(t, s1);
                 }
                 if (!ok) break;
                 mx::mma_commit(bar(BAR_V_EMPTY + s));
-                if (j + 1 < n_max) mx::mma_commit(bar(BAR_K_EMPTY + s1));
             }
         }
         __syncwarp();
+        }
     } else {
         // ------------------------- softmax groups -----------------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         const int t = warp >> 2;             // query tile of this group
         const int row_in_tile = tid & 127;
         const int row = q0 + t * BM + row_in_tile;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tm_s = tmem + lane_off + TM_S + t * BN;
+        const uint32_t tm_p = tmem + lane_off + TM_P + t * (BN / 2);
         const uint32_t tm_o = tmem + lane_off + TM_O + t * HD;
         const float c = 0.125f * 1.4426950408889634f;  // scale * log2(e)
+        const unsigned long long c2 = pack2(c, c);
         const int n_t = n_it[t];
         float m = -CUDART_INF_F, l = 0.0f;
         bool ok = true;
@@ -202,75 +255,83 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), j & 1, abort_flag, P.status));
             if (!ok) break;
             mx::tc_fence_after();
+            // the whole score row into registers with one round trip, then S_t is free again
+            uint32_t v[BN];
+#pragma unroll
+            for (int cc = 0; cc < BN / 32; ++cc) mx::tmem_ld32(tm_s + cc * 32, *(uint32_t(*)[32])(v + cc * 32));
+            mx::tmem_wait_ld();
+            mx::tc_fence_before();
+            mx::mbar_arrive(bar(BAR_S_FREE + t));
+
             const int key0 = j * BN;
-            const bool need_mask = (key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM);
-            // pass 1: row max
-            float mx_ = m;
+            if ((key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM)) {
 #pragma unroll
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                uint32_t v[32];
-                mx::tmem_ld32(tm_s + cc * 32, v);
-                mx::tmem_wait_ld();
-                if (need_mask) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        int key = key0 + cc * 32 + i;
-                        bool valid = key < N && (!P.causal || key <= row);
-                        mx_ = valid ? fmaxf(mx_, __uint_as_float(v[i])) : mx_;
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx_ = fmaxf(mx_, __uint_as_float(v[i]));
+                for (int i = 0; i < BN; ++i) {
+                    int key = key0 + i;
+                    if (!(key < N && (!P.causal || key <= row))) v[i] = 0xFF800000u;  // -inf
                 }
             }
-            const float m_new = mx_;
-            const float mc = m_new * c;
-            const float alpha = mx::ex2(m * c - mc);  // 0 on the first tile (m = -inf)
-            // pass 2: p = exp2(s*c - m*c), packed to bf16 over the S columns
-            float rs = 0.0f;
+            // four independent max chains (a single chain would serialise on the ALU latency)
+            float mx4[4];
 #pragma unroll
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                uint32_t v[32];
-                mx::tmem_ld32(tm_s + cc * 32, v);
-                mx::tmem_wait_ld();
-                uint32_t pk[16];
+            for (int u = 0; u < 4; ++u)
+                mx4[u] = fmax3(__uint_as_float(v[u * 32]), __uint_as_float(v[u * 32 + 1]), __uint_as_float(v[u * 32 + 2]));
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = mx::ex2(fmaf(__uint_as_float(v[i]), c, -mc));
-                    float p1 = mx::ex2(fmaf(__uint_as_float(v[i + 1]), c, -mc));
-                    if (need_mask) {
-                        int key = key0 + cc * 32 + i;
-                        if (!(key < N && (!P.causal || key <= row))) p0 = 0.0f;
-                        if (!(key + 1 < N && (!P.causal || key + 1 <= row))) p1 = 0.0f;
-                    }
-                    rs += p0 + p1;
-                    pk[i >> 1] = mx::pack_bf16(p0, p1);
-                }
-                mx::tmem_st16(tm_s + cc * 16, pk);
-            }
-            l = l * alpha + rs;
-            m = m_new;
-            // rescale O once the previous P V has landed
+            for (int i = 3; i + 1 < 32; i += 2)
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    mx4[u] = fmax3(mx4[u], __uint_as_float(v[u * 32 + i]), __uint_as_float(v[u * 32 + i + 1]));
+            float mx_ = fmaxf(fmax3(mx4[0], mx4[1], mx4[2]), mx4[3]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) mx_ = fmaxf(mx_, __uint_as_float(v[u * 32 + 31]));
+            // raise the running max only when it pays (always on the first tile)
+            const bool raise = (j == 0) || ((mx_ - m) * c > RESCALE_LOG2);
+            const float m_new = raise ? mx_ : m;
+            const float alpha = (raise && j > 0) ? mx::ex2((m - m_new) * c) : 1.0f;
+            const float nmc = -m_new * c;
+            const unsigned long long nmc2 = pack2(nmc, nmc);
             if (j > 0) {
+                // P_t and O_t are stable once the previous P V has completed (issued a whole
+                // softmax ago, so this wait is normally already satisfied)
                 ok = __all_sync(0xFFFFFFFFu,
                                 mx::mbar_wait(bar(BAR_O_DONE + t), (j - 1) & 1, abort_flag, P.status));
                 if (!ok) break;
                 mx::tc_fence_after();
-                if (__any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
-#pragma unroll
-                    for (int cc = 0; cc < HD / 32; ++cc) {
-                        uint32_t v[32];
-                        mx::tmem_ld32(tm_o + cc * 32, v);
+                if (__any_sync(0xFFFFFFFFu, raise)) {
+#pragma unroll 1
+                    for (int cc = 0; cc < HD / 16; ++cc) {
+                        uint32_t o[16];
+                        mx::tmem_ld16(tm_o + cc * 16, o);
                         mx::tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        mx::tmem_st32(tm_o + cc * 32, v);
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        mx::tmem_st16(tm_o + cc * 16, o);
                     }
                 }
             }
+            unsigned long long rsum[2] = {0ull, 0ull};  // two packed (2 x fp32) row-sum accumulators
+#pragma unroll
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float x0, x1;
+                    unpack2(ffma2(pack2(__uint_as_float(v[cc * 32 + i]), __uint_as_float(v[cc * 32 + i + 1])), c2,
+                                  nmc2), x0, x1);
+                    float p0 = mx::ex2(x0), p1 = mx::ex2(x1);
+                    rsum[(i >> 1) & 1] = fadd2(rsum[(i >> 1) & 1], pack2(p0, p1));
+                    pk[i >> 1] = mx::pack_bf16(p0, p1);
+                }
+                mx::tmem_st16(tm_p + cc * 16, pk);
+            }
+            float rs0, rs1, rs2, rs3;
+            unpack2(rsum[0], rs0, rs1);
+            unpack2(rsum[1], rs2, rs3);
+            l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
+            m = m_new;
             mx::tmem_wait_st();
             mx::tc_fence_before();
-            mx::mbar_arrive(bar(BAR_P_READY + t));
+            mx::mbar_arrive(bar(BAR_P_FULL + t));
         }
         // epilogue: O / l and the log-sum-exp
         if (ok && n_t > 0) {
@@ -282,14 +343,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 float *orow = P.O + ((size_t)bh * N + row) * HD;
 #pragma unroll
                 for (int cc = 0; cc < HD / 32; ++cc) {
-                    uint32_t v[32];
-                    mx::tmem_ld32(tm_o + cc * 32, v);
+                    uint32_t o[32];
+                    mx::tmem_ld32(tm_o + cc * 32, o);
                     mx::tmem_wait_ld();
                     if (row < N) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
-                            float4 o4 = make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
-                                                    __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+                            float4 o4 = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
+                                                    __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
                             *(float4 *)(orow + cc * 32 + i) = o4;
                         }
                     }
@@ -371,7 +432,7 @@ int mx230_launch_flash_fwd(mx230_handle *h, cudaStream_t st, const void *Qb, con
     P.n = n;
     P.causal = causal ? 1 : 0;
     P.status = h->status_dev;
-    dim3 grid((n + QT * BM - 1) / (QT * BM), batch_heads);
+    dim3 grid(batch_heads, (n + QT * BM - 1) / (QT * BM));
     MX_LAUNCH(h, st, MX230_K_FLASH_FWD,
               (flash_fwd_kernel<<<grid, FWD_THREADS, SMEM_ALLOC, st>>>(tq, tk, tv, P)));
     return MX230_OK;
