@@ -284,6 +284,38 @@ int mx230_attn_decode_partial(mx230_handle *h, void *stream, float *part_m, floa
 int mx230_merge_partials(mx230_handle *h, void *stream, float *out, const float *m,
                          const float *l, const float *acc, int parts, int rows, int head_dim);
 
+/* prefill attention of n_tok new rows at absolute positions pos0+qi over cache keys
+ * 0..=pos0+qi: attn_prefill / _q8 / _paged / _q8_paged / _dp4a / _dp4a_paged
+ * (llm.cu:3806-3872).  q row qi of head h is read at qkv[qi*qkv_stride + h*64], the result
+ * goes to out[qi*out_stride + h*64]; K and V come only from the cache, which must already
+ * hold positions pos0..pos0+n_tok-1 (the reference writes them first, gpu.rs:3243-3320).
+ * Operands are rounded to bf16 (int8 codes after dequantisation) for the tensor cores.
+ * The _dp4a forms (the reference's opt-in int8-score approximation) use the exact scores. */
+size_t mx230_prefill_workspace_bytes(int n_tok, int n_keys, int n_head, int n_kv_head);
+int mx230_attn_prefill(mx230_handle *h, void *stream, float *out, const float *qkv,
+                       const float *kcache, const float *vcache, int pos0, int n_tok, int n_head,
+                       int n_kv_head, int qkv_stride, int out_stride);
+int mx230_attn_prefill_paged(mx230_handle *h, void *stream, float *out, const float *qkv,
+                             const float *kcache, const float *vcache, int pos0, int n_tok,
+                             int n_head, int n_kv_head, int qkv_stride, int out_stride,
+                             const int *bt, int bs);
+int mx230_attn_prefill_q8(mx230_handle *h, void *stream, float *out, const float *qkv,
+                          const int8_t *kq, const int8_t *vq, const float *ks, const float *vs,
+                          const float *kb, const float *vb, int pos0, int n_tok, int n_head,
+                          int n_kv_head, int qkv_stride, int out_stride);
+int mx230_attn_prefill_q8_paged(mx230_handle *h, void *stream, float *out, const float *qkv,
+                                const int8_t *kq, const int8_t *vq, const float *ks,
+                                const float *vs, const float *kb, const float *vb, int pos0,
+                                int n_tok, int n_head, int n_kv_head, int qkv_stride,
+                                int out_stride, const int *bt, int bs);
+int mx230_attn_prefill_dp4a(mx230_handle *h, void *stream, float *out, const float *qkv,
+                            const float *kcache, const float *vcache, int pos0, int n_tok, int n_head,
+                            int n_kv_head, int qkv_stride, int out_stride);
+int mx230_attn_prefill_dp4a_paged(mx230_handle *h, void *stream, float *out, const float *qkv,
+                                  const float *kcache, const float *vcache, int pos0, int n_tok,
+                                  int n_head, int n_kv_head, int qkv_stride, int out_stride,
+                                  const int *bt, int bs);
+
 #ifdef __cplusplus
 }
 #endif

@@ -111,6 +111,13 @@ int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, ui
 int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src, void *const *dst,
                       int n_tensors, size_t count);
 
+// tcgen05 flash forward over staged bf16 operands (flash_fwd.cu).  Q [heads][n_q][64]; K, V
+// [heads / kv_group][n_k][64]; causal row r sees keys <= r + q_off; output row r of head h at
+// O + h*o_head_stride + r*o_row_stride.
+int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
+                              const void *Vb, float *O, float *L, int heads, int n_q, int n_k, int q_off,
+                              int kv_group, long long o_head_stride, long long o_row_stride, int causal);
+
 // ---------------------------------------------------------------------------
 // device
 // ---------------------------------------------------------------------------

@@ -22,7 +22,7 @@ namespace {
 constexpr int DEC_THREADS = 128;
 constexpr int TILE_KEYS = 128;  // keys per ring stage (int8: 128 x 64 B = 8 KB)
 constexpr int RING = 4;         // cp.async stages
-constexpr int CHUNK_KEYS = 1024;
+constexpr int CHUNK_KEYS = 512;
 
 struct DecodeParams {
     float *out;               // [n_seq][out_stride]; head h at h*64 (null in partial mode)
@@ -56,6 +56,27 @@ __device__ __forceinline__ float warp_sum_f(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
     return v;
+}
+
+// packed 2 x fp32 arithmetic: two lanes per issue slot
+__device__ __forceinline__ unsigned long long pack2f(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2f(unsigned long long r, float &a, float &b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
+}
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b,
+                                                    unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fmul2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
@@ -140,7 +161,7 @@ __device__ void merge_and_store(const DecodeParams &P, int s, int head0, int gc,
 // int8 cache
 // ---------------------------------------------------------------------------
 template <int G>
-__global__ void __launch_bounds__(DEC_THREADS)
+__global__ void __launch_bounds__(DEC_THREADS, (G >= 7 ? 4 : 6))
 decode_q8_kernel(const DecodeParams P) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     unsigned char *ring = smem_raw;                                  // RING x 8 KB
@@ -201,14 +222,14 @@ decode_q8_kernel(const DecodeParams P) {
     __syncthreads();
 
     float m_run[G], l_thr[G], b_thr[G];
-    float acc[G][8];
+    unsigned long long acc2[G][4];  // 8 output dims per head as four packed fp32 pairs
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         m_run[g] = -CUDART_INF_F;
         l_thr[g] = 0.0f;
         b_thr[g] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+        for (int j = 0; j < 4; ++j) acc2[g][j] = 0ull;
     }
 
     const int n_keys = kb_ - ka;
@@ -343,8 +364,9 @@ decode_q8_kernel(const DecodeParams P) {
             float alpha = (m_run[g] == -CUDART_INF_F) ? 0.0f : __expf(m_run[g] - m_new[g]);
             l_thr[g] *= alpha;
             b_thr[g] *= alpha;
+            const unsigned long long a2 = pack2f(alpha, alpha);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[g][j] *= alpha;
+            for (int j = 0; j < 4; ++j) acc2[g][j] = fmul2(acc2[g][j], a2);
             m_run[g] = m_new[g];
         }
 
@@ -378,21 +400,18 @@ decode_q8_kernel(const DecodeParams P) {
             for (int step = 0; step < TILE_KEYS / 16; ++step) {
                 int k = step * 16 + kl;
                 int2 vw = *(const int2 *)(st + stage_off(k, dsl >> 1) + (dsl & 1) * 8);
-                float v[8];
-                v[0] = (float)(int8_t)(vw.x & 0xFF);
-                v[1] = (float)(int8_t)((vw.x >> 8) & 0xFF);
-                v[2] = (float)(int8_t)((vw.x >> 16) & 0xFF);
-                v[3] = (float)(int8_t)((vw.x >> 24) & 0xFF);
-                v[4] = (float)(int8_t)(vw.y & 0xFF);
-                v[5] = (float)(int8_t)((vw.y >> 8) & 0xFF);
-                v[6] = (float)(int8_t)((vw.y >> 16) & 0xFF);
-                v[7] = (float)(int8_t)((vw.y >> 24) & 0xFF);
+                unsigned long long v2[4];
+                v2[0] = pack2f((float)(int8_t)(vw.x & 0xFF), (float)(int8_t)((vw.x >> 8) & 0xFF));
+                v2[1] = pack2f((float)(int8_t)((vw.x >> 16) & 0xFF), (float)(int8_t)((vw.x >> 24) & 0xFF));
+                v2[2] = pack2f((float)(int8_t)(vw.y & 0xFF), (float)(int8_t)((vw.y >> 8) & 0xFF));
+                v2[3] = pack2f((float)(int8_t)((vw.y >> 16) & 0xFF), (float)(int8_t)((vw.y >> 24) & 0xFF));
                 const float *wk = sc + (tile * TILE_KEYS + k) * G;
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
-                    float w = wk[g];
+                    const float w = wk[g];
+                    const unsigned long long w2 = pack2f(w, w);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(w, v[j], acc[g][j]);
+                    for (int j = 0; j < 4; ++j) acc2[g][j] = ffma2(w2, v2[j], acc2[g][j]);
                 }
             }
         }
@@ -420,6 +439,11 @@ decode_q8_kernel(const DecodeParams P) {
         b_tot[g] = bv;
     }
     // key lanes inside a warp differ in lane bits 3,4
+    float acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) unpack2f(acc2[g][j], acc[g][2 * j], acc[g][2 * j + 1]);
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
@@ -770,6 +794,7 @@ int launch_decode(mx230_handle *h, void *stream, DecodeParams P, int n_seq, int 
     if (g == 1) return launch_g<1>(h, st, P, grid, q8);
     if (g == 2) return launch_g<2>(h, st, P, grid, q8);
     if (g <= 4) return launch_g<4>(h, st, P, grid, q8);
+    if (g <= 7) return launch_g<7>(h, st, P, grid, q8);
     return launch_g<8>(h, st, P, grid, q8);
 }
 

@@ -65,9 +65,13 @@ constexpr int TM_COLS = 512;
 constexpr float RESCALE_LOG2 = 8.0f;
 
 struct FwdParams {
-    float *O;        // [BH][N][64]
-    float *L;        // [BH][N] or null
-    int n;
+    float *O;             // row r of head h at O + h*o_head_stride + r*o_row_stride (floats)
+    float *L;             // [heads][n_q] or null
+    long long o_head_stride, o_row_stride;
+    int n_q;              // query rows per head
+    int n_k;              // keys per head
+    int q_off;            // causal: query row r sees keys <= r + q_off (0 for self-attention)
+    int kv_group;         // query heads per K/V head (K/V head of query head h is h / kv_group)
     int causal;
     int *status;
 };
@@ -110,7 +114,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     volatile int *abort_flag = (volatile int *)(smem + SMEM_BAR + 8 * N_BARS + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int N = P.n;
+    const int NQ = P.n_q, N = P.n_k;  // N: keys (bounds the K/V loop and the key mask)
     // heads vary fastest in launch order and, when causal, the latest (heaviest) query
     // blocks of every head are dispatched first
     const int bh = blockIdx.x;
@@ -121,8 +125,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
     for (int t = 0; t < QT; ++t) {
         int r0 = q0 + t * BM;
-        if (r0 >= N) n_it[t] = 0;
-        else n_it[t] = P.causal ? min(n_kv_total, r0 / BN + 1) : n_kv_total;
+        if (r0 >= NQ) n_it[t] = 0;
+        else n_it[t] = P.causal ? min(n_kv_total, (r0 + BM - 1 + P.q_off) / BN + 1) : n_kv_total;
     }
     const int n_max = max(n_it[0], n_it[1]);
 
@@ -165,18 +169,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 mx::tma_load_3d(smem_base + SMEM_Q + t * TILE_BYTES, &tmQ, bar(BAR_Q_FULL), 0,
                                 q0 + t * BM, bh);
             bool ok = true;
+            const int kvh = bh / P.kv_group;
             for (int j = 0; j < n_max && ok; ++j) {
                 int s = j % KV_STAGES, r = j / KV_STAGES;
                 if (r > 0) ok = mx::mbar_wait(bar(BAR_K_EMPTY + s), (r - 1) & 1, abort_flag, P.status);
                 if (!ok) break;
                 mx::mbar_expect_tx(bar(BAR_K_FULL + s), TILE_BYTES);
                 mx::tma_load_3d(smem_base + SMEM_K + s * TILE_BYTES, &tmK, bar(BAR_K_FULL + s), 0,
-                                j * BN, bh);
+                                j * BN, kvh);
                 if (r > 0) ok = mx::mbar_wait(bar(BAR_V_EMPTY + s), (r - 1) & 1, abort_flag, P.status);
                 if (!ok) break;
                 mx::mbar_expect_tx(bar(BAR_V_FULL + s), TILE_BYTES);
                 mx::tma_load_3d(smem_base + SMEM_V + s * TILE_BYTES, &tmV, bar(BAR_V_FULL + s), 0,
-                                j * BN, bh);
+                                j * BN, kvh);
             }
         }
         __syncwarp();
@@ -264,12 +269,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             mx::mbar_arrive(bar(BAR_S_FREE + t));
 
             const int key0 = j * BN;
-            if ((key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM)) {
+            if ((key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM + P.q_off)) {
+                const int last = P.causal ? min(N - 1, row + P.q_off) : N - 1;  // last visible key
 #pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    int key = key0 + i;
-                    if (!(key < N && (!P.causal || key <= row))) v[i] = 0xFF800000u;  // -inf
-                }
+                for (int i = 0; i < BN; ++i)
+                    if (key0 + i > last) v[i] = 0xFF800000u;  // -inf
             }
             // four independent max chains (a single chain would serialise on the ALU latency)
             float mx4[4];
@@ -340,13 +344,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (ok) {
                 mx::tc_fence_after();
                 const float inv = 1.0f / l;
-                float *orow = P.O + ((size_t)bh * N + row) * HD;
+                float *orow = P.O + (size_t)bh * P.o_head_stride + (size_t)row * P.o_row_stride;
 #pragma unroll
                 for (int cc = 0; cc < HD / 32; ++cc) {
                     uint32_t o[32];
                     mx::tmem_ld32(tm_o + cc * 32, o);
                     mx::tmem_wait_ld();
-                    if (row < N) {
+                    if (row < NQ) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
                             float4 o4 = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
@@ -355,7 +359,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         }
                     }
                 }
-                if (P.L != nullptr && row < N) P.L[(size_t)bh * N + row] = m * 0.125f + __logf(l);
+                if (P.L != nullptr && row < NQ) P.L[(size_t)bh * NQ + row] = m * 0.125f + __logf(l);
             }
         }
     }
@@ -412,14 +416,16 @@ int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src,
     return MX230_OK;
 }
 
-int mx230_launch_flash_fwd(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
-                           const void *Vb, float *O, float *L, int batch_heads, int n, int causal) {
+// General launcher.  Q: bf16 [heads][n_q][64]; K, V: bf16 [heads / kv_group][n_k][64].
+int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
+                              const void *Vb, float *O, float *L, int heads, int n_q, int n_k, int q_off,
+                              int kv_group, long long o_head_stride, long long o_row_stride, int causal) {
     CUtensorMap tq, tk, tv;
-    uint64_t rs = HD * 2, os = (uint64_t)n * HD * 2;
+    uint64_t rs = HD * 2;
     int rc;
-    if ((rc = mx230_make_tmap_bf16(h, &tq, Qb, n, batch_heads, rs, os, BM))) return rc;
-    if ((rc = mx230_make_tmap_bf16(h, &tk, Kb, n, batch_heads, rs, os, BN))) return rc;
-    if ((rc = mx230_make_tmap_bf16(h, &tv, Vb, n, batch_heads, rs, os, BN))) return rc;
+    if ((rc = mx230_make_tmap_bf16(h, &tq, Qb, n_q, heads, rs, (uint64_t)n_q * HD * 2, BM))) return rc;
+    if ((rc = mx230_make_tmap_bf16(h, &tk, Kb, n_k, heads / kv_group, rs, (uint64_t)n_k * HD * 2, BN))) return rc;
+    if ((rc = mx230_make_tmap_bf16(h, &tv, Vb, n_k, heads / kv_group, rs, (uint64_t)n_k * HD * 2, BN))) return rc;
     static bool attr_set = false;
     if (!attr_set) {
         MX_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -429,13 +435,24 @@ int mx230_launch_flash_fwd(mx230_handle *h, cudaStream_t st, const void *Qb, con
     FwdParams P;
     P.O = O;
     P.L = L;
-    P.n = n;
+    P.o_head_stride = o_head_stride;
+    P.o_row_stride = o_row_stride;
+    P.n_q = n_q;
+    P.n_k = n_k;
+    P.q_off = q_off;
+    P.kv_group = kv_group;
     P.causal = causal ? 1 : 0;
     P.status = h->status_dev;
-    dim3 grid(batch_heads, (n + QT * BM - 1) / (QT * BM));
+    dim3 grid(heads, (n_q + QT * BM - 1) / (QT * BM));
     MX_LAUNCH(h, st, MX230_K_FLASH_FWD,
               (flash_fwd_kernel<<<grid, FWD_THREADS, SMEM_ALLOC, st>>>(tq, tk, tv, P)));
     return MX230_OK;
+}
+
+int mx230_launch_flash_fwd(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
+                           const void *Vb, float *O, float *L, int batch_heads, int n, int causal) {
+    return mx230_launch_flash_fwd_ex(h, st, Qb, Kb, Vb, O, L, batch_heads, n, n, 0, 1, (long long)n * HD, HD,
+                                     causal);
 }
 
 static int check_flash_args(const char *who, mx230_handle *h, int batch_heads, int n) {

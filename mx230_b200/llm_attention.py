@@ -282,3 +282,46 @@ def batched_step(h: Handle, out, qkv, c: KvCache, pos, n_seq, n_head, n_kv_head,
         copy_kv_seqpos(h, c, qkv, pos, n_seq, q_dim, kv_dim, qkv_stride, pg, stream)
     attn_decode_batched(h, out, qkv, c, pos, n_seq, n_head, n_kv_head, head_dim, pg, qkv_stride,
                         out_stride, stream)
+
+
+# ---------------------------------------------------------------- prefill attention
+def prefill_workspace_bytes(n_tok, n_keys, n_head, n_kv_head) -> int:
+    return int(lib().mx230_prefill_workspace_bytes(n_tok, n_keys, n_head, n_kv_head))
+
+
+def attn_prefill(h: Handle, out, qkv, c: KvCache, pos0, n_tok, n_head, n_kv_head, qkv_stride, out_stride,
+                 pg: Paging | None = None, stream=None):
+    """attn_prefill / _paged / _q8 / _q8_paged chosen by (cache format, paging) as
+    batch_body_from does (gpu.rs:3269-3345).  The cache must already hold the new rows."""
+    s = stream_ptr(stream)
+    L = lib()
+    if c.quant:
+        if pg is None:
+            check(L.mx230_attn_prefill_q8(h._h, s, ptr(out), ptr(qkv), *c.q8_args(), pos0, n_tok, n_head,
+                                          n_kv_head, qkv_stride, out_stride))
+        else:
+            check(L.mx230_attn_prefill_q8_paged(h._h, s, ptr(out), ptr(qkv), *c.q8_args(), pos0, n_tok, n_head,
+                                                n_kv_head, qkv_stride, out_stride, ptr(pg.table_dev),
+                                                pg.block_size))
+    else:
+        if pg is None:
+            check(L.mx230_attn_prefill(h._h, s, ptr(out), ptr(qkv), ptr(c.k), ptr(c.v), pos0, n_tok, n_head,
+                                       n_kv_head, qkv_stride, out_stride))
+        else:
+            check(L.mx230_attn_prefill_paged(h._h, s, ptr(out), ptr(qkv), ptr(c.k), ptr(c.v), pos0, n_tok,
+                                             n_head, n_kv_head, qkv_stride, out_stride, ptr(pg.table_dev),
+                                             pg.block_size))
+
+
+def prefill_step(h: Handle, out, qkv, c: KvCache, pos0, n_tok, n_head, n_kv_head, head_dim, theta,
+                 qkv_stride, out_stride, pg: Paging | None = None, use_rope=True, stream=None):
+    """The prefill attention step of batch_body_from (gpu.rs:3204-3347): RoPE on the n_tok rows,
+    KV write of all of them, then causal attention over the cache."""
+    q_dim, kv_dim = n_head * head_dim, n_kv_head * head_dim
+    if use_rope:
+        rope_batch(h, qkv, pos0, n_tok, n_head, n_kv_head, head_dim, qkv_stride, theta, stream)
+    if c.quant:
+        quantize_kv_batch(h, c, qkv, pos0, n_tok, q_dim, n_kv_head, head_dim, qkv_stride, pg, stream)
+    else:
+        copy_kv_batch(h, c, qkv, pos0, n_tok, q_dim, kv_dim, qkv_stride, pg, stream)
+    attn_prefill(h, out, qkv, c, pos0, n_tok, n_head, n_kv_head, qkv_stride, out_stride, pg, stream)

@@ -1,0 +1,99 @@
+"""Prefill attention (n_tok new rows over the KV cache) through the C ABI vs the oracle.
+
+Operands go through the tensor cores in bf16, so the gate is the floating-point parity bar:
+max-abs 2e-2, norm-wise mean-rel 5e-3 against the oracle's fp32 result -- cpu.rs attention
+over the fp32 cache, and attention over the dequantised codes for the int8 cache, with the
+codes themselves produced by the (bit-exact) quantize-on-write kernel.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from mx230_b200 import llm_attention as la
+from tests.conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def i32(a):
+    return torch.tensor(a, dtype=torch.int32, device="cuda")
+
+
+CASES = [  # n_head, n_kv_head, pos0, n_tok
+    (14, 2, 0, 300), (14, 2, 77, 130), (32, 4, 0, 257), (12, 12, 5, 64), (8, 2, 200, 1), (4, 4, 0, 512),
+]
+
+
+@pytest.mark.parametrize("quant", [False, True])
+@pytest.mark.parametrize("paged", [False, True])
+@pytest.mark.parametrize("nh,nkv,pos0,n_tok", CASES)
+def test_prefill_matches_oracle(handle, nh, nkv, pos0, n_tok, quant, paged):
+    qd, kvd, bs = nh * 64, nkv * 64, 16
+    stride = qd + 2 * kvd + 64       # padded row stride, as a qkv buffer with extra columns
+    out_stride = qd + 32
+    n_keys = pos0 + n_tok
+    rows = np.zeros((n_keys, stride), np.float32)
+    rows[:, :qd + 2 * kvd] = oracle.normal((n_keys, qd + 2 * kvd), 300 + nh + pos0, 0)
+    n_log = (n_keys + bs - 1) // bs
+    table = (np.random.default_rng(1).permutation(n_log).astype(np.int32) + 1) if paged else None
+    slots = (n_log + 1) * bs
+    kc, vc = np.zeros((slots, kvd), np.float32), np.zeros((slots, kvd), np.float32)
+    q8 = oracle.Q8Cache(slots, nkv)
+    for t in range(n_keys):
+        oracle.rope_qkv_row(rows[t], t, nh, nkv, 64, 1e6)
+        oracle.copy_kv_row(kc, vc, rows[t], t, qd, kvd, table, bs)
+        oracle.quantize_kv_row(q8, rows[t], t, qd, table, bs)
+    c = la.KvCache(slots, nkv, 64, quant)
+    if quant:
+        c.k.copy_(dev(q8.kq)), c.v.copy_(dev(q8.vq)), c.ks.copy_(dev(q8.ks)), c.vs.copy_(dev(q8.vs))
+        c.kb.copy_(dev(q8.kb)), c.vb.copy_(dev(q8.vb))
+        want = oracle.prefill(rows[pos0:], pos0, n_tok, nh, nkv, stride, out_stride, cache=q8, table=table,
+                              block_size=bs)
+    else:
+        c.k.copy_(dev(kc)), c.v.copy_(dev(vc))
+        want = oracle.prefill(rows[pos0:], pos0, n_tok, nh, nkv, stride, out_stride, kcache=kc, vcache=vc,
+                              table=table, block_size=bs)
+    out = torch.zeros(n_tok, out_stride, device="cuda")
+    pg = la.Paging(i32(table), bs) if paged else None
+    la.attn_prefill(handle, out, dev(rows[pos0:]), c, pos0, n_tok, nh, nkv, stride, out_stride, pg)
+    handle.check_status()
+    got = out.cpu().numpy()
+    assert_close(got[:, :qd], want[:, :qd], "prefill")
+    assert (got[:, qd:] == 0).all()  # the padding columns of the output rows are not touched
+
+
+def test_prefill_step_writes_cache_then_attends(handle):
+    """RoPE -> KV write -> attention on the device for a chunk that follows 40 cached tokens."""
+    nh, nkv, pos0, n_tok, theta = 14, 2, 40, 100, 1e6
+    qd, kvd = nh * 64, nkv * 64
+    stride = qd + 2 * kvd
+    raw = oracle.normal((pos0 + n_tok, stride), 400, 0)
+    c = la.KvCache(pos0 + n_tok, nkv, 64, True)
+    d = dev(raw)
+    out0 = torch.zeros(pos0, qd, device="cuda")
+    la.prefill_step(handle, out0, d[:pos0], c, 0, pos0, nh, nkv, 64, theta, stride, qd)
+    out = torch.zeros(n_tok, qd, device="cuda")
+    la.prefill_step(handle, out, d[pos0:], c, pos0, n_tok, nh, nkv, 64, theta, stride, qd)
+    handle.check_status()
+    # oracle on the device's RoPE output so that the int8 codes agree bit for bit
+    roped = d.cpu().numpy()
+    w = oracle.Q8Cache(pos0 + n_tok, nkv)
+    for t in range(pos0 + n_tok):
+        oracle.quantize_kv_row(w, roped[t], t, qd)
+    assert np.array_equal(c.k.cpu().numpy(), w.kq) and np.array_equal(c.v.cpu().numpy(), w.vq)
+    want = oracle.prefill(roped[pos0:], pos0, n_tok, nh, nkv, stride, qd, cache=w)
+    assert_close(out.cpu().numpy(), want, "prefill step")
+    # the last prefill row equals a decode step at the same position (exact-score mode)
+    from mx230_b200 import _lib
+    handle.set_option(_lib.OPT_Q8_SCORE_MODE, _lib.Q8_SCORE_EXACT)
+    try:
+        o1 = torch.zeros(qd, device="cuda")
+        la.attn_decode(handle, o1, d[pos0 + n_tok - 1], c, pos0 + n_tok - 1, nh, nkv, 64)
+    finally:
+        handle.set_option(_lib.OPT_Q8_SCORE_MODE, _lib.Q8_SCORE_REF)
+    assert_close(out[-1].cpu().numpy(), o1.cpu().numpy(), "prefill row vs decode")
