@@ -20,8 +20,6 @@
 namespace {
 
 constexpr int DEC_THREADS = 128;
-constexpr int TILE_KEYS = 128;  // keys per ring stage (int8: 128 x 64 B = 8 KB)
-constexpr int RING = 4;         // cp.async stages
 constexpr int CHUNK_KEYS = 512;
 
 struct DecodeParams {
@@ -84,6 +82,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int sr
                  "r"(src_bytes)
                  : "memory");
 }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -125,9 +126,10 @@ __device__ __forceinline__ int stage_off(int k, int p) { return k * 64 + ((p ^ (
 // Final or partial write of one (sequence, kv head) group from merged values held
 // by the first threads of the CTA.
 template <int G>
-__device__ void merge_and_store(const DecodeParams &P, int s, int head0, int gc, int n_splits) {
-    // thread t handles (g = t / 16, 4 consecutive dims at (t % 16) * 4) and loops g by 8
-    for (int g = threadIdx.x / 16; g < gc; g += DEC_THREADS / 16) {
+__device__ void merge_and_store(const DecodeParams &P, int s, int head0, int gc, int n_splits,
+                                int n_threads = DEC_THREADS) {
+    // thread t handles (g = t / 16, 4 consecutive dims at (t % 16) * 4) and loops g
+    for (int g = threadIdx.x / 16; g < gc; g += n_threads / 16) {
         int d4 = (threadIdx.x % 16) * 4;
         int h = head0 + g;
         size_t pbase = ((size_t)s * P.n_head + h) * n_splits;
@@ -158,18 +160,63 @@ __device__ void merge_and_store(const DecodeParams &P, int s, int head0, int gc,
 }
 
 // ---------------------------------------------------------------------------
-// int8 cache
+// int8 cache: warp-autonomous streaming
+//
+// A CTA of Q8_WARPS warps owns one (key split, kv head, sequence); its key range is cut
+// into one contiguous sub-range per warp.  Each warp streams its sub-range in tiles of 32
+// keys through its own two-stage cp.async ring (K codes, V codes and the four side-array
+// slices of the tile) and keeps a private online-softmax state, so the main loop contains
+// no block-wide barrier: 16 independent warps per SM hide each other's latencies.
+//   scores:  lane = key; the 64-byte K row against the G query heads (dp4a, or fp32 FMA in
+//            the exact score mode); running max per head raised lazily (only when a score
+//            exceeds it by more than RAISE, found with one vote per head and tile);
+//   weights: w = exp(s - m) * vs through a per-warp shared buffer;
+//   values:  lane = (key lane, 8-byte slice); int8 -> fp32 with byte permutes, packed FMAs.
+// At the end the warps' (m, l, acc) are merged by log-sum-exp in shared memory.
 // ---------------------------------------------------------------------------
+constexpr int Q8_WARPS = 8;
+constexpr int Q8_THREADS = Q8_WARPS * 32;
+constexpr int WT_KEYS = 32;                         // keys per warp tile
+constexpr int WT_STAGE = 2 * WT_KEYS * 64 + 4 * WT_KEYS * 4;  // K + V codes + ks,kb,vs,vb = 4608 B
+constexpr int WT_STAGES = 2;
+constexpr float RAISE = 8.0f;                       // natural-log units
+
 template <int G>
-__global__ void __launch_bounds__(DEC_THREADS, (G >= 7 ? 4 : 6))
+struct Q8Smem {
+    static constexpr int GP = (G + 3) & ~3;         // heads padded to a multiple of 4 floats
+    static constexpr int Q_BYTES = G * 64 * 4 + G * 16 * 4 + 2 * G * 4 + 64;
+    static constexpr int WBUF = WT_KEYS * GP * 4;   // per-warp weight exchange
+    static constexpr int PER_WARP = WT_STAGES * WT_STAGE + WBUF;
+    static constexpr int MERGE = Q8_WARPS * G * 68 * 4;  // per-warp (m, l, beta-sum, pad, acc[64])
+    static constexpr int TOTAL = ((Q_BYTES + 127) & ~127) + (Q8_WARPS * PER_WARP > MERGE ? Q8_WARPS * PER_WARP : MERGE);
+};
+
+// four signed bytes of `w` -> four fp32 values, on the ALU/FMA pipes: flip the sign bit to get
+// u = b + 128, plant u into the mantissa of 2^23, subtract 2^23 + 128 (exact)
+__device__ __forceinline__ void s8x4_to_f32(int w, unsigned long long &lo, unsigned long long &hi) {
+    unsigned x = (unsigned)w ^ 0x80808080u;
+    const unsigned magic = 0x4B000000u;
+    unsigned f0 = __byte_perm(x, magic, 0x7650), f1 = __byte_perm(x, magic, 0x7651);
+    unsigned f2 = __byte_perm(x, magic, 0x7652), f3 = __byte_perm(x, magic, 0x7653);
+    const unsigned long long bias = pack2f(-8388736.0f, -8388736.0f);  // -(2^23 + 128)
+    unsigned long long a, b;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "r"(f0), "r"(f1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "r"(f2), "r"(f3));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(lo) : "l"(a), "l"(bias));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(hi) : "l"(b), "l"(bias));
+}
+
+template <int G, bool PAGED>
+__global__ void __launch_bounds__(Q8_THREADS, 2)
 decode_q8_kernel(const DecodeParams P) {
+    using SM = Q8Smem<G>;
+    constexpr int GP = SM::GP;
+    constexpr float LOG2E = 1.4426950408889634f;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    unsigned char *ring = smem_raw;                                  // RING x 8 KB
-    float *sc = (float *)(smem_raw + RING * TILE_KEYS * 64);         // [CHUNK_KEYS][G]
-    float *qf = sc + CHUNK_KEYS * G;                                 // [G][64]
-    int *qq = (int *)(qf + G * 64);                                  // [G][16]
-    float *red = (float *)(qq + G * 16);                             // [4][G] scratch
-    float *hv = red + 4 * G;                                         // [4][G]: qs, qsum, m_new, alpha
+    float *qf = (float *)smem_raw;                        // [G][64]
+    int *qq = (int *)(qf + G * 64);                       // [G][16]
+    float *hq = (float *)(qq + G * 16);                   // [2][G]: score scale (log2 domain), sum of q
+    unsigned char *warp_base = smem_raw + ((SM::Q_BYTES + 127) & ~127);
     __shared__ int is_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -177,314 +224,298 @@ decode_q8_kernel(const DecodeParams P) {
     const int kvh = blockIdx.y / P.head_groups;
     const int hg = blockIdx.y - kvh * P.head_groups;
     const int head0 = kvh * P.group + hg * 8;
-    const int gc = min(G, P.group - hg * 8);  // heads served by this CTA
+    const int gc = min(G, P.group - hg * 8);
     const int n_splits = gridDim.x;
     const int nkv = P.n_kv_head, kvd = nkv * 64;
 
     int kbeg, kend, ka, kb_;
     key_range(P, s, kbeg, kend);
     split_range(kbeg, kend, blockIdx.x, n_splits, ka, kb_);
-    const int *table = P.tables ? P.tables + (P.pos_kind == 2 ? (size_t)s * P.n_log : 0) : nullptr;
-    const long long base = P.tables ? 0 : (long long)s * P.seq_rows;
+    const int *table = PAGED ? P.tables + (P.pos_kind == 2 ? (size_t)s * P.n_log : 0) : nullptr;
+    const long long base = PAGED ? 0 : (long long)s * P.seq_rows;
     const bool affine = P.kb != nullptr;
-    const float scale = 0.125f;  // 1/sqrt(64)
+    const bool ref_mode = P.score_mode == MX230_Q8_SCORE_REF;
+    const float scale = 0.125f * LOG2E;  // scores are kept in the log2 domain
 
     // ---- q: fp32 copy, and (reference score mode) per-head int8 codes ----
     const float *qrow = P.qkv + (size_t)s * P.qkv_stride + head0 * 64;
-    for (int i = tid; i < G * 64; i += DEC_THREADS) qf[i] = (i / 64 < gc) ? qrow[i] : 0.0f;
+    for (int i = tid; i < G * 64; i += Q8_THREADS) qf[i] = (i / 64 < gc) ? qrow[i] : 0.0f;
     __syncthreads();
-    if (warp < 4) {
-        // one warp per head, heads warp, warp+4
-        for (int g = warp; g < G; g += 4) {
-            float a = qf[g * 64 + lane], b = qf[g * 64 + 32 + lane];
-            if (P.score_mode == MX230_Q8_SCORE_REF) {
-                float qmax = warp_max_f(fmaxf(fabsf(a), fabsf(b)));
-                float qid = qmax > 0.0f ? __fdiv_rn(127.0f, qmax) : 0.0f;
-                int ca = max(-127, min(127, __float2int_rn(a * qid)));
-                int cb = max(-127, min(127, __float2int_rn(b * qid)));
-                int8_t *qb = (int8_t *)(qq + g * 16);
-                qb[lane] = (int8_t)ca;
-                qb[32 + lane] = (int8_t)cb;
-                float qsum = warp_sum_f((float)(ca + cb));  // exact: small integers
-                if (lane == 0) {
-                    hv[0 * G + g] = (qmax > 0.0f ? __fdiv_rn(qmax, 127.0f) : 0.0f) * scale;
-                    hv[1 * G + g] = qsum;
-                }
-            } else {
-                float qsum = warp_sum_f(a + b);
-                if (lane == 0) {
-                    hv[0 * G + g] = scale;
-                    hv[1 * G + g] = qsum;
-                }
+    for (int g = warp; g < G; g += Q8_WARPS) {
+        float a = qf[g * 64 + lane], b = qf[g * 64 + 32 + lane];
+        if (ref_mode) {
+            float qmax = warp_max_f(fmaxf(fabsf(a), fabsf(b)));
+            float qid = qmax > 0.0f ? __fdiv_rn(127.0f, qmax) : 0.0f;
+            int ca = max(-127, min(127, __float2int_rn(a * qid)));
+            int cb = max(-127, min(127, __float2int_rn(b * qid)));
+            int8_t *qb = (int8_t *)(qq + g * 16);
+            qb[lane] = (int8_t)ca;
+            qb[32 + lane] = (int8_t)cb;
+            float qsum = warp_sum_f((float)(ca + cb));  // exact: small integers
+            if (lane == 0) {
+                hq[g] = (qmax > 0.0f ? __fdiv_rn(qmax, 127.0f) : 0.0f) * scale;
+                hq[G + g] = qsum;
+            }
+        } else {
+            float qsum = warp_sum_f(a + b);
+            if (lane == 0) {
+                hq[g] = scale;
+                hq[G + g] = qsum;
             }
         }
     }
     __syncthreads();
 
-    float m_run[G], l_thr[G], b_thr[G];
-    unsigned long long acc2[G][4];  // 8 output dims per head as four packed fp32 pairs
+    // ---- this warp's key sub-range ----
+    const int n_keys = kb_ - ka;
+    int per_w = (n_keys + Q8_WARPS - 1) / Q8_WARPS;
+    per_w = (per_w + WT_KEYS - 1) & ~(WT_KEYS - 1);
+    const int wa = min(kb_, ka + warp * per_w), wb = min(kb_, wa + per_w);
+    const int n_tiles = (wb - wa + WT_KEYS - 1) / WT_KEYS;
+    unsigned char *ring = warp_base + warp * SM::PER_WARP;
+    float *wbuf = (float *)(ring + WT_STAGES * WT_STAGE);
+    const uint32_t ring_u32 = mx::smem_u32(ring);
+
+    // Stage layout: K codes [32][64 B] with 16-byte pieces XOR-swizzled (lane = key reads),
+    // V codes [32][64 B] plain, then ks, kb, vs, vb slices of 32 floats.
+    // Lane l moves pieces l, l+32, l+64, l+96 of K and V: key = it*8 + l/4, piece = l%4.
+    const int pk = lane >> 2, pp = lane & 3;
+    const uint32_t dk0 = (uint32_t)(pk * 64 + ((pp ^ ((pk >> 1) & 3)) << 4));
+    const uint32_t dv0 = (uint32_t)(WT_KEYS * 64 + pk * 64 + pp * 16);
+    const uint32_t ds0 = (uint32_t)(2 * WT_KEYS * 64 + lane * 4);
+    // linear caches: per-lane source cursors, advanced by one tile per issue
+    const int8_t *ksrc = nullptr, *vsrc = nullptr;
+    const float *s_ks = nullptr, *s_kb = nullptr, *s_vs = nullptr, *s_vb = nullptr;
+    if (!PAGED) {
+        size_t r0 = (size_t)(base + wa);
+        ksrc = P.kq + (r0 + pk) * kvd + kvh * 64 + pp * 16;
+        vsrc = P.vq + (r0 + pk) * kvd + kvh * 64 + pp * 16;
+        size_t sd = (r0 + lane) * nkv + kvh;
+        s_ks = P.ks + sd, s_vs = P.vs + sd;
+        s_kb = affine ? P.kb + sd : P.ks + sd;
+        s_vb = affine ? P.vb + sd : P.vs + sd;
+    }
+    const size_t it_stride = (size_t)8 * kvd, tile_stride = (size_t)WT_KEYS * kvd;
+
+    auto issue = [&](int tile) {
+        const uint32_t dst = ring_u32 + (tile % WT_STAGES) * WT_STAGE;
+        const int key0 = wa + tile * WT_KEYS;
+        if (!PAGED && key0 + WT_KEYS <= wb) {  // full tile of a linear cache: no predicates, no lookups
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                cp_async16(dst + dk0 + it * 512, ksrc + it * it_stride, 16);
+                cp_async16(dst + dv0 + it * 512, vsrc + it * it_stride, 16);
+            }
+            cp_async4(dst + ds0, s_ks);
+            cp_async4(dst + ds0 + 128, s_kb);
+            cp_async4(dst + ds0 + 256, s_vs);
+            cp_async4(dst + ds0 + 384, s_vb);
+        } else {
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                int t = key0 + it * 8 + pk;
+                bool ok = t < wb;
+                size_t row = cache_row(P, table, base, ok ? t : wa);
+                cp_async16(dst + dk0 + it * 512, P.kq + row * kvd + kvh * 64 + pp * 16, ok ? 16 : 0);
+                cp_async16(dst + dv0 + it * 512, P.vq + row * kvd + kvh * 64 + pp * 16, ok ? 16 : 0);
+            }
+            int t = key0 + lane;
+            size_t sd = cache_row(P, table, base, t < wb ? t : wa) * nkv + kvh;
+            cp_async4(dst + ds0, P.ks + sd);
+            cp_async4(dst + ds0 + 128, affine ? P.kb + sd : P.ks + sd);
+            cp_async4(dst + ds0 + 256, P.vs + sd);
+            cp_async4(dst + ds0 + 384, affine ? P.vb + sd : P.vs + sd);
+        }
+        if (!PAGED) {
+            ksrc += tile_stride, vsrc += tile_stride;
+            s_ks += WT_KEYS * nkv, s_kb += WT_KEYS * nkv, s_vs += WT_KEYS * nkv, s_vb += WT_KEYS * nkv;
+        }
+    };
+
+    float m_run[G], thr[G], l_thr[G], b_thr[G];
+    unsigned long long acc2[G][4];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         m_run[g] = -CUDART_INF_F;
+        thr[g] = -CUDART_INF_F;   // raise the running max when a score exceeds this
         l_thr[g] = 0.0f;
         b_thr[g] = 0.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc2[g][j] = 0ull;
     }
 
-    const int n_keys = kb_ - ka;
-    const int n_chunks = (n_keys + CHUNK_KEYS - 1) / CHUNK_KEYS;
-    // tile sequence: per chunk, its K tiles then its V tiles
-    auto tiles_in_chunk = [&](int c) {
-        int len = min(CHUNK_KEYS, n_keys - c * CHUNK_KEYS);
-        return (len + TILE_KEYS - 1) / TILE_KEYS;
-    };
-    int total_tiles = 0;
-    for (int c = 0; c < n_chunks; ++c) total_tiles += 2 * tiles_in_chunk(c);
-
-    // producer state: next tile to issue
-    int pc = 0, pt = 0, issued = 0;  // chunk, tile-in-chunk (0..2T-1), count
-    auto issue_next = [&]() {
-        if (issued < total_tiles) {
-            int T = tiles_in_chunk(pc);
-            bool isv = pt >= T;
-            int tile = isv ? pt - T : pt;
-            int key0 = ka + pc * CHUNK_KEYS + tile * TILE_KEYS;
-            const int8_t *src = isv ? P.vq : P.kq;
-            uint32_t dst = mx::smem_u32(ring + (issued % RING) * (TILE_KEYS * 64));
-#pragma unroll
-            for (int it = 0; it < (TILE_KEYS * 4) / DEC_THREADS; ++it) {
-                int piece = it * DEC_THREADS + tid;
-                int k = piece >> 2, p = piece & 3;
-                int t = key0 + k;
-                bool ok = t < kb_;
-                size_t row = cache_row(P, table, base, ok ? t : ka);
-                cp_async16(dst + stage_off(k, p), src + row * kvd + kvh * 64 + p * 16, ok ? 16 : 0);
-            }
-            ++issued;
-            if (++pt == 2 * T) {
-                pt = 0;
-                ++pc;
-            }
-        }
+    if (n_tiles > 0) issue(0);
+    cp_async_commit();
+    const int kl = lane >> 3, dsl = lane & 7;
+    const int koff = lane * 64, kswz = (lane >> 1) & 3;           // K row of this lane's key
+    const int voff = WT_KEYS * 64 + kl * 64 + dsl * 8;            // V slice of (key lane, dims)
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        if (tile + 1 < n_tiles) issue(tile + 1);
         cp_async_commit();
-    };
+        cp_async_wait<1>();
+        __syncwarp();
+        const unsigned char *st = ring + (tile % WT_STAGES) * WT_STAGE;
+        const float *side = (const float *)(st + 2 * WT_KEYS * 64);
+        const bool ok = wa + tile * WT_KEYS + lane < wb;
+        const float ksc = side[lane], kbe = affine ? side[32 + lane] : 0.0f;
+        const float vsc = side[64 + lane], vbe = affine ? side[96 + lane] : 0.0f;
 
-    for (int i = 0; i < RING - 1; ++i) issue_next();
-
-    int consumed = 0;
-    for (int c = 0; c < n_chunks; ++c) {
-        const int T = tiles_in_chunk(c);
-        const int clen = min(CHUNK_KEYS, n_keys - c * CHUNK_KEYS);
-        const int ck0 = ka + c * CHUNK_KEYS;
-        float tmax[G];
+        // ---- scores (log2 domain) of this lane's key against the G heads ----
+        float sco[G];
+        if (ref_mode) {
+            int dot[G];
 #pragma unroll
-        for (int g = 0; g < G; ++g) tmax[g] = -CUDART_INF_F;
-
-        // ---- phase 1: scores of this chunk, one key per thread per tile ----
-        for (int tile = 0; tile < T; ++tile, ++consumed) {
-            int t = ck0 + tile * TILE_KEYS + tid;
-            bool ok = t < kb_;
-            size_t row = cache_row(P, table, base, ok ? t : ka);
-            float ksc = P.ks[row * nkv + kvh];
-            float kbe = affine ? P.kb[row * nkv + kvh] : 0.0f;
-            cp_async_wait<RING - 2>();
-            __syncthreads();
-            issue_next();
-            const unsigned char *st = ring + (consumed % RING) * (TILE_KEYS * 64);
-            float sco[G];
-            if (P.score_mode == MX230_Q8_SCORE_REF) {
-                int dot[G];
+            for (int g = 0; g < G; ++g) dot[g] = 0;
 #pragma unroll
-                for (int g = 0; g < G; ++g) dot[g] = 0;
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    int4 kw = *(const int4 *)(st + stage_off(tid, p));
-#pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        int4 qw = *(const int4 *)(qq + g * 16 + p * 4);
-                        dot[g] = __dp4a(kw.x, qw.x, dot[g]);
-                        dot[g] = __dp4a(kw.y, qw.y, dot[g]);
-                        dot[g] = __dp4a(kw.z, qw.z, dot[g]);
-                        dot[g] = __dp4a(kw.w, qw.w, dot[g]);
-                    }
-                }
-#pragma unroll
-                for (int g = 0; g < G; ++g)
-                    sco[g] = hv[0 * G + g] * (ksc * (float)dot[g] + kbe * hv[1 * G + g]);
-            } else {
-                float dot[G];
-#pragma unroll
-                for (int g = 0; g < G; ++g) dot[g] = 0.0f;
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    int4 kw = *(const int4 *)(st + stage_off(tid, p));
-                    const int w4[4] = {kw.x, kw.y, kw.z, kw.w};
-#pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        float c0 = (float)(int8_t)(w4[w] & 0xFF);
-                        float c1 = (float)(int8_t)((w4[w] >> 8) & 0xFF);
-                        float c2 = (float)(int8_t)((w4[w] >> 16) & 0xFF);
-                        float c3 = (float)(int8_t)((w4[w] >> 24) & 0xFF);
-#pragma unroll
-                        for (int g = 0; g < G; ++g) {
-                            float4 qv = *(const float4 *)(qf + g * 64 + p * 16 + w * 4);
-                            dot[g] += qv.x * c0 + qv.y * c1 + qv.z * c2 + qv.w * c3;
-                        }
-                    }
-                }
-#pragma unroll
-                for (int g = 0; g < G; ++g)
-                    sco[g] = scale * (ksc * dot[g] + kbe * hv[1 * G + g]);
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float v = ok ? sco[g] : -CUDART_INF_F;
-                sc[(tile * TILE_KEYS + tid) * G + g] = v;
-                tmax[g] = fmaxf(tmax[g], v);
-            }
-        }
-
-        // ---- chunk max per head, running max, rescale factor ----
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float v = warp_max_f(tmax[g]);
-            if (lane == 0) red[warp * G + g] = v;
-        }
-        __syncthreads();
-        if (tid < G) {
-            float v = fmaxf(fmaxf(red[tid], red[G + tid]), fmaxf(red[2 * G + tid], red[3 * G + tid]));
-            hv[2 * G + tid] = v;
-        }
-        __syncthreads();
-        float m_new[G];
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            m_new[g] = fmaxf(m_run[g], hv[2 * G + g]);
-            float alpha = (m_run[g] == -CUDART_INF_F) ? 0.0f : __expf(m_run[g] - m_new[g]);
-            l_thr[g] *= alpha;
-            b_thr[g] *= alpha;
-            const unsigned long long a2 = pack2f(alpha, alpha);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc2[g][j] = fmul2(acc2[g][j], a2);
-            m_run[g] = m_new[g];
-        }
-
-        // ---- phase 2a: p = exp(s - m); weights w = p * vs written back in place ----
-        for (int k = tid; k < clen; k += DEC_THREADS) {
-            size_t row = cache_row(P, table, base, ck0 + k);
-            float vsc = P.vs[row * nkv + kvh];
-            float vbe = affine ? P.vb[row * nkv + kvh] : 0.0f;
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float p = __expf(sc[k * G + g] - m_new[g]);
-                l_thr[g] += p;
-                b_thr[g] += p * vbe;
-                sc[k * G + g] = p * vsc;
-            }
-        }
-        // keys of the last tile beyond the chunk get weight 0
-        for (int k = clen + tid; k < T * TILE_KEYS; k += DEC_THREADS) {
-#pragma unroll
-            for (int g = 0; g < G; ++g) sc[k * G + g] = 0.0f;
-        }
-
-        // ---- phase 2b: acc += w * V; thread = (key lane kl, 8-byte slice dsl) ----
-        const int kl = tid >> 3, dsl = tid & 7;
-        for (int tile = 0; tile < T; ++tile, ++consumed) {
-            cp_async_wait<RING - 2>();
-            __syncthreads();  // also orders the weight writes above before their use
-            issue_next();
-            const unsigned char *st = ring + (consumed % RING) * (TILE_KEYS * 64);
-#pragma unroll 4
-            for (int step = 0; step < TILE_KEYS / 16; ++step) {
-                int k = step * 16 + kl;
-                int2 vw = *(const int2 *)(st + stage_off(k, dsl >> 1) + (dsl & 1) * 8);
-                unsigned long long v2[4];
-                v2[0] = pack2f((float)(int8_t)(vw.x & 0xFF), (float)(int8_t)((vw.x >> 8) & 0xFF));
-                v2[1] = pack2f((float)(int8_t)((vw.x >> 16) & 0xFF), (float)(int8_t)((vw.x >> 24) & 0xFF));
-                v2[2] = pack2f((float)(int8_t)(vw.y & 0xFF), (float)(int8_t)((vw.y >> 8) & 0xFF));
-                v2[3] = pack2f((float)(int8_t)((vw.y >> 16) & 0xFF), (float)(int8_t)((vw.y >> 24) & 0xFF));
-                const float *wk = sc + (tile * TILE_KEYS + k) * G;
+            for (int p = 0; p < 4; ++p) {
+                int4 kw = *(const int4 *)(st + koff + ((p ^ kswz) << 4));
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
-                    const float w = wk[g];
-                    const unsigned long long w2 = pack2f(w, w);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) acc2[g][j] = ffma2(w2, v2[j], acc2[g][j]);
+                    int4 qw = *(const int4 *)(qq + g * 16 + p * 4);
+                    dot[g] = __dp4a(kw.x, qw.x, dot[g]);
+                    dot[g] = __dp4a(kw.y, qw.y, dot[g]);
+                    dot[g] = __dp4a(kw.z, qw.z, dot[g]);
+                    dot[g] = __dp4a(kw.w, qw.w, dot[g]);
                 }
             }
+#pragma unroll
+            for (int g = 0; g < G; ++g) sco[g] = hq[g] * fmaf(ksc, (float)dot[g], kbe * hq[G + g]);
+        } else {
+            unsigned long long dot2[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) dot2[g] = 0ull;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                int4 kw = *(const int4 *)(st + koff + ((p ^ kswz) << 4));
+                const int w4[4] = {kw.x, kw.y, kw.z, kw.w};
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    unsigned long long c01, c23;
+                    s8x4_to_f32(w4[w], c01, c23);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const ulonglong2 qv = *(const ulonglong2 *)(qf + g * 64 + p * 16 + w * 4);
+                        dot2[g] = ffma2(qv.x, c01, dot2[g]);
+                        dot2[g] = ffma2(qv.y, c23, dot2[g]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float d0, d1;
+                unpack2f(dot2[g], d0, d1);
+                sco[g] = hq[g] * fmaf(ksc, d0 + d1, kbe * hq[G + g]);
+            }
         }
-        __syncthreads();  // sc is rewritten by the next chunk's phase 1
+
+        // ---- lazy running max, probabilities, weights ----
+        float wv[GP];
+#pragma unroll
+        for (int g = 0; g < GP; ++g) wv[g] = 0.0f;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float sg = ok ? sco[g] : -CUDART_INF_F;
+            if (__any_sync(0xFFFFFFFFu, sg > thr[g])) {  // warp-uniform, rare after the first tiles
+                const float m_new = warp_max_f(fmaxf(sg, m_run[g]));
+                const float alpha = (m_run[g] == -CUDART_INF_F) ? 0.0f : mx::ex2(m_run[g] - m_new);
+                l_thr[g] *= alpha;
+                b_thr[g] *= alpha;
+                const unsigned long long a2 = pack2f(alpha, alpha);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc2[g][j] = fmul2(acc2[g][j], a2);
+                m_run[g] = m_new;
+                thr[g] = m_new + RAISE * LOG2E;
+            }
+            const float p = mx::ex2(sg - m_run[g]);
+            l_thr[g] += p;
+            b_thr[g] = fmaf(p, vbe, b_thr[g]);
+            wv[g] = p * vsc;
+        }
+#pragma unroll
+        for (int g4 = 0; g4 < GP / 4; ++g4)
+            *(float4 *)(wbuf + lane * GP + g4 * 4) = make_float4(wv[g4 * 4], wv[g4 * 4 + 1], wv[g4 * 4 + 2], wv[g4 * 4 + 3]);
+        __syncwarp();
+
+        // ---- values: lane = (key lane kl, 8-byte slice dsl), 8 steps of 4 keys ----
+#pragma unroll 4
+        for (int step = 0; step < WT_KEYS / 4; ++step) {
+            const int2 vw = *(const int2 *)(st + voff + step * 256);
+            unsigned long long v2[4];
+            s8x4_to_f32(vw.x, v2[0], v2[1]);
+            s8x4_to_f32(vw.y, v2[2], v2[3]);
+            float wk[GP];
+#pragma unroll
+            for (int g4 = 0; g4 < GP / 4; ++g4) {
+                const float4 w4 = *(const float4 *)(wbuf + (step * 4 + kl) * GP + g4 * 4);
+                wk[g4 * 4] = w4.x, wk[g4 * 4 + 1] = w4.y, wk[g4 * 4 + 2] = w4.z, wk[g4 * 4 + 3] = w4.w;
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const unsigned long long w2 = pack2f(wk[g], wk[g]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc2[g][j] = ffma2(w2, v2[j], acc2[g][j]);
+            }
+        }
+        __syncwarp();  // the ring slot and the weight buffer are rewritten by the next iterations
     }
     cp_async_wait<0>();
 
-    // ---- CTA reduction: l, beta sum, acc over the 16 key lanes ----
-    float l_tot[G], b_tot[G];
+    // ---- warp totals, then the CTA-level log-sum-exp merge of the Q8_WARPS warps ----
+    float accw[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        float lv = warp_sum_f(l_thr[g]), bv = warp_sum_f(b_thr[g]);
-        if (lane == 0) {
-            red[warp * G + g] = lv;
-            hv[2 * G + g] = 0.0f;
-        }
-        __syncthreads();
-        lv = red[g] + red[G + g] + red[2 * G + g] + red[3 * G + g];
-        __syncthreads();
-        if (lane == 0) red[warp * G + g] = bv;
-        __syncthreads();
-        bv = red[g] + red[G + g] + red[2 * G + g] + red[3 * G + g];
-        __syncthreads();
-        l_tot[g] = lv;
-        b_tot[g] = bv;
-    }
-    // key lanes inside a warp differ in lane bits 3,4
-    float acc[G][8];
+        l_thr[g] = warp_sum_f(l_thr[g]);
+        b_thr[g] = warp_sum_f(b_thr[g]);
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+        for (int j = 0; j < 4; ++j) unpack2f(acc2[g][j], accw[g][2 * j], accw[g][2 * j + 1]);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) unpack2f(acc2[g][j], acc[g][2 * j], acc[g][2 * j + 1]);
-#pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float v = acc[g][j];
+        for (int j = 0; j < 8; ++j) {  // key lanes differ in lane bits 3,4
+            float v = accw[g][j];
             v += __shfl_xor_sync(0xFFFFFFFFu, v, 8);
             v += __shfl_xor_sync(0xFFFFFFFFu, v, 16);
-            acc[g][j] = v;
+            accw[g][j] = v;
         }
-    float *accs = sc;  // [4 warps][G][64]
-    if (lane < 8) {
+    }
+    __syncthreads();  // every warp is done with its ring: reuse the memory for the merge
+    float *mg = (float *)warp_base;  // [warp][g][68]: m (log2 domain), l, beta sum, pad, acc[64]
 #pragma unroll
-        for (int g = 0; g < G; ++g)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) accs[(warp * G + g) * 64 + lane * 8 + j] = acc[g][j];
+    for (int g = 0; g < G; ++g) {
+        float *dst = mg + (warp * G + g) * 68;
+        if (lane == 0) {
+            dst[0] = m_run[g];
+            dst[1] = l_thr[g];
+            dst[2] = b_thr[g];
+        }
+        if (lane < 8) {
+            *(float4 *)(dst + 4 + lane * 8) = make_float4(accw[g][0], accw[g][1], accw[g][2], accw[g][3]);
+            *(float4 *)(dst + 8 + lane * 8) = make_float4(accw[g][4], accw[g][5], accw[g][6], accw[g][7]);
+        }
     }
     __syncthreads();
 
     const bool direct = (n_splits == 1) && (P.fin_acc == nullptr);
-    for (int i = tid; i < gc * 64; i += DEC_THREADS) {
-        int g = i >> 6, d = i & 63;
-        float a = accs[(0 * G + g) * 64 + d] + accs[(1 * G + g) * 64 + d] +
-                  accs[(2 * G + g) * 64 + d] + accs[(3 * G + g) * 64 + d];
-        // pick this head's totals without dynamic register indexing
-        float lt = 0.0f, bt = 0.0f, mt = 0.0f;
+    for (int i = tid; i < gc * 64; i += Q8_THREADS) {
+        const int g = i >> 6, d = i & 63;
+        float mm = -CUDART_INF_F;
 #pragma unroll
-        for (int gg = 0; gg < G; ++gg)
-            if (gg == g) {
-                lt = l_tot[gg];
-                bt = b_tot[gg];
-                mt = m_run[gg];
-            }
-        a += bt;  // V's affine offset: sum_j p_j * vb_j, the same for every dim
-        int h = head0 + g;
+        for (int w = 0; w < Q8_WARPS; ++w) mm = fmaxf(mm, mg[(w * G + g) * 68]);
+        float lt = 0.0f, a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < Q8_WARPS; ++w) {
+            const float *src = mg + (w * G + g) * 68;
+            const float wgt = (src[0] == -CUDART_INF_F) ? 0.0f : mx::ex2(src[0] - mm);
+            lt += src[1] * wgt;
+            a += (src[4 + d] + src[2]) * wgt;  // V's affine offset sum_j p_j vb_j folds into every dim
+        }
+        const int h = head0 + g;
         if (direct) {
             P.out[(size_t)s * P.out_stride + h * 64 + d] = a / lt;
         } else {
+            // partial triples carry the max in natural-log units, as the split-KV interface states
             size_t pi = ((size_t)s * P.n_head + h) * n_splits + blockIdx.x;
             P.ws_acc[pi * 64 + d] = a;
             if (d == 0) {
-                P.ws_m[pi] = mt;
+                P.ws_m[pi] = mm * 0.6931471805599453f;
                 P.ws_l[pi] = lt;
             }
         }
@@ -501,7 +532,7 @@ decode_q8_kernel(const DecodeParams P) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    merge_and_store<G>(P, s, head0, gc, n_splits);
+    merge_and_store<G>(P, s, head0, gc, n_splits, Q8_THREADS);
 }
 
 // ---------------------------------------------------------------------------
@@ -700,9 +731,9 @@ __global__ void merge_partials_kernel(float *out, const float *m, const float *l
     *(float4 *)(out + (size_t)r * 64 + d4) = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
 }
 
-size_t q8_smem_bytes(int G) {
-    return (size_t)RING * TILE_KEYS * 64 + sizeof(float) * ((size_t)CHUNK_KEYS * G + G * 64 + 4 * G + 4 * G) +
-           sizeof(int) * (size_t)G * 16;
+template <int G>
+size_t q8_smem_bytes() {
+    return (size_t)Q8Smem<G>::TOTAL;
 }
 size_t f32_smem_bytes(int G) {
     return sizeof(float) * ((size_t)CHUNK_KEYS * G + G * 64 + 4 * G + G);
@@ -711,10 +742,16 @@ size_t f32_smem_bytes(int G) {
 template <int G>
 int launch_g(mx230_handle *h, cudaStream_t st, const DecodeParams &P, dim3 grid, bool q8) {
     if (q8) {
-        size_t sm = q8_smem_bytes(G);
-        MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_kernel<G>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_kernel<G><<<grid, DEC_THREADS, sm, st>>>(P)));
+        size_t sm = q8_smem_bytes<G>();
+        if (P.tables) {
+            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_kernel<G, true>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_kernel<G, true><<<grid, Q8_THREADS, sm, st>>>(P)));
+        } else {
+            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_kernel<G, false>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_kernel<G, false><<<grid, Q8_THREADS, sm, st>>>(P)));
+        }
     } else {
         size_t sm = f32_smem_bytes(G);
         MX_CHECK_CUDA(cudaFuncSetAttribute(decode_f32_kernel<G>,
@@ -761,9 +798,12 @@ int launch_decode(mx230_handle *h, void *stream, DecodeParams P, int n_seq, int 
     MX_REQUIRE((size_t)n_seq * gy <= h->n_counters, MX230_ERR_UNSUPPORTED,
                "attn_decode: n_seq*n_kv_head %lld exceeds %zu", (long long)n_seq * gy, h->n_counters);
 
-    // how many key splits: fill the machine (~3 CTAs per SM) but keep >= 256 keys each
+    // how many key splits: fill the machine (2 resident CTAs per SM for the int8 kernel, 3 for
+    // the fp32 one) but keep >= 256 keys each
+    // (rounded down so that the whole grid is resident at once: a partial second wave would
+    // nearly double the time)
     long long base_ctas = (long long)n_seq * gy;
-    int want = (int)((3LL * h->sm_count + base_ctas - 1) / base_ctas);
+    int want = (int)(((q8 ? 2LL : 3LL) * h->sm_count) / base_ctas);
     int n_splits;
     if (h->decode_chunk > 0 && known_keys > 0) {
         n_splits = (int)((known_keys + h->decode_chunk - 1) / h->decode_chunk);
