@@ -125,7 +125,7 @@ int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, 
 
 namespace mx {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s of SM cycles per wait
 constexpr int STATUS_WAIT_TIMEOUT = 1;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -149,6 +149,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+#if defined(MX_EXP) && (MX_EXP & 4)
+    bytes = 0;
+#endif
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
@@ -165,17 +168,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any role of the CTA gave
-// up, everybody else leaves its waits at the next poll.  Returns false on abort.
+// up, everybody else leaves its waits at the next check.  Returns false on abort.
+// The bound is counted on the SM's own cycle counter (cheap to read; reading the global
+// nanosecond timer on every contended wait costs far more than the wait itself).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                           int *status) {
     if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t0 = globaltimer_ns();
+    const long long t0 = clock64();
     unsigned polls = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++polls & 63u) == 0) {
+        if ((++polls & 255u) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
                 *abort_flag = 1;
                 atomicExch(status, STATUS_WAIT_TIMEOUT);
                 return false;
@@ -187,6 +192,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // ---- TMA: plain (per-CTA) tiled loads into this CTA's shared memory ----
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *tmap, uint32_t bar,
                                             int x, int y, int z) {
+#if defined(MX_EXP) && (MX_EXP & 4)
+    return;
+#endif
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%3, %4, %5}], [%2];"
@@ -223,6 +231,9 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 
 // 32 lanes x 32 columns of 32-bit: thread i of the warp gets lane (base_lane + i).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+#if defined(MX_EXP) && (MX_EXP & 8)
+    return;
+#endif
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -236,6 +247,9 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+#if defined(MX_EXP) && (MX_EXP & 8)
+    return;
+#endif
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -246,6 +260,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+#if defined(MX_EXP) && (MX_EXP & 8)
+    return;
+#endif
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -258,6 +275,9 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+#if defined(MX_EXP) && (MX_EXP & 8)
+    return;
+#endif
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
@@ -303,6 +323,9 @@ __host__ __device__ constexpr uint32_t mma_idesc_bf16(int m, int n, bool a_mn_ma
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
                                        uint32_t idesc, uint32_t accumulate) {
+#if defined(MX_EXP) && (MX_EXP & 2)
+    return;
+#endif
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
@@ -312,6 +335,9 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
                                        uint32_t idesc, uint32_t accumulate) {
+#if defined(MX_EXP) && (MX_EXP & 2)
+    return;
+#endif
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
@@ -334,6 +360,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
+}
+
+// Two fp32 -> packed bf16 pair on the integer pipe: add half an ulp to the magnitude and keep
+// the upper halves (round to nearest, ties away from zero).  cvt.rn.bf16x2.f32 shares the
+// 16-lane special-function pipe with ex2, which is the bottleneck of the softmax loops.
+__device__ __forceinline__ uint32_t pack_bf16_alu(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
 }
 
 }  // namespace mx

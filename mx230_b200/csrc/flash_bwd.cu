@@ -7,19 +7,22 @@
 //   p_ij  = exp(scale * q_i.k_j - L_i),  dP_ij = dO_i . v_j
 //   dS_ij = p_ij (dP_ij - Delta_i) scale
 //   dQ_i += dS_ij k_j ;  dK_j += dS_ij q_i ;  dV_j += p_ij dO_i
-// The same atomic-free split is kept -- a dQ pass owned by query tiles and a dK/dV
-// pass owned by key tiles, each output element written exactly once -- with all
-// contractions on tcgen05 tensor cores (bf16 operands, fp32 accumulators in tensor
-// memory).  In both passes the recomputed P / dS tiles go back into tensor memory as
-// bf16 and are consumed from there as the A operand, so no operand is ever written
-// to shared memory by a thread.
+// The same atomic-free split is kept -- a dQ pass owned by query tiles and a dK/dV pass
+// owned by key tiles, each output element written exactly once -- with all contractions on
+// tcgen05 tensor cores (bf16 operands, fp32 accumulators in tensor memory).  Both passes are
+// one kernel template: a CTA owns ONE 128-row tile (queries for dQ, keys for dK/dV) and
+// streams 64-row tiles of the other axis through a TMA ring:
 //
-// dQ pass:    CTA = two 128-query tiles; streams 64-key K/V tiles.
-//             S = Q K^T, dP = dO V^T  ->  dS  ->  dQ += dS K
-// dK/dV pass: CTA = two 128-key tiles; streams 64-query Q/dO tiles (+ their L, Delta).
-//             S^T = K Q^T, dP^T = V dO^T  ->  P^T, dS^T  ->  dV += P^T dO, dK += dS^T Q
-// Warp roles as in the forward: warps 0-3 / 4-7 compute tile 0 / 1 (one thread per
-// row), warp 8 is the TMA producer, warp 9 issues the MMAs; the two tiles ping-pong.
+//   X = A_own A_str^T, Y = B_own B_str^T      (S, dP   |  S^T, dP^T)      SS MMAs into TMEM
+//   P = exp2(X c - L), E = P o (Y - Delta)    one thread per owned row, registers
+//   acc0 += E A_str   (dQ += dS K | dK += dS^T Q),   acc1 += P B_str (dV += P^T dO)   TS MMAs
+//
+// Two streamed tiles are in flight at once ("slots" = even / odd iteration), each with its own
+// X, Y, E, P columns in tensor memory and its own compute warpgroup, so nothing aliases: the
+// MMA warp issues X, Y of iteration j+2 as soon as the warpgroup has pulled iteration j into
+// registers, and the accumulate MMAs of j when E, P are written.  The recomputed tiles go back
+// to tensor memory as bf16 A operands; no operand is ever written to shared memory by a thread.
+// The 1/sqrt(d) factor of dS is applied to the fp32 accumulators in the epilogue (exact: 2^-3).
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -27,20 +30,19 @@
 namespace {
 
 constexpr int HD = 64;
-constexpr int BT = 128;          // rows of an owned tile (queries in dQ, keys in dK/dV)
+constexpr int BT = 128;          // rows of the owned tile (queries in dQ, keys in dK/dV)
 constexpr int BS = 64;           // rows of a streamed tile
-constexpr int NT = 2;            // owned tiles per CTA
-constexpr int STAGES = 4;
+constexpr int STAGES = 6;
 constexpr int OWN_BYTES = BT * HD * 2;   // 16 KB
 constexpr int STR_BYTES = BS * HD * 2;   // 8 KB
-constexpr int BWD_THREADS = 320;
+constexpr int BWD_THREADS = 384;         // warpgroups: compute slot 0, compute slot 1, {TMA, MMA, 2 idle}
 
 // shared memory map (after 1024-byte alignment)
-constexpr int SM_OWN_A = 0;                              // NT x 16 KB: Q (dQ pass) / K (dK/dV pass)
-constexpr int SM_OWN_B = SM_OWN_A + NT * OWN_BYTES;      // NT x 16 KB: dO / V
-constexpr int SM_STR_A = SM_OWN_B + NT * OWN_BYTES;      // STAGES x 8 KB: K / Q
+constexpr int SM_OWN_A = 0;                              // Q (dQ pass) / K (dK/dV pass)
+constexpr int SM_OWN_B = SM_OWN_A + OWN_BYTES;           // dO / V
+constexpr int SM_STR_A = SM_OWN_B + OWN_BYTES;           // STAGES x 8 KB: K / Q
 constexpr int SM_STR_B = SM_STR_A + STAGES * STR_BYTES;  // STAGES x 8 KB: V / dO
-constexpr int SM_LD = SM_STR_B + STAGES * STR_BYTES;     // STAGES x 2 x 64 floats: L, Delta (dK/dV)
+constexpr int SM_LD = SM_STR_B + STAGES * STR_BYTES;     // STAGES x 2 x 64 floats: -L*log2e, -Delta (dK/dV)
 constexpr int SM_BAR = SM_LD + STAGES * 2 * BS * 4;
 constexpr int SM_TOTAL = SM_BAR + 256;
 constexpr int SM_ALLOC = SM_TOTAL + 1024;
@@ -48,13 +50,27 @@ constexpr int SM_ALLOC = SM_TOTAL + 1024;
 constexpr int BAR_OWN_FULL = 0;
 constexpr int BAR_STR_FULL = 1;                          // [STAGES]
 constexpr int BAR_STR_EMPTY = BAR_STR_FULL + STAGES;     // [STAGES]
-constexpr int BAR_SDP_FULL = BAR_STR_EMPTY + STAGES;     // [NT]
-constexpr int BAR_DS_READY = BAR_SDP_FULL + NT;          // [NT]
-constexpr int BAR_ACC_DONE = BAR_DS_READY + NT;          // [NT]
-constexpr int N_BARS = BAR_ACC_DONE + NT;
+constexpr int BAR_SDP_FULL = BAR_STR_EMPTY + STAGES;     // [2] MMA -> compute: X, Y written
+constexpr int BAR_SDP_FREE = BAR_SDP_FULL + 2;           // [2] compute -> MMA: X, Y in registers
+constexpr int BAR_DS_READY = BAR_SDP_FREE + 2;           // [2] compute -> MMA: E, P written
+constexpr int BAR_DS_FREE = BAR_DS_READY + 2;            // [2] MMA -> compute: E, P consumed
+constexpr int BAR_ACC_DONE = BAR_DS_FREE + 2;
+constexpr int N_BARS = BAR_ACC_DONE + 1;
 
+// tensor memory columns: slot u at u*192: X [0,64) Y [64,128) E [128,160) P [160,192)
+constexpr int TM_SLOT = 192, TM_X = 0, TM_Y = 64, TM_E = 128, TM_P = 160;
+constexpr int TM_ACC0 = 384, TM_ACC1 = 448;
 constexpr int TM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
+
+#ifdef MX_TRACE
+__device__ long long g_trace[64];
+#define TR_DECL long long _t0 = clock64(), _t1; const bool _tr = (blockIdx.x == 0 && blockIdx.y == 1 && (tid & 127) == 0);
+#define TR(slot) do { _t1 = clock64(); if (_tr) g_trace[(MODE * 2 + u) * 8 + (slot)] += _t1 - _t0; _t0 = _t1; } while (0)
+#else
+#define TR_DECL
+#define TR(slot)
+#endif
 
 struct BwdParams {
     const float *L;      // [BH][N]
@@ -66,419 +82,313 @@ struct BwdParams {
     int *status;
 };
 
-struct Ctx {
-    uint32_t smem_base;
-    unsigned char *smem;
-    uint32_t bar0;
-    volatile uint32_t *tmem_slot;
-    volatile int *abort_flag;
-    __device__ uint32_t bar(int i) const { return bar0 + 8u * (uint32_t)i; }
-};
-
-__device__ __forceinline__ Ctx make_ctx(unsigned char *smem_dyn) {
-    Ctx c;
-    c.smem_base = (mx::smem_u32(smem_dyn) + 1023u) & ~1023u;
-    c.smem = smem_dyn + (c.smem_base - mx::smem_u32(smem_dyn));
-    c.bar0 = c.smem_base + SM_BAR;
-    c.tmem_slot = (volatile uint32_t *)(c.smem + SM_BAR + 8 * N_BARS);
-    c.abort_flag = (volatile int *)(c.smem + SM_BAR + 8 * N_BARS + 8);
-    return c;
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long r, float &a, float &b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
+}
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b,
+                                                    unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fmul2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
 }
 
-__device__ __forceinline__ void init_barriers(const Ctx &c, int str_full_count) {
-    mx::mbar_init(c.bar(BAR_OWN_FULL), 1);
-    for (int s = 0; s < STAGES; ++s) {
-        mx::mbar_init(c.bar(BAR_STR_FULL + s), str_full_count);
-        mx::mbar_init(c.bar(BAR_STR_EMPTY + s), 1);
-    }
-    for (int t = 0; t < NT; ++t) {
-        mx::mbar_init(c.bar(BAR_SDP_FULL + t), 1);
-        mx::mbar_init(c.bar(BAR_DS_READY + t), BT);
-        mx::mbar_init(c.bar(BAR_ACC_DONE + t), 1);
-    }
-    *c.abort_flag = 0;
-    mx::mbar_fence_init();
-}
-
-// Stores one 64-column fp32 accumulator row from tensor memory to global memory.
-__device__ __forceinline__ void store_acc_row(uint32_t taddr, float *dst, bool valid) {
-#pragma unroll
-    for (int cc = 0; cc < HD / 32; ++cc) {
-        uint32_t v[32];
-        mx::tmem_ld32(taddr + cc * 32, v);
-        mx::tmem_wait_ld();
-        if (valid) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-                *(float4 *)(dst + cc * 32 + i) =
-                    make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]),
-                                __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-        }
-    }
-}
-
-// ===========================================================================
-// dQ pass.  tensor memory per query tile t (192 columns): S [0,64), dP [64,128)
-// (dS overlays the first 32 columns of dP as packed bf16), dQ [128,192).
-// ===========================================================================
+// MODE 0: dQ pass (own = Q, dO; stream = K, V).  MODE 1: dK/dV pass (own = K, V; stream = Q, dO).
+template <int MODE>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
-bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
-              const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-              const BwdParams P) {
+bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ CUtensorMap tmOwnB,
+           const __grid_constant__ CUtensorMap tmStrA, const __grid_constant__ CUtensorMap tmStrB,
+           const BwdParams P) {
     extern __shared__ unsigned char smem_dyn[];
-    const Ctx cx = make_ctx(smem_dyn);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int N = P.n, bh = blockIdx.y;
-    const int qb = P.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-    const int q0 = qb * (NT * BT);
-    const int n_kv_total = (N + BS - 1) / BS;
-    int n_it[NT];
-#pragma unroll
-    for (int t = 0; t < NT; ++t) {
-        int r0 = q0 + t * BT;
-        if (r0 >= N) n_it[t] = 0;
-        else n_it[t] = P.causal ? min(n_kv_total, (r0 + BT - 1) / BS + 1) : n_kv_total;
-    }
-    const int n_max = max(n_it[0], n_it[1]);
+    const uint32_t smem_base = (mx::smem_u32(smem_dyn) + 1023u) & ~1023u;
+    unsigned char *smem = smem_dyn + (smem_base - mx::smem_u32(smem_dyn));
+    const uint32_t bar0 = smem_base + SM_BAR;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    volatile uint32_t *tmem_slot = (volatile uint32_t *)(smem + SM_BAR + 8 * N_BARS);
+    volatile int *abort_flag = (volatile int *)(smem + SM_BAR + 8 * N_BARS + 8);
 
-    if (tid == 0) init_barriers(cx, 1);
-    if (warp == 9) mx::tmem_alloc(mx::smem_u32((const void *)cx.tmem_slot), TM_COLS);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int N = P.n, bh = blockIdx.x;
+    const int n_str_total = (N + BS - 1) / BS;
+    // dQ: late query tiles see the most keys; dK/dV: early key tiles see the most queries.
+    // Either way the heaviest tiles of every head are dispatched first.
+    const int tile = (MODE == 0 && P.causal) ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
+    const int own0 = tile * BT;
+    int it_beg = 0, it_end = n_str_total;
+    if (P.causal) {
+        if (MODE == 0) it_end = min(n_str_total, (own0 + BT - 1) / BS + 1);
+        else it_beg = own0 / BS;
+    }
+    const int n = it_end - it_beg;  // >= 1
+
+    if (tid == 0) {
+        mx::mbar_init(bar(BAR_OWN_FULL), 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mx::mbar_init(bar(BAR_STR_FULL + s), MODE == 1 ? 33 : 1);
+            mx::mbar_init(bar(BAR_STR_EMPTY + s), 1);
+        }
+        for (int u = 0; u < 2; ++u) {
+            mx::mbar_init(bar(BAR_SDP_FULL + u), 1);
+            mx::mbar_init(bar(BAR_SDP_FREE + u), BT / 32);  // one elected lane per warp arrives
+            mx::mbar_init(bar(BAR_DS_READY + u), BT / 32);
+            mx::mbar_init(bar(BAR_DS_FREE + u), 1);
+        }
+        mx::mbar_init(bar(BAR_ACC_DONE), 1);
+        *abort_flag = 0;
+        mx::mbar_fence_init();
+    }
+    if (warp == 9) mx::tmem_alloc(mx::smem_u32((const void *)tmem_slot), TM_COLS);
     mx::tc_fence_before();
     __syncthreads();
     mx::tc_fence_after();
-    const uint32_t tmem = *cx.tmem_slot;
+    const uint32_t tmem = *tmem_slot;
 
-    if (warp == 8) {
-        if (lane == 0) {
-            mx::tma_prefetch_desc(&tmQ);
-            mx::tma_prefetch_desc(&tmdO);
-            mx::tma_prefetch_desc(&tmK);
-            mx::tma_prefetch_desc(&tmV);
-            int nq = (n_it[1] > 0) ? 2 : 1;
-            mx::mbar_expect_tx(cx.bar(BAR_OWN_FULL), nq * 2 * OWN_BYTES);
-            for (int t = 0; t < nq; ++t) {
-                mx::tma_load_3d(cx.smem_base + SM_OWN_A + t * OWN_BYTES, &tmQ, cx.bar(BAR_OWN_FULL), 0,
-                                q0 + t * BT, bh);
-                mx::tma_load_3d(cx.smem_base + SM_OWN_B + t * OWN_BYTES, &tmdO, cx.bar(BAR_OWN_FULL), 0,
-                                q0 + t * BT, bh);
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        if (warp == 8) {
+            // ------------------------- producer -------------------------
+            if (lane == 0) {
+                mx::tma_prefetch_desc(&tmOwnA);
+                mx::tma_prefetch_desc(&tmOwnB);
+                mx::tma_prefetch_desc(&tmStrA);
+                mx::tma_prefetch_desc(&tmStrB);
+                mx::mbar_expect_tx(bar(BAR_OWN_FULL), 2 * OWN_BYTES);
+                mx::tma_load_3d(smem_base + SM_OWN_A, &tmOwnA, bar(BAR_OWN_FULL), 0, own0, bh);
+                mx::tma_load_3d(smem_base + SM_OWN_B, &tmOwnB, bar(BAR_OWN_FULL), 0, own0, bh);
             }
-            for (int j = 0; j < n_max; ++j) {
-                int s = j % STAGES, r = j / STAGES;
-                if (r > 0 && !mx::mbar_wait(cx.bar(BAR_STR_EMPTY + s), (r - 1) & 1, cx.abort_flag, P.status))
-                    break;
-                mx::mbar_expect_tx(cx.bar(BAR_STR_FULL + s), 2 * STR_BYTES);
-                mx::tma_load_3d(cx.smem_base + SM_STR_A + s * STR_BYTES, &tmK, cx.bar(BAR_STR_FULL + s), 0,
-                                j * BS, bh);
-                mx::tma_load_3d(cx.smem_base + SM_STR_B + s * STR_BYTES, &tmV, cx.bar(BAR_STR_FULL + s), 0,
-                                j * BS, bh);
-            }
-        }
-        __syncwarp();
-    } else if (warp == 9) {
-        if (lane == 0) {
-            constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BT, BS, false, false);  // [128 x 64] += A B^T
-            constexpr uint32_t IDESC_G = mx::mma_idesc_bf16(BT, HD, false, true);   // dQ += dS K
-            auto issue_sdp = [&](int t, int stage) {
-                uint64_t aq = mx::smem_desc_sw128(cx.smem_base + SM_OWN_A + t * OWN_BYTES);
-                uint64_t ad = mx::smem_desc_sw128(cx.smem_base + SM_OWN_B + t * OWN_BYTES);
-                uint64_t bk = mx::smem_desc_sw128(cx.smem_base + SM_STR_A + stage * STR_BYTES);
-                uint64_t bv = mx::smem_desc_sw128(cx.smem_base + SM_STR_B + stage * STR_BYTES);
+            bool ok = true;
+            for (int y = 0; y < n; ++y) {
+                const int s = y % STAGES, r = y / STAGES;
+                const int row0 = (it_beg + y) * BS;
+                if (r > 0)
+                    ok = __all_sync(0xFFFFFFFFu,
+                                    mx::mbar_wait(bar(BAR_STR_EMPTY + s), (r - 1) & 1, abort_flag, P.status));
+                if (!ok) break;
+                if (lane == 0) {
+                    mx::mbar_expect_tx(bar(BAR_STR_FULL + s), 2 * STR_BYTES);
+                    mx::tma_load_3d(smem_base + SM_STR_A + s * STR_BYTES, &tmStrA, bar(BAR_STR_FULL + s), 0, row0, bh);
+                    mx::tma_load_3d(smem_base + SM_STR_B + s * STR_BYTES, &tmStrB, bar(BAR_STR_FULL + s), 0, row0, bh);
+                }
+                if (MODE == 1) {
+                    // -L*log2(e) and -Delta of the 64 streamed queries
+                    float *ld = (float *)(smem + SM_LD + s * (2 * BS * 4));
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k)
-                    mx::mma_ss(tmem + t * 192, aq + 2 * k, bk + 2 * k, IDESC_S, k > 0);
-#pragma unroll
-                for (int k = 0; k < HD / 16; ++k)
-                    mx::mma_ss(tmem + t * 192 + 64, ad + 2 * k, bv + 2 * k, IDESC_S, k > 0);
-                mx::mma_commit(cx.bar(BAR_SDP_FULL + t));
-            };
-            bool ok = mx::mbar_wait(cx.bar(BAR_OWN_FULL), 0, cx.abort_flag, P.status);
-            if (ok) ok = mx::mbar_wait(cx.bar(BAR_STR_FULL + 0), 0, cx.abort_flag, P.status);
-            if (ok) {
-                mx::tc_fence_after();
-                for (int t = 0; t < NT; ++t)
-                    if (n_it[t] > 0) issue_sdp(t, 0);
+                    for (int u = 0; u < 2; ++u) {
+                        int q = row0 + u * 32 + lane;
+                        bool v = q < N;
+                        ld[u * 32 + lane] = v ? -P.L[(size_t)bh * N + q] * LOG2E : 0.0f;
+                        ld[BS + u * 32 + lane] = v ? -P.Delta[(size_t)bh * N + q] : 0.0f;
+                    }
+                    mx::mbar_arrive(bar(BAR_STR_FULL + s));
+                }
             }
-            for (int j = 0; j < n_max && ok; ++j) {
-                int s = j % STAGES;
-                int s1 = (j + 1) % STAGES, r1 = (j + 1) / STAGES;
-                if (j + 1 < n_max) ok = mx::mbar_wait(cx.bar(BAR_STR_FULL + s1), r1 & 1, cx.abort_flag, P.status);
-                for (int t = 0; t < NT && ok; ++t) {
-                    if (j >= n_it[t]) continue;
-                    ok = mx::mbar_wait(cx.bar(BAR_DS_READY + t), j & 1, cx.abort_flag, P.status);
+            __syncwarp();
+        } else if (warp == 9) {
+            // ------------------------- MMA issuer 1: X, Y --------------------
+            // (issuing one tcgen05.mma costs the issuing thread ~65 cycles, twice what a
+            // 128x64x16 MMA takes to execute: the two MMA streams get a thread each)
+            if (lane == 0) {
+                constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BT, BS, false, false);  // [128 x 64] = A B^T
+                const uint64_t own_a = mx::smem_desc_sw128(smem_base + SM_OWN_A);
+                const uint64_t own_b = mx::smem_desc_sw128(smem_base + SM_OWN_B);
+                auto issue_sdp = [&](int y) {
+                    const int s = y % STAGES, u = y & 1;
+                    const uint64_t sa = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
+                    const uint64_t sb = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
+#pragma unroll
+                    for (int k = 0; k < HD / 16; ++k)
+                        mx::mma_ss(tmem + u * TM_SLOT + TM_X, own_a + 2 * k, sa + 2 * k, IDESC_S, k > 0);
+#pragma unroll
+                    for (int k = 0; k < HD / 16; ++k)
+                        mx::mma_ss(tmem + u * TM_SLOT + TM_Y, own_b + 2 * k, sb + 2 * k, IDESC_S, k > 0);
+                    mx::mma_commit(bar(BAR_SDP_FULL + u));
+                };
+                bool ok = mx::mbar_wait(bar(BAR_OWN_FULL), 0, abort_flag, P.status);
+                for (int y = 0; y < 2 && y < n && ok; ++y) {
+                    ok = mx::mbar_wait(bar(BAR_STR_FULL + y), 0, abort_flag, P.status);
                     if (!ok) break;
                     mx::tc_fence_after();
-                    uint64_t bk = mx::smem_desc_sw128(cx.smem_base + SM_STR_A + s * STR_BYTES);
-#pragma unroll
-                    for (int k = 0; k < BS / 16; ++k)
-                        mx::mma_ts(tmem + t * 192 + 128, tmem + t * 192 + 64 + 8 * k, bk + 128 * k, IDESC_G,
-                                   (j > 0 || k > 0));
-                    if (j + 1 == n_it[t]) mx::mma_commit(cx.bar(BAR_ACC_DONE + t));
-                    if (j + 1 < n_it[t]) issue_sdp(t, s1);
+                    issue_sdp(y);
                 }
-                if (!ok) break;
-                mx::mma_commit(cx.bar(BAR_STR_EMPTY + s));
+                // X, Y two iterations ahead, as soon as the slot's registers hold the current ones
+                for (int y = 0; y + 2 < n && ok; ++y) {
+                    const int s2 = (y + 2) % STAGES, r2 = (y + 2) / STAGES;
+                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s2), r2 & 1, abort_flag, P.status);
+                    if (ok) ok = mx::mbar_wait(bar(BAR_SDP_FREE + (y & 1)), (y >> 1) & 1, abort_flag, P.status);
+                    if (!ok) break;
+                    mx::tc_fence_after();
+                    issue_sdp(y + 2);
+                }
             }
+            __syncwarp();
+        } else if (warp == 10) {
+            // ------------------------- MMA issuer 2: accumulators ------------
+            if (lane == 0) {
+                constexpr uint32_t IDESC_G = mx::mma_idesc_bf16(BT, HD, false, true);   // acc += (tmem A) B
+                bool ok = true;
+                for (int y = 0; y < n && ok; ++y) {
+                    const int s = y % STAGES, r = y / STAGES, u = y & 1;
+                    // the streamed tile (read here as the MN-major B operand) and E, P of this slot
+                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
+                    if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY + u), (y >> 1) & 1, abort_flag, P.status);
+                    if (!ok) break;
+                    mx::tc_fence_after();
+                    const uint64_t sa = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
+                    const uint64_t sb = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
+                    if (MODE == 1) {
+#pragma unroll
+                        for (int k = 0; k < BS / 16; ++k)  // dV += P^T dO
+                            mx::mma_ts(tmem + TM_ACC1, tmem + u * TM_SLOT + TM_P + 8 * k, sb + 128 * k, IDESC_G,
+                                       (y > 0 || k > 0));
+                    }
+#pragma unroll
+                    for (int k = 0; k < BS / 16; ++k)      // dQ += dS K  |  dK += dS^T Q
+                        mx::mma_ts(tmem + TM_ACC0, tmem + u * TM_SLOT + TM_E + 8 * k, sa + 128 * k, IDESC_G,
+                                   (y > 0 || k > 0));
+                    mx::mma_commit(bar(BAR_DS_FREE + u));
+                    // X, Y of this iteration were complete before its E, P could be formed, so this
+                    // commit also covers every read of the stage
+                    mx::mma_commit(bar(BAR_STR_EMPTY + s));
+                    if (y == n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                }
+            }
+            __syncwarp();
         }
-        __syncwarp();
     } else {
-        const int t = warp >> 2;
-        const int row = q0 + t * BT + (tid & 127);
+        // ------------------------- compute warpgroups -------------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int u = warp >> 2;                        // slot of this warpgroup
+        const int row = own0 + (tid & 127);             // owned row (query | key) of this thread
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tm_s = tmem + lane_off + t * 192;
-        const uint32_t tm_dp = tm_s + 64;
-        const uint32_t tm_dq = tm_s + 128;
+        const uint32_t tm_slot = tmem + lane_off + u * TM_SLOT;
         const float c = 0.125f * LOG2E;
-        const int n_t = n_it[t];
         const bool rv = row < N;
-        const float Li = rv ? P.L[(size_t)bh * N + row] * LOG2E : 0.0f;
-        const float Di = rv ? P.Delta[(size_t)bh * N + row] : 0.0f;
+        float nl0 = 0.0f, nl1 = 0.0f, nd0 = 0.0f, nd1 = 0.0f;  // -L*log2e and -Delta (MODE 0: of this row)
+        if (MODE == 0) {
+            nl0 = nl1 = rv ? -P.L[(size_t)bh * N + row] * LOG2E : 0.0f;
+            nd0 = nd1 = rv ? -P.Delta[(size_t)bh * N + row] : 0.0f;
+        }
         bool ok = true;
-        for (int j = 0; j < n_t; ++j) {
-            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(cx.bar(BAR_SDP_FULL + t), j & 1, cx.abort_flag, P.status));
+#ifdef MX_SKEW
+        if (u == 1) { const long long s0 = clock64(); while (clock64() - s0 < MX_SKEW) {} }
+#endif
+        TR_DECL
+        for (int y = u; y < n; y += 2) {
+            const int q = y >> 1;
+            TR(0);
+            const int s = y % STAGES, r = y / STAGES;
+            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_SDP_FULL + u), q & 1, abort_flag, P.status));
+            if (MODE == 1 && ok)  // the stage's L / Delta slices were written with plain stores
+                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status));
             if (!ok) break;
             mx::tc_fence_after();
-            const int key0 = j * BS;
-            const bool need_mask = (key0 + BS > N) || (P.causal && key0 + BS - 1 > q0 + t * BT);
-#pragma unroll
-            for (int cc = 0; cc < BS / 32; ++cc) {
-                uint32_t sv[32], dv[32];
-                mx::tmem_ld32(tm_s + cc * 32, sv);
-                mx::tmem_ld32(tm_dp + cc * 32, dv);
-                mx::tmem_wait_ld();
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = mx::ex2(fmaf(__uint_as_float(sv[i]), c, -Li));
-                    float p1 = mx::ex2(fmaf(__uint_as_float(sv[i + 1]), c, -Li));
-                    if (need_mask) {
-                        int key = key0 + cc * 32 + i;
-                        if (!(key < N && (!P.causal || key <= row))) p0 = 0.0f;
-                        if (!(key + 1 < N && (!P.causal || key + 1 <= row))) p1 = 0.0f;
-                    }
-                    float d0 = p0 * (__uint_as_float(dv[i]) - Di) * 0.125f;
-                    float d1 = p1 * (__uint_as_float(dv[i + 1]) - Di) * 0.125f;
-                    pk[i >> 1] = mx::pack_bf16(d0, d1);
-                }
-                mx::tmem_st16(tm_dp + cc * 16, pk);
-            }
-            mx::tmem_wait_st();
+            TR(1);
+            uint32_t xv[BS], yv[BS];
+            mx::tmem_ld32(tm_slot + TM_X, *(uint32_t(*)[32])(xv));
+            mx::tmem_ld32(tm_slot + TM_X + 32, *(uint32_t(*)[32])(xv + 32));
+            mx::tmem_ld32(tm_slot + TM_Y, *(uint32_t(*)[32])(yv));
+            mx::tmem_ld32(tm_slot + TM_Y + 32, *(uint32_t(*)[32])(yv + 32));
+            mx::tmem_wait_ld();
+            TR(2);
             mx::tc_fence_before();
-            mx::mbar_arrive(cx.bar(BAR_DS_READY + t));
-        }
-        if (ok && n_t > 0) {
-            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(cx.bar(BAR_ACC_DONE + t), 0, cx.abort_flag, P.status));
-            if (ok) {
-                mx::tc_fence_after();
-                store_acc_row(tm_dq, P.out0 + ((size_t)bh * N + row) * HD, rv);
-            }
-        }
-    }
-    mx::tc_fence_before();
-    __syncthreads();
-    mx::tc_fence_after();
-    if (warp == 9) mx::tmem_dealloc(tmem, TM_COLS);
-}
+            __syncwarp();
+            if (lane == 0) mx::mbar_arrive(bar(BAR_SDP_FREE + u));
 
-// ===========================================================================
-// dK/dV pass.  tensor memory per key tile t (256 columns): S^T [0,64) (P^T overlays
-// its first 32 columns), dP^T [64,128) (dS^T overlays), dK [128,192), dV [192,256).
-// ===========================================================================
-__global__ void __launch_bounds__(BWD_THREADS, 1)
-bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-               const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
-               const BwdParams P) {
-    extern __shared__ unsigned char smem_dyn[];
-    const Ctx cx = make_ctx(smem_dyn);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int N = P.n, bh = blockIdx.y;
-    const int k0 = blockIdx.x * (NT * BT);  // causal: early key blocks see the most queries
-    const int n_q_total = (N + BS - 1) / BS;
-    int i_beg[NT];
-    bool act[NT];
+            const int str0 = (it_beg + y) * BS;
+            const bool need_mask = (str0 + BS > N) ||
+                                   (P.causal && (MODE == 0 ? (str0 + BS - 1 > own0) : (str0 < own0 + BT - 1)));
+            const float *ld = (const float *)(smem + SM_LD + s * (2 * BS * 4));
+            if (need_mask) {
+                // masked scores become -inf up front (p = 0, so E = 0): the main loop stays branch-free
 #pragma unroll
-    for (int t = 0; t < NT; ++t) {
-        int r0 = k0 + t * BT;
-        act[t] = r0 < N;
-        i_beg[t] = P.causal ? r0 / BS : 0;  // first query tile that can see this key tile
-    }
-    const int i0 = i_beg[0];
-    const int n_iter = n_q_total - i0;  // query tiles i0 .. n_q_total-1 (tile 0 is always active)
-
-    if (tid == 0) init_barriers(cx, 1 + 32);
-    if (warp == 9) mx::tmem_alloc(mx::smem_u32((const void *)cx.tmem_slot), TM_COLS);
-    mx::tc_fence_before();
-    __syncthreads();
-    mx::tc_fence_after();
-    const uint32_t tmem = *cx.tmem_slot;
-
-    if (warp == 8) {
-        if (lane == 0) {
-            mx::tma_prefetch_desc(&tmQ);
-            mx::tma_prefetch_desc(&tmdO);
-            mx::tma_prefetch_desc(&tmK);
-            mx::tma_prefetch_desc(&tmV);
-            int nk = act[1] ? 2 : 1;
-            mx::mbar_expect_tx(cx.bar(BAR_OWN_FULL), nk * 2 * OWN_BYTES);
-            for (int t = 0; t < nk; ++t) {
-                mx::tma_load_3d(cx.smem_base + SM_OWN_A + t * OWN_BYTES, &tmK, cx.bar(BAR_OWN_FULL), 0,
-                                k0 + t * BT, bh);
-                mx::tma_load_3d(cx.smem_base + SM_OWN_B + t * OWN_BYTES, &tmV, cx.bar(BAR_OWN_FULL), 0,
-                                k0 + t * BT, bh);
-            }
-        }
-        bool ok = true;
-        for (int it = 0; it < n_iter; ++it) {
-            int s = it % STAGES, r = it / STAGES;
-            int qrow0 = (i0 + it) * BS;
-            if (r > 0)
-                ok = __all_sync(0xFFFFFFFFu,
-                                mx::mbar_wait(cx.bar(BAR_STR_EMPTY + s), (r - 1) & 1, cx.abort_flag, P.status));
-            if (!ok) break;
-            if (lane == 0) {
-                mx::mbar_expect_tx(cx.bar(BAR_STR_FULL + s), 2 * STR_BYTES);
-                mx::tma_load_3d(cx.smem_base + SM_STR_A + s * STR_BYTES, &tmQ, cx.bar(BAR_STR_FULL + s), 0,
-                                qrow0, bh);
-                mx::tma_load_3d(cx.smem_base + SM_STR_B + s * STR_BYTES, &tmdO, cx.bar(BAR_STR_FULL + s), 0,
-                                qrow0, bh);
-            }
-            // L (pre-multiplied by log2 e) and Delta of the 64 streamed queries
-            float *ld = (float *)(cx.smem + SM_LD + s * (2 * BS * 4));
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                int q = qrow0 + u * 32 + lane;
-                bool v = q < N;
-                ld[u * 32 + lane] = v ? P.L[(size_t)bh * N + q] * LOG2E : 0.0f;
-                ld[BS + u * 32 + lane] = v ? P.Delta[(size_t)bh * N + q] : 0.0f;
-            }
-            mx::mbar_arrive(cx.bar(BAR_STR_FULL + s));
-        }
-        __syncwarp();
-    } else if (warp == 9) {
-        if (lane == 0) {
-            constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BT, BS, false, false);
-            constexpr uint32_t IDESC_G = mx::mma_idesc_bf16(BT, HD, false, true);
-            auto issue_sdp = [&](int t, int stage) {
-                uint64_t ak = mx::smem_desc_sw128(cx.smem_base + SM_OWN_A + t * OWN_BYTES);
-                uint64_t av = mx::smem_desc_sw128(cx.smem_base + SM_OWN_B + t * OWN_BYTES);
-                uint64_t bq = mx::smem_desc_sw128(cx.smem_base + SM_STR_A + stage * STR_BYTES);
-                uint64_t bd = mx::smem_desc_sw128(cx.smem_base + SM_STR_B + stage * STR_BYTES);
-#pragma unroll
-                for (int k = 0; k < HD / 16; ++k)
-                    mx::mma_ss(tmem + t * 256, ak + 2 * k, bq + 2 * k, IDESC_S, k > 0);
-#pragma unroll
-                for (int k = 0; k < HD / 16; ++k)
-                    mx::mma_ss(tmem + t * 256 + 64, av + 2 * k, bd + 2 * k, IDESC_S, k > 0);
-                mx::mma_commit(cx.bar(BAR_SDP_FULL + t));
-            };
-            // iteration `it` of tile t is active when the query tile can see the key tile
-            auto active = [&](int t, int it) { return act[t] && (i0 + it) >= i_beg[t]; };
-            int cnt[NT] = {0, 0};  // active iterations issued so far per tile (accumulate flag)
-            bool ok = mx::mbar_wait(cx.bar(BAR_OWN_FULL), 0, cx.abort_flag, P.status);
-            if (ok && n_iter > 0) ok = mx::mbar_wait(cx.bar(BAR_STR_FULL + 0), 0, cx.abort_flag, P.status);
-            if (ok && n_iter > 0) {
-                mx::tc_fence_after();
-                for (int t = 0; t < NT; ++t)
-                    if (active(t, 0)) issue_sdp(t, 0);
-            }
-            for (int it = 0; it < n_iter && ok; ++it) {
-                int s = it % STAGES;
-                int s1 = (it + 1) % STAGES, r1 = (it + 1) / STAGES;
-                if (it + 1 < n_iter)
-                    ok = mx::mbar_wait(cx.bar(BAR_STR_FULL + s1), r1 & 1, cx.abort_flag, P.status);
-                for (int t = 0; t < NT && ok; ++t) {
-                    if (!active(t, it)) {
-                        // the tile joins at the next query tile: its first S^T/dP^T go out now
-                        if (it + 1 < n_iter && active(t, it + 1)) {
-                            mx::tc_fence_after();
-                            issue_sdp(t, s1);
-                        }
-                        continue;
-                    }
-                    ok = mx::mbar_wait(cx.bar(BAR_DS_READY + t), cnt[t] & 1, cx.abort_flag, P.status);
-                    if (!ok) break;
-                    mx::tc_fence_after();
-                    uint64_t bq = mx::smem_desc_sw128(cx.smem_base + SM_STR_A + s * STR_BYTES);
-                    uint64_t bd = mx::smem_desc_sw128(cx.smem_base + SM_STR_B + s * STR_BYTES);
-#pragma unroll
-                    for (int k = 0; k < BS / 16; ++k)  // dV += P^T dO
-                        mx::mma_ts(tmem + t * 256 + 192, tmem + t * 256 + 8 * k, bd + 128 * k, IDESC_G,
-                                   (cnt[t] > 0 || k > 0));
-#pragma unroll
-                    for (int k = 0; k < BS / 16; ++k)  // dK += dS^T Q
-                        mx::mma_ts(tmem + t * 256 + 128, tmem + t * 256 + 64 + 8 * k, bq + 128 * k, IDESC_G,
-                                   (cnt[t] > 0 || k > 0));
-                    ++cnt[t];
-                    if (it + 1 == n_iter) mx::mma_commit(cx.bar(BAR_ACC_DONE + t));
-                    else issue_sdp(t, s1);
+                for (int i = 0; i < BS; ++i) {
+                    const int c0 = str0 + i;
+                    const bool v0 = c0 < N && (!P.causal || (MODE == 0 ? c0 <= row : c0 >= row));
+                    if (!v0) xv[i] = 0xFF800000u;
                 }
-                if (!ok) break;
-                mx::mma_commit(cx.bar(BAR_STR_EMPTY + s));
             }
-        }
-        __syncwarp();
-    } else {
-        const int t = warp >> 2;
-        const int krow = k0 + t * BT + (tid & 127);  // this thread's key
-        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tm_s = tmem + lane_off + t * 256;
-        const uint32_t tm_dp = tm_s + 64;
-        const float c = 0.125f * LOG2E;
-        const bool kvalid = krow < N;
-        bool ok = true;
-        int cnt = 0;
-        if (act[t]) {
-            for (int it = 0; it < n_iter; ++it) {
-                if (i0 + it < i_beg[t]) continue;
-                ok = __all_sync(0xFFFFFFFFu,
-                                mx::mbar_wait(cx.bar(BAR_SDP_FULL + t), cnt & 1, cx.abort_flag, P.status));
-                if (!ok) break;
-                // the streamed stage's L/Delta became visible with the same full barrier the
-                // MMA warp waited on before issuing; wait on it here too for the plain loads
-                int s = it % STAGES, r = it / STAGES;
-                ok = __all_sync(0xFFFFFFFFu,
-                                mx::mbar_wait(cx.bar(BAR_STR_FULL + s), r & 1, cx.abort_flag, P.status));
+            uint32_t pe[BS / 2], pp[MODE == 1 ? BS / 2 : 1];
+#pragma unroll
+            for (int i = 0; i < BS; i += 2) {
+                if (MODE == 1) {
+                    const float2 l2 = *(const float2 *)(ld + i), d2 = *(const float2 *)(ld + BS + i);
+                    nl0 = l2.x, nl1 = l2.y, nd0 = d2.x, nd1 = d2.y;
+                }
+#if defined(MX_EXP) && (MX_EXP & 1)
+                const float p0 = __uint_as_float(xv[i]), p1 = __uint_as_float(xv[i + 1]);
+                const float e0 = __uint_as_float(yv[i]) + nd0 + nl0 * c, e1 = __uint_as_float(yv[i + 1]) + nd1 + nl1;
+#else
+                const float p0 = mx::ex2(fmaf(__uint_as_float(xv[i]), c, nl0));
+                const float p1 = mx::ex2(fmaf(__uint_as_float(xv[i + 1]), c, nl1));
+                const float e0 = p0 * (__uint_as_float(yv[i]) + nd0);
+                const float e1 = p1 * (__uint_as_float(yv[i + 1]) + nd1);
+#endif
+                pe[i >> 1] = mx::pack_bf16(e0, e1);
+                if (MODE == 1) pp[i >> 1] = mx::pack_bf16(p0, p1);
+            }
+            TR(3);
+            if (q > 0) {  // the accumulate MMAs of this slot's previous iteration have consumed E, P
+                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_DS_FREE + u), (q - 1) & 1, abort_flag, P.status));
                 if (!ok) break;
                 mx::tc_fence_after();
-                const float *ld = (const float *)(cx.smem + SM_LD + s * (2 * BS * 4));
-                const int qrow0 = (i0 + it) * BS;
-                const bool need_mask = (qrow0 + BS > N) || (P.causal && qrow0 < k0 + t * BT + BT - 1);
+            }
+            TR(4);
+            mx::tmem_st32(tm_slot + TM_E, *(uint32_t(*)[32])(pe));
+            if (MODE == 1) mx::tmem_st32(tm_slot + TM_P, *(uint32_t(*)[32])(pp));
+            mx::tmem_wait_st();
+            TR(5);
+            mx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mx::mbar_arrive(bar(BAR_DS_READY + u));
+            TR(6);
+        }
+        // ---- epilogue: accumulators -> global, dS's 1/sqrt(d) applied here ----
+        if (ok) ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag, P.status));
+        if (ok) {
+            mx::tc_fence_after();
+            const uint32_t tm_row = tmem + lane_off;
+            if (MODE == 0) {
+                // both warpgroups hold the same 128 rows: slot 0 stores dims 0..31, slot 1 dims 32..63
+                uint32_t v[32];
+                mx::tmem_ld32(tm_row + TM_ACC0 + u * 32, v);
+                mx::tmem_wait_ld();
+                if (rv) {
+                    float *dst = P.out0 + ((size_t)bh * N + row) * HD + u * 32;
 #pragma unroll
-                for (int cc = 0; cc < BS / 32; ++cc) {
-                    uint32_t sv[32], dv[32];
-                    mx::tmem_ld32(tm_s + cc * 32, sv);
-                    mx::tmem_ld32(tm_dp + cc * 32, dv);
+                    for (int i = 0; i < 32; i += 4)
+                        *(float4 *)(dst + i) = make_float4(__uint_as_float(v[i]) * 0.125f, __uint_as_float(v[i + 1]) * 0.125f,
+                                                           __uint_as_float(v[i + 2]) * 0.125f, __uint_as_float(v[i + 3]) * 0.125f);
+                }
+            } else {
+                // slot 0 stores dK (scaled), slot 1 stores dV
+                const float sc = u == 0 ? 0.125f : 1.0f;
+                float *dst = (u == 0 ? P.out0 : P.out1) + ((size_t)bh * N + row) * HD;
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t v[32];
+                    mx::tmem_ld32(tm_row + (u == 0 ? TM_ACC0 : TM_ACC1) + cc * 32, v);
                     mx::tmem_wait_ld();
-                    uint32_t pp[16], pd[16];
+                    if (rv) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float2 l2 = *(const float2 *)(ld + cc * 32 + i);
-                        float2 d2 = *(const float2 *)(ld + BS + cc * 32 + i);
-                        float p0 = mx::ex2(fmaf(__uint_as_float(sv[i]), c, -l2.x));
-                        float p1 = mx::ex2(fmaf(__uint_as_float(sv[i + 1]), c, -l2.y));
-                        if (need_mask) {
-                            int q = qrow0 + cc * 32 + i;
-                            if (!(q < N && (!P.causal || q >= krow))) p0 = 0.0f;
-                            if (!(q + 1 < N && (!P.causal || q + 1 >= krow))) p1 = 0.0f;
-                        }
-                        float e0 = p0 * (__uint_as_float(dv[i]) - d2.x) * 0.125f;
-                        float e1 = p1 * (__uint_as_float(dv[i + 1]) - d2.y) * 0.125f;
-                        pp[i >> 1] = mx::pack_bf16(p0, p1);
-                        pd[i >> 1] = mx::pack_bf16(e0, e1);
+                        for (int i = 0; i < 32; i += 4)
+                            *(float4 *)(dst + cc * 32 + i) =
+                                make_float4(__uint_as_float(v[i]) * sc, __uint_as_float(v[i + 1]) * sc,
+                                            __uint_as_float(v[i + 2]) * sc, __uint_as_float(v[i + 3]) * sc);
                     }
-                    mx::tmem_st16(tm_s + cc * 16, pp);
-                    mx::tmem_st16(tm_dp + cc * 16, pd);
-                }
-                mx::tmem_wait_st();
-                mx::tc_fence_before();
-                mx::mbar_arrive(cx.bar(BAR_DS_READY + t));
-                ++cnt;
-            }
-            if (ok && cnt > 0) {
-                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(cx.bar(BAR_ACC_DONE + t), 0, cx.abort_flag, P.status));
-                if (ok) {
-                    mx::tc_fence_after();
-                    store_acc_row(tm_s + 128, P.out0 + ((size_t)bh * N + krow) * HD, kvalid);
-                    store_acc_row(tm_s + 192, P.out1 + ((size_t)bh * N + krow) * HD, kvalid);
                 }
             }
         }
@@ -508,8 +418,8 @@ __global__ void bwd_preprocess_kernel(const float *dO, const float *O, float *De
 int set_attrs() {
     static bool done = false;
     if (!done) {
-        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
-        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
+        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
+        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
         done = true;
     }
     return MX230_OK;
@@ -535,9 +445,9 @@ int make_maps(mx230_handle *h, Maps &m, const void *Qb, const void *Kb, const vo
 int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dQ,
               int batch_heads, int n, int causal) {
     BwdParams P{L, Delta, dQ, nullptr, n, causal ? 1 : 0, h->status_dev};
-    dim3 grid((n + NT * BT - 1) / (NT * BT), batch_heads);
+    dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_DQ,
-              (bwd_dq_kernel<<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.own128[0], m.own128[3], m.str64[1],
+              (bwd_kernel<0><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.own128[0], m.own128[3], m.str64[1],
                                                                   m.str64[2], P)));
     return MX230_OK;
 }
@@ -545,10 +455,10 @@ int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, c
 int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dK,
                float *dV, int batch_heads, int n, int causal) {
     BwdParams P{L, Delta, dK, dV, n, causal ? 1 : 0, h->status_dev};
-    dim3 grid((n + NT * BT - 1) / (NT * BT), batch_heads);
+    dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_DKV,
-              (bwd_dkv_kernel<<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.own128[1], m.own128[2], m.str64[0],
-                                                                   m.str64[3], P)));
+              (bwd_kernel<1><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.own128[1], m.own128[2], m.str64[0],
+                                                                  m.str64[3], P)));
     return MX230_OK;
 }
 
@@ -648,3 +558,16 @@ extern "C" int mx230_attn_bwd_flash_bf16(mx230_handle *h, void *stream, const vo
     return bwd_bf16(h, stream, Qb, Kb, Vb, dOb, L, Delta, dQ, dK, dV, batch_heads, n, causal, 3,
                     "attn_bwd_flash_bf16");
 }
+
+#ifdef MX_TRACE
+extern "C" int mx230_debug_trace(long long *out, int reset) {
+    if (reset) {
+        long long z[64] = {0};
+        cudaMemcpyToSymbol(g_trace, z, sizeof(z));
+        return 0;
+    }
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 64);
+    return 0;
+}
+#endif

@@ -63,6 +63,19 @@ constexpr int TM_COLS = 512;
 // exponent; until then probabilities are taken against the stale max (they stay below
 // 2^RESCALE_LOG2, harmless in bf16/fp32) and O needs no rescale.
 constexpr float RESCALE_LOG2 = 8.0f;
+// of every 8 element pairs of a score row, this many take the polynomial exp2 (rest: ex2.approx)
+constexpr int POLY_OF_8 = 0;
+
+#ifdef MX_TRACE
+__device__ long long g_ftrace[32];
+#define FT_DECL long long _ft[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long _f0 = clock64();
+#define FT(k) do { long long _f1 = clock64(); _ft[k] += _f1 - _f0; _f0 = _f1; } while (0)
+#define FT_DUMP if (blockIdx.x == 0 && blockIdx.y == 3 && (tid & 127) == 0) { for (int _i = 0; _i < 8; ++_i) g_ftrace[t * 8 + _i] = _ft[_i]; g_ftrace[16 + t] = n_t; }
+#else
+#define FT_DECL
+#define FT(k)
+#define FT_DUMP
+#endif
 
 struct FwdParams {
     float *O;             // row r of head h at O + h*o_head_stride + r*o_row_stride (floats)
@@ -95,6 +108,28 @@ __device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsign
     unsigned long long r;
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
+}
+// exp2 of two fp32 values on the FMA/ALU pipes (the special-function unit is the bottleneck of
+// the softmax at head dim 64): x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3
+// minimax polynomial (relative error 2e-4, far below the bf16 rounding of P), 2^n by adding n to
+// the exponent field.  Inputs are clamped at -126 (2^-126 stands in for 0 on masked scores).
+__device__ __forceinline__ unsigned long long exp2_poly2(unsigned long long x2) {
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    x2 = pack2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const unsigned long long magic = pack2(12582912.0f, 12582912.0f);  // 1.5 * 2^23
+    const unsigned long long t2 = fadd2(x2, magic);                   // integer part lands in the low mantissa bits
+    const unsigned long long n2 = fadd2(t2, pack2(-12582912.0f, -12582912.0f));
+    const unsigned long long f2 = ffma2(n2, pack2(-1.0f, -1.0f), x2);
+    unsigned long long r2 = ffma2(f2, pack2(0.053027522f, 0.053027522f), pack2(0.24221395f, 0.24221395f));
+    r2 = ffma2(r2, f2, pack2(0.69357258f, 0.69357258f));
+    r2 = ffma2(r2, f2, pack2(0.99995905f, 0.99995905f));
+    float t0, t1, r0, r1;
+    unpack2(t2, t0, t1);
+    unpack2(r2, r0, r1);
+    r0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
+    r1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
+    return pack2(r0, r1);
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float r;
@@ -140,8 +175,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         for (int t = 0; t < QT; ++t) {
             mx::mbar_init(bar(BAR_S_FULL + t), 1);
-            mx::mbar_init(bar(BAR_S_FREE + t), BM);
-            mx::mbar_init(bar(BAR_P_FULL + t), BM);
+            mx::mbar_init(bar(BAR_S_FREE + t), BM / 32);  // one elected lane per warp arrives
+            mx::mbar_init(bar(BAR_P_FULL + t), BM / 32);
             mx::mbar_init(bar(BAR_O_DONE + t), 1);
         }
         *abort_flag = 0;
@@ -186,10 +221,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         __syncwarp();
         } else if (warp == 9) {
-        // ------------------------- MMA issuer ---------------------------
+        // ------------------------- MMA issuer 1: S_t = Q_t K^T ----------
+        // (issuing one tcgen05.mma costs the issuing thread ~65 cycles whatever its size, more
+        // than a 128x64x16 MMA takes to execute, so the two MMA streams get a thread each)
         if (lane == 0) {
             constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BM, BN, false, false);
-            constexpr uint32_t IDESC_O = mx::mma_idesc_bf16(BM, HD, false, true);
             bool ok = mx::mbar_wait(bar(BAR_Q_FULL), 0, abort_flag, P.status);
             auto issue_s = [&](int t, int stage) {
                 uint64_t a = mx::smem_desc_sw128(smem_base + SMEM_Q + t * TILE_BYTES);
@@ -206,29 +242,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     if (n_it[t] > 0) issue_s(t, 0);
                 mx::mma_commit(bar(BAR_K_EMPTY + 0));
             }
+            // next scores as soon as the softmax groups hold the current ones in registers
+            for (int j = 0; j + 1 < n_max && ok; ++j) {
+                const int s1 = (j + 1) % KV_STAGES, r1 = (j + 1) / KV_STAGES;
+                ok = mx::mbar_wait(bar(BAR_K_FULL + s1), r1 & 1, abort_flag, P.status);
+                for (int t = 0; t < QT && ok; ++t) {
+                    if (j + 1 >= n_it[t]) continue;
+                    ok = mx::mbar_wait(bar(BAR_S_FREE + t), j & 1, abort_flag, P.status);
+                    if (!ok) break;
+                    mx::tc_fence_after();
+                    issue_s(t, s1);
+                }
+                if (!ok) break;
+                mx::mma_commit(bar(BAR_K_EMPTY + s1));
+            }
+        }
+        __syncwarp();
+        } else if (warp == 10) {
+        // ------------------------- MMA issuer 2: O_t += P_t V -----------
+        if (lane == 0) {
+            constexpr uint32_t IDESC_O = mx::mma_idesc_bf16(BM, HD, false, true);
+            bool ok = true;
             for (int j = 0; j < n_max && ok; ++j) {
                 const int s = j % KV_STAGES, r = j / KV_STAGES;
-                const int s1 = (j + 1) % KV_STAGES, r1 = (j + 1) / KV_STAGES;
-                // next scores as soon as the softmax groups hold the current ones in registers
-                if (j + 1 < n_max) {
-                    ok = mx::mbar_wait(bar(BAR_K_FULL + s1), r1 & 1, abort_flag, P.status);
-                    for (int t = 0; t < QT && ok; ++t) {
-                        if (j + 1 >= n_it[t]) continue;
-                        ok = mx::mbar_wait(bar(BAR_S_FREE + t), j & 1, abort_flag, P.status);
-                        if (!ok) break;
-                        mx::tc_fence_after();
-                        issue_s(t, s1);
-                    }
-                    if (!ok) break;
-                    mx::mma_commit(bar(BAR_K_EMPTY + s1));
-                }
                 ok = mx::mbar_wait(bar(BAR_V_FULL + s), r & 1, abort_flag, P.status);
+                const uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_V + s * TILE_BYTES);
                 for (int t = 0; t < QT && ok; ++t) {
                     if (j >= n_it[t]) continue;
                     ok = mx::mbar_wait(bar(BAR_P_FULL + t), j & 1, abort_flag, P.status);
                     if (!ok) break;
                     mx::tc_fence_after();
-                    uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_V + s * TILE_BYTES);
 #pragma unroll
                     for (int k = 0; k < BN / 16; ++k)  // 16 keys: 8 packed columns of P, 2048 bytes of V
                         mx::mma_ts(tmem + TM_O + t * HD, tmem + TM_P + t * (BN / 2) + 8 * k, b + 128 * k,
@@ -252,12 +295,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t tm_p = tmem + lane_off + TM_P + t * (BN / 2);
         const uint32_t tm_o = tmem + lane_off + TM_O + t * HD;
         const float c = 0.125f * 1.4426950408889634f;  // scale * log2(e)
-        const unsigned long long c2 = pack2(c, c);
         const int n_t = n_it[t];
         float m = -CUDART_INF_F, l = 0.0f;
+#ifdef MX_SKEW
+        if (t == 1) { const long long s0 = clock64(); while (clock64() - s0 < MX_SKEW) {} }
+#endif
+        FT_DECL
         bool ok = true;
         for (int j = 0; j < n_t; ++j) {
+            FT(0);
             ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), j & 1, abort_flag, P.status));
+            FT(1);
             if (!ok) break;
             mx::tc_fence_after();
             // the whole score row into registers with one round trip, then S_t is free again
@@ -266,7 +314,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int cc = 0; cc < BN / 32; ++cc) mx::tmem_ld32(tm_s + cc * 32, *(uint32_t(*)[32])(v + cc * 32));
             mx::tmem_wait_ld();
             mx::tc_fence_before();
-            mx::mbar_arrive(bar(BAR_S_FREE + t));
+            __syncwarp();
+            if (lane == 0) mx::mbar_arrive(bar(BAR_S_FREE + t));
+            FT(2);
 
             const int key0 = j * BN;
             if ((key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM + P.q_off)) {
@@ -289,11 +339,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
             for (int u = 0; u < 4; ++u) mx_ = fmaxf(mx_, __uint_as_float(v[u * 32 + 31]));
             // raise the running max only when it pays (always on the first tile)
+            FT(3);
             const bool raise = (j == 0) || ((mx_ - m) * c > RESCALE_LOG2);
             const float m_new = raise ? mx_ : m;
             const float alpha = (raise && j > 0) ? mx::ex2((m - m_new) * c) : 1.0f;
             const float nmc = -m_new * c;
-            const unsigned long long nmc2 = pack2(nmc, nmc);
             if (j > 0) {
                 // P_t and O_t are stable once the previous P V has completed (issued a whole
                 // softmax ago, so this wait is normally already satisfied)
@@ -313,30 +363,33 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     }
                 }
             }
-            unsigned long long rsum[2] = {0ull, 0ull};  // two packed (2 x fp32) row-sum accumulators
+            // scalar fma / ex2 / add: measured on B200, the packed f32x2 forms issue slower than
+            // two scalar instructions, and cvt.rn.bf16x2 costs no more than an integer-pipe pack
+            FT(4);
+            float rs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int cc = 0; cc < BN / 32; ++cc) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float x0, x1;
-                    unpack2(ffma2(pack2(__uint_as_float(v[cc * 32 + i]), __uint_as_float(v[cc * 32 + i + 1])), c2,
-                                  nmc2), x0, x1);
-                    float p0 = mx::ex2(x0), p1 = mx::ex2(x1);
-                    rsum[(i >> 1) & 1] = fadd2(rsum[(i >> 1) & 1], pack2(p0, p1));
+                    const float p0 = mx::ex2(fmaf(__uint_as_float(v[cc * 32 + i]), c, nmc));
+                    const float p1 = mx::ex2(fmaf(__uint_as_float(v[cc * 32 + i + 1]), c, nmc));
+                    rs[i & 2] += p0;
+                    rs[(i & 2) + 1] += p1;
                     pk[i >> 1] = mx::pack_bf16(p0, p1);
                 }
                 mx::tmem_st16(tm_p + cc * 16, pk);
             }
-            float rs0, rs1, rs2, rs3;
-            unpack2(rsum[0], rs0, rs1);
-            unpack2(rsum[1], rs2, rs3);
-            l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
+            l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));
             m = m_new;
+            FT(5);
             mx::tmem_wait_st();
             mx::tc_fence_before();
-            mx::mbar_arrive(bar(BAR_P_FULL + t));
+            __syncwarp();
+            if (lane == 0) mx::mbar_arrive(bar(BAR_P_FULL + t));
+            FT(6);
         }
+        FT_DUMP
         // epilogue: O / l and the log-sum-exp
         if (ok && n_t > 0) {
             ok = __all_sync(0xFFFFFFFFu,
@@ -517,3 +570,11 @@ extern "C" int mx230_attn_flash_lse(mx230_handle *h, void *stream, const float *
                "attn_flash_lse: null L");
     return flash_fp32(h, stream, Q, K, V, O, L, batch_heads, n, causal, "attn_flash_lse");
 }
+
+#ifdef MX_TRACE
+extern "C" int mx230_debug_ftrace(long long *out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_ftrace, sizeof(long long) * 32);
+    return 0;
+}
+#endif
