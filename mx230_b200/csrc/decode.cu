@@ -56,27 +56,6 @@ __device__ __forceinline__ float warp_sum_f(float v) {
     return v;
 }
 
-// packed 2 x fp32 arithmetic: two lanes per issue slot
-__device__ __forceinline__ unsigned long long pack2f(float a, float b) {
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unpack2f(unsigned long long r, float &a, float &b) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
-}
-__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b,
-                                                    unsigned long long c) {
-    unsigned long long r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-__device__ __forceinline__ unsigned long long fmul2(unsigned long long a, unsigned long long b) {
-    unsigned long long r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
                  "r"(src_bytes)
@@ -118,10 +97,6 @@ __device__ __forceinline__ void split_range(int kbeg, int kend, int c, int n, in
     if (a > kend) a = kend;
     if (b < a) b = a;
 }
-
-// Byte offset of 16-byte piece `p` of key row `k` inside a ring stage: the XOR keeps
-// eight consecutive keys reading the same piece index on distinct banks.
-__device__ __forceinline__ int stage_off(int k, int p) { return k * 64 + ((p ^ ((k >> 1) & 3)) << 4); }
 
 // Final or partial write of one (sequence, kv head) group from merged values held
 // by the first threads of the CTA.
@@ -191,19 +166,17 @@ struct Q8Smem {
     static constexpr int TOTAL = ((Q_BYTES + 127) & ~127) + (Q8_WARPS * PER_WARP > MERGE ? Q8_WARPS * PER_WARP : MERGE);
 };
 
-// four signed bytes of `w` -> four fp32 values, on the ALU/FMA pipes: flip the sign bit to get
-// u = b + 128, plant u into the mantissa of 2^23, subtract 2^23 + 128 (exact)
-__device__ __forceinline__ void s8x4_to_f32(int w, unsigned long long &lo, unsigned long long &hi) {
-    unsigned x = (unsigned)w ^ 0x80808080u;
+// four signed bytes of `w` -> four fp32 values on the integer/FMA pipes (int->float converts
+// share the narrow special-function pipe): flip the sign bit to get u = b + 128, plant u into
+// the mantissa of 2^23, subtract 2^23 + 128 (exact).  Scalar fp32 throughout: measured on B200,
+// the packed f32x2 instructions issue slower than two scalar ones.
+__device__ __forceinline__ void s8x4_to_f32(int w, float (&f)[4]) {
+    const unsigned x = (unsigned)w ^ 0x80808080u;
     const unsigned magic = 0x4B000000u;
-    unsigned f0 = __byte_perm(x, magic, 0x7650), f1 = __byte_perm(x, magic, 0x7651);
-    unsigned f2 = __byte_perm(x, magic, 0x7652), f3 = __byte_perm(x, magic, 0x7653);
-    const unsigned long long bias = pack2f(-8388736.0f, -8388736.0f);  // -(2^23 + 128)
-    unsigned long long a, b;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "r"(f0), "r"(f1));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "r"(f2), "r"(f3));
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(lo) : "l"(a), "l"(bias));
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(hi) : "l"(b), "l"(bias));
+    f[0] = __uint_as_float(__byte_perm(x, magic, 0x7650)) - 8388736.0f;
+    f[1] = __uint_as_float(__byte_perm(x, magic, 0x7651)) - 8388736.0f;
+    f[2] = __uint_as_float(__byte_perm(x, magic, 0x7652)) - 8388736.0f;
+    f[3] = __uint_as_float(__byte_perm(x, magic, 0x7653)) - 8388736.0f;
 }
 
 template <int G, bool PAGED>
@@ -332,16 +305,15 @@ decode_q8_kernel(const DecodeParams P) {
         }
     };
 
-    float m_run[G], thr[G], l_thr[G], b_thr[G];
-    unsigned long long acc2[G][4];
+    float m_run[G], l_thr[G], b_thr[G];
+    float acc[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         m_run[g] = -CUDART_INF_F;
-        thr[g] = -CUDART_INF_F;   // raise the running max when a score exceeds this
         l_thr[g] = 0.0f;
         b_thr[g] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc2[g][j] = 0ull;
+        for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
     }
 
     if (n_tiles > 0) issue(0);
@@ -381,31 +353,28 @@ decode_q8_kernel(const DecodeParams P) {
 #pragma unroll
             for (int g = 0; g < G; ++g) sco[g] = hq[g] * fmaf(ksc, (float)dot[g], kbe * hq[G + g]);
         } else {
-            unsigned long long dot2[G];
+            float dotf[G][2];
 #pragma unroll
-            for (int g = 0; g < G; ++g) dot2[g] = 0ull;
+            for (int g = 0; g < G; ++g) dotf[g][0] = dotf[g][1] = 0.0f;
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
                 int4 kw = *(const int4 *)(st + koff + ((p ^ kswz) << 4));
                 const int w4[4] = {kw.x, kw.y, kw.z, kw.w};
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    unsigned long long c01, c23;
-                    s8x4_to_f32(w4[w], c01, c23);
+                    float cf[4];
+                    s8x4_to_f32(w4[w], cf);
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
-                        const ulonglong2 qv = *(const ulonglong2 *)(qf + g * 64 + p * 16 + w * 4);
-                        dot2[g] = ffma2(qv.x, c01, dot2[g]);
-                        dot2[g] = ffma2(qv.y, c23, dot2[g]);
+                        const float4 qv = *(const float4 *)(qf + g * 64 + p * 16 + w * 4);
+                        dotf[g][0] = fmaf(qv.x, cf[0], fmaf(qv.z, cf[2], dotf[g][0]));
+                        dotf[g][1] = fmaf(qv.y, cf[1], fmaf(qv.w, cf[3], dotf[g][1]));
                     }
                 }
             }
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float d0, d1;
-                unpack2f(dot2[g], d0, d1);
-                sco[g] = hq[g] * fmaf(ksc, d0 + d1, kbe * hq[G + g]);
-            }
+            for (int g = 0; g < G; ++g)
+                sco[g] = hq[g] * fmaf(ksc, dotf[g][0] + dotf[g][1], kbe * hq[G + g]);
         }
 
         // ---- lazy running max, probabilities, weights ----
@@ -415,16 +384,15 @@ decode_q8_kernel(const DecodeParams P) {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             const float sg = ok ? sco[g] : -CUDART_INF_F;
-            if (__any_sync(0xFFFFFFFFu, sg > thr[g])) {  // warp-uniform, rare after the first tiles
+            // raise the running max only when a score exceeds it by RAISE (warp-uniform, rare)
+            if (__any_sync(0xFFFFFFFFu, sg > m_run[g] + RAISE * LOG2E)) {
                 const float m_new = warp_max_f(fmaxf(sg, m_run[g]));
                 const float alpha = (m_run[g] == -CUDART_INF_F) ? 0.0f : mx::ex2(m_run[g] - m_new);
                 l_thr[g] *= alpha;
                 b_thr[g] *= alpha;
-                const unsigned long long a2 = pack2f(alpha, alpha);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc2[g][j] = fmul2(acc2[g][j], a2);
+                for (int j = 0; j < 8; ++j) acc[g][j] *= alpha;
                 m_run[g] = m_new;
-                thr[g] = m_new + RAISE * LOG2E;
             }
             const float p = mx::ex2(sg - m_run[g]);
             l_thr[g] += p;
@@ -437,12 +405,12 @@ decode_q8_kernel(const DecodeParams P) {
         __syncwarp();
 
         // ---- values: lane = (key lane kl, 8-byte slice dsl), 8 steps of 4 keys ----
-#pragma unroll 4
+#pragma unroll 2
         for (int step = 0; step < WT_KEYS / 4; ++step) {
             const int2 vw = *(const int2 *)(st + voff + step * 256);
-            unsigned long long v2[4];
-            s8x4_to_f32(vw.x, v2[0], v2[1]);
-            s8x4_to_f32(vw.y, v2[2], v2[3]);
+            float vlo[4], vhi[4];
+            s8x4_to_f32(vw.x, vlo);
+            s8x4_to_f32(vw.y, vhi);
             float wk[GP];
 #pragma unroll
             for (int g4 = 0; g4 < GP / 4; ++g4) {
@@ -451,9 +419,11 @@ decode_q8_kernel(const DecodeParams P) {
             }
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                const unsigned long long w2 = pack2f(wk[g], wk[g]);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc2[g][j] = ffma2(w2, v2[j], acc2[g][j]);
+                for (int j = 0; j < 4; ++j) {
+                    acc[g][j] = fmaf(wk[g], vlo[j], acc[g][j]);
+                    acc[g][4 + j] = fmaf(wk[g], vhi[j], acc[g][4 + j]);
+                }
             }
         }
         __syncwarp();  // the ring slot and the weight buffer are rewritten by the next iterations
@@ -461,19 +431,16 @@ decode_q8_kernel(const DecodeParams P) {
     cp_async_wait<0>();
 
     // ---- warp totals, then the CTA-level log-sum-exp merge of the Q8_WARPS warps ----
-    float accw[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         l_thr[g] = warp_sum_f(l_thr[g]);
         b_thr[g] = warp_sum_f(b_thr[g]);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) unpack2f(acc2[g][j], accw[g][2 * j], accw[g][2 * j + 1]);
-#pragma unroll
         for (int j = 0; j < 8; ++j) {  // key lanes differ in lane bits 3,4
-            float v = accw[g][j];
+            float v = acc[g][j];
             v += __shfl_xor_sync(0xFFFFFFFFu, v, 8);
             v += __shfl_xor_sync(0xFFFFFFFFu, v, 16);
-            accw[g][j] = v;
+            acc[g][j] = v;
         }
     }
     __syncthreads();  // every warp is done with its ring: reuse the memory for the merge
@@ -487,8 +454,8 @@ decode_q8_kernel(const DecodeParams P) {
             dst[2] = b_thr[g];
         }
         if (lane < 8) {
-            *(float4 *)(dst + 4 + lane * 8) = make_float4(accw[g][0], accw[g][1], accw[g][2], accw[g][3]);
-            *(float4 *)(dst + 8 + lane * 8) = make_float4(accw[g][4], accw[g][5], accw[g][6], accw[g][7]);
+            *(float4 *)(dst + 4 + lane * 8) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+            *(float4 *)(dst + 8 + lane * 8) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
         }
     }
     __syncthreads();

@@ -35,7 +35,9 @@ constexpr int BS = 64;           // rows of a streamed tile
 constexpr int STAGES = 6;
 constexpr int OWN_BYTES = BT * HD * 2;   // 16 KB
 constexpr int STR_BYTES = BS * HD * 2;   // 8 KB
-constexpr int BWD_THREADS = 384;         // warpgroups: compute slot 0, compute slot 1, {TMA, MMA, 2 idle}
+constexpr int BWD_THREADS = 384;
+// setmaxnreg moves registers only inside the CTA's launch-time allocation (168 per thread)
+static_assert(8 * 216 + 4 * 72 <= 12 * 168, "setmaxnreg budget exceeds the launch-time register allocation");         // warpgroups: compute slot 0, compute slot 1, {TMA, MMA, 2 idle}
 
 // shared memory map (after 1024-byte alignment)
 constexpr int SM_OWN_A = 0;                              // Q (dQ pass) / K (dK/dV pass)
@@ -63,15 +65,6 @@ constexpr int TM_ACC0 = 384, TM_ACC1 = 448;
 constexpr int TM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 
-#ifdef MX_TRACE
-__device__ long long g_trace[64];
-#define TR_DECL long long _t0 = clock64(), _t1; const bool _tr = (blockIdx.x == 0 && blockIdx.y == 1 && (tid & 127) == 0);
-#define TR(slot) do { _t1 = clock64(); if (_tr) g_trace[(MODE * 2 + u) * 8 + (slot)] += _t1 - _t0; _t0 = _t1; } while (0)
-#else
-#define TR_DECL
-#define TR(slot)
-#endif
-
 struct BwdParams {
     const float *L;      // [BH][N]
     const float *Delta;  // [BH][N]
@@ -81,31 +74,6 @@ struct BwdParams {
     int causal;
     int *status;
 };
-
-__device__ __forceinline__ unsigned long long pack2(float a, float b) {
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unpack2(unsigned long long r, float &a, float &b) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
-}
-__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b,
-                                                    unsigned long long c) {
-    unsigned long long r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-__device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsigned long long b) {
-    unsigned long long r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ unsigned long long fmul2(unsigned long long a, unsigned long long b) {
-    unsigned long long r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
 
 // MODE 0: dQ pass (own = Q, dO; stream = K, V).  MODE 1: dK/dV pass (own = K, V; stream = Q, dO).
 template <int MODE>
@@ -283,27 +251,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             nd0 = nd1 = rv ? -P.Delta[(size_t)bh * N + row] : 0.0f;
         }
         bool ok = true;
-#ifdef MX_SKEW
-        if (u == 1) { const long long s0 = clock64(); while (clock64() - s0 < MX_SKEW) {} }
-#endif
-        TR_DECL
         for (int y = u; y < n; y += 2) {
             const int q = y >> 1;
-            TR(0);
             const int s = y % STAGES, r = y / STAGES;
             ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_SDP_FULL + u), q & 1, abort_flag, P.status));
             if (MODE == 1 && ok)  // the stage's L / Delta slices were written with plain stores
                 ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status));
             if (!ok) break;
             mx::tc_fence_after();
-            TR(1);
             uint32_t xv[BS], yv[BS];
             mx::tmem_ld32(tm_slot + TM_X, *(uint32_t(*)[32])(xv));
             mx::tmem_ld32(tm_slot + TM_X + 32, *(uint32_t(*)[32])(xv + 32));
             mx::tmem_ld32(tm_slot + TM_Y, *(uint32_t(*)[32])(yv));
             mx::tmem_ld32(tm_slot + TM_Y + 32, *(uint32_t(*)[32])(yv + 32));
             mx::tmem_wait_ld();
-            TR(2);
             mx::tc_fence_before();
             __syncwarp();
             if (lane == 0) mx::mbar_arrive(bar(BAR_SDP_FREE + u));
@@ -328,33 +289,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                     const float2 l2 = *(const float2 *)(ld + i), d2 = *(const float2 *)(ld + BS + i);
                     nl0 = l2.x, nl1 = l2.y, nd0 = d2.x, nd1 = d2.y;
                 }
-#if defined(MX_EXP) && (MX_EXP & 1)
-                const float p0 = __uint_as_float(xv[i]), p1 = __uint_as_float(xv[i + 1]);
-                const float e0 = __uint_as_float(yv[i]) + nd0 + nl0 * c, e1 = __uint_as_float(yv[i + 1]) + nd1 + nl1;
-#else
                 const float p0 = mx::ex2(fmaf(__uint_as_float(xv[i]), c, nl0));
                 const float p1 = mx::ex2(fmaf(__uint_as_float(xv[i + 1]), c, nl1));
                 const float e0 = p0 * (__uint_as_float(yv[i]) + nd0);
                 const float e1 = p1 * (__uint_as_float(yv[i + 1]) + nd1);
-#endif
                 pe[i >> 1] = mx::pack_bf16(e0, e1);
                 if (MODE == 1) pp[i >> 1] = mx::pack_bf16(p0, p1);
             }
-            TR(3);
             if (q > 0) {  // the accumulate MMAs of this slot's previous iteration have consumed E, P
                 ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_DS_FREE + u), (q - 1) & 1, abort_flag, P.status));
                 if (!ok) break;
                 mx::tc_fence_after();
             }
-            TR(4);
             mx::tmem_st32(tm_slot + TM_E, *(uint32_t(*)[32])(pe));
             if (MODE == 1) mx::tmem_st32(tm_slot + TM_P, *(uint32_t(*)[32])(pp));
             mx::tmem_wait_st();
-            TR(5);
             mx::tc_fence_before();
             __syncwarp();
             if (lane == 0) mx::mbar_arrive(bar(BAR_DS_READY + u));
-            TR(6);
         }
         // ---- epilogue: accumulators -> global, dS's 1/sqrt(d) applied here ----
         if (ok) ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag, P.status));
@@ -559,15 +511,3 @@ extern "C" int mx230_attn_bwd_flash_bf16(mx230_handle *h, void *stream, const vo
                     "attn_bwd_flash_bf16");
 }
 
-#ifdef MX_TRACE
-extern "C" int mx230_debug_trace(long long *out, int reset) {
-    if (reset) {
-        long long z[64] = {0};
-        cudaMemcpyToSymbol(g_trace, z, sizeof(z));
-        return 0;
-    }
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 64);
-    return 0;
-}
-#endif

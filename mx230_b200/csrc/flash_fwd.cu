@@ -32,7 +32,11 @@ constexpr int BN = 128;        // keys per K/V tile
 constexpr int HD = 64;
 constexpr int KV_STAGES = 4;
 constexpr int TILE_BYTES = BN * HD * 2;  // 16 KB
-constexpr int FWD_THREADS = 384;        // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
+constexpr int FWD_THREADS = 384;        // 3 warpgroups: softmax 0, softmax 1, {TMA, 2 MMA issuers, idle}
+// setmaxnreg moves registers only inside the CTA's launch-time allocation (168 per thread for 384
+// threads): what the softmax warps gain must have been released by the third warpgroup, or the
+// increase would block for ever.
+static_assert(8 * 216 + 4 * 72 <= 12 * 168, "setmaxnreg budget exceeds the launch-time register allocation");
 
 constexpr int SMEM_Q = 0;
 constexpr int SMEM_K = SMEM_Q + QT * TILE_BYTES;
@@ -63,19 +67,6 @@ constexpr int TM_COLS = 512;
 // exponent; until then probabilities are taken against the stale max (they stay below
 // 2^RESCALE_LOG2, harmless in bf16/fp32) and O needs no rescale.
 constexpr float RESCALE_LOG2 = 8.0f;
-// of every 8 element pairs of a score row, this many take the polynomial exp2 (rest: ex2.approx)
-constexpr int POLY_OF_8 = 0;
-
-#ifdef MX_TRACE
-__device__ long long g_ftrace[32];
-#define FT_DECL long long _ft[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long _f0 = clock64();
-#define FT(k) do { long long _f1 = clock64(); _ft[k] += _f1 - _f0; _f0 = _f1; } while (0)
-#define FT_DUMP if (blockIdx.x == 0 && blockIdx.y == 3 && (tid & 127) == 0) { for (int _i = 0; _i < 8; ++_i) g_ftrace[t * 8 + _i] = _ft[_i]; g_ftrace[16 + t] = n_t; }
-#else
-#define FT_DECL
-#define FT(k)
-#define FT_DUMP
-#endif
 
 struct FwdParams {
     float *O;             // row r of head h at O + h*o_head_stride + r*o_row_stride (floats)
@@ -89,48 +80,6 @@ struct FwdParams {
     int *status;
 };
 
-__device__ __forceinline__ unsigned long long pack2(float a, float b) {
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unpack2(unsigned long long r, float &a, float &b) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
-}
-// (a.x*b.x + c.x, a.y*b.y + c.y) in one issue slot
-__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b,
-                                                    unsigned long long c) {
-    unsigned long long r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-__device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsigned long long b) {
-    unsigned long long r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-// exp2 of two fp32 values on the FMA/ALU pipes (the special-function unit is the bottleneck of
-// the softmax at head dim 64): x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3
-// minimax polynomial (relative error 2e-4, far below the bf16 rounding of P), 2^n by adding n to
-// the exponent field.  Inputs are clamped at -126 (2^-126 stands in for 0 on masked scores).
-__device__ __forceinline__ unsigned long long exp2_poly2(unsigned long long x2) {
-    float x0, x1;
-    unpack2(x2, x0, x1);
-    x2 = pack2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
-    const unsigned long long magic = pack2(12582912.0f, 12582912.0f);  // 1.5 * 2^23
-    const unsigned long long t2 = fadd2(x2, magic);                   // integer part lands in the low mantissa bits
-    const unsigned long long n2 = fadd2(t2, pack2(-12582912.0f, -12582912.0f));
-    const unsigned long long f2 = ffma2(n2, pack2(-1.0f, -1.0f), x2);
-    unsigned long long r2 = ffma2(f2, pack2(0.053027522f, 0.053027522f), pack2(0.24221395f, 0.24221395f));
-    r2 = ffma2(r2, f2, pack2(0.69357258f, 0.69357258f));
-    r2 = ffma2(r2, f2, pack2(0.99995905f, 0.99995905f));
-    float t0, t1, r0, r1;
-    unpack2(t2, t0, t1);
-    unpack2(r2, r0, r1);
-    r0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
-    r1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
-    return pack2(r0, r1);
-}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -297,15 +246,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float c = 0.125f * 1.4426950408889634f;  // scale * log2(e)
         const int n_t = n_it[t];
         float m = -CUDART_INF_F, l = 0.0f;
-#ifdef MX_SKEW
-        if (t == 1) { const long long s0 = clock64(); while (clock64() - s0 < MX_SKEW) {} }
-#endif
-        FT_DECL
         bool ok = true;
         for (int j = 0; j < n_t; ++j) {
-            FT(0);
             ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), j & 1, abort_flag, P.status));
-            FT(1);
             if (!ok) break;
             mx::tc_fence_after();
             // the whole score row into registers with one round trip, then S_t is free again
@@ -316,7 +259,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             mx::tc_fence_before();
             __syncwarp();
             if (lane == 0) mx::mbar_arrive(bar(BAR_S_FREE + t));
-            FT(2);
 
             const int key0 = j * BN;
             if ((key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM + P.q_off)) {
@@ -339,7 +281,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
             for (int u = 0; u < 4; ++u) mx_ = fmaxf(mx_, __uint_as_float(v[u * 32 + 31]));
             // raise the running max only when it pays (always on the first tile)
-            FT(3);
             const bool raise = (j == 0) || ((mx_ - m) * c > RESCALE_LOG2);
             const float m_new = raise ? mx_ : m;
             const float alpha = (raise && j > 0) ? mx::ex2((m - m_new) * c) : 1.0f;
@@ -365,7 +306,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             // scalar fma / ex2 / add: measured on B200, the packed f32x2 forms issue slower than
             // two scalar instructions, and cvt.rn.bf16x2 costs no more than an integer-pipe pack
-            FT(4);
             float rs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int cc = 0; cc < BN / 32; ++cc) {
@@ -382,14 +322,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));
             m = m_new;
-            FT(5);
             mx::tmem_wait_st();
             mx::tc_fence_before();
             __syncwarp();
             if (lane == 0) mx::mbar_arrive(bar(BAR_P_FULL + t));
-            FT(6);
         }
-        FT_DUMP
         // epilogue: O / l and the log-sum-exp
         if (ok && n_t > 0) {
             ok = __all_sync(0xFFFFFFFFu,
@@ -571,10 +508,3 @@ extern "C" int mx230_attn_flash_lse(mx230_handle *h, void *stream, const float *
     return flash_fp32(h, stream, Q, K, V, O, L, batch_heads, n, causal, "attn_flash_lse");
 }
 
-#ifdef MX_TRACE
-extern "C" int mx230_debug_ftrace(long long *out) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_ftrace, sizeof(long long) * 32);
-    return 0;
-}
-#endif
