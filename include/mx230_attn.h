@@ -258,6 +258,19 @@ int mx230_attn_decode_q8_batched(mx230_handle *h, void *stream, float *out, cons
                                  const int *tables, int block_size, int n_log, int qkv_stride,
                                  int out_stride);
 
+/* Decode over an int8 cache without a handle and without any allocation (no counterpart in
+ * the reference, whose kernels use no scratch memory at all).  For hosts that cannot call
+ * cudaMalloc when they need attention -- all free HBM already given to their KV pool, or only
+ * allowed to enqueue on a stream they were handed -- the split-KV scratch lives in a fixed
+ * 1 MiB + 4 KiB __device__ array inside the library image (resident per GPU until exit).
+ * Single sequence, contiguous cache, keys 0..=t_cur, reference score mode, current device.
+ * Shapes needing more than n_head * n_splits * 264 B <= 1 MiB are refused (MX230_ERR_WORKSPACE).
+ * The first call on a device resolves the array's address: make it before any stream capture.
+ * Calls share the array; calls that overlap on the GPU race on it. */
+int mx230_attn_decode_q8_noalloc(void *stream, float *out, const float *qkv, const int8_t *kq,
+                                 const int8_t *vq, const float *ks, const float *vs, const float *kb,
+                                 const float *vb, int t_cur, int n_head, int n_kv_head, int head_dim);
+
 /* Batched decode over per-sequence contiguous cache slabs (no counterpart in the
  * reference, which batches only through block tables): sequence s reads cache
  * rows [s*seq_rows, s*seq_rows + pos[s]].  fp32 cache when kq == NULL. */

@@ -977,3 +977,135 @@ extern "C" int mx230_merge_partials(mx230_handle *h, void *stream, float *out, c
               (merge_partials_kernel<<<(rows * 16 + 127) / 128, 128, 0, st>>>(out, m, l, acc, parts, rows)));
     return MX230_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Decode over an int8 cache for callers that must not allocate.
+//
+// Every other entry point works through a handle, and a handle's split-KV scratch (partial
+// (m, l, acc) triples and arrival counters) comes from cudaMalloc.  Some hosts cannot do that
+// at the point where they first need attention: an engine that has already handed every free
+// byte of HBM to its KV-block pool (cudaMalloc would fail), or a component that is only
+// allowed to enqueue work on a stream it was given and must not touch the allocator (cudaMalloc
+// can block on the whole device).  For them this one entry point takes no handle and keeps its
+// scratch in a fixed array inside the library image.
+//
+//  * The array is NOALLOC_SCRATCH_BYTES (1 MiB + 4 KiB) per GPU that loads the library and stays
+//    resident until the process exits.  A call needs n_head * n_splits * 264 bytes of it
+//    (n_splits <= 64) plus n_kv_head counters; a shape that does not fit is refused with
+//    MX230_ERR_WORKSPACE.  Single sequence, contiguous cache, reference score mode.
+//  * The first call on each device resolves the array's device address (the name of a __device__
+//    array is not a device pointer in host code) and reads the SM count; make that first call
+//    outside of any stream capture.
+//  * All calls on a device share the array.  It keeps what the previous call left there: the
+//    counters are cleared on the stream before every launch, the partials are always rewritten
+//    before they are read.  Two calls that overlap on the GPU (different streams) race on it.
+//  * It calls no cudaMalloc / cudaFree and nothing that allocates.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t NOALLOC_PARTIAL_BYTES = 1u << 20;
+constexpr size_t NOALLOC_COUNTER_BYTES = 4096;
+constexpr size_t NOALLOC_SCRATCH_BYTES = NOALLOC_PARTIAL_BYTES + NOALLOC_COUNTER_BYTES;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+struct NoallocDevice {
+    void *scratch;  // device address of g_noalloc_scratch on this device
+    int sm_count;
+};
+NoallocDevice g_noalloc_dev[NOALLOC_MAX_DEVICES];  // zero-initialised: scratch == nullptr means "not set up"
+
+template <int G>
+int noalloc_launch(cudaStream_t st, const DecodeParams &P, dim3 grid) {
+    const size_t sm = q8_smem_bytes<G>();
+    MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_kernel<G, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)sm));
+    decode_q8_kernel<G, false><<<grid, Q8_THREADS, sm, st>>>(P);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return mx230_fail(MX230_ERR_CUDA, "attn_decode_q8_noalloc: launch failed: %s", cudaGetErrorString(e));
+    return MX230_OK;
+}
+
+}  // namespace
+
+extern "C" int mx230_attn_decode_q8_noalloc(void *stream, float *out, const float *qkv, const int8_t *kq,
+                                            const int8_t *vq, const float *ks, const float *vs,
+                                            const float *kb, const float *vb, int t_cur, int n_head,
+                                            int n_kv_head, int head_dim) {
+    const char *who = "attn_decode_q8_noalloc";
+    MX_REQUIRE(out && qkv && kq && vq && ks && vs, MX230_ERR_INVALID_ARG, "%s: null argument", who);
+    MX_REQUIRE((kb == nullptr) == (vb == nullptr), MX230_ERR_INVALID_ARG,
+               "%s: kb and vb must both be given (affine) or both be null (absmax)", who);
+    MX_REQUIRE(head_dim == 64, MX230_ERR_UNSUPPORTED, "%s: head_dim %d unsupported (must be 64)", who, head_dim);
+    MX_REQUIRE(n_head > 0 && n_kv_head > 0 && n_head % n_kv_head == 0, MX230_ERR_UNSUPPORTED,
+               "%s: n_head %d must be a positive multiple of n_kv_head %d", who, n_head, n_kv_head);
+    MX_REQUIRE(t_cur >= 0, MX230_ERR_INVALID_ARG, "%s: negative position %d", who, t_cur);
+    MX_REQUIRE((((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)kq | (uintptr_t)vq) & 15) == 0,
+               MX230_ERR_INVALID_ARG, "%s: buffers must be 16-byte aligned", who);
+
+    int dev = -1;
+    MX_CHECK_CUDA(cudaGetDevice(&dev));
+    MX_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, MX230_ERR_UNSUPPORTED, "%s: device %d out of range", who, dev);
+    NoallocDevice &nd = g_noalloc_dev[dev];
+    if (nd.scratch == nullptr) {
+        // one-time set-up for this device, with this device current
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return mx230_fail(MX230_ERR_CUDA, "%s: cudaGetSymbolAddress failed: %s", who, cudaGetErrorString(e));
+        int sms = 0;
+        MX_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        int major = 0;
+        MX_CHECK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        MX_REQUIRE(major == 10, MX230_ERR_NO_DEVICE, "%s: device %d is not sm_100", who, dev);
+        nd.sm_count = sms;
+        nd.scratch = p;
+    }
+
+    DecodeParams P;
+    memset(&P, 0, sizeof(P));
+    P.out = out;
+    P.out_stride = n_head * 64;
+    P.qkv = qkv;
+    P.n_head = n_head;
+    P.n_kv_head = n_kv_head;
+    P.kq = kq, P.vq = vq, P.ks = ks, P.vs = vs, P.kb = kb, P.vb = vb;
+    P.pos_kind = 0;
+    P.pos = t_cur;
+    P.group = n_head / n_kv_head;
+    P.head_groups = (P.group + 7) / 8;
+    P.score_mode = MX230_Q8_SCORE_REF;
+    const int gy = n_kv_head * P.head_groups;
+    MX_REQUIRE((size_t)gy * sizeof(unsigned) <= NOALLOC_COUNTER_BYTES, MX230_ERR_WORKSPACE,
+               "%s: %d kv-head groups exceed the %zu built-in counters", who, gy,
+               NOALLOC_COUNTER_BYTES / sizeof(unsigned));
+
+    // same split rule as the handle path: fill the machine in one wave, >= 256 keys per split
+    const long long keys = (long long)t_cur + 1;
+    int n_splits = (int)((2LL * nd.sm_count) / gy);
+    const int max_by_len = (int)((keys + 255) / 256);
+    if (n_splits > max_by_len) n_splits = max_by_len;
+    if (n_splits > 64) n_splits = 64;
+    if (n_splits < 1) n_splits = 1;
+    const size_t rows = (size_t)n_head * n_splits;
+    const size_t need = rows * 66 * sizeof(float);
+    MX_REQUIRE(need <= NOALLOC_PARTIAL_BYTES, MX230_ERR_WORKSPACE,
+               "%s: n_head %d x %d key splits needs %zu B of scratch, the built-in array holds %zu B", who,
+               n_head, n_splits, need, NOALLOC_PARTIAL_BYTES);
+    P.ws_acc = (float *)nd.scratch;
+    P.ws_m = P.ws_acc + rows * 64;
+    P.ws_l = P.ws_m + rows;
+    P.counters = (unsigned *)((unsigned char *)nd.scratch + NOALLOC_PARTIAL_BYTES);
+
+    cudaStream_t st = (cudaStream_t)stream;
+    // the arrival counters must start at zero whatever an earlier call left behind
+    MX_CHECK_CUDA(cudaMemsetAsync(P.counters, 0, (size_t)gy * sizeof(unsigned), st));
+    dim3 grid(n_splits, gy, 1);
+    const int g = P.group > 8 ? 8 : P.group;
+    if (g == 1) return noalloc_launch<1>(st, P, grid);
+    if (g == 2) return noalloc_launch<2>(st, P, grid);
+    if (g <= 4) return noalloc_launch<4>(st, P, grid);
+    if (g <= 7) return noalloc_launch<7>(st, P, grid);
+    return noalloc_launch<8>(st, P, grid);
+}

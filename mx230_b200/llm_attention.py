@@ -325,3 +325,11 @@ def prefill_step(h: Handle, out, qkv, c: KvCache, pos0, n_tok, n_head, n_kv_head
     else:
         copy_kv_batch(h, c, qkv, pos0, n_tok, q_dim, kv_dim, qkv_stride, pg, stream)
     attn_prefill(h, out, qkv, c, pos0, n_tok, n_head, n_kv_head, qkv_stride, out_stride, pg, stream)
+
+
+def attn_decode_q8_noalloc(out, qkv, c: KvCache, t_cur: int, n_head, n_kv_head, head_dim, stream=None):
+    """Handle-free int8-cache decode of one sequence whose split-KV scratch is a fixed array inside
+    the library: for hosts that may not call cudaMalloc (all HBM already owned by their KV pool, or
+    only allowed to enqueue on a given stream).  Current device; see include/mx230_attn.h."""
+    check(lib().mx230_attn_decode_q8_noalloc(stream_ptr(stream), ptr(out), ptr(qkv), *c.q8_args(), t_cur,
+                                             n_head, n_kv_head, head_dim))
