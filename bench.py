@@ -339,14 +339,57 @@ def run_ours(args):
     h.close()
 
 
+def run_case(args):
+    """One kernel family on a fixed shape, a few launches and nothing else: the command that the
+    ncu captures under profiles/ wrap (`--case fwd|bwd|decode_c4|decode_long`)."""
+    import torch
+    from mx230_b200 import flash_attention as fa
+    from mx230_b200 import llm_attention as la
+    from mx230_b200.common import Handle
+    torch.cuda.set_device(0)
+    h = Handle(0, 1 << 30)
+    reps = max(1, args.steps)
+    if args.case in ("fwd", "bwd"):
+        q, k, v, do = (torch.randn(BH, N, D, device="cuda") for _ in range(4))
+        o = torch.empty_like(q)
+        l = torch.empty(BH, N, device="cuda")
+        delta = torch.empty_like(l)
+        dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+        for _ in range(reps):
+            fa.run_flash_lse(h, q, k, v, o, l, N, True)
+            if args.case == "bwd":
+                fa.run_preprocess(h, do, o, delta, N)
+                fa.run_bwd_flash(h, q, k, v, do, l, delta, dq, dk, dv, N, True)
+    else:
+        nh, nkv, ctx, n_seq = (14, 2, 2048, 64) if args.case == "decode_c4" else (32, 4, 32768, 8)
+        caches = []
+        for _ in range(3):
+            c = la.KvCache(n_seq * ctx, nkv, 64, True)
+            c.k.random_(-128, 128), c.v.random_(-128, 128), c.ks.uniform_(0.01, 0.03), c.vs.uniform_(0.01, 0.03)
+            caches.append(c)
+        qd = nh * 64
+        q = torch.randn(n_seq, qd, device="cuda")
+        out = torch.empty(n_seq, qd, device="cuda")
+        pos = torch.full((n_seq,), ctx - 1, dtype=torch.int32, device="cuda")
+        for i in range(reps):
+            la.attn_decode_slab(h, out, q, caches[i % 3], pos, n_seq, nh, nkv, 64, ctx, qd, qd)
+    h.check_status()
+    print(json.dumps({"case": args.case, "launches": h.launches}))
+    h.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "decode_c4", "decode_long"],
+                    help="profiling aid: run one kernel family a few times and exit")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
