@@ -152,14 +152,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+// The suspend-time hint lets the hardware park the polling thread until the phase completes (or the
+// hint runs out) instead of re-issuing the poll: a spinning single-lane issuer warp otherwise takes
+// issue slots from the compute warp that shares its scheduler.
+constexpr uint32_t TRY_WAIT_SUSPEND_HINT = 0x989680u;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(TRY_WAIT_SUSPEND_HINT)
         : "memory");
     return ok != 0;
 }

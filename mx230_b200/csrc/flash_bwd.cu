@@ -11,16 +11,20 @@
 // owned by key tiles, each output element written exactly once -- with all contractions on
 // tcgen05 tensor cores (bf16 operands, fp32 accumulators in tensor memory).  Both passes are
 // one kernel template: a CTA owns ONE 128-row tile (queries for dQ, keys for dK/dV) and
-// streams 64-row tiles of the other axis through a TMA ring:
+// streams 128-row tiles of the other axis through a TMA ring.  Per streamed tile:
 //
-//   X = A_own A_str^T, Y = B_own B_str^T      (S, dP   |  S^T, dP^T)      SS MMAs into TMEM
-//   P = exp2(X c - L), E = P o (Y - Delta)    one thread per owned row, registers
+//   X = A_own A_str^T, Y = B_own B_str^T      (S, dP   |  S^T, dP^T)   128 x 128, N = 128 MMAs
+//   P = exp2(X c - L), E = P o (Y - Delta)    one thread per owned row and column half
 //   acc0 += E A_str   (dQ += dS K | dK += dS^T Q),   acc1 += P B_str (dV += P^T dO)   TS MMAs
 //
-// Two streamed tiles are in flight at once ("slots" = even / odd iteration), each with its own
-// X, Y, E, P columns in tensor memory and its own compute warpgroup, so nothing aliases: the
-// MMA warp issues X, Y of iteration j+2 as soon as the warpgroup has pulled iteration j into
-// registers, and the accumulate MMAs of j when E, P are written.  The recomputed tiles go back
+// Every MMA stream (X, Y, acc0, acc1) has its own issuing thread: a thread issues an MMA about
+// every 60 cycles and stalls on each commit until its MMAs have drained, so one thread cannot
+// keep the tensor pipe busy with 32-cycle N = 64 MMAs.  The two compute warpgroups take the left
+// and right 64 columns of X, Y: X, Y of the next tile are issued as soon as both hold the current
+// ones in registers, and the accumulate MMAs of a tile run under the next tile's exponentials.
+// In the dQ pass the owned Q and dO tiles are read as A operands from tensor memory (written there
+// once by the compute threads), which leaves shared-memory bandwidth to the streamed operand; in
+// the dK/dV pass tensor memory is full and they stay in shared memory.  The recomputed tiles go back
 // to tensor memory as bf16 A operands; no operand is ever written to shared memory by a thread.
 // The 1/sqrt(d) factor of dS is applied to the fp32 accumulators in the epilogue (exact: 2^-3).
 #include <math_constants.h>
@@ -31,37 +35,41 @@ namespace {
 
 constexpr int HD = 64;
 constexpr int BT = 128;          // rows of the owned tile (queries in dQ, keys in dK/dV)
-constexpr int BS = 64;           // rows of a streamed tile
-constexpr int STAGES = 6;
+constexpr int BS = 128;          // rows of a streamed tile
+constexpr int HS = BS / 2;       // columns of X, Y per compute warpgroup
+constexpr int STAGES = 4;
 constexpr int OWN_BYTES = BT * HD * 2;   // 16 KB
-constexpr int STR_BYTES = BS * HD * 2;   // 8 KB
-constexpr int BWD_THREADS = 384;
-// setmaxnreg moves registers only inside the CTA's launch-time allocation (168 per thread)
-static_assert(8 * 216 + 4 * 72 <= 12 * 168, "setmaxnreg budget exceeds the launch-time register allocation");         // warpgroups: compute slot 0, compute slot 1, {TMA, MMA, 2 idle}
+constexpr int STR_BYTES = BS * HD * 2;   // 16 KB
+constexpr int BWD_THREADS = 512;
+// warpgroups: compute left, compute right, {TMA, X, acc0, Y}, {acc1, 3 idle}.
+// setmaxnreg moves registers only inside the CTA's launch-time allocation (128 per thread for 512 threads)
+constexpr int REGS_COMPUTE = 216, REGS_SERVICE = 40;
+static_assert(8 * REGS_COMPUTE + 8 * REGS_SERVICE <= 16 * 128, "setmaxnreg budget exceeds the launch-time register allocation");
 
 // shared memory map (after 1024-byte alignment)
-constexpr int SM_OWN_A = 0;                              // Q (dQ pass) / K (dK/dV pass)
-constexpr int SM_OWN_B = SM_OWN_A + OWN_BYTES;           // dO / V
-constexpr int SM_STR_A = SM_OWN_B + OWN_BYTES;           // STAGES x 8 KB: K / Q
-constexpr int SM_STR_B = SM_STR_A + STAGES * STR_BYTES;  // STAGES x 8 KB: V / dO
-constexpr int SM_LD = SM_STR_B + STAGES * STR_BYTES;     // STAGES x 2 x 64 floats: -L*log2e, -Delta (dK/dV)
+constexpr int SM_OWN_A = 0;                              // K (dK/dV pass)
+constexpr int SM_OWN_B = SM_OWN_A + OWN_BYTES;           // V (dK/dV pass)
+constexpr int SM_STR_A = SM_OWN_B + OWN_BYTES;           // STAGES x 16 KB: K / Q
+constexpr int SM_STR_B = SM_STR_A + STAGES * STR_BYTES;  // STAGES x 16 KB: V / dO
+constexpr int SM_LD = SM_STR_B + STAGES * STR_BYTES;     // STAGES x 2 x 128 floats: -L*log2e, -Delta (dK/dV)
 constexpr int SM_BAR = SM_LD + STAGES * 2 * BS * 4;
 constexpr int SM_TOTAL = SM_BAR + 256;
 constexpr int SM_ALLOC = SM_TOTAL + 1024;
 
 constexpr int BAR_OWN_FULL = 0;
 constexpr int BAR_STR_FULL = 1;                          // [STAGES]
-constexpr int BAR_STR_EMPTY = BAR_STR_FULL + STAGES;     // [STAGES]
-constexpr int BAR_SDP_FULL = BAR_STR_EMPTY + STAGES;     // [2] MMA -> compute: X, Y written
-constexpr int BAR_SDP_FREE = BAR_SDP_FULL + 2;           // [2] compute -> MMA: X, Y in registers
-constexpr int BAR_DS_READY = BAR_SDP_FREE + 2;           // [2] compute -> MMA: E, P written
-constexpr int BAR_DS_FREE = BAR_DS_READY + 2;            // [2] MMA -> compute: E, P consumed
-constexpr int BAR_ACC_DONE = BAR_DS_FREE + 2;
+constexpr int BAR_STR_EMPTY = BAR_STR_FULL + STAGES;     // [STAGES] accumulate MMAs of the stage's tile done
+constexpr int BAR_SDP_FULL = BAR_STR_EMPTY + STAGES;     // MMA -> compute: X, Y written
+constexpr int BAR_SDP_FREE = BAR_SDP_FULL + 1;           // compute -> MMA: X, Y in registers
+constexpr int BAR_DS_READY = BAR_SDP_FREE + 1;           // compute -> MMA: E, P written
+constexpr int BAR_ACC_DONE = BAR_DS_READY + 1;
 constexpr int N_BARS = BAR_ACC_DONE + 1;
 
-// tensor memory columns: slot u at u*192: X [0,64) Y [64,128) E [128,160) P [160,192)
-constexpr int TM_SLOT = 192, TM_X = 0, TM_Y = 64, TM_E = 128, TM_P = 160;
+// tensor memory columns
+constexpr int TM_X = 0, TM_Y = 128, TM_E = 256, TM_P = 320;   // E, P: bf16 pairs, 64 columns each
 constexpr int TM_ACC0 = 384, TM_ACC1 = 448;
+// dQ pass only (no second accumulator there): the owned Q and dO tiles as bf16 A operands, 32 columns each
+constexpr int TM_OWN_A = 448, TM_OWN_B = 480;
 constexpr int TM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -70,6 +78,8 @@ struct BwdParams {
     const float *Delta;  // [BH][N]
     float *out0;         // dQ (dQ pass) / dK (dK/dV pass)   [BH][N][64]
     float *out1;         // unused / dV
+    const uint4 *own_a;  // dQ pass: bf16 Q  [BH][N][64], read straight into tensor memory
+    const uint4 *own_b;  // dQ pass: bf16 dO [BH][N][64]
     int n;
     int causal;
     int *status;
@@ -104,18 +114,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
     const int n = it_end - it_beg;  // >= 1
 
     if (tid == 0) {
-        mx::mbar_init(bar(BAR_OWN_FULL), 1);
+        mx::mbar_init(bar(BAR_OWN_FULL), MODE == 0 ? 2 * BT / 32 : 1);  // dQ: every compute warp; dK/dV: TMA
         for (int s = 0; s < STAGES; ++s) {
             mx::mbar_init(bar(BAR_STR_FULL + s), MODE == 1 ? 33 : 1);
-            mx::mbar_init(bar(BAR_STR_EMPTY + s), 1);
+            mx::mbar_init(bar(BAR_STR_EMPTY + s), MODE == 1 ? 2 : 1);   // one commit per accumulate issuer
         }
-        for (int u = 0; u < 2; ++u) {
-            mx::mbar_init(bar(BAR_SDP_FULL + u), 1);
-            mx::mbar_init(bar(BAR_SDP_FREE + u), BT / 32);  // one elected lane per warp arrives
-            mx::mbar_init(bar(BAR_DS_READY + u), BT / 32);
-            mx::mbar_init(bar(BAR_DS_FREE + u), 1);
-        }
-        mx::mbar_init(bar(BAR_ACC_DONE), 1);
+        mx::mbar_init(bar(BAR_SDP_FULL), 2);              // the X and the Y issuer
+        mx::mbar_init(bar(BAR_SDP_FREE), 2 * BT / 32);    // one elected lane per compute warp arrives
+        mx::mbar_init(bar(BAR_DS_READY), 2 * BT / 32);
+        mx::mbar_init(bar(BAR_ACC_DONE), MODE == 1 ? 2 : 1);
         *abort_flag = 0;
         mx::mbar_fence_init();
     }
@@ -126,22 +133,35 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
     const uint32_t tmem = *tmem_slot;
 
     if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_SERVICE));
         if (warp == 8) {
             // ------------------------- producer -------------------------
             if (lane == 0) {
-                mx::tma_prefetch_desc(&tmOwnA);
-                mx::tma_prefetch_desc(&tmOwnB);
                 mx::tma_prefetch_desc(&tmStrA);
                 mx::tma_prefetch_desc(&tmStrB);
-                mx::mbar_expect_tx(bar(BAR_OWN_FULL), 2 * OWN_BYTES);
-                mx::tma_load_3d(smem_base + SM_OWN_A, &tmOwnA, bar(BAR_OWN_FULL), 0, own0, bh);
-                mx::tma_load_3d(smem_base + SM_OWN_B, &tmOwnB, bar(BAR_OWN_FULL), 0, own0, bh);
+                if (MODE == 1) {
+                    mx::tma_prefetch_desc(&tmOwnA);
+                    mx::tma_prefetch_desc(&tmOwnB);
+                    mx::mbar_expect_tx(bar(BAR_OWN_FULL), 2 * OWN_BYTES);
+                    mx::tma_load_3d(smem_base + SM_OWN_A, &tmOwnA, bar(BAR_OWN_FULL), 0, own0, bh);
+                    mx::tma_load_3d(smem_base + SM_OWN_B, &tmOwnB, bar(BAR_OWN_FULL), 0, own0, bh);
+                }
             }
             bool ok = true;
             for (int y = 0; y < n; ++y) {
                 const int s = y % STAGES, r = y / STAGES;
                 const int row0 = (it_beg + y) * BS;
+                // -L*log2(e) and -Delta of the streamed queries: fetched before the wait, stored after it
+                float lv[4], dv[4];
+                if (MODE == 1) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int q = row0 + u * 32 + lane;
+                        const bool v = q < N;
+                        lv[u] = v ? -P.L[(size_t)bh * N + q] * LOG2E : 0.0f;
+                        dv[u] = v ? -P.Delta[(size_t)bh * N + q] : 0.0f;
+                    }
+                }
                 if (r > 0)
                     ok = __all_sync(0xFFFFFFFFu,
                                     mx::mbar_wait(bar(BAR_STR_EMPTY + s), (r - 1) & 1, abort_flag, P.status));
@@ -152,84 +172,72 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                     mx::tma_load_3d(smem_base + SM_STR_B + s * STR_BYTES, &tmStrB, bar(BAR_STR_FULL + s), 0, row0, bh);
                 }
                 if (MODE == 1) {
-                    // -L*log2(e) and -Delta of the 64 streamed queries
                     float *ld = (float *)(smem + SM_LD + s * (2 * BS * 4));
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        int q = row0 + u * 32 + lane;
-                        bool v = q < N;
-                        ld[u * 32 + lane] = v ? -P.L[(size_t)bh * N + q] * LOG2E : 0.0f;
-                        ld[BS + u * 32 + lane] = v ? -P.Delta[(size_t)bh * N + q] : 0.0f;
+                    for (int u = 0; u < 4; ++u) {
+                        ld[u * 32 + lane] = lv[u];
+                        ld[BS + u * 32 + lane] = dv[u];
                     }
                     mx::mbar_arrive(bar(BAR_STR_FULL + s));
                 }
             }
             __syncwarp();
-        } else if (warp == 9) {
-            // ------------------------- MMA issuer 1: X, Y --------------------
-            // (issuing one tcgen05.mma costs the issuing thread ~65 cycles, twice what a
-            // 128x64x16 MMA takes to execute: the two MMA streams get a thread each)
+        } else if (warp == 9 || warp == 11) {
+            // ------------------------- MMA issuers 1, 2: X (warp 9) and Y (warp 11) ---------
+            // (the loops are kept free of run-time choices between instruction forms, which slow
+            // the issuing thread down)
             if (lane == 0) {
-                constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BT, BS, false, false);  // [128 x 64] = A B^T
-                const uint64_t own_a = mx::smem_desc_sw128(smem_base + SM_OWN_A);
-                const uint64_t own_b = mx::smem_desc_sw128(smem_base + SM_OWN_B);
-                auto issue_sdp = [&](int y) {
-                    const int s = y % STAGES, u = y & 1;
-                    const uint64_t sa = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
-                    const uint64_t sb = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
-#pragma unroll
-                    for (int k = 0; k < HD / 16; ++k)
-                        mx::mma_ss(tmem + u * TM_SLOT + TM_X, own_a + 2 * k, sa + 2 * k, IDESC_S, k > 0);
-#pragma unroll
-                    for (int k = 0; k < HD / 16; ++k)
-                        mx::mma_ss(tmem + u * TM_SLOT + TM_Y, own_b + 2 * k, sb + 2 * k, IDESC_S, k > 0);
-                    mx::mma_commit(bar(BAR_SDP_FULL + u));
-                };
+                const bool is_y = warp == 11;
+                constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BT, BS, false, false);  // [128 x 128] = A B^T
+                const uint64_t own = mx::smem_desc_sw128(smem_base + (is_y ? SM_OWN_B : SM_OWN_A));
+                const uint32_t own_t = tmem + (is_y ? TM_OWN_B : TM_OWN_A);
+                const uint32_t str_base = smem_base + (is_y ? SM_STR_B : SM_STR_A);
+                const uint32_t dst = tmem + (is_y ? TM_Y : TM_X);
                 bool ok = mx::mbar_wait(bar(BAR_OWN_FULL), 0, abort_flag, P.status);
-                for (int y = 0; y < 2 && y < n && ok; ++y) {
-                    ok = mx::mbar_wait(bar(BAR_STR_FULL + y), 0, abort_flag, P.status);
+                for (int y = 0; y < n && ok; ++y) {
+                    const int s = y % STAGES, r = y / STAGES;
+                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
+                    // as soon as both warpgroups hold the previous X, Y in registers
+                    if (ok && y > 0) ok = mx::mbar_wait(bar(BAR_SDP_FREE), (y - 1) & 1, abort_flag, P.status);
                     if (!ok) break;
                     mx::tc_fence_after();
-                    issue_sdp(y);
-                }
-                // X, Y two iterations ahead, as soon as the slot's registers hold the current ones
-                for (int y = 0; y + 2 < n && ok; ++y) {
-                    const int s2 = (y + 2) % STAGES, r2 = (y + 2) / STAGES;
-                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s2), r2 & 1, abort_flag, P.status);
-                    if (ok) ok = mx::mbar_wait(bar(BAR_SDP_FREE + (y & 1)), (y >> 1) & 1, abort_flag, P.status);
-                    if (!ok) break;
-                    mx::tc_fence_after();
-                    issue_sdp(y + 2);
+                    const uint64_t sd = mx::smem_desc_sw128(str_base + s * STR_BYTES);
+                    if (MODE == 0) {
+#pragma unroll
+                        for (int k = 0; k < HD / 16; ++k) mx::mma_ts(dst, own_t + 8 * k, sd + 2 * k, IDESC_S, k > 0);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < HD / 16; ++k) mx::mma_ss(dst, own + 2 * k, sd + 2 * k, IDESC_S, k > 0);
+                    }
+                    mx::mma_commit(bar(BAR_SDP_FULL));
                 }
             }
             __syncwarp();
-        } else if (warp == 10) {
-            // ------------------------- MMA issuer 2: accumulators ------------
+        } else if (warp == 10 || (MODE == 1 && warp == 12)) {
+            // ------------------------- MMA issuers 3, 4: accumulators ------------
+            // warp 10: acc0 += E A_str (dQ += dS K | dK += dS^T Q); warp 12 (dK/dV pass): acc1 += P B_str
+            // (dV += P^T dO).  One commit per tile and thread: it frees the stage for the producer and
+            // tells the compute warpgroups that E, P have been consumed.
             if (lane == 0) {
+                const bool second = warp == 12;
                 constexpr uint32_t IDESC_G = mx::mma_idesc_bf16(BT, HD, false, true);   // acc += (tmem A) B
+                const uint32_t acc = tmem + (second ? TM_ACC1 : TM_ACC0);
+                const uint32_t a = tmem + (second ? TM_P : TM_E);
+                const uint32_t str_base = smem_base + (second ? SM_STR_B : SM_STR_A);
                 bool ok = true;
                 for (int y = 0; y < n && ok; ++y) {
-                    const int s = y % STAGES, r = y / STAGES, u = y & 1;
-                    // the streamed tile (read here as the MN-major B operand) and E, P of this slot
+                    const int s = y % STAGES;
+                    const int r = y / STAGES;
+                    // the streamed tile (read here as the MN-major B operand) and E, P
                     ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
-                    if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY + u), (y >> 1) & 1, abort_flag, P.status);
+                    if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), y & 1, abort_flag, P.status);
                     if (!ok) break;
                     mx::tc_fence_after();
-                    const uint64_t sa = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
-                    const uint64_t sb = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
-                    if (MODE == 1) {
+                    const uint64_t sd = mx::smem_desc_sw128(str_base + s * STR_BYTES);
 #pragma unroll
-                        for (int k = 0; k < BS / 16; ++k)  // dV += P^T dO
-                            mx::mma_ts(tmem + TM_ACC1, tmem + u * TM_SLOT + TM_P + 8 * k, sb + 128 * k, IDESC_G,
-                                       (y > 0 || k > 0));
-                    }
-#pragma unroll
-                    for (int k = 0; k < BS / 16; ++k)      // dQ += dS K  |  dK += dS^T Q
-                        mx::mma_ts(tmem + TM_ACC0, tmem + u * TM_SLOT + TM_E + 8 * k, sa + 128 * k, IDESC_G,
-                                   (y > 0 || k > 0));
-                    mx::mma_commit(bar(BAR_DS_FREE + u));
-                    // X, Y of this iteration were complete before its E, P could be formed, so this
-                    // commit also covers every read of the stage
+                    for (int k = 0; k < BS / 16; ++k) mx::mma_ts(acc, a + 8 * k, sd + 128 * k, IDESC_G, (y > 0 || k > 0));
+                    // X, Y of this tile were complete before its E, P could be formed, so this commit
+                    // also covers every read of the stage
                     mx::mma_commit(bar(BAR_STR_EMPTY + s));
                     if (y == n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
                 }
@@ -238,53 +246,65 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
         }
     } else {
         // ------------------------- compute warpgroups -------------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-        const int u = warp >> 2;                        // slot of this warpgroup
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_COMPUTE));
+        const int h = warp >> 2;                        // column half of this warpgroup
         const int row = own0 + (tid & 127);             // owned row (query | key) of this thread
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tm_slot = tmem + lane_off + u * TM_SLOT;
+        const uint32_t tm_row = tmem + lane_off;
         const float c = 0.125f * LOG2E;
         const bool rv = row < N;
         float nl0 = 0.0f, nl1 = 0.0f, nd0 = 0.0f, nd1 = 0.0f;  // -L*log2e and -Delta (MODE 0: of this row)
         if (MODE == 0) {
             nl0 = nl1 = rv ? -P.L[(size_t)bh * N + row] * LOG2E : 0.0f;
             nd0 = nd1 = rv ? -P.Delta[(size_t)bh * N + row] : 0.0f;
+            // this thread's row of Q (left warpgroup) or dO (right) as a bf16 A operand: 32 packed columns
+            uint32_t w[32];
+            const uint4 *src = (h == 0 ? P.own_a : P.own_b) + ((size_t)bh * N + row) * (HD * 2 / 16);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint4 x = rv ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+                w[4 * i] = x.x, w[4 * i + 1] = x.y, w[4 * i + 2] = x.z, w[4 * i + 3] = x.w;
+            }
+            mx::tmem_st32(tm_row + (h == 0 ? TM_OWN_A : TM_OWN_B), w);
+            mx::tmem_wait_st();
+            mx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mx::mbar_arrive(bar(BAR_OWN_FULL));
         }
         bool ok = true;
-        for (int y = u; y < n; y += 2) {
-            const int q = y >> 1;
+        for (int y = 0; y < n; ++y) {
             const int s = y % STAGES, r = y / STAGES;
-            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_SDP_FULL + u), q & 1, abort_flag, P.status));
+            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_SDP_FULL), y & 1, abort_flag, P.status));
             if (MODE == 1 && ok)  // the stage's L / Delta slices were written with plain stores
                 ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status));
             if (!ok) break;
             mx::tc_fence_after();
-            uint32_t xv[BS], yv[BS];
-            mx::tmem_ld32(tm_slot + TM_X, *(uint32_t(*)[32])(xv));
-            mx::tmem_ld32(tm_slot + TM_X + 32, *(uint32_t(*)[32])(xv + 32));
-            mx::tmem_ld32(tm_slot + TM_Y, *(uint32_t(*)[32])(yv));
-            mx::tmem_ld32(tm_slot + TM_Y + 32, *(uint32_t(*)[32])(yv + 32));
+            uint32_t xv[HS], yv[HS];
+            mx::tmem_ld32(tm_row + TM_X + h * HS, *(uint32_t(*)[32])(xv));
+            mx::tmem_ld32(tm_row + TM_X + h * HS + 32, *(uint32_t(*)[32])(xv + 32));
+            mx::tmem_ld32(tm_row + TM_Y + h * HS, *(uint32_t(*)[32])(yv));
+            mx::tmem_ld32(tm_row + TM_Y + h * HS + 32, *(uint32_t(*)[32])(yv + 32));
             mx::tmem_wait_ld();
             mx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) mx::mbar_arrive(bar(BAR_SDP_FREE + u));
+            if (lane == 0) mx::mbar_arrive(bar(BAR_SDP_FREE));
 
-            const int str0 = (it_beg + y) * BS;
-            const bool need_mask = (str0 + BS > N) ||
-                                   (P.causal && (MODE == 0 ? (str0 + BS - 1 > own0) : (str0 < own0 + BT - 1)));
-            const float *ld = (const float *)(smem + SM_LD + s * (2 * BS * 4));
+            const int str0 = (it_beg + y) * BS + h * HS;    // first streamed row of this half
+            const bool need_mask = (str0 + HS > N) ||
+                                   (P.causal && (MODE == 0 ? (str0 + HS - 1 > own0) : (str0 < own0 + BT - 1)));
+            const float *ld = (const float *)(smem + SM_LD + s * (2 * BS * 4)) + h * HS;
             if (need_mask) {
                 // masked scores become -inf up front (p = 0, so E = 0): the main loop stays branch-free
 #pragma unroll
-                for (int i = 0; i < BS; ++i) {
+                for (int i = 0; i < HS; ++i) {
                     const int c0 = str0 + i;
                     const bool v0 = c0 < N && (!P.causal || (MODE == 0 ? c0 <= row : c0 >= row));
                     if (!v0) xv[i] = 0xFF800000u;
                 }
             }
-            uint32_t pe[BS / 2], pp[MODE == 1 ? BS / 2 : 1];
+            uint32_t pe[HS / 2], pp[MODE == 1 ? HS / 2 : 1];
 #pragma unroll
-            for (int i = 0; i < BS; i += 2) {
+            for (int i = 0; i < HS; i += 2) {
                 if (MODE == 1) {
                     const float2 l2 = *(const float2 *)(ld + i), d2 = *(const float2 *)(ld + BS + i);
                     nl0 = l2.x, nl1 = l2.y, nd0 = d2.x, nd1 = d2.y;
@@ -296,43 +316,43 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 pe[i >> 1] = mx::pack_bf16(e0, e1);
                 if (MODE == 1) pp[i >> 1] = mx::pack_bf16(p0, p1);
             }
-            if (q > 0) {  // the accumulate MMAs of this slot's previous iteration have consumed E, P
-                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_DS_FREE + u), (q - 1) & 1, abort_flag, P.status));
+            if (y > 0) {  // the accumulate MMAs of the previous tile have consumed E, P
+                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_EMPTY + (y - 1) % STAGES),
+                                                           ((y - 1) / STAGES) & 1, abort_flag, P.status));
                 if (!ok) break;
                 mx::tc_fence_after();
             }
-            mx::tmem_st32(tm_slot + TM_E, *(uint32_t(*)[32])(pe));
-            if (MODE == 1) mx::tmem_st32(tm_slot + TM_P, *(uint32_t(*)[32])(pp));
+            mx::tmem_st32(tm_row + TM_E + h * (HS / 2), *(uint32_t(*)[32])(pe));
+            if (MODE == 1) mx::tmem_st32(tm_row + TM_P + h * (HS / 2), *(uint32_t(*)[32])(pp));
             mx::tmem_wait_st();
             mx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) mx::mbar_arrive(bar(BAR_DS_READY + u));
+            if (lane == 0) mx::mbar_arrive(bar(BAR_DS_READY));
         }
         // ---- epilogue: accumulators -> global, dS's 1/sqrt(d) applied here ----
         if (ok) ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag, P.status));
         if (ok) {
             mx::tc_fence_after();
-            const uint32_t tm_row = tmem + lane_off;
             if (MODE == 0) {
-                // both warpgroups hold the same 128 rows: slot 0 stores dims 0..31, slot 1 dims 32..63
+                // both warpgroups hold the same 128 rows: the left one stores dims 0..31, the right one 32..63
                 uint32_t v[32];
-                mx::tmem_ld32(tm_row + TM_ACC0 + u * 32, v);
+                mx::tmem_ld32(tm_row + TM_ACC0 + h * 32, v);
                 mx::tmem_wait_ld();
                 if (rv) {
-                    float *dst = P.out0 + ((size_t)bh * N + row) * HD + u * 32;
+                    float *dst = P.out0 + ((size_t)bh * N + row) * HD + h * 32;
 #pragma unroll
                     for (int i = 0; i < 32; i += 4)
                         *(float4 *)(dst + i) = make_float4(__uint_as_float(v[i]) * 0.125f, __uint_as_float(v[i + 1]) * 0.125f,
                                                            __uint_as_float(v[i + 2]) * 0.125f, __uint_as_float(v[i + 3]) * 0.125f);
                 }
             } else {
-                // slot 0 stores dK (scaled), slot 1 stores dV
-                const float sc = u == 0 ? 0.125f : 1.0f;
-                float *dst = (u == 0 ? P.out0 : P.out1) + ((size_t)bh * N + row) * HD;
+                // the left warpgroup stores dK (scaled), the right one dV
+                const float sc = h == 0 ? 0.125f : 1.0f;
+                float *dst = (h == 0 ? P.out0 : P.out1) + ((size_t)bh * N + row) * HD;
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
                     uint32_t v[32];
-                    mx::tmem_ld32(tm_row + (u == 0 ? TM_ACC0 : TM_ACC1) + cc * 32, v);
+                    mx::tmem_ld32(tm_row + (h == 0 ? TM_ACC0 : TM_ACC1) + cc * 32, v);
                     mx::tmem_wait_ld();
                     if (rv) {
 #pragma unroll
@@ -378,8 +398,8 @@ int set_attrs() {
 }
 
 struct Maps {
-    CUtensorMap own128[4];  // Q, K, V, dO with 128-row boxes
-    CUtensorMap str64[4];   // Q, K, V, dO with 64-row boxes
+    CUtensorMap box128[4];  // Q, K, V, dO with 128-row boxes (owned and streamed tiles alike)
+    const void *ptr[4];     // the bf16 tensors themselves
 };
 
 int make_maps(mx230_handle *h, Maps &m, const void *Qb, const void *Kb, const void *Vb, const void *dOb,
@@ -388,29 +408,29 @@ int make_maps(mx230_handle *h, Maps &m, const void *Qb, const void *Kb, const vo
     uint64_t rs = HD * 2, os = (uint64_t)n * HD * 2;
     for (int i = 0; i < 4; ++i) {
         int rc;
-        if ((rc = mx230_make_tmap_bf16(h, &m.own128[i], p[i], n, batch_heads, rs, os, BT))) return rc;
-        if ((rc = mx230_make_tmap_bf16(h, &m.str64[i], p[i], n, batch_heads, rs, os, BS))) return rc;
+        m.ptr[i] = p[i];
+        if ((rc = mx230_make_tmap_bf16(h, &m.box128[i], p[i], n, batch_heads, rs, os, BT))) return rc;
     }
     return MX230_OK;
 }
 
 int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dQ,
               int batch_heads, int n, int causal) {
-    BwdParams P{L, Delta, dQ, nullptr, n, causal ? 1 : 0, h->status_dev};
+    BwdParams P{L, Delta, dQ, nullptr, (const uint4 *)m.ptr[0], (const uint4 *)m.ptr[3], n, causal ? 1 : 0, h->status_dev};
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_DQ,
-              (bwd_kernel<0><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.own128[0], m.own128[3], m.str64[1],
-                                                                  m.str64[2], P)));
+              (bwd_kernel<0><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[0], m.box128[3], m.box128[1],
+                                                                  m.box128[2], P)));
     return MX230_OK;
 }
 
 int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dK,
                float *dV, int batch_heads, int n, int causal) {
-    BwdParams P{L, Delta, dK, dV, n, causal ? 1 : 0, h->status_dev};
+    BwdParams P{L, Delta, dK, dV, nullptr, nullptr, n, causal ? 1 : 0, h->status_dev};
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_DKV,
-              (bwd_kernel<1><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.own128[1], m.own128[2], m.str64[0],
-                                                                  m.str64[3], P)));
+              (bwd_kernel<1><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
+                                                                  m.box128[3], P)));
     return MX230_OK;
 }
 
