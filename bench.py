@@ -378,16 +378,74 @@ def run_case(args):
     h.close()
 
 
+def run_splitkv(args):
+    """Long-context int8-KV decode (BASELINE.json configs[4]: 32q/4kv, ctx 131072, 8 sequences) with the
+    key axis split over the ranks: partial attention on this rank's keys, one all-gather of the
+    (m, l, acc) triples, log-sum-exp merge on every rank.  Strong scaling: the total context is fixed.
+    Run under torchrun for N > 1; prints one JSON line on rank 0."""
+    import torch
+    import torch.distributed as dist
+    from mx230_b200 import llm_attention as la
+    from mx230_b200.common import Handle
+    from mx230_b200.multi_gpu import SplitKvDecoder, SplitKvPlan
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    nh, nkv, ctx, n_seq = 32, 4, 131072, 8
+    h = Handle(local, 64 << 20)
+    plan = SplitKvPlan(ctx=ctx, world=world, n_seq=n_seq, n_head=nh)
+    t0, t1 = plan.key_range(rank)
+    span = t1 - t0
+    caches = []
+    for _ in range(2):  # two copies of this rank's share (604 MB / world each): larger than L2 together
+        c = la.KvCache(n_seq * span, nkv, 64, True)
+        c.k.random_(-128, 128), c.v.random_(-128, 128), c.ks.uniform_(0.01, 0.03), c.vs.uniform_(0.01, 0.03)
+        caches.append(c)
+    q = torch.randn(n_seq, nh * 64, device="cuda")
+    dec = SplitKvDecoder(h, plan, rank)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    steps, warm = max(1, args.steps), max(3, args.warmup)
+    for i in range(warm):
+        dec.step(q, caches[i % 2], nkv, span, nh * 64)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev[0].record()
+    for i in range(steps):
+        dec.step(q, caches[i % 2], nkv, span, nh * 64)
+    ev[1].record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([ev[0].elapsed_time(ev[1]) / steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    h.check_status()
+    total_bytes = n_seq * ctx * nkv * (128 + 16)
+    if rank == 0:
+        print(json.dumps({"case": "splitkv", "n_gpus": world, "ms_per_step": float(ms), "steps": steps,
+                          "kv_bytes_total": total_bytes, "aggregate_gbs": total_bytes / float(ms) / 1e6,
+                          "scaling": "strong", "exchange_bytes_per_rank": plan.bytes_per_rank(),
+                          "config": {"workload": "int8-KV GQA decode 32q/4kv ctx 131072 x 8 sequences, keys split over ranks"}}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    h.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "decode_c4", "decode_long"],
-                    help="profiling aid: run one kernel family a few times and exit")
+    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "decode_c4", "decode_long", "splitkv"],
+                    help="fwd|bwd|decode_*: profiling aid, runs one kernel family a few times and exits; "
+                         "splitkv: long-context decode with keys split over the ranks (torchrun for N > 1)")
     args = ap.parse_args()
-    if args.case:
+    if args.case == "splitkv":
+        run_splitkv(args)
+    elif args.case:
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -1,0 +1,115 @@
+"""Two GPUs, one process each, NCCL: split-KV decode (partial attention on each rank's key
+range, one all-gather, log-sum-exp merge) and (batch, head) sharding of the flash forward.
+Skipped on a box with fewer than two GPUs.  NVLS is switched off for these short-lived
+child processes; the kernels use no peer memory at all."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = dict(max_abs=2e-2, mean_rel=5e-3)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _problem(ctx, n_seq, nh, nkv):
+    qs = oracle.normal((n_seq, nh * 64), 170, 0)
+    q8 = oracle.Q8Cache(n_seq * ctx, nkv)
+    for s in range(n_seq):
+        kv = oracle.normal((ctx, 2 * nkv * 64), 171 + s, 0)
+        for t in range(ctx):
+            oracle.quantize_kv_row(q8, kv[t], s * ctx + t, 0)
+    return qs, q8
+
+
+def _worker(rank, world, port, ctx, n_seq, nh, nkv, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    from mx230_b200 import _lib, flash_attention as fa, llm_attention as la
+    from mx230_b200.common import Handle
+    from mx230_b200.multi_gpu import SplitKvDecoder, SplitKvPlan, shard_range
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        h = Handle(rank, 64 << 20)
+        dev = f"cuda:{rank}"
+        # ---- split-KV decode: this rank holds keys [t0, t1) of every sequence ----
+        qs, q8 = _problem(ctx, n_seq, nh, nkv)
+        plan = SplitKvPlan(ctx=ctx, world=world, n_seq=n_seq, n_head=nh)
+        t0, t1 = plan.key_range(rank)
+        span = max(1, t1 - t0)
+        c = la.KvCache(n_seq * span, nkv, 64, True, True, device=dev)
+        for s in range(n_seq):
+            sl, dl = slice(s * ctx + t0, s * ctx + t1), slice(s * span, s * span + (t1 - t0))
+            c.k[dl] = torch.from_numpy(q8.kq[sl]).to(dev)
+            c.v[dl] = torch.from_numpy(q8.vq[sl]).to(dev)
+            c.ks[dl] = torch.from_numpy(q8.ks[sl]).to(dev)
+            c.vs[dl] = torch.from_numpy(q8.vs[sl]).to(dev)
+            c.kb[dl] = torch.from_numpy(q8.kb[sl]).to(dev)
+            c.vb[dl] = torch.from_numpy(q8.vb[sl]).to(dev)
+        h.set_option(_lib.OPT_Q8_SCORE_MODE, _lib.Q8_SCORE_EXACT)
+        dec = SplitKvDecoder(h, plan, rank, device=dev)
+        q_dev = torch.from_numpy(qs).to(dev)
+        for _ in range(2):  # the second step reuses every buffer
+            out = dec.step(q_dev, c, nkv, span, nh * 64)
+        torch.cuda.synchronize()
+        h.check_status()
+        want = oracle.gqa_decode_batched(qs, [ctx - 1] * n_seq, nh, nkv, cache=q8, seq_rows=ctx, mode=0)
+        got = out.cpu().numpy().reshape(n_seq, nh * 64)
+        err_dec = float(np.abs(got - want).max())
+        rel_dec = float(np.abs(got - want).sum() / np.abs(want).sum())
+        # ---- (batch, head) sharding of the forward: no collective on the data path ----
+        bh, n = 6, 384
+        Q, K, V = (oracle.normal((bh, n, 64), 180 + i, 0) for i in range(3))
+        lo, hi = shard_range(bh, rank, world)
+        o = torch.zeros(hi - lo, n, 64, device=dev)
+        l = torch.zeros(hi - lo, n, device=dev)
+        fa.run_flash_lse(h, *(torch.from_numpy(x[lo:hi]).to(dev) for x in (Q, K, V)), o, l, n, True)
+        torch.cuda.synchronize()
+        h.check_status()
+        wo, _ = oracle.attn_fwd(Q[lo:hi], K[lo:hi], V[lo:hi], True)
+        err_fwd = float(np.abs(o.cpu().numpy() - wo).max())
+        # every rank ends with the same merged decode output
+        chk = torch.tensor([float(out.double().sum())], device=dev)
+        both = [torch.zeros_like(chk) for _ in range(world)]
+        dist.all_gather(both, chk)
+        ret[rank] = (err_dec, rel_dec, err_fwd, [float(b) for b in both], (lo, hi))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("ctx", [640, 130])
+def test_split_kv_decode_and_sharded_forward_two_gpus(ctx):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world, n_seq, nh, nkv = 2, 2, 8, 2
+    ctxm = mp.get_context("spawn")
+    ret = ctxm.Manager().dict()
+    port = _free_port()
+    procs = [ctxm.Process(target=_worker, args=(r, world, port, ctx, n_seq, nh, nkv, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+    assert sorted(ret.keys()) == [0, 1]
+    for r in range(world):
+        err_dec, rel_dec, err_fwd, sums, _ = ret[r]
+        assert err_dec < TOL["max_abs"] and rel_dec < TOL["mean_rel"], (r, err_dec, rel_dec)
+        assert err_fwd < TOL["max_abs"], (r, err_fwd)
+        assert abs(sums[0] - sums[1]) <= 1e-6 * max(1.0, abs(sums[0]))
+    assert ret[0][4] == (0, 3) and ret[1][4] == (3, 6)
