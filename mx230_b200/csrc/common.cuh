@@ -5,7 +5,7 @@
 // plain per-CTA loads only), tensor memory (tcgen05.alloc/ld/st) and the 5th-gen
 // tensor-core MMA (tcgen05.mma + tcgen05.commit).
 //
-// Every device-side wait is bounded: a waiter polls for at most WAIT_LIMIT_NS
+// Every device-side wait is bounded: a waiter polls for at most WAIT_LIMIT_CYCLES SM cycles
 // and then records an error in the handle's status word and abandons the tile,
 // so a protocol bug shows up as a status code, never as a hung GPU.
 #pragma once
@@ -132,11 +132,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
 
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
 
 // ---- mbarrier ----
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
