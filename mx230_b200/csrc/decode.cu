@@ -503,6 +503,348 @@ decode_q8_kernel(const DecodeParams P) {
 }
 
 // ---------------------------------------------------------------------------
+// int8 cache, reference score mode: the same warp-autonomous streaming, with the two
+// contractions of the GQA group on the warp-level tensor-core path
+//
+// With G query heads per K/V head a key costs 2*G*64 multiply-adds against 144 bytes: on the
+// CUDA cores that is more issue slots than the HBM stream leaves (8 heads: ~22 warp instructions
+// per key at best, ~6 available), so the group is treated as the M dimension of mma.sync tiles:
+//   scores:  S[16 x 8 keys] = Qc[16 x 64] Kc^T, int8 x int8 -> int32 (m16n8k32, two per 8 keys);
+//            rows >= G are zero padding.  The 64 dims are assigned to the MMA's k slots so that a
+//            thread's B fragments are 16 contiguous bytes of a key (one shared-memory load);
+//   weights: p = exp2(s - m) in the accumulator layout, which is the A-fragment layout of the
+//            next MMA (thread (g, j) holds head g, keys 2j, 2j+1 of each 8-key group);
+//   values:  O[16 x 64] += (p vs)[16 x 16 keys] Vc[16 x 64], f16 x f16 -> f32 (m16n8k16).  The int8
+//            codes become f16 exactly (byte permutes onto the mantissa of 1024, minus 1152); p vs
+//            goes in as a high and a low f16 part, so the product carries ~22 bits.
+// ---------------------------------------------------------------------------
+constexpr int MG = 8;                               // heads per CTA (rows 8..15 of the tiles are padding)
+// Probabilities are taken against a running max that may lag by up to RAISE_MMA (natural-log units);
+// kept small here because p * vs has to stay inside the f16 range (65504): p <= e^2, so any V scale
+// below ~8000 is safe.
+constexpr float RAISE_MMA = 2.0f;
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], int a0, int a2, int b0, int b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(0), "r"(a2), "r"(0), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16(float &c0, float &c1, float &z0, float &z1, uint32_t a0, uint32_t a2,
+                                        uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c0), "+f"(c1), "+f"(z0), "+f"(z1)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float2 unpack_f16(uint32_t v) {
+    float2 r;
+    asm("{.reg .f16 l, h; mov.b32 {l, h}, %2; cvt.f32.f16 %0, l; cvt.f32.f16 %1, h;}" : "=f"(r.x), "=f"(r.y) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+struct Q8MmaSmem {
+    static constexpr int Q_BYTES = MG * 64 * 4 + MG * 16 * 4 + 2 * MG * 4 + 64;
+    static constexpr int PER_WARP = WT_STAGES * WT_STAGE;
+    static constexpr int MERGE = Q8_WARPS * MG * 68 * 4;
+    static constexpr int TOTAL = ((Q_BYTES + 127) & ~127) + (Q8_WARPS * PER_WARP > MERGE ? Q8_WARPS * PER_WARP : MERGE);
+};
+
+template <bool PAGED>
+__global__ void __launch_bounds__(Q8_THREADS, 2)
+decode_q8_mma_kernel(const DecodeParams P) {
+    using SM = Q8MmaSmem;
+    constexpr float LOG2E = 1.4426950408889634f;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float *qf = (float *)smem_raw;                        // [8][64]
+    int *qq = (int *)(qf + MG * 64);                      // [8][16] int8 codes
+    float *hq = (float *)(qq + MG * 16);                  // [2][8]: score scale (log2 domain), sum of q codes
+    unsigned char *warp_base = smem_raw + ((SM::Q_BYTES + 127) & ~127);
+    __shared__ int is_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int s = blockIdx.z;
+    const int kvh = blockIdx.y / P.head_groups;
+    const int hg = blockIdx.y - kvh * P.head_groups;
+    const int head0 = kvh * P.group + hg * 8;
+    const int gc = min(MG, P.group - hg * 8);
+    const int n_splits = gridDim.x;
+    const int nkv = P.n_kv_head, kvd = nkv * 64;
+
+    int kbeg, kend, ka, kb_;
+    key_range(P, s, kbeg, kend);
+    split_range(kbeg, kend, blockIdx.x, n_splits, ka, kb_);
+    const int *table = PAGED ? P.tables + (P.pos_kind == 2 ? (size_t)s * P.n_log : 0) : nullptr;
+    const long long base = PAGED ? 0 : (long long)s * P.seq_rows;
+    const bool affine = P.kb != nullptr;
+    const float scale = 0.125f * LOG2E;  // scores are kept in the log2 domain
+
+    // ---- q: per-head int8 codes as the reference kernel forms them (padding heads: zeros) ----
+    const float *qrow = P.qkv + (size_t)s * P.qkv_stride + head0 * 64;
+    for (int i = tid; i < MG * 64; i += Q8_THREADS) qf[i] = (i / 64 < gc) ? qrow[i] : 0.0f;
+    __syncthreads();
+    {
+        const int g = warp;  // Q8_WARPS == MG
+        float a = qf[g * 64 + lane], b = qf[g * 64 + 32 + lane];
+        float qmax = warp_max_f(fmaxf(fabsf(a), fabsf(b)));
+        float qid = qmax > 0.0f ? __fdiv_rn(127.0f, qmax) : 0.0f;
+        int ca = max(-127, min(127, __float2int_rn(a * qid)));
+        int cb = max(-127, min(127, __float2int_rn(b * qid)));
+        int8_t *qb = (int8_t *)(qq + g * 16);
+        qb[lane] = (int8_t)ca;
+        qb[32 + lane] = (int8_t)cb;
+        float qsum = warp_sum_f((float)(ca + cb));  // exact: small integers
+        if (lane == 0) {
+            hq[g] = (qmax > 0.0f ? __fdiv_rn(qmax, 127.0f) : 0.0f) * scale;
+            hq[MG + g] = qsum;
+        }
+    }
+    __syncthreads();
+    static_assert(Q8_WARPS == MG, "one warp quantises one head");
+
+    // fragment coordinates: g = head row (and key / value-dim column of the B fragments), j = k group
+    const int g = lane >> 2, j = lane & 3;
+    const int4 qa = *(const int4 *)(qq + g * 16 + 4 * j);   // bytes 16j .. 16j+15 of head g
+    const float hq_g = hq[g], qsum_g = hq[MG + g];
+
+    // ---- this warp's key sub-range ----
+    const int n_keys = kb_ - ka;
+    int per_w = (n_keys + Q8_WARPS - 1) / Q8_WARPS;
+    per_w = (per_w + WT_KEYS - 1) & ~(WT_KEYS - 1);
+    const int wa = min(kb_, ka + warp * per_w), wb = min(kb_, wa + per_w);
+    const int n_tiles = (wb - wa + WT_KEYS - 1) / WT_KEYS;
+    unsigned char *ring = warp_base + warp * SM::PER_WARP;
+    const uint32_t ring_u32 = mx::smem_u32(ring);
+
+    // Stage layout: K codes [32 keys][64 B] plain; V codes as 16 lines of 128 B (two keys each) whose
+    // 16-byte pieces are XOR-swizzled with the line index, so that the 8-byte reads of four lines at
+    // once are bank-conflict free; then ks, kb, vs, vb slices of 32 floats.
+    // Lane l moves pieces l, l+32, l+64, l+96 of K and V: key = it*8 + l/4, piece = l%4.
+    const int pk = lane >> 2, pp = lane & 3;
+    const uint32_t dk0 = (uint32_t)(pk * 64 + pp * 16);
+    auto v_dst = [&](int key) {  // key: tile-local
+        return (uint32_t)(WT_KEYS * 64 + (key >> 1) * 128 + ((((key & 1) << 2) + pp) ^ (((key >> 1) & 3) << 1)) * 16);
+    };
+    const uint32_t ds0 = (uint32_t)(2 * WT_KEYS * 64 + lane * 4);
+    const int8_t *ksrc = nullptr, *vsrc = nullptr;
+    const float *s_ks = nullptr, *s_kb = nullptr, *s_vs = nullptr, *s_vb = nullptr;
+    if (!PAGED) {
+        size_t r0 = (size_t)(base + wa);
+        ksrc = P.kq + (r0 + pk) * kvd + kvh * 64 + pp * 16;
+        vsrc = P.vq + (r0 + pk) * kvd + kvh * 64 + pp * 16;
+        size_t sd = (r0 + lane) * nkv + kvh;
+        s_ks = P.ks + sd, s_vs = P.vs + sd;
+        s_kb = affine ? P.kb + sd : P.ks + sd;
+        s_vb = affine ? P.vb + sd : P.vs + sd;
+    }
+    const size_t it_stride = (size_t)8 * kvd, tile_stride = (size_t)WT_KEYS * kvd;
+
+    auto issue = [&](int tile) {
+        const uint32_t dst = ring_u32 + (tile % WT_STAGES) * WT_STAGE;
+        const int key0 = wa + tile * WT_KEYS;
+        if (!PAGED && key0 + WT_KEYS <= wb) {  // full tile of a linear cache: no predicates, no lookups
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                cp_async16(dst + dk0 + it * 512, ksrc + it * it_stride, 16);
+                cp_async16(dst + v_dst(it * 8 + pk), vsrc + it * it_stride, 16);
+            }
+            cp_async4(dst + ds0, s_ks);
+            cp_async4(dst + ds0 + 128, s_kb);
+            cp_async4(dst + ds0 + 256, s_vs);
+            cp_async4(dst + ds0 + 384, s_vb);
+        } else {
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                int t = key0 + it * 8 + pk;
+                bool ok = t < wb;
+                size_t row = cache_row(P, table, base, ok ? t : wa);
+                cp_async16(dst + dk0 + it * 512, P.kq + row * kvd + kvh * 64 + pp * 16, ok ? 16 : 0);
+                cp_async16(dst + v_dst(it * 8 + pk), P.vq + row * kvd + kvh * 64 + pp * 16, ok ? 16 : 0);
+            }
+            int t = key0 + lane;
+            size_t sd = cache_row(P, table, base, t < wb ? t : wa) * nkv + kvh;
+            cp_async4(dst + ds0, P.ks + sd);
+            cp_async4(dst + ds0 + 128, affine ? P.kb + sd : P.ks + sd);
+            cp_async4(dst + ds0 + 256, P.vs + sd);
+            cp_async4(dst + ds0 + 384, affine ? P.vb + sd : P.vs + sd);
+        }
+        if (!PAGED) {
+            ksrc += tile_stride, vsrc += tile_stride;
+            s_ks += WT_KEYS * nkv, s_kb += WT_KEYS * nkv, s_vs += WT_KEYS * nkv, s_vb += WT_KEYS * nkv;
+        }
+    };
+
+    float m_run = -CUDART_INF_F, l_thr = 0.0f, b_thr = 0.0f;
+    float oacc[8][2];
+    float z0 = 0.0f, z1 = 0.0f;   // rows 8..15 of the output tiles: stay zero
+#pragma unroll
+    for (int t = 0; t < 8; ++t) oacc[t][0] = oacc[t][1] = 0.0f;
+
+    if (n_tiles > 0) issue(0);
+    cp_async_commit();
+    const uint32_t MAGIC = 0x64646464u, BIAS = 0x64806480u;  // f16 1024 | byte, minus 1152
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        if (tile + 1 < n_tiles) issue(tile + 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const unsigned char *st = ring + (tile % WT_STAGES) * WT_STAGE;
+        const float *side = (const float *)(st + 2 * WT_KEYS * 64);
+        const int key_lim = wb - (wa + tile * WT_KEYS);  // valid keys in this tile
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            // ---- scores (log2 domain): two 8-key groups ----
+            float sc[2][2], vsw[2][2], vbw[2][2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int key8 = blk * 16 + r * 8;
+                const int4 kw = *(const int4 *)(st + (key8 + g) * 64 + 16 * j);
+                int c[4] = {0, 0, 0, 0};
+                mma_s8(c, qa.x, qa.y, kw.x, kw.y);
+                mma_s8(c, qa.z, qa.w, kw.z, kw.w);
+                const float2 ks2 = *(const float2 *)(side + key8 + 2 * j);
+                float2 kb2 = make_float2(0.0f, 0.0f), vb2 = make_float2(0.0f, 0.0f);
+                if (affine) {
+                    kb2 = *(const float2 *)(side + 32 + key8 + 2 * j);
+                    vb2 = *(const float2 *)(side + 96 + key8 + 2 * j);
+                }
+                const float2 vs2 = *(const float2 *)(side + 64 + key8 + 2 * j);
+                const float s0 = hq_g * fmaf(ks2.x, (float)c[0], kb2.x * qsum_g);
+                const float s1 = hq_g * fmaf(ks2.y, (float)c[1], kb2.y * qsum_g);
+                sc[r][0] = key8 + 2 * j < key_lim ? s0 : -CUDART_INF_F;
+                sc[r][1] = key8 + 2 * j + 1 < key_lim ? s1 : -CUDART_INF_F;
+                vsw[r][0] = vs2.x, vsw[r][1] = vs2.y, vbw[r][0] = vb2.x, vbw[r][1] = vb2.y;
+            }
+            // ---- lazy running max: raised only when a score exceeds it by RAISE (warp-uniform, rare) ----
+            const float smax = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+            if (__any_sync(0xFFFFFFFFu, smax > m_run + RAISE_MMA * LOG2E)) {
+                float hm = fmaxf(smax, __shfl_xor_sync(0xFFFFFFFFu, smax, 1));
+                hm = fmaxf(hm, __shfl_xor_sync(0xFFFFFFFFu, hm, 2));
+                const float m_new = fmaxf(hm, m_run);
+                const float alpha = (m_run == -CUDART_INF_F) ? 0.0f : mx::ex2(m_run - m_new);
+                l_thr *= alpha;
+                b_thr *= alpha;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) oacc[t][0] *= alpha, oacc[t][1] *= alpha;
+                m_run = m_new;
+            }
+            // ---- probabilities, weights (high + low f16 parts) ----
+            uint32_t ah[2], al[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const float p0 = mx::ex2(sc[r][0] - m_run), p1 = mx::ex2(sc[r][1] - m_run);
+                l_thr += p0 + p1;
+                b_thr = fmaf(p0, vbw[r][0], fmaf(p1, vbw[r][1], b_thr));
+                const float w0 = p0 * vsw[r][0], w1 = p1 * vsw[r][1];
+                ah[r] = pack_f16(w0, w1);
+                const float2 hf = unpack_f16(ah[r]);
+                al[r] = pack_f16(w0 - hf.x, w1 - hf.y);
+            }
+            // ---- values: keys 2j, 2j+1 (+8) of the block, dims 8g .. 8g+7 -> eight 16x8 tiles ----
+            uint32_t b[2][8];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int line = blk * 8 + j + 4 * r;
+                const unsigned char *lp = st + WT_KEYS * 64 + line * 128;
+                const int2 v0 = *(const int2 *)(lp + ((g) ^ (4 * j)) * 8);          // key 2j   (+8r)
+                const int2 v1 = *(const int2 *)(lp + ((8 + g) ^ (4 * j)) * 8);      // key 2j+1 (+8r)
+                const uint32_t x0 = (uint32_t)v0.x ^ 0x80808080u, x1 = (uint32_t)v1.x ^ 0x80808080u;
+                const uint32_t y0 = (uint32_t)v0.y ^ 0x80808080u, y1 = (uint32_t)v1.y ^ 0x80808080u;
+                const uint32_t zx01 = __byte_perm(x0, x1, 0x5140), zx23 = __byte_perm(x0, x1, 0x7362);
+                const uint32_t zy01 = __byte_perm(y0, y1, 0x5140), zy23 = __byte_perm(y0, y1, 0x7362);
+                b[r][0] = hsub2(__byte_perm(zx01, MAGIC, 0x4140), BIAS);
+                b[r][1] = hsub2(__byte_perm(zx01, MAGIC, 0x4342), BIAS);
+                b[r][2] = hsub2(__byte_perm(zx23, MAGIC, 0x4140), BIAS);
+                b[r][3] = hsub2(__byte_perm(zx23, MAGIC, 0x4342), BIAS);
+                b[r][4] = hsub2(__byte_perm(zy01, MAGIC, 0x4140), BIAS);
+                b[r][5] = hsub2(__byte_perm(zy01, MAGIC, 0x4342), BIAS);
+                b[r][6] = hsub2(__byte_perm(zy23, MAGIC, 0x4140), BIAS);
+                b[r][7] = hsub2(__byte_perm(zy23, MAGIC, 0x4342), BIAS);
+            }
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                mma_f16(oacc[t][0], oacc[t][1], z0, z1, ah[0], ah[1], b[0][t], b[1][t]);
+                mma_f16(oacc[t][0], oacc[t][1], z0, z1, al[0], al[1], b[0][t], b[1][t]);
+            }
+        }
+        __syncwarp();  // the ring slot is rewritten by the next iterations
+    }
+    cp_async_wait<0>();
+
+    // ---- head totals over the four threads of a row, then the CTA-level merge of the warps ----
+    l_thr += __shfl_xor_sync(0xFFFFFFFFu, l_thr, 1);
+    l_thr += __shfl_xor_sync(0xFFFFFFFFu, l_thr, 2);
+    b_thr += __shfl_xor_sync(0xFFFFFFFFu, b_thr, 1);
+    b_thr += __shfl_xor_sync(0xFFFFFFFFu, b_thr, 2);
+    __syncthreads();  // every warp is done with its ring: reuse the memory for the merge
+    float *mg = (float *)warp_base;  // [warp][g][68]: m (log2 domain), l, beta sum, pad, acc[64]
+    {
+        float *dst = mg + (warp * MG + g) * 68;
+        if (j == 0) {
+            dst[0] = m_run;
+            dst[1] = l_thr;
+            dst[2] = b_thr;
+        }
+        // tile t, columns 2j, 2j+1 <-> dims 16j + t, 16j + 8 + t
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            dst[4 + 16 * j + t] = oacc[t][0];
+            dst[4 + 16 * j + 8 + t] = oacc[t][1];
+        }
+    }
+    __syncthreads();
+
+    const bool direct = (n_splits == 1) && (P.fin_acc == nullptr);
+    for (int i = tid; i < gc * 64; i += Q8_THREADS) {
+        const int gg = i >> 6, d = i & 63;
+        float mm = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < Q8_WARPS; ++w) mm = fmaxf(mm, mg[(w * MG + gg) * 68]);
+        float lt = 0.0f, a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < Q8_WARPS; ++w) {
+            const float *src = mg + (w * MG + gg) * 68;
+            const float wgt = (src[0] == -CUDART_INF_F) ? 0.0f : mx::ex2(src[0] - mm);
+            lt += src[1] * wgt;
+            a += (src[4 + d] + src[2]) * wgt;  // V's affine offset sum_j p_j vb_j folds into every dim
+        }
+        const int h = head0 + gg;
+        if (direct) {
+            P.out[(size_t)s * P.out_stride + h * 64 + d] = a / lt;
+        } else {
+            // partial triples carry the max in natural-log units, as the split-KV interface states
+            size_t pi = ((size_t)s * P.n_head + h) * n_splits + blockIdx.x;
+            P.ws_acc[pi * 64 + d] = a;
+            if (d == 0) {
+                P.ws_m[pi] = mm * 0.6931471805599453f;
+                P.ws_l[pi] = lt;
+            }
+        }
+    }
+    if (direct) return;
+
+    // ---- last CTA of this (sequence, kv head group) merges the splits ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned prev = atomicInc(&P.counters[(size_t)s * gridDim.y + blockIdx.y], n_splits - 1);
+        is_last = (prev == (unsigned)(n_splits - 1));
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    merge_and_store<MG>(P, s, head0, gc, n_splits, Q8_THREADS);
+}
+
+// ---------------------------------------------------------------------------
 // fp32 cache (control path): direct 128-bit global loads, 4 lanes per key
 // ---------------------------------------------------------------------------
 template <int G>
@@ -708,7 +1050,19 @@ size_t f32_smem_bytes(int G) {
 
 template <int G>
 int launch_g(mx230_handle *h, cudaStream_t st, const DecodeParams &P, dim3 grid, bool q8) {
-    if (q8) {
+    if (q8 && P.score_mode == MX230_Q8_SCORE_REF) {
+        // reference score mode: the tensor-core kernel serves any group size up to 8 per CTA
+        size_t sm = (size_t)Q8MmaSmem::TOTAL;
+        if (P.tables) {
+            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_mma_kernel<true>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_mma_kernel<true><<<grid, Q8_THREADS, sm, st>>>(P)));
+        } else {
+            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_mma_kernel<false>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_mma_kernel<false><<<grid, Q8_THREADS, sm, st>>>(P)));
+        }
+    } else if (q8) {
         size_t sm = q8_smem_bytes<G>();
         if (P.tables) {
             MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_kernel<G, true>,
