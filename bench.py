@@ -156,12 +156,12 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------- GPU arm
-def decode_bench(h, torch, la, n_seq=64, nh=14, nkv=2, ctx=2048, iters=40):
+def decode_bench(h, torch, la, n_seq=64, nh=14, nkv=2, ctx=2048, iters=40, quants=(True, False)):
     """int8-KV GQA decode (and fp32 control): GB/s of algorithmic bytes, caches rotated so that
     consecutive launches never hit L2-resident data."""
     out = {}
     qd, kvd = nh * 64, nkv * 64
-    for quant in (True, False):
+    for quant in quants:
         per_seq = ctx * kvd * 2 * (1 if quant else 4) + (ctx * nkv * 16 if quant else 0) + qd * 8
         nbytes = n_seq * per_seq
         copies = max(2, int(4 * 126e6 / nbytes) + 1)
@@ -285,6 +285,9 @@ def run_ours(args):
         ms, e2e_ms = float(t[0]), float(t[1])
 
     dec = decode_bench(h, torch, la) if rank == 0 else None
+    if dec is not None:  # BASELINE.json configs[4]: 32q/4kv, ctx 131072, 8 sequences, int8 cache (604 MB per launch)
+        dec["int8_kv_long"] = decode_bench(h, torch, la, n_seq=8, nh=32, nkv=4, ctx=131072, iters=10,
+                                           quants=(True,))["int8_kv"]
     if rank == 0:
         peaks = measured_peaks()
         ms_step = ms / args.steps

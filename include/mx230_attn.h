@@ -56,7 +56,9 @@ enum {
 
 enum {
     MX230_OPT_Q8_SCORE_MODE = 1, /* MX230_Q8_SCORE_* (default REF) */
-    MX230_OPT_DECODE_CHUNK = 2   /* keys per decode CTA; 0 = automatic */
+    MX230_OPT_DECODE_CHUNK = 2,  /* keys per decode CTA; 0 = automatic */
+    MX230_OPT_DECODE_TENSOR = 3  /* int8 decode in the reference score mode: 1 (default) = the GQA group's two
+                                    contractions on warp-level tensor-core tiles, 0 = CUDA cores only */
 };
 
 /* kernel ids of the profiling interface */

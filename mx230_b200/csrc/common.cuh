@@ -36,6 +36,7 @@ struct mx230_handle {
     size_t n_counters;
     int q8_score_mode;     // MX230_Q8_SCORE_*
     int decode_chunk;      // keys per decode CTA (0 = automatic)
+    int decode_tensor;     // int8 decode, reference score mode: tensor-core tiles (1) or CUDA cores (0)
     long long launches;    // kernels launched through this handle
     mx230_encode_tiled_fn encode_tiled;
     // per-kernel timing: event pairs recorded around launches while enabled

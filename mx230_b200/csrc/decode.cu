@@ -1050,7 +1050,7 @@ size_t f32_smem_bytes(int G) {
 
 template <int G>
 int launch_g(mx230_handle *h, cudaStream_t st, const DecodeParams &P, dim3 grid, bool q8) {
-    if (q8 && P.score_mode == MX230_Q8_SCORE_REF) {
+    if (q8 && P.score_mode == MX230_Q8_SCORE_REF && h->decode_tensor) {
         // reference score mode: the tensor-core kernel serves any group size up to 8 per CTA
         size_t sm = (size_t)Q8MmaSmem::TOTAL;
         if (P.tables) {
@@ -1133,6 +1133,9 @@ int launch_decode(mx230_handle *h, void *stream, DecodeParams P, int n_seq, int 
         int max_by_len = (int)((keys + 255) / 256);
         n_splits = want < 1 ? 1 : want;
         if (n_splits > max_by_len) n_splits = max_by_len;
+        // a second split is not worth its merge pass when one CTA per (sequence, kv head) already
+        // covers most of the SMs and the contexts are short (measured: batch 64 x 2048 keys, 19.7 vs 22.3 us)
+        if (n_splits == 2 && base_ctas * 5 >= (long long)h->sm_count * 4 && keys <= 4096) n_splits = 1;
     }
     if (n_splits < 1) n_splits = 1;
     if (n_splits > 256) n_splits = 256;

@@ -67,6 +67,7 @@ extern "C" int mx230_create(mx230_handle **out, int device, size_t workspace_byt
     h->device = device;
     h->sm_count = prop.multiProcessorCount;
     h->q8_score_mode = MX230_Q8_SCORE_REF;
+    h->decode_tensor = 1;
     h->n_counters = N_COUNTERS;
 
     void *fn = nullptr;
@@ -143,6 +144,11 @@ extern "C" int mx230_set_option(mx230_handle *h, int option, int value) {
             MX_REQUIRE(value >= 0 && value <= 2048 && value % 128 == 0, MX230_ERR_INVALID_ARG,
                        "mx230_set_option: decode chunk must be 0 or a multiple of 128 up to 2048");
             h->decode_chunk = value;
+            return MX230_OK;
+        case MX230_OPT_DECODE_TENSOR:
+            MX_REQUIRE(value == 0 || value == 1, MX230_ERR_INVALID_ARG,
+                       "mx230_set_option: decode tensor switch must be 0 or 1");
+            h->decode_tensor = value;
             return MX230_OK;
         default:
             return mx230_fail(MX230_ERR_INVALID_ARG, "mx230_set_option: unknown option %d", option);

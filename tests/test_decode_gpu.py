@@ -95,6 +95,45 @@ def test_decode_q8_matches_both_oracles(handle, nh, nkv, ctx, affine):
     handle.check_status()
 
 
+@pytest.mark.parametrize("nh,nkv,ctx", [(14, 2, 300), (32, 4, 1000), (8, 8, 77)])
+def test_decode_q8_ref_mode_on_cuda_cores_equals_tensor_path(handle, nh, nkv, ctx):
+    """The reference score mode has two implementations (tensor-core tiles, default, and CUDA
+    cores): both meet the oracle's kernel-faithful mode at the same tolerance."""
+    rows, _, _, q8 = build_caches(nh, nkv, ctx, 33, True)
+    c = to_dev_q8(q8)
+    t_cur = ctx - 1
+    want = oracle.gqa_decode_q8(rows[t_cur], q8, t_cur, nh, 1)
+    try:
+        for tensor in (1, 0):
+            handle.set_option(_lib.OPT_DECODE_TENSOR, tensor)
+            out = torch.full((nh * 64,), float("nan"), device="cuda")
+            la.attn_decode(handle, out, dev(rows[t_cur]), c, t_cur, nh, nkv, 64)
+            assert_close(out.cpu().numpy(), want, f"decode q8 ref, tensor={tensor}", **TOL)
+    finally:
+        handle.set_option(_lib.OPT_DECODE_TENSOR, 1)
+    handle.check_status()
+
+
+def test_decode_q8_large_value_scales(handle):
+    """V rows a thousand times larger than usual: the weights p * vs of the tensor-core path stay
+    inside the f16 range (no inf / nan) and the result scales with the values."""
+    nh, nkv, ctx = 16, 2, 520
+    qd, kvd = nh * 64, nkv * 64
+    q = oracle.normal((qd,), 90, 0)
+    kv = oracle.normal((ctx, 2 * kvd), 91, 0)
+    kv[:, kvd:] *= 1000.0
+    q8 = oracle.Q8Cache(ctx, nkv)
+    for t in range(ctx):
+        oracle.quantize_kv_row(q8, kv[t], t, 0)
+    want = oracle.gqa_decode_q8(q, q8, ctx - 1, nh, 1)
+    out = torch.full((qd,), float("nan"), device="cuda")
+    la.attn_decode(handle, out, dev(q), to_dev_q8(q8), ctx - 1, nh, nkv, 64)
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert_close(got / 1000.0, want / 1000.0, "decode q8 large V", **TOL)
+    handle.check_status()
+
+
 @pytest.mark.parametrize("chunk", [0, 128, 256, 1024])
 def test_decode_key_splits_agree(handle, chunk):
     """Any split of the key axis gives the same answer as the oracle (merge by log-sum-exp)."""
