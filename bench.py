@@ -258,23 +258,55 @@ def run_ours(args):
     hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, do))
     ho, hl, hdq, hdk, hdv = (torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (o, lse, dq, dk, dv))
 
-    def e2e_step():
-        for dst, src in ((q, hq), (k, hk), (v, hv), (do, hdo)):
-            dst.copy_(src, non_blocking=True)
-        step()
-        for dst, src in ((ho, o), (hl, lse), (hdq, dq), (hdk, dk), (hdv, dv)):
-            dst.copy_(src, non_blocking=True)
+    # Software pipeline over three streams and two sets of device buffers: the host->device copy of
+    # step i+1 and the device->host copy of step i-1 run under the kernels of step i (PCIe is full
+    # duplex).  Every step still moves all of its inputs in and all of its results out inside the
+    # timed region.
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    dev_in = [(q, k, v, do), tuple(torch.empty_like(t) for t in (q, k, v, do))]
+    dev_out = [(o, lse, dq, dk, dv), tuple(torch.empty_like(t) for t in (o, lse, dq, dk, dv))]
+    delta2 = [delta, torch.empty_like(delta)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_c = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    e2e_steps = max(3, min(args.steps, 10))
-    e2e_step()
+    def e2e_run(n_steps):
+        for i in range(n_steps):
+            b = i & 1
+            qi, ki, vi, doi = dev_in[b]
+            oi, li, dqi, dki, dvi = dev_out[b]
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(ev_c[b])      # the kernels of step i-2 have read these inputs
+                for dst, src in ((qi, hq), (ki, hk), (vi, hv), (doi, hdo)):
+                    dst.copy_(src, non_blocking=True)
+                ev_in[b].record(s_in)
+            stream.wait_event(ev_in[b])
+            if i >= 2:
+                stream.wait_event(ev_out[b])      # the results of step i-2 have left these outputs
+            fa.run_flash_lse(h, qi, ki, vi, oi, li, N, True)
+            fa.run_preprocess(h, doi, oi, delta2[b], N)
+            fa.run_bwd_flash(h, qi, ki, vi, doi, li, delta2[b], dqi, dki, dvi, N, True)
+            ev_c[b].record(stream)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_c[b])
+                for dst, src in ((ho, oi), (hl, li), (hdq, dqi), (hdk, dki), (hdv, dvi)):
+                    dst.copy_(src, non_blocking=True)
+                ev_out[b].record(s_out)
+        stream.wait_event(ev_out[0])
+        stream.wait_event(ev_out[1])
+
+    e2e_steps = max(4, min(args.steps, 10))
+    e2e_run(2)
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
+    s_in.wait_event(f0)
+    e2e_run(e2e_steps)
     f1.record(stream)
     barrier()
     e2e_ms = f0.elapsed_time(f1)
+    h.check_status()
     clocks = sampler.stop() if rank == 0 else None
     h2d = sum(t.numel() * 4 for t in (hq, hk, hv, hdo))
     d2h = sum(t.numel() * 4 for t in (ho, hl, hdq, hdk, hdv))
@@ -332,7 +364,8 @@ def run_ours(args):
                                                kern["bwd_dkv_kernel"]["ms_per_launch"]) * 1e-3) / 1e12,
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / e2e_steps},
+                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
+                    "pipeline": "3 streams, 2 buffer sets: the copies of steps i+1 / i-1 overlap the kernels of step i"},
             "gpu_launches": launches, "clocks": clocks, "decode": dec,
         }
         print(json.dumps(line), flush=True)
