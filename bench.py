@@ -47,6 +47,10 @@ STEP_FLOP = FWD_FLOP + BWD_FLOP
 DQ_FLOP = BWD_FLOP * 2.0 / 5.0
 DKV_FLOP = BWD_FLOP * 3.0 / 5.0
 WORKLOAD = "causal flash-attention fwd+bwd, B=4 H=12 N=4096 d=64 (BASELINE.json configs[1])"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the three tensor kernels on this exact
+# workload, from the committed ncu capture (the operands, 4 x 25 MB bf16 + fp32 outputs, mostly stay in the 126 MB L2)
+NCU_DRAM_BYTES_PER_LAUNCH = {"flash_fwd_kernel": 80763392 + 16772864, "bwd_dq_kernel": 107303424 + 24600320,
+                             "bwd_dkv_kernel": 109310720 + 57106176}
 NOMINAL_BF16_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
 
@@ -339,7 +343,9 @@ def run_ours(args):
         dom = max((n for n in kern if "achieved_tflops" in kern[n]), key=lambda n: kern[n]["ms_per_launch"] * kern[n]["launches"])
         peak = peaks["bf16_tflops"]
         roofline = {"bound": "tensor", "kernel": dom, "achieved": kern[dom]["achieved_tflops"], "peak": peak,
-                    "unit": "TFLOP/s", "frac": kern[dom]["achieved_tflops"] / peak, "traffic": None,
+                    "unit": "TFLOP/s", "frac": kern[dom]["achieved_tflops"] / peak,
+                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(dom), "traffic_unit": "bytes per launch (dram read + write)",
+                    "traffic_source": "one ncu --set full capture of this workload: profiles/flash_fwd_bwd_c2_ncu_full.md",
                     "peak_source": f"{peaks['source']} dense bf16 burst (MEASURED_PEAKS.json)",
                     "frac_of_nominal": kern[dom]["achieved_tflops"] / NOMINAL_BF16_TFLOPS,
                     "per_kernel": kern}
