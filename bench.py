@@ -475,18 +475,71 @@ def run_splitkv(args):
     h.close()
 
 
+def run_configs(args):
+    """Every BASELINE.json configuration on one GPU, kernel time from the library's own event pairs
+    (median-free mean over `--steps` launches after warm-up): C1 and C3 forward through the fp32 entry
+    point (cast + kernel), C4 decode at batch 1 / 16 / 64 (int8 affine cache and fp32 control), C5 decode.
+    One JSON line per configuration."""
+    import torch
+    from mx230_b200 import flash_attention as fa
+    from mx230_b200 import llm_attention as la
+    from mx230_b200.common import Handle
+    torch.cuda.set_device(0)
+    h = Handle(0, 1 << 30)
+    peaks = measured_peaks()
+    reps = max(5, args.steps)
+
+    def fwd_config(name, bh, n, causal):
+        q, k, v = (torch.randn(bh, n, D, device="cuda") for _ in range(3))
+        o = torch.empty_like(q)
+        l = torch.empty(bh, n, device="cuda")
+        for _ in range(3):
+            fa.run_flash_lse(h, q, k, v, o, l, n, causal)
+        torch.cuda.synchronize()
+        h.profile_reset()
+        h.profile_enable(True)
+        for _ in range(reps):
+            fa.run_flash_lse(h, q, k, v, o, l, n, causal)
+        h.profile_enable(False)
+        prof = h.profile_read()
+        flop = (2 if causal else 4) * bh * n * n * D
+        kms = prof["flash_fwd_kernel"][1] / prof["flash_fwd_kernel"][0]
+        cms = prof["cast_bf16_kernel"][1] / prof["cast_bf16_kernel"][0]
+        print(json.dumps({"config": name, "shape": f"BH={bh} N={n} d=64 causal={causal}", "flop": flop,
+                          "kernel_ms": kms, "kernel_tflops": flop / kms / 1e9, "with_cast_tflops": flop / (kms + cms) / 1e9,
+                          "frac_of_measured_bf16": flop / kms / 1e9 / peaks["bf16_tflops"]}), flush=True)
+        del q, k, v, o
+
+    fwd_config("C1", 12, 1024, True)
+    fwd_config("C2-forward", 48, 4096, True)
+    fwd_config("C3", 8, 32768, False)
+    for b in (1, 16, 64):
+        d = decode_bench(h, torch, la, n_seq=b, iters=reps)
+        for kname, v in d.items():
+            v["frac_of_measured_hbm"] = v["gbs"] / peaks["hbm_gbs"]
+            print(json.dumps({"config": f"C4 batch {b} {kname}", **v}), flush=True)
+    d = decode_bench(h, torch, la, n_seq=8, nh=32, nkv=4, ctx=131072, iters=reps, quants=(True,))["int8_kv"]
+    d["frac_of_measured_hbm"] = d["gbs"] / peaks["hbm_gbs"]
+    print(json.dumps({"config": "C5 one GPU int8_kv", **d}), flush=True)
+    h.check_status()
+    h.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "decode_c4", "decode_long", "splitkv"],
+    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "decode_c4", "decode_long", "splitkv", "configs"],
                     help="fwd|bwd|decode_*: profiling aid, runs one kernel family a few times and exits; "
-                         "splitkv: long-context decode with keys split over the ranks (torchrun for N > 1)")
+                         "splitkv: long-context decode with keys split over the ranks (torchrun for N > 1); "
+                         "configs: every BASELINE.json configuration on one GPU")
     args = ap.parse_args()
     if args.case == "splitkv":
         run_splitkv(args)
+    elif args.case == "configs":
+        run_configs(args)
     elif args.case:
         run_case(args)
     elif args.impl == "reference":
