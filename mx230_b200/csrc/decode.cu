@@ -523,6 +523,10 @@ constexpr int MG = 8;                               // heads per CTA (rows 8..15
 // kept small here because p * vs has to stay inside the f16 range (65504): p <= e^2, so any V scale
 // below ~8000 is safe.
 constexpr float RAISE_MMA = 2.0f;
+#ifndef MX_MMA_STAGES
+#define MX_MMA_STAGES 2
+#endif
+constexpr int MMA_STAGES = MX_MMA_STAGES;             // ring depth per warp: MMA_STAGES - 1 tiles of 4.6 KB in flight
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], int a0, int a2, int b0, int b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -553,7 +557,7 @@ __device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
 
 struct Q8MmaSmem {
     static constexpr int Q_BYTES = MG * 64 * 4 + MG * 16 * 4 + 2 * MG * 4 + 64;
-    static constexpr int PER_WARP = WT_STAGES * WT_STAGE;
+    static constexpr int PER_WARP = MMA_STAGES * WT_STAGE;
     static constexpr int MERGE = Q8_WARPS * MG * 68 * 4;
     static constexpr int TOTAL = ((Q_BYTES + 127) & ~127) + (Q8_WARPS * PER_WARP > MERGE ? Q8_WARPS * PER_WARP : MERGE);
 };
@@ -648,7 +652,7 @@ decode_q8_mma_kernel(const DecodeParams P) {
     const size_t it_stride = (size_t)8 * kvd, tile_stride = (size_t)WT_KEYS * kvd;
 
     auto issue = [&](int tile) {
-        const uint32_t dst = ring_u32 + (tile % WT_STAGES) * WT_STAGE;
+        const uint32_t dst = ring_u32 + (tile % MMA_STAGES) * WT_STAGE;
         const int key0 = wa + tile * WT_KEYS;
         if (!PAGED && key0 + WT_KEYS <= wb) {  // full tile of a linear cache: no predicates, no lookups
 #pragma unroll
@@ -688,15 +692,18 @@ decode_q8_mma_kernel(const DecodeParams P) {
 #pragma unroll
     for (int t = 0; t < 8; ++t) oacc[t][0] = oacc[t][1] = 0.0f;
 
-    if (n_tiles > 0) issue(0);
-    cp_async_commit();
+#pragma unroll
+    for (int t = 0; t < MMA_STAGES - 1; ++t) {
+        if (t < n_tiles) issue(t);
+        cp_async_commit();
+    }
     const uint32_t MAGIC = 0x64646464u, BIAS = 0x64806480u;  // f16 1024 | byte, minus 1152
     for (int tile = 0; tile < n_tiles; ++tile) {
-        if (tile + 1 < n_tiles) issue(tile + 1);
+        if (tile + MMA_STAGES - 1 < n_tiles) issue(tile + MMA_STAGES - 1);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<MMA_STAGES - 1>();
         __syncwarp();
-        const unsigned char *st = ring + (tile % WT_STAGES) * WT_STAGE;
+        const unsigned char *st = ring + (tile % MMA_STAGES) * WT_STAGE;
         const float *side = (const float *)(st + 2 * WT_KEYS * 64);
         const int key_lim = wb - (wa + tile * WT_KEYS);  // valid keys in this tile
 #pragma unroll
