@@ -6,13 +6,14 @@
 // (scores+max, exp+sum, PV), whole score row in shared s[2048].
 //
 // This design: one CTA per (key split, kv head, sequence) serves ALL query heads of
-// the kv head's group, so every cache byte leaves HBM once.  The key range is
-// walked in chunks; per chunk the same three phases run, K and V tiles stream
-// through a cp.async shared-memory ring (memory parallelism independent of
-// register pressure), and chunks are chained by an online-softmax rescale, so the
-// context length is unbounded.  Split CTAs leave (m, l, acc) partials in the
-// workspace; the last CTA to arrive for a (sequence, kv head) merges them by
-// log-sum-exp.  HBM-bound: no tensor cores, int8 codes dequantised in registers.
+// the kv head's group, so every cache byte leaves HBM once.  Inside the CTA every warp
+// streams its own key sub-range through a private cp.async shared-memory ring (memory
+// parallelism independent of register pressure, no block barrier in the loop) and keeps
+// a private online-softmax state, so the context length is unbounded; the warps are merged
+// by log-sum-exp at the end.  Split CTAs leave (m, l, acc) partials in the workspace; the
+// last CTA to arrive for a (sequence, kv head) merges them.  Three kernels share this
+// skeleton: fp32 cache on CUDA cores; int8 cache on CUDA cores (exact score mode); int8
+// cache with the GQA group on warp-level tensor-core tiles (reference score mode).
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -20,7 +21,6 @@
 namespace {
 
 constexpr int DEC_THREADS = 128;
-constexpr int CHUNK_KEYS = 512;
 
 struct DecodeParams {
     float *out;               // [n_seq][out_stride]; head h at h*64 (null in partial mode)
@@ -852,16 +852,42 @@ decode_q8_mma_kernel(const DecodeParams P) {
 }
 
 // ---------------------------------------------------------------------------
-// fp32 cache (control path): direct 128-bit global loads, 4 lanes per key
+// fp32 cache: warp-autonomous streaming on CUDA cores (a key is 512 B per kv head here, so the
+// 2*G*64 multiply-adds per key fit the FMA pipes under the HBM stream)
+//
+// A CTA of F32_WARPS warps owns one (key split, kv head, sequence); each warp streams its own key
+// sub-range in tiles of 16 keys (K and V rows, 8 KB) through a private two-stage cp.async ring.
+//   scores:  lane = (key, half of the 64 dims); the halves are added with one shuffle per head;
+//            running max per head raised lazily, as in the int8 kernel;
+//   values:  lane = (key lane of 4, 8-dim slice), weights through a per-warp shared buffer.
+// K rows are XOR-swizzled by key, V rows fold their upper half, so both read patterns are
+// bank-conflict free.  Three CTAs are resident per SM.
 // ---------------------------------------------------------------------------
+constexpr int F32_WARPS = 4;
+constexpr int F32_THREADS = F32_WARPS * 32;
+constexpr int FT_KEYS = 16;                          // keys per warp tile
+constexpr int FT_STAGE = 2 * FT_KEYS * 256;          // K + V rows = 8192 B
+constexpr int FT_STAGES = 2;
+
 template <int G>
-__global__ void __launch_bounds__(DEC_THREADS)
-decode_f32_kernel(const DecodeParams P) {
+struct F32Smem {
+    static constexpr int GP = (G + 3) & ~3;
+    static constexpr int Q_BYTES = G * 64 * 4;
+    static constexpr int WBUF = FT_KEYS * GP * 4;
+    static constexpr int PER_WARP = FT_STAGES * FT_STAGE + WBUF;
+    static constexpr int MERGE = F32_WARPS * G * 68 * 4;
+    static constexpr int TOTAL = ((Q_BYTES + 127) & ~127) + (F32_WARPS * PER_WARP > MERGE ? F32_WARPS * PER_WARP : MERGE);
+};
+
+template <int G, bool PAGED>
+__global__ void __launch_bounds__(F32_THREADS, 3)
+decode_f32_ring_kernel(const DecodeParams P) {
+    using SM = F32Smem<G>;
+    constexpr int GP = SM::GP;
+    constexpr float LOG2E = 1.4426950408889634f;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    float *sc = (float *)smem_raw;          // [CHUNK_KEYS][G]
-    float *qf = sc + CHUNK_KEYS * G;        // [G][64]
-    float *red = qf + G * 64;               // [4][G]
-    float *hv = red + 4 * G;                // [G] chunk max
+    float *qf = (float *)smem_raw;                        // [G][64]
+    unsigned char *warp_base = smem_raw + ((SM::Q_BYTES + 127) & ~127);
     __shared__ int is_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -876,144 +902,213 @@ decode_f32_kernel(const DecodeParams P) {
     int kbeg, kend, ka, kb_;
     key_range(P, s, kbeg, kend);
     split_range(kbeg, kend, blockIdx.x, n_splits, ka, kb_);
-    const int *table = P.tables ? P.tables + (P.pos_kind == 2 ? (size_t)s * P.n_log : 0) : nullptr;
-    const long long base = P.tables ? 0 : (long long)s * P.seq_rows;
-    const float scale = 0.125f;
+    const int *table = PAGED ? P.tables + (P.pos_kind == 2 ? (size_t)s * P.n_log : 0) : nullptr;
+    const long long base = PAGED ? 0 : (long long)s * P.seq_rows;
+    const float scale = 0.125f * LOG2E;  // scores are kept in the log2 domain
 
     const float *qrow = P.qkv + (size_t)s * P.qkv_stride + head0 * 64;
-    for (int i = tid; i < G * 64; i += DEC_THREADS) qf[i] = (i / 64 < gc) ? qrow[i] : 0.0f;
+    for (int i = tid; i < G * 64; i += F32_THREADS) qf[i] = (i / 64 < gc) ? qrow[i] : 0.0f;
     __syncthreads();
 
+    // ---- this warp's key sub-range ----
+    const int n_keys = kb_ - ka;
+    int per_w = (n_keys + F32_WARPS - 1) / F32_WARPS;
+    per_w = (per_w + FT_KEYS - 1) & ~(FT_KEYS - 1);
+    const int wa = min(kb_, ka + warp * per_w), wb = min(kb_, wa + per_w);
+    const int n_tiles = (wb - wa + FT_KEYS - 1) / FT_KEYS;
+    unsigned char *ring = warp_base + warp * SM::PER_WARP;
+    float *wbuf = (float *)(ring + FT_STAGES * FT_STAGE);
+    const uint32_t ring_u32 = mx::smem_u32(ring);
+
+    // Lane l moves 16-byte pieces l, l+32, ... of the tile's K rows and V rows: piece p of a matrix is
+    // (key = p / 16, chunk = p % 16) = (it*2 + l/16, l%16).
+    const int pk = lane >> 4, pc = lane & 15;
+    auto k_off = [&](int key) { return (uint32_t)(key * 256 + (((pc & 8) | ((pc ^ key) & 7)) << 4)); };
+    const uint32_t v_chunk = (uint32_t)((pc ^ (pc >> 3)) << 4);
+    const float *ksrc = nullptr, *vsrc = nullptr;
+    if (!PAGED) {
+        size_t r0 = (size_t)(base + wa);
+        ksrc = P.kcache + (r0 + pk) * kvd + kvh * 64 + pc * 4;
+        vsrc = P.vcache + (r0 + pk) * kvd + kvh * 64 + pc * 4;
+    }
+    const size_t it_stride = (size_t)2 * kvd, tile_stride = (size_t)FT_KEYS * kvd;
+
+    auto issue = [&](int tile) {
+        const uint32_t dst = ring_u32 + (tile % FT_STAGES) * FT_STAGE;
+        const int key0 = wa + tile * FT_KEYS;
+        if (!PAGED && key0 + FT_KEYS <= wb) {  // full tile of a linear cache: no predicates, no lookups
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int key = it * 2 + pk;
+                cp_async16(dst + k_off(key), ksrc + it * it_stride, 16);
+                cp_async16(dst + FT_KEYS * 256 + key * 256 + v_chunk, vsrc + it * it_stride, 16);
+            }
+        } else {
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int key = it * 2 + pk;
+                const int t = key0 + key;
+                const bool ok = t < wb;
+                const size_t row = cache_row(P, table, base, ok ? t : wa);
+                cp_async16(dst + k_off(key), P.kcache + row * kvd + kvh * 64 + pc * 4, ok ? 16 : 0);
+                cp_async16(dst + FT_KEYS * 256 + key * 256 + v_chunk, P.vcache + row * kvd + kvh * 64 + pc * 4,
+                           ok ? 16 : 0);
+            }
+        }
+        if (!PAGED) ksrc += tile_stride, vsrc += tile_stride;
+    };
+
     float m_run[G], l_thr[G];
-    float acc[G][4];
+    float acc[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         m_run[g] = -CUDART_INF_F;
         l_thr[g] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[g][j] = 0.0f;
+        for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
     }
 
-    const int n_keys = kb_ - ka;
-    const int kq4 = tid >> 2, part = tid & 3;  // phase 1: key lane (0..31), 16-float slice
-    const int kl = tid >> 4, dsl = tid & 15;   // phase 2: key lane (0..7), 4-float slice
-    for (int c0 = 0; c0 < n_keys; c0 += CHUNK_KEYS) {
-        const int clen = min(CHUNK_KEYS, n_keys - c0);
-        const int ck0 = ka + c0;
-        float tmax[G];
-#pragma unroll
-        for (int g = 0; g < G; ++g) tmax[g] = -CUDART_INF_F;
-        for (int k = kq4; k < ((clen + 31) & ~31); k += 32) {
-            bool ok = k < clen;
-            size_t row = cache_row(P, table, base, ck0 + (ok ? k : 0));
-            const float4 *kp = (const float4 *)(P.kcache + row * kvd + kvh * 64 + part * 16);
-            float4 k0 = kp[0], k1 = kp[1], k2 = kp[2], k3 = kp[3];
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float4 *qp = (const float4 *)(qf + g * 64 + part * 16);
-                float4 q0 = qp[0], q1 = qp[1], q2 = qp[2], q3 = qp[3];
-                float d = q0.x * k0.x + q0.y * k0.y + q0.z * k0.z + q0.w * k0.w;
-                d += q1.x * k1.x + q1.y * k1.y + q1.z * k1.z + q1.w * k1.w;
-                d += q2.x * k2.x + q2.y * k2.y + q2.z * k2.z + q2.w * k2.w;
-                d += q3.x * k3.x + q3.y * k3.y + q3.z * k3.z + q3.w * k3.w;
-                d += __shfl_xor_sync(0xFFFFFFFFu, d, 1);
-                d += __shfl_xor_sync(0xFFFFFFFFu, d, 2);
-                float v = ok ? d * scale : -CUDART_INF_F;
-                if (part == 0 && ok) sc[k * G + g] = v;
-                tmax[g] = fmaxf(tmax[g], v);
-            }
-        }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float v = warp_max_f(tmax[g]);
-            if (lane == 0) red[warp * G + g] = v;
-        }
-        __syncthreads();
-        if (tid < G)
-            hv[tid] = fmaxf(fmaxf(red[tid], red[G + tid]), fmaxf(red[2 * G + tid], red[3 * G + tid]));
-        __syncthreads();
-        float m_new[G];
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            m_new[g] = fmaxf(m_run[g], hv[g]);
-            float alpha = (m_run[g] == -CUDART_INF_F) ? 0.0f : __expf(m_run[g] - m_new[g]);
-            l_thr[g] *= alpha;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[g][j] *= alpha;
-            m_run[g] = m_new[g];
-        }
-        for (int k = tid; k < clen; k += DEC_THREADS) {
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float p = __expf(sc[k * G + g] - m_new[g]);
-                l_thr[g] += p;
-                sc[k * G + g] = p;
-            }
-        }
-        __syncthreads();
-#pragma unroll 4
-        for (int k = kl; k < clen; k += 8) {
-            size_t row = cache_row(P, table, base, ck0 + k);
-            float4 v = *(const float4 *)(P.vcache + row * kvd + kvh * 64 + dsl * 4);
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float w = sc[k * G + g];
-                acc[g][0] = fmaf(w, v.x, acc[g][0]);
-                acc[g][1] = fmaf(w, v.y, acc[g][1]);
-                acc[g][2] = fmaf(w, v.z, acc[g][2]);
-                acc[g][3] = fmaf(w, v.w, acc[g][3]);
-            }
-        }
-        __syncthreads();
-    }
+    if (n_tiles > 0) issue(0);
+    cp_async_commit();
+    const int sk = lane & 15, sh = lane >> 4;          // scores: key, dim half
+    const int kl = lane >> 3, dsl = lane & 7;          // values: key lane, 8-dim slice
+    const uint32_t vo0 = (uint32_t)(((2 * dsl) ^ ((2 * dsl) >> 3)) << 4);
+    const uint32_t vo1 = (uint32_t)(((2 * dsl + 1) ^ ((2 * dsl + 1) >> 3)) << 4);
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        if (tile + 1 < n_tiles) issue(tile + 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const unsigned char *st = ring + (tile % FT_STAGES) * FT_STAGE;
+        const bool ok = wa + tile * FT_KEYS + sk < wb;
 
-    float l_tot[G];
+        // ---- scores (log2 domain): this lane's half of its key's row against the G heads ----
+        float d0[G], d1[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) d0[g] = d1[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 kv = *(const float4 *)(st + sk * 256 + (((sh << 3) | ((i ^ sk) & 7)) << 4));
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float4 qv = *(const float4 *)(qf + g * 64 + sh * 32 + i * 4);
+                d0[g] = fmaf(qv.x, kv.x, fmaf(qv.z, kv.z, d0[g]));
+                d1[g] = fmaf(qv.y, kv.y, fmaf(qv.w, kv.w, d1[g]));
+            }
+        }
+        float wv[GP];
+#pragma unroll
+        for (int g = 0; g < GP; ++g) wv[g] = 0.0f;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float dot = d0[g] + d1[g];
+            dot += __shfl_xor_sync(0xFFFFFFFFu, dot, 16);
+            const float sg = ok ? dot * scale : -CUDART_INF_F;
+            // raise the running max only when a score exceeds it by RAISE (warp-uniform, rare)
+            if (__any_sync(0xFFFFFFFFu, sg > m_run[g] + RAISE * LOG2E)) {
+                const float m_new = warp_max_f(fmaxf(sg, m_run[g]));
+                const float alpha = (m_run[g] == -CUDART_INF_F) ? 0.0f : mx::ex2(m_run[g] - m_new);
+                l_thr[g] *= alpha;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[g][j] *= alpha;
+                m_run[g] = m_new;
+            }
+            const float p = mx::ex2(sg - m_run[g]);
+            if (sh == 0) l_thr[g] += p;   // the two halves of a key hold the same score
+            wv[g] = p;
+        }
+        if (sh == 0) {
+#pragma unroll
+            for (int g4 = 0; g4 < GP / 4; ++g4)
+                *(float4 *)(wbuf + sk * GP + g4 * 4) = make_float4(wv[g4 * 4], wv[g4 * 4 + 1], wv[g4 * 4 + 2], wv[g4 * 4 + 3]);
+        }
+        __syncwarp();
+
+        // ---- values: lane = (key lane kl, 8-dim slice dsl), 4 steps of 4 keys ----
+#pragma unroll
+        for (int step = 0; step < FT_KEYS / 4; ++step) {
+            const unsigned char *vr = st + FT_KEYS * 256 + (step * 4 + kl) * 256;
+            const float4 va = *(const float4 *)(vr + vo0), vb4 = *(const float4 *)(vr + vo1);
+            float wk[GP];
+#pragma unroll
+            for (int g4 = 0; g4 < GP / 4; ++g4) {
+                const float4 w4 = *(const float4 *)(wbuf + (step * 4 + kl) * GP + g4 * 4);
+                wk[g4 * 4] = w4.x, wk[g4 * 4 + 1] = w4.y, wk[g4 * 4 + 2] = w4.z, wk[g4 * 4 + 3] = w4.w;
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                acc[g][0] = fmaf(wk[g], va.x, acc[g][0]);
+                acc[g][1] = fmaf(wk[g], va.y, acc[g][1]);
+                acc[g][2] = fmaf(wk[g], va.z, acc[g][2]);
+                acc[g][3] = fmaf(wk[g], va.w, acc[g][3]);
+                acc[g][4] = fmaf(wk[g], vb4.x, acc[g][4]);
+                acc[g][5] = fmaf(wk[g], vb4.y, acc[g][5]);
+                acc[g][6] = fmaf(wk[g], vb4.z, acc[g][6]);
+                acc[g][7] = fmaf(wk[g], vb4.w, acc[g][7]);
+            }
+        }
+        __syncwarp();  // the ring slot and the weight buffer are rewritten by the next iterations
+    }
+    cp_async_wait<0>();
+
+    // ---- warp totals, then the CTA-level log-sum-exp merge of the warps ----
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        float lv = warp_sum_f(l_thr[g]);
-        if (lane == 0) red[warp * G + g] = lv;
-        __syncthreads();
-        l_tot[g] = red[g] + red[G + g] + red[2 * G + g] + red[3 * G + g];
-        __syncthreads();
+        l_thr[g] = warp_sum_f(l_thr[g]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {  // key lanes differ in lane bits 3,4
+            float v = acc[g][j];
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 8);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 16);
+            acc[g][j] = v;
+        }
     }
-    // key lanes inside a warp differ in lane bit 4
+    __syncthreads();  // every warp is done with its ring: reuse the memory for the merge
+    float *mg = (float *)warp_base;  // [warp][g][68]: m (log2 domain), l, pad, pad, acc[64]
 #pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[g][j] += __shfl_xor_sync(0xFFFFFFFFu, acc[g][j], 16);
-    float *accs = sc;  // [4][G][64]
-    if (lane < 16) {
-#pragma unroll
-        for (int g = 0; g < G; ++g)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) accs[(warp * G + g) * 64 + lane * 4 + j] = acc[g][j];
+    for (int g = 0; g < G; ++g) {
+        float *dst = mg + (warp * G + g) * 68;
+        if (lane == 0) {
+            dst[0] = m_run[g];
+            dst[1] = l_thr[g];
+        }
+        if (lane < 8) {
+            *(float4 *)(dst + 4 + lane * 8) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+            *(float4 *)(dst + 8 + lane * 8) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+        }
     }
     __syncthreads();
+
     const bool direct = (n_splits == 1) && (P.fin_acc == nullptr);
-    for (int i = tid; i < gc * 64; i += DEC_THREADS) {
-        int g = i >> 6, d = i & 63;
-        float a = accs[(0 * G + g) * 64 + d] + accs[(1 * G + g) * 64 + d] +
-                  accs[(2 * G + g) * 64 + d] + accs[(3 * G + g) * 64 + d];
-        float lt = 0.0f, mt = 0.0f;
+    for (int i = tid; i < gc * 64; i += F32_THREADS) {
+        const int g = i >> 6, d = i & 63;
+        float mm = -CUDART_INF_F;
 #pragma unroll
-        for (int gg = 0; gg < G; ++gg)
-            if (gg == g) {
-                lt = l_tot[gg];
-                mt = m_run[gg];
-            }
-        int h = head0 + g;
+        for (int w = 0; w < F32_WARPS; ++w) mm = fmaxf(mm, mg[(w * G + g) * 68]);
+        float lt = 0.0f, a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < F32_WARPS; ++w) {
+            const float *src = mg + (w * G + g) * 68;
+            const float wgt = (src[0] == -CUDART_INF_F) ? 0.0f : mx::ex2(src[0] - mm);
+            lt += src[1] * wgt;
+            a += src[4 + d] * wgt;
+        }
+        const int h = head0 + g;
         if (direct) {
             P.out[(size_t)s * P.out_stride + h * 64 + d] = a / lt;
         } else {
+            // partial triples carry the max in natural-log units, as the split-KV interface states
             size_t pi = ((size_t)s * P.n_head + h) * n_splits + blockIdx.x;
             P.ws_acc[pi * 64 + d] = a;
             if (d == 0) {
-                P.ws_m[pi] = mt;
+                P.ws_m[pi] = mm * 0.6931471805599453f;
                 P.ws_l[pi] = lt;
             }
         }
     }
     if (direct) return;
+
+    // ---- last CTA of this (sequence, kv head group) merges the splits ----
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -1023,7 +1118,7 @@ decode_f32_kernel(const DecodeParams P) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    merge_and_store<G>(P, s, head0, gc, n_splits);
+    merge_and_store<G>(P, s, head0, gc, n_splits, F32_THREADS);
 }
 
 // Log-sum-exp merge of gathered partial triples: one thread per (row, 4 dims).
@@ -1050,9 +1145,6 @@ __global__ void merge_partials_kernel(float *out, const float *m, const float *l
 template <int G>
 size_t q8_smem_bytes() {
     return (size_t)Q8Smem<G>::TOTAL;
-}
-size_t f32_smem_bytes(int G) {
-    return sizeof(float) * ((size_t)CHUNK_KEYS * G + G * 64 + 4 * G + G);
 }
 
 template <int G>
@@ -1081,10 +1173,16 @@ int launch_g(mx230_handle *h, cudaStream_t st, const DecodeParams &P, dim3 grid,
             MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_kernel<G, false><<<grid, Q8_THREADS, sm, st>>>(P)));
         }
     } else {
-        size_t sm = f32_smem_bytes(G);
-        MX_CHECK_CUDA(cudaFuncSetAttribute(decode_f32_kernel<G>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        MX_LAUNCH(h, st, MX230_K_DECODE_F32, (decode_f32_kernel<G><<<grid, DEC_THREADS, sm, st>>>(P)));
+        size_t sm = (size_t)F32Smem<G>::TOTAL;
+        if (P.tables) {
+            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_f32_ring_kernel<G, true>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_LAUNCH(h, st, MX230_K_DECODE_F32, (decode_f32_ring_kernel<G, true><<<grid, F32_THREADS, sm, st>>>(P)));
+        } else {
+            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_f32_ring_kernel<G, false>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_LAUNCH(h, st, MX230_K_DECODE_F32, (decode_f32_ring_kernel<G, false><<<grid, F32_THREADS, sm, st>>>(P)));
+        }
     }
     return MX230_OK;
 }
