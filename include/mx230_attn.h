@@ -331,6 +331,38 @@ int mx230_attn_prefill_dp4a_paged(mx230_handle *h, void *stream, float *out, con
                                   int n_head, int n_kv_head, int qkv_stride, int out_stride,
                                   const int *bt, int bs);
 
+/* ---- host side of paged attention: KV block pool with a block-granular prefix tree ----------
+ * Paging and RadixCache, 03-llm-engine/src/gpu.rs:211-343,372-539; the request protocol is that
+ * of prefill_cached, gpu.rs:2273-2345.  Pure host state (no CUDA call): the table it keeps is what
+ * the *_paged entry points above take as `bt`.  prefix_cache = 0 (Paging::new): one sequence owns
+ * every block, logical block i -> physical block n_blocks-1-i.  prefix_cache = 1 (Paging::new_pool):
+ * blocks start free, are reference-counted per request and by the tree, and a request whose token
+ * prefix is resident reuses those blocks; when the free list is empty the least recently used tree
+ * leaf that no live request borrows is evicted.  One pool is used by one thread at a time. */
+typedef struct mx230_kv_pool mx230_kv_pool;
+int mx230_kv_pool_create(mx230_kv_pool **out, int n_slots, int block_size, int prefix_cache);
+void mx230_kv_pool_destroy(mx230_kv_pool *p);
+int mx230_kv_pool_n_blocks(const mx230_kv_pool *p);
+int mx230_kv_pool_free_blocks(const mx230_kv_pool *p);
+int mx230_kv_pool_cached_blocks(const mx230_kv_pool *p);
+long long mx230_kv_pool_evictions(const mx230_kv_pool *p);            /* Engine::pool_evictions, gpu.rs:2259 */
+int mx230_kv_pool_refcount(const mx230_kv_pool *p, int block);
+int mx230_kv_pool_table(const mx230_kv_pool *p, int *table_out, int n); /* first n logical blocks */
+int mx230_kv_pool_phys_row(const mx230_kv_pool *p, int t);             /* Paging::phys_row, gpu.rs:536 */
+int mx230_kv_pool_alloc(mx230_kv_pool *p, int *block_out);             /* Paging::alloc, gpu.rs:443 */
+int mx230_kv_pool_incref(mx230_kv_pool *p, int block);
+int mx230_kv_pool_decref(mx230_kv_pool *p, int block);
+int mx230_kv_pool_evict(mx230_kv_pool *p, int *freed_block);           /* Paging::evict; -1 = nothing reclaimable */
+int mx230_kv_pool_lookup(mx230_kv_pool *p, const uint32_t *tokens, int n, int *blocks_out, int cap,
+                         int *n_matched);                               /* RadixCache::lookup, gpu.rs:254 */
+int mx230_kv_pool_insert(mx230_kv_pool *p, const uint32_t *tokens, int n, const int *blocks,
+                         int n_blk, int *created_out, int cap, int *n_created); /* RadixCache::insert */
+/* prefill_cached steps 1-2 (match, borrow, claim; *reused_tokens = positions already resident) and
+ * step 4 (the tree takes over the new full chunks, the request's borrow is released). */
+int mx230_kv_pool_begin_request(mx230_kv_pool *p, const uint32_t *tokens, int n, int *reused_tokens);
+int mx230_kv_pool_end_request(mx230_kv_pool *p, const uint32_t *tokens, int n);
+int mx230_kv_pool_audit(const mx230_kv_pool *p);                        /* Paging::audit, gpu.rs:476 */
+
 #ifdef __cplusplus
 }
 #endif
