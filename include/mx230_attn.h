@@ -343,6 +343,7 @@ typedef struct mx230_kv_pool mx230_kv_pool;
 int mx230_kv_pool_create(mx230_kv_pool **out, int n_slots, int block_size, int prefix_cache);
 void mx230_kv_pool_destroy(mx230_kv_pool *p);
 int mx230_kv_pool_n_blocks(const mx230_kv_pool *p);
+int mx230_kv_pool_block_size(const mx230_kv_pool *p);
 int mx230_kv_pool_free_blocks(const mx230_kv_pool *p);
 int mx230_kv_pool_cached_blocks(const mx230_kv_pool *p);
 long long mx230_kv_pool_evictions(const mx230_kv_pool *p);            /* Engine::pool_evictions, gpu.rs:2259 */
@@ -362,6 +363,30 @@ int mx230_kv_pool_insert(mx230_kv_pool *p, const uint32_t *tokens, int n, const 
 int mx230_kv_pool_begin_request(mx230_kv_pool *p, const uint32_t *tokens, int n, int *reused_tokens);
 int mx230_kv_pool_end_request(mx230_kv_pool *p, const uint32_t *tokens, int n);
 int mx230_kv_pool_audit(const mx230_kv_pool *p);                        /* Paging::audit, gpu.rs:476 */
+
+/* ---- continuous-batching scheduler over batched decode ---------------------------------------
+ * The state machine of Engine::run_continuous, 03-llm-engine/src/gpu.rs:3800-3915, without the
+ * model: admission (a request reserves ceil((prompt + max_new) / block) blocks for its whole life
+ * from the pool, so a running sequence never fails to allocate), the active batch of each decode
+ * step (tokens, positions, packed tables = the arguments of the *_batched entry points) and
+ * retirement.  Driver loop:
+ *   for (;;) {
+ *     while (mx230_sched_admit(s, &r, table), r >= 0) { first = prefill(prompt[r], table); mx230_sched_admitted(s, r, first); }
+ *     mx230_sched_batch(s, &n, cur, pos, tables); if (n == 0) break;
+ *     decode_batched(cur, pos, tables, n) -> next; mx230_sched_step_done(s, next);
+ *   }
+ * The pool must be a prefix_cache = 1 pool (only its reference-counted allocator is used). */
+typedef struct mx230_sched mx230_sched;
+int mx230_sched_create(mx230_sched **out, mx230_kv_pool *pool, int n_ctx, int max_batch,
+                       const int *prompt_len, const int *max_new, int n_requests);
+void mx230_sched_destroy(mx230_sched *s);
+int mx230_sched_n_log(const mx230_sched *s);
+int mx230_sched_admit(mx230_sched *s, int *request, int *table_out);
+int mx230_sched_admitted(mx230_sched *s, int request, uint32_t first_token);
+int mx230_sched_batch(mx230_sched *s, int *n_active, uint32_t *cur, int *pos, int *tables);
+int mx230_sched_step_done(mx230_sched *s, const uint32_t *next_tokens);
+int mx230_sched_result(const mx230_sched *s, int request, uint32_t *out, int cap, int *n);
+long long mx230_sched_stat(const mx230_sched *s, int which); /* ServeStats gpu.rs:366: 0 decode_steps, 1 seq_decodes, 2 admitted */
 
 #ifdef __cplusplus
 }

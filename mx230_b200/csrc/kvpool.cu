@@ -179,6 +179,7 @@ extern "C" int mx230_kv_pool_create(mx230_kv_pool **out, int n_slots, int block_
 extern "C" void mx230_kv_pool_destroy(mx230_kv_pool *p) { delete p; }
 
 extern "C" int mx230_kv_pool_n_blocks(const mx230_kv_pool *p) { return p ? p->n_blocks : -1; }
+extern "C" int mx230_kv_pool_block_size(const mx230_kv_pool *p) { return p ? p->block_size : -1; }
 extern "C" int mx230_kv_pool_free_blocks(const mx230_kv_pool *p) { return p ? (int)p->free_list.size() : -1; }
 extern "C" long long mx230_kv_pool_evictions(const mx230_kv_pool *p) { return p ? p->evictions : -1; }
 extern "C" int mx230_kv_pool_cached_blocks(const mx230_kv_pool *p) {
