@@ -160,7 +160,7 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------- GPU arm
-def decode_bench(h, torch, la, n_seq=64, nh=14, nkv=2, ctx=2048, iters=40, quants=(True, False)):
+def decode_bench(h, torch, la, n_seq=64, nh=14, nkv=2, ctx=2048, iters=40, quants=(True, False), graph=False):
     """int8-KV GQA decode (and fp32 control): GB/s of algorithmic bytes, caches rotated so that
     consecutive launches never hit L2-resident data."""
     out = {}
@@ -192,8 +192,11 @@ def decode_bench(h, torch, la, n_seq=64, nh=14, nkv=2, ctx=2048, iters=40, quant
         prof = h.profile_read()
         name = "decode_q8_kernel" if quant else "decode_f32_kernel"
         cnt, ms = prof[name]
+        g_us = graph_time_us(torch, [(lambda cc=cc: la.attn_decode_slab(h, o, q, cc, pos, n_seq, nh, nkv, 64, ctx, qd, qd))
+                                     for cc in (caches * 3)[:max(copies, 12)]]) if graph else None
         out["int8_kv" if quant else "fp32_kv"] = {
             "gbs": nbytes / (ms / cnt) / 1e6, "us_per_launch": 1e3 * ms / cnt, "bytes_per_launch": nbytes,
+            **({"graph_us_per_launch": g_us, "graph_gbs": nbytes / g_us / 1e3} if graph else {}),
             "batch": n_seq, "ctx": ctx, "heads": f"{nh}q/{nkv}kv", "cache_copies_rotated": copies}
         del caches
     return out
@@ -475,6 +478,30 @@ def run_splitkv(args):
     h.close()
 
 
+def graph_time_us(torch, launches, replays=5):
+    """Device time per launch of a list of enqueue-only callables, replayed from a CUDA graph: for
+    kernels of a few microseconds the host cannot submit launches fast enough for an event pair around
+    each one to measure anything but the submission gap."""
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for f in launches:
+            f()
+    side.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for f in launches:
+            f()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (replays * len(launches))
+
+
 def run_configs(args):
     """Every BASELINE.json configuration on one GPU, kernel time from the library's own event pairs
     (median-free mean over `--steps` launches after warm-up): C1 and C3 forward through the fp32 entry
@@ -514,7 +541,7 @@ def run_configs(args):
     fwd_config("C2-forward", 48, 4096, True)
     fwd_config("C3", 8, 32768, False)
     for b in (1, 16, 64):
-        d = decode_bench(h, torch, la, n_seq=b, iters=reps)
+        d = decode_bench(h, torch, la, n_seq=b, iters=reps, graph=True)
         for kname, v in d.items():
             v["frac_of_measured_hbm"] = v["gbs"] / peaks["hbm_gbs"]
             print(json.dumps({"config": f"C4 batch {b} {kname}", **v}), flush=True)
@@ -525,21 +552,110 @@ def run_configs(args):
     h.close()
 
 
+def run_proj(args):
+    """The projections either side of attention for one decode token (Qwen2-0.5B-like 896 -> 1152 and
+    TinyLlama-like 2048 -> 2560, fp16 and fp32 weights): GB/s of weight bytes per launch, and the decode
+    step with the fused qkv launch against the reference's sequence of gemv + rope + KV write."""
+    import torch
+    from mx230_b200 import llm_attention as la
+    from mx230_b200.common import Handle
+    torch.cuda.set_device(0)
+    h = Handle(0, 64 << 20)
+    peaks = measured_peaks()
+    reps = max(20, args.steps)
+
+    def timed(fn, name):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps   # us per call, launches back to back
+
+    for model, n_in, nh, nkv in (("qwen2-0.5b-like", 896, 14, 2), ("tinyllama-like", 2048, 32, 4)):
+        n_out = (nh + 2 * nkv) * 64
+        for dt in (torch.float16, torch.float32):
+            # a ring of weight copies larger than L2, as successive layers of a model would be
+            copies = max(2, int(2 * 126e6 / (n_in * n_out * dt.itemsize)) + 1)
+            ws = [(torch.randn(n_in, n_out, device="cuda") * 0.05).to(dt) for _ in range(copies)]
+            b = torch.randn(n_out, device="cuda")
+            x = torch.randn(n_in, device="cuda")
+            qkv = torch.empty(n_out, device="cuda")
+            c = la.KvCache(256, nkv, 64, True)
+            st = {"i": 0}
+
+            def w():
+                st["i"] += 1
+                return ws[st["i"] % copies]
+            t_gemv = timed(lambda: la.gemv(h, qkv, x, w(), b), "gemv")
+            t_fused = timed(lambda: la.qkv_rope_kvwrite(h, qkv, x, w(), b, 100, c, nh, nkv, 1e6), "fused")
+            # the kernels alone: the library's event pair around each launch
+            h.profile_reset()
+            h.profile_enable(True)
+            for _ in range(reps):
+                la.gemv(h, qkv, x, w(), b)
+            h.profile_enable(False)
+            cnt, ms = h.profile_read()["gemv_heads_kernel"]
+            k_gemv = 1e3 * ms / cnt
+            h.profile_reset()
+            h.profile_enable(True)
+            for _ in range(reps):
+                la.qkv_rope_kvwrite(h, qkv, x, w(), b, 100, c, nh, nkv, 1e6)
+            h.profile_enable(False)
+            cnt, ms = h.profile_read()["gemv_heads_kernel"]
+            k_fused = 1e3 * ms / cnt
+
+            def separate():
+                la.gemv(h, qkv, x, w(), b)
+                la.rope(h, qkv, 100, nh, nkv, 64, 1e6)
+                la.quantize_kv(h, c, qkv, 100, nh * 64, nkv, 64)
+            t_sep = timed(separate, "separate")
+            g_gemv = graph_time_us(torch, [(lambda ww=ww: la.gemv(h, qkv, x, ww, b)) for ww in (ws * 12)[:max(copies, 12)]])
+            g_fused = graph_time_us(torch, [(lambda ww=ww: la.qkv_rope_kvwrite(h, qkv, x, ww, b, 100, c, nh, nkv, 1e6))
+                                            for ww in (ws * 12)[:max(copies, 12)]])
+
+            def sep3(ww):
+                la.gemv(h, qkv, x, ww, b)
+                la.rope(h, qkv, 100, nh, nkv, 64, 1e6)
+                la.quantize_kv(h, c, qkv, 100, nh * 64, nkv, 64)
+            g_sep = graph_time_us(torch, [(lambda ww=ww: sep3(ww)) for ww in (ws * 12)[:max(copies, 12)]])
+            wbytes = n_in * n_out * dt.itemsize
+            print(json.dumps({"case": "proj", "model": model, "weights": str(dt).split(".")[-1], "n_in": n_in, "n_out": n_out,
+                              "weight_bytes": wbytes, "graph_us": {"gemv": g_gemv, "fused_qkv_rope_kvwrite": g_fused,
+                                                                       "gemv+rope+quantize_kv (3 launches)": g_sep},
+                              "gemv_gbs": wbytes / g_gemv / 1e3, "gemv_frac_of_measured_hbm": wbytes / g_gemv / 1e3 / peaks["hbm_gbs"],
+                              "fused_gbs": wbytes / g_fused / 1e3,
+                              "event_pair_us": {"gemv": k_gemv, "fused_qkv_rope_kvwrite": k_fused},
+                              "host_call_us": {"gemv": t_gemv, "fused_qkv_rope_kvwrite": t_fused,
+                                               "gemv+rope+quantize_kv (3 launches)": t_sep},
+                              "weight_copies_rotated": copies}), flush=True)
+            del ws
+    h.check_status()
+    h.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "decode_c4", "decode_long", "splitkv", "configs"],
+    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "decode_c4", "decode_long", "splitkv", "configs", "proj"],
                     help="fwd|bwd|decode_*: profiling aid, runs one kernel family a few times and exits; "
                          "splitkv: long-context decode with keys split over the ranks (torchrun for N > 1); "
-                         "configs: every BASELINE.json configuration on one GPU")
+                         "configs: every BASELINE.json configuration on one GPU; "
+                         "proj: the projections either side of attention for one decode token")
     args = ap.parse_args()
     if args.case == "splitkv":
         run_splitkv(args)
     elif args.case == "configs":
         run_configs(args)
+    elif args.case == "proj":
+        run_proj(args)
     elif args.case:
         run_case(args)
     elif args.impl == "reference":

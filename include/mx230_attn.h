@@ -75,7 +75,8 @@ enum {
     MX230_K_DECODE_Q8 = 9,
     MX230_K_MERGE = 10,
     MX230_K_PREFILL = 11,
-    MX230_K_COUNT = 12
+    MX230_K_GEMV = 12,
+    MX230_K_COUNT = 13
 };
 
 typedef struct mx230_handle mx230_handle;
@@ -330,6 +331,25 @@ int mx230_attn_prefill_dp4a_paged(mx230_handle *h, void *stream, float *out, con
                                   const float *kcache, const float *vcache, int pos0, int n_tok,
                                   int n_head, int n_kv_head, int qkv_stride, int out_stride,
                                   const int *bt, int bs);
+
+/* ---- the projections either side of the attention step (one decode token) --------------------
+ * gemv / gemv_half, 03-llm-engine/kernels/llm.cu:144-177 (host gemv(), src/gpu.rs:1158-1198):
+ * y[o] (+)= sum_i x[i] w[i*n_out + o] + b[o], w row-major [n_in][n_out] in fp32 (w_fp16 = 0) or
+ * fp16 (1), b may be null, accum != 0 adds into y (the residual add fused into the output
+ * projection, gpu.rs:2676-2686).  n_out a multiple of 4; uses the handle's workspace
+ * (n_slices * n_out floats, at most ceil(n_in / 16) slices). */
+int mx230_gemv(mx230_handle *h, void *stream, float *y, const float *x, const void *w, int w_fp16,
+               const float *b, int n_in, int n_out, int accum);
+/* The qkv step in one launch: qkv = x W + b (W [n_in][(n_head + 2 n_kv_head) * 64]), RoPE at `pos`
+ * (or *pos_ptr when non-null: the graph-captured decode) on the Q and K heads, K and V rows written
+ * to cache row pos (through bt/bs when paged) as fp32 (kcache, vcache) or int8 quantize-on-write
+ * (kq .. vb; kb == vb == NULL selects absmax), the rotated q left in qkv for mx230_attn_decode*.
+ * Replaces gemv + rope[_dyn] + memcpy / copy_kv_* / quantize_kv_* of gpu.rs:2558-2646, :2808-2893. */
+int mx230_qkv_rope_kvwrite(mx230_handle *h, void *stream, float *qkv, const float *x, const void *w,
+                           int w_fp16, const float *b, int n_in, int pos, const int *pos_ptr,
+                           int n_head, int n_kv_head, int head_dim, float theta, float *kcache,
+                           float *vcache, int8_t *kq, int8_t *vq, float *ks, float *vs, float *kb,
+                           float *vb, const int *bt, int bs);
 
 /* ---- host side of paged attention: KV block pool with a block-granular prefix tree ----------
  * Paging and RadixCache, 03-llm-engine/src/gpu.rs:211-343,372-539; the request protocol is that

@@ -254,7 +254,8 @@ extern "C" const char *mx230_kernel_name(int kernel) {
     static const char *names[MX230_K_COUNT] = {
         "cast_bf16_kernel", "flash_fwd_kernel", "bwd_preprocess_kernel", "bwd_dq_kernel",
         "bwd_dkv_kernel", "rope_kernel", "copy_kv_kernel", "quantize_kv_kernel",
-        "decode_f32_kernel", "decode_q8_kernel", "merge_partials_kernel", "prefill_stage_kernels"};
+        "decode_f32_kernel", "decode_q8_kernel", "merge_partials_kernel", "prefill_stage_kernels",
+        "gemv_heads_kernel"};
     return (kernel >= 0 && kernel < MX230_K_COUNT) ? names[kernel] : "?";
 }
 

@@ -333,3 +333,24 @@ def attn_decode_q8_noalloc(out, qkv, c: KvCache, t_cur: int, n_head, n_kv_head, 
     only allowed to enqueue on a given stream).  Current device; see include/mx230_attn.h."""
     check(lib().mx230_attn_decode_q8_noalloc(stream_ptr(stream), ptr(out), ptr(qkv), *c.q8_args(), t_cur,
                                              n_head, n_kv_head, head_dim))
+
+
+# ---------------------------------------------------------------- projections either side of attention
+def gemv(h: Handle, y, x, w, b=None, accum=False, stream=None):
+    """gemv / gemv_half (llm.cu:144-177; gpu.rs:1158-1198): y (+)= x W + b, W [n_in][n_out] fp32 or fp16."""
+    n_in, n_out = w.shape
+    check(lib().mx230_gemv(h._h, stream_ptr(stream), ptr(y), ptr(x), ptr(w), int(w.dtype == torch.float16),
+                           ptr(b), n_in, n_out, int(accum)))
+
+
+def qkv_rope_kvwrite(h: Handle, qkv, x, w, b, pos, c: KvCache, n_head, n_kv_head, theta, pg: Paging | None = None,
+                     stream=None):
+    """The qkv step of one decode token in one launch (gemv + rope + KV write of gpu.rs:2558-2646):
+    `pos` is a host int or an int32 device tensor (the graph-captured form)."""
+    n_in = w.shape[0]
+    dyn = not isinstance(pos, int)
+    caches = (None, None, *c.q8_args()) if c.quant else (ptr(c.k), ptr(c.v), None, None, None, None, None, None)
+    check(lib().mx230_qkv_rope_kvwrite(h._h, stream_ptr(stream), ptr(qkv), ptr(x), ptr(w),
+                                       int(w.dtype == torch.float16), ptr(b), n_in, 0 if dyn else pos,
+                                       ptr(pos) if dyn else None, n_head, n_kv_head, 64, theta, *caches,
+                                       ptr(pg.table_dev) if pg else None, pg.block_size if pg else 0))

@@ -289,3 +289,15 @@ def prefill(qkv, pos0, n_tok, n_head, n_kv_head, qkv_stride, out_stride, kcache=
                       n_kv_head, qkv_stride, out_stride, _i(table), block_size,
                       1 if c is not None else 0, threads)
     return out
+
+
+def gemv(x, w, b=None, y=None, accum=False):
+    """The reference gemv (llm.cu:144-177): y[o] (+)= sum_i x[i] w[i, o] + b[o]; fp16 weights are
+    widened to fp32 first, as gemv_half does."""
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(np.asarray(w).astype(np.float32))
+    n_in, n_out = w.shape
+    out = np.zeros(n_out, np.float32) if y is None else np.ascontiguousarray(y, np.float32).copy()
+    lib().orc_gemv(_f(out), _f(x), _f(w), _f(None if b is None else np.ascontiguousarray(b, np.float32)),
+                   n_in, n_out, 1 if accum else 0)
+    return out

@@ -659,3 +659,15 @@ void orc_prefill(float *out, const float *qkv, const float *kcache, const float 
                               0);
     }
 }
+
+/* y[o] (+)= sum_i x[i] w[i*n_out + o] + b[o]: the reference's gemv, one sequential fp32 sum per
+ * output column (03-llm-engine/kernels/llm.cu:144-160; gemv_half :162-177 widens fp16 weights to
+ * fp32 first, which the caller does before calling this).  b may be null. */
+void orc_gemv(float *y, const float *x, const float *w, const float *b, int n_in, int n_out, int accum) {
+    for (int o = 0; o < n_out; ++o) {
+        float acc = 0.0f;
+        for (int i = 0; i < n_in; ++i) acc += x[i] * w[(size_t)i * n_out + o];
+        float r = acc + (b ? b[o] : 0.0f);
+        y[o] = accum ? y[o] + r : r;
+    }
+}
