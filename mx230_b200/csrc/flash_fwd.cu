@@ -10,8 +10,9 @@
 //   * one CTA owns 256 query rows of one head as two 128-row tiles;
 //   * warp 8 streams Q once and K/V tiles (128 keys) through a 4-stage shared-memory
 //     ring with plain per-CTA TMA tile loads (128-byte swizzle);
-//   * warp 9 issues tcgen05.mma: S_t = Q_t K^T into tensor memory (128 fp32 columns per
-//     tile) and O_t += P_t V with P_t read from tensor memory as bf16;
+//   * warp 9 issues the tcgen05.mma stream S_t = Q_t K^T into tensor memory (128 fp32 columns
+//     per tile), warp 10 the stream O_t += P_t V with P_t read from tensor memory as bf16 (a
+//     thread issues an MMA about every 60 cycles, so each stream has its own thread);
 //   * warps 0-3 / 4-7 are the softmax groups of tile 0 / 1, one thread per query row: the
 //     score row is pulled into registers in one round trip (which frees S_t for the next
 //     QK^T at once), then row max, exp2, row sum, bf16 P into its own tensor-memory
@@ -138,7 +139,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
 
     // register budget: the softmax warpgroups hold a 128-value score row per thread, the
-    // third warpgroup (TMA, MMA, two idle warps) needs few
+    // third warpgroup (TMA, two MMA issuers, one idle warp) needs few
     if (warp >= 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         if (warp == 8) {
