@@ -387,12 +387,14 @@ __global__ void bwd_preprocess_kernel(const float *dO, const float *O, float *De
     if (row < rows && part == 0) Delta[row] = d;
 }
 
-int set_attrs() {
-    static bool done = false;
-    if (!done) {
+// function attributes are per device: one handle per GPU may live in the same process
+int set_attrs(int device) {
+    static bool done[64] = {};
+    MX_REQUIRE(device >= 0 && device < 64, MX230_ERR_UNSUPPORTED, "flash backward: device index %d", device);
+    if (!done[device]) {
         MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
         MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
-        done = true;
+        done[device] = true;
     }
     return MX230_OK;
 }
@@ -450,7 +452,7 @@ int bwd_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb, cons
     MX_REQUIRE(!(which & 2) || (dK && dV), MX230_ERR_INVALID_ARG, "%s: null dK/dV", who);
     MX_REQUIRE((((uintptr_t)dQ | (uintptr_t)dK | (uintptr_t)dV) & 15) == 0, MX230_ERR_INVALID_ARG,
                "%s: outputs must be 16-byte aligned", who);
-    int rc = set_attrs();
+    int rc = set_attrs(h->device);
     if (rc) return rc;
     Maps m;
     if ((rc = make_maps(h, m, Qb, Kb, Vb, dOb, batch_heads, n))) return rc;

@@ -417,11 +417,13 @@ int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, 
     if ((rc = mx230_make_tmap_bf16(h, &tq, Qb, n_q, heads, rs, (uint64_t)n_q * HD * 2, BM))) return rc;
     if ((rc = mx230_make_tmap_bf16(h, &tk, Kb, n_k, heads / kv_group, rs, (uint64_t)n_k * HD * 2, BN))) return rc;
     if ((rc = mx230_make_tmap_bf16(h, &tv, Vb, n_k, heads / kv_group, rs, (uint64_t)n_k * HD * 2, BN))) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
+    // function attributes are per device: one handle per GPU may live in the same process
+    static bool attr_set[64] = {};
+    MX_REQUIRE(h->device >= 0 && h->device < 64, MX230_ERR_UNSUPPORTED, "flash forward: device index %d", h->device);
+    if (!attr_set[h->device]) {
         MX_CHECK_CUDA(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            SMEM_ALLOC));
-        attr_set = true;
+        attr_set[h->device] = true;
     }
     FwdParams P;
     P.O = O;

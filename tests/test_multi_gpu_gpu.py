@@ -113,3 +113,40 @@ def test_split_kv_decode_and_sharded_forward_two_gpus(ctx):
         assert err_fwd < TOL["max_abs"], (r, err_fwd)
         assert abs(sums[0] - sums[1]) <= 1e-6 * max(1.0, abs(sums[0]))
     assert ret[0][4] == (0, 3) and ret[1][4] == (3, 6)
+
+
+def test_two_handles_in_one_process():
+    """One process driving two GPUs round-robin, a handle and a stream per device: the kernels'
+    per-device function attributes and workspaces do not leak from one device to the other."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from mx230_b200 import flash_attention as fa, llm_attention as la
+    from mx230_b200.common import Handle
+    bh, n = 3, 300
+    Q, K, V, dO = (oracle.normal((bh, n, 64), 190 + i, 0) for i in range(4))
+    wo, wl = oracle.attn_fwd(Q, K, V, True)
+    handles = [Handle(d, 32 << 20) for d in (1, 0)]   # device 1 first: nothing may assume device 0
+    outs = []
+    for h, d in zip(handles, (1, 0)):
+        with torch.cuda.device(d):
+            q, k, v, do = (torch.from_numpy(x).cuda(d) for x in (Q, K, V, dO))
+            o, l = torch.zeros_like(q), torch.zeros(bh, n, device=f"cuda:{d}")
+            delta = torch.zeros_like(l)
+            dq, dk, dv = (torch.zeros_like(q) for _ in range(3))
+            fa.run_flash_lse(h, q, k, v, o, l, n, True)
+            fa.run_preprocess(h, do, o, delta, n)
+            fa.run_bwd_flash(h, q, k, v, do, l, delta, dq, dk, dv, n, True)
+            # int8 decode on this device too
+            nh, nkv, ctx = 8, 2, 200
+            c = la.KvCache(ctx, nkv, 64, True, device=f"cuda:{d}")
+            c.k.random_(-128, 128), c.v.random_(-128, 128), c.ks.uniform_(0.01, 0.03), c.vs.uniform_(0.01, 0.03)
+            qd = torch.randn(nh * 64, device=f"cuda:{d}")
+            od = torch.zeros(nh * 64, device=f"cuda:{d}")
+            la.attn_decode(h, od, qd, c, ctx - 1, nh, nkv, 64)
+            h.check_status()
+            outs.append((o.cpu().numpy(), dq.cpu().numpy(), dk.cpu().numpy(), dv.cpu().numpy(), od.cpu().numpy()))
+    for o, dq, dk, dv, od in outs:
+        assert np.abs(o - wo).max() < TOL["max_abs"] and np.isfinite(od).all()
+    # both devices ran the same kernels on the same inputs
+    for a, b in zip(outs[0][:4], outs[1][:4]):
+        np.testing.assert_array_equal(a, b)
