@@ -49,8 +49,8 @@ DKV_FLOP = BWD_FLOP * 3.0 / 5.0
 WORKLOAD = "causal flash-attention fwd+bwd, B=4 H=12 N=4096 d=64 (BASELINE.json configs[1])"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the three tensor kernels on this exact
 # workload, from the committed ncu capture (the operands, 4 x 25 MB bf16 + fp32 outputs, mostly stay in the 126 MB L2)
-NCU_DRAM_BYTES_PER_LAUNCH = {"flash_fwd_kernel": 80763392 + 16772864, "bwd_dq_kernel": 107303424 + 24600320,
-                             "bwd_dkv_kernel": 109310720 + 57106176}
+NCU_DRAM_BYTES_PER_LAUNCH = {"flash_fwd_kernel": 80008960 + 15823872, "bwd_dq_kernel": 106645504 + 24320512,
+                             "bwd_dkv_kernel": 111527680 + 56352768}
 NOMINAL_BF16_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
 
