@@ -340,16 +340,23 @@ int mx230_attn_prefill_dp4a_paged(mx230_handle *h, void *stream, float *out, con
  * (n_slices * n_out floats, at most ceil(n_in / 16) slices). */
 int mx230_gemv(mx230_handle *h, void *stream, float *y, const float *x, const void *w, int w_fp16,
                const float *b, int n_in, int n_out, int accum);
-/* The qkv step in one launch: qkv = x W + b (W [n_in][(n_head + 2 n_kv_head) * 64]), RoPE at `pos`
- * (or *pos_ptr when non-null: the graph-captured decode) on the Q and K heads, K and V rows written
- * to cache row pos (through bt/bs when paged) as fp32 (kcache, vcache) or int8 quantize-on-write
- * (kq .. vb; kb == vb == NULL selects absmax), the rotated q left in qkv for mx230_attn_decode*.
- * Replaces gemv + rope[_dyn] + memcpy / copy_kv_* / quantize_kv_* of gpu.rs:2558-2646, :2808-2893. */
+/* gemv_int8, llm.cu:226-316 (host gemv() Weights::Int8, gpu.rs:1200-1211): int8 weights packed as int32
+ * words of four consecutive input rows, w_packed[(i/4)*n_out + o]; activations quantised inside the
+ * kernel per group of act_group (4 or 8: the reference's compile-time AG) values, absmax/127, round to
+ * nearest even; integer dots by dp4a; y[o] (+)= (sum_g dot_g * xs_g) * scales[o] + b[o].  n_in % 8 == 0. */
+int mx230_gemv_int8(mx230_handle *h, void *stream, float *y, const float *x, const void *w_packed,
+                    const float *scales, const float *b, int n_in, int n_out, int accum, int act_group);
+/* The qkv step in one launch: qkv = x W + b (W [n_in][(n_head + 2 n_kv_head) * 64]; w_kind 0 fp32, 1 fp16,
+ * 2 int8 packed with w_scales and act_group as for mx230_gemv_int8), RoPE at `pos` (or *pos_ptr when
+ * non-null: the graph-captured decode) on the Q and K heads, K and V rows written to cache row pos
+ * (through bt/bs when paged) as fp32 (kcache, vcache) or int8 quantize-on-write (kq .. vb; kb == vb == NULL
+ * selects absmax), the rotated q left in qkv for mx230_attn_decode*.  Replaces gemv + rope[_dyn] +
+ * memcpy / copy_kv_* / quantize_kv_* of gpu.rs:2558-2646, :2808-2893. */
 int mx230_qkv_rope_kvwrite(mx230_handle *h, void *stream, float *qkv, const float *x, const void *w,
-                           int w_fp16, const float *b, int n_in, int pos, const int *pos_ptr,
-                           int n_head, int n_kv_head, int head_dim, float theta, float *kcache,
-                           float *vcache, int8_t *kq, int8_t *vq, float *ks, float *vs, float *kb,
-                           float *vb, const int *bt, int bs);
+                           int w_kind, const float *w_scales, int act_group, const float *b, int n_in,
+                           int pos, const int *pos_ptr, int n_head, int n_kv_head, int head_dim,
+                           float theta, float *kcache, float *vcache, int8_t *kq, int8_t *vq, float *ks,
+                           float *vs, float *kb, float *vb, const int *bt, int bs);
 
 /* ---- host side of paged attention: KV block pool with a block-granular prefix tree ----------
  * Paging and RadixCache, 03-llm-engine/src/gpu.rs:211-343,372-539; the request protocol is that

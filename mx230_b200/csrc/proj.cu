@@ -7,7 +7,12 @@
 //                    attention -- one launch for the reference's gemv + rope + KV write
 //                    (gpu.rs:2558-2646; rope llm.cu:1072-1100, quant_affine :1137-1149).
 //
-// HBM-bound on the weight matrix (n_in x n_out fp32 or fp16, each byte read once).  The reference
+//   gemv_int8:       the same with int8 weights and on-the-fly int8 activations (llm.cu:226-316): the
+//                    activation row is quantised per group of AG values (absmax / 127, round to nearest
+//                    even), weights are int32 words of four consecutive input rows, w32[(i/4)*n_out + o],
+//                    integer dots by dp4a, one float multiply-add per group, one scale per output column.
+//
+// HBM-bound on the weight matrix (n_in x n_out fp32, fp16 or int8, each byte read once).  The reference
 // gives one thread a whole output column, which leaves most of a B200 idle for a 1152-column
 // matrix; here a CTA owns a 64-column block (one attention head) and a slice of the input rows, so
 // that the grid covers the machine: 16 lanes x 128-bit loads across the columns, 8 row lanes down
@@ -45,6 +50,8 @@ struct GemvParams {
     const void *w;
     const float *b;
     int n_in, n_out, accum;
+    const float *scales;     // int8 weights: one scale per output column
+    int ag;                  // int8 weights: activations are quantised in groups of `ag` values (4 or 8)
     int rows_per_slice;
     float *partials;         // [n_slices][n_out]
     unsigned *counters;      // one per column block, self-resetting
@@ -70,27 +77,66 @@ gemv_heads_kernel(const GemvParams P) {
     __shared__ float red[PJ_ROWLANES][PJ_COLS];
     __shared__ float val[PJ_COLS];
     __shared__ int is_last;
-    extern __shared__ float xs[];                      // this slice of x
+    extern __shared__ float xs[];                      // this slice of x (int8: packed codes, then group scales)
+    constexpr bool I8 = sizeof(WT) == 1;
     const int tid = threadIdx.x;
     const int col0 = blockIdx.x * PJ_COLS;
     const int k0 = blockIdx.y * P.rows_per_slice;
     const int k1 = min(P.n_in, k0 + P.rows_per_slice);
-    for (int i = tid; i < k1 - k0; i += PJ_THREADS) xs[i] = P.x[k0 + i];
+    int *xq = (int *)xs;                               // int8: (k1 - k0) / 4 words
+    float *xsc = xs + P.rows_per_slice / 4;            // int8: (k1 - k0) / ag scales
+    if (!I8) {
+        for (int i = tid; i < k1 - k0; i += PJ_THREADS) xs[i] = P.x[k0 + i];
+    } else {
+        // quantise this slice of the activations exactly as the reference kernel does
+        const int ag = P.ag;
+        for (int g = tid; g < (k1 - k0) / ag; g += PJ_THREADS) {
+            const float *xg = P.x + k0 + g * ag;
+            float amax = 0.0f;
+            for (int j = 0; j < ag; ++j) amax = fmaxf(amax, fabsf(xg[j]));
+            const float id = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+            for (int q = 0; q < ag / 4; ++q) {
+                int packed = 0;
+                for (int j = 0; j < 4; ++j) {
+                    const int v = max(-127, min(127, __float2int_rn(xg[4 * q + j] * id)));
+                    packed |= (v & 0xFF) << (8 * j);
+                }
+                xq[g * (ag / 4) + q] = packed;
+            }
+            xsc[g] = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+        }
+    }
     __syncthreads();
 
     const int cq = tid & 15, rl = tid >> 4;
     const int col = col0 + 4 * cq;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (col + 3 < P.n_out) {
-        const WT *w = (const WT *)P.w;
+        if constexpr (!I8) {
+            const WT *w = (const WT *)P.w;
 #pragma unroll 8
-        for (int i = k0 + rl; i < k1; i += PJ_ROWLANES) {
-            const float4 w4 = load_w4(w, (size_t)i * P.n_out + col);
-            const float xv = xs[i - k0];
-            acc.x = fmaf(xv, w4.x, acc.x);
-            acc.y = fmaf(xv, w4.y, acc.y);
-            acc.z = fmaf(xv, w4.z, acc.z);
-            acc.w = fmaf(xv, w4.w, acc.w);
+            for (int i = k0 + rl; i < k1; i += PJ_ROWLANES) {
+                const float4 w4 = load_w4(w, (size_t)i * P.n_out + col);
+                const float xv = xs[i - k0];
+                acc.x = fmaf(xv, w4.x, acc.x);
+                acc.y = fmaf(xv, w4.y, acc.y);
+                acc.z = fmaf(xv, w4.z, acc.z);
+                acc.w = fmaf(xv, w4.w, acc.w);
+            }
+        } else {
+            // word q holds input rows 4q .. 4q+3 of a column; its group scale is xsc[q / (ag / 4)]
+            const int *w32 = (const int *)P.w;
+            const int wpg = P.ag / 4;
+#pragma unroll 8
+            for (int q = k0 / 4 + rl; q < k1 / 4; q += PJ_ROWLANES) {
+                const int4 wv = *(const int4 *)(w32 + (size_t)q * P.n_out + col);
+                const int xv = xq[q - k0 / 4];
+                const float sx = xsc[(q - k0 / 4) / wpg];
+                acc.x = fmaf((float)__dp4a(wv.x, xv, 0), sx, acc.x);
+                acc.y = fmaf((float)__dp4a(wv.y, xv, 0), sx, acc.y);
+                acc.z = fmaf((float)__dp4a(wv.z, xv, 0), sx, acc.z);
+                acc.w = fmaf((float)__dp4a(wv.w, xv, 0), sx, acc.w);
+            }
         }
     }
     *(float4 *)&red[rl][4 * cq] = acc;
@@ -120,7 +166,7 @@ gemv_heads_kernel(const GemvParams P) {
     // ---- epilogue on the 64 finished sums of this column block ----
     if (tid < PJ_COLS) {
         const int o = col0 + tid;
-        if (o < P.n_out) val[tid] += P.b ? P.b[o] : 0.0f;
+        if (o < P.n_out) val[tid] = (I8 ? val[tid] * P.scales[o] : val[tid]) + (P.b ? P.b[o] : 0.0f);
     }
     __syncthreads();
     if (!P.e.enabled) {
@@ -181,7 +227,8 @@ gemv_heads_kernel(const GemvParams P) {
     }
 }
 
-int launch_gemv(mx230_handle *h, void *stream, GemvParams P, int w_fp16, const char *who) {
+// w_kind: 0 fp32, 1 fp16, 2 int8 (packed words, P.scales and P.ag set)
+int launch_gemv(mx230_handle *h, void *stream, GemvParams P, int w_kind, const char *who) {
     MX_REQUIRE(h && P.y && P.x && P.w, MX230_ERR_INVALID_ARG, "%s: null argument", who);
     MX_REQUIRE(P.n_in > 0 && P.n_out > 0 && P.n_out % 4 == 0, MX230_ERR_INVALID_ARG,
                "%s: n_in %d, n_out %d (n_out must be a positive multiple of 4)", who, P.n_in, P.n_out);
@@ -193,7 +240,13 @@ int launch_gemv(mx230_handle *h, void *stream, GemvParams P, int w_fp16, const c
     const int max_slices = (P.n_in + 15) / 16;
     if (n_slices > max_slices) n_slices = max_slices;
     if (n_slices < 1) n_slices = 1;
-    P.rows_per_slice = ((P.n_in + n_slices - 1) / n_slices + PJ_ROWLANES - 1) / PJ_ROWLANES * PJ_ROWLANES;
+    // int8: a slice holds whole activation groups and whole passes of the eight row lanes over 4-row words
+    const int gran = w_kind == 2 ? 4 * PJ_ROWLANES : PJ_ROWLANES;
+    if (w_kind == 2) {
+        MX_REQUIRE(P.scales && (P.ag == 4 || P.ag == 8) && P.n_in % 8 == 0, MX230_ERR_INVALID_ARG,
+                   "%s: int8 weights need scales, an activation group of 4 or 8 and n_in %% 8 == 0 (n_in %d)", who, P.n_in);
+    }
+    P.rows_per_slice = ((P.n_in + n_slices - 1) / n_slices + gran - 1) / gran * gran;
     n_slices = (P.n_in + P.rows_per_slice - 1) / P.rows_per_slice;
     if (n_slices > 1) {
         const size_t need = (size_t)n_slices * P.n_out * sizeof(float);
@@ -207,8 +260,9 @@ int launch_gemv(mx230_handle *h, void *stream, GemvParams P, int w_fp16, const c
     mx230_device_guard guard(h->device);
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid(n_blocks, n_slices);
-    const size_t sm = (size_t)P.rows_per_slice * sizeof(float);
-    if (w_fp16) MX_LAUNCH(h, st, MX230_K_GEMV, (gemv_heads_kernel<__half><<<grid, PJ_THREADS, sm, st>>>(P)));
+    const size_t sm = (size_t)P.rows_per_slice * sizeof(float);   // int8: n/4 words + n/ag scales <= n floats
+    if (w_kind == 2) MX_LAUNCH(h, st, MX230_K_GEMV, (gemv_heads_kernel<int8_t><<<grid, PJ_THREADS, sm, st>>>(P)));
+    else if (w_kind == 1) MX_LAUNCH(h, st, MX230_K_GEMV, (gemv_heads_kernel<__half><<<grid, PJ_THREADS, sm, st>>>(P)));
     else MX_LAUNCH(h, st, MX230_K_GEMV, (gemv_heads_kernel<float><<<grid, PJ_THREADS, sm, st>>>(P)));
     return MX230_OK;
 }
@@ -219,11 +273,20 @@ extern "C" int mx230_gemv(mx230_handle *h, void *stream, float *y, const float *
                           const float *b, int n_in, int n_out, int accum) {
     GemvParams P{};
     P.y = y, P.x = x, P.w = w, P.b = b, P.n_in = n_in, P.n_out = n_out, P.accum = accum ? 1 : 0;
-    return launch_gemv(h, stream, P, w_fp16, "gemv");
+    return launch_gemv(h, stream, P, w_fp16 ? 1 : 0, "gemv");
+}
+
+extern "C" int mx230_gemv_int8(mx230_handle *h, void *stream, float *y, const float *x, const void *w_packed,
+                               const float *scales, const float *b, int n_in, int n_out, int accum, int act_group) {
+    GemvParams P{};
+    P.y = y, P.x = x, P.w = w_packed, P.b = b, P.n_in = n_in, P.n_out = n_out, P.accum = accum ? 1 : 0;
+    P.scales = scales, P.ag = act_group;
+    return launch_gemv(h, stream, P, 2, "gemv_int8");
 }
 
 extern "C" int mx230_qkv_rope_kvwrite(mx230_handle *h, void *stream, float *qkv, const float *x, const void *w,
-                                      int w_fp16, const float *b, int n_in, int pos, const int *pos_ptr,
+                                      int w_kind, const float *w_scales, int act_group, const float *b, int n_in,
+                                      int pos, const int *pos_ptr,
                                       int n_head, int n_kv_head, int head_dim, float theta, float *kcache,
                                       float *vcache, int8_t *kq, int8_t *vq, float *ks, float *vs, float *kb,
                                       float *vb, const int *bt, int bs) {
@@ -234,9 +297,11 @@ extern "C" int mx230_qkv_rope_kvwrite(mx230_handle *h, void *stream, float *qkv,
     MX_REQUIRE(pos_ptr || pos >= 0, MX230_ERR_INVALID_ARG, "qkv_rope_kvwrite: negative position %d", pos);
     MX_REQUIRE(bt == nullptr || bs > 0, MX230_ERR_INVALID_ARG, "qkv_rope_kvwrite: block size %d", bs);
     GemvParams P{};
+    MX_REQUIRE(w_kind >= 0 && w_kind <= 2, MX230_ERR_INVALID_ARG, "qkv_rope_kvwrite: weight kind %d", w_kind);
     P.y = qkv, P.x = x, P.w = w, P.b = b, P.n_in = n_in, P.n_out = (n_head + 2 * n_kv_head) * 64, P.accum = 0;
+    P.scales = w_scales, P.ag = act_group;
     P.e.enabled = 1, P.e.pos = pos, P.e.pos_dev = pos_ptr, P.e.n_head = n_head, P.e.n_kv_head = n_kv_head;
     P.e.theta = theta, P.e.kcache = kcache, P.e.vcache = vcache, P.e.kq = kq, P.e.vq = vq;
     P.e.ks = ks, P.e.vs = vs, P.e.kb = kb, P.e.vb = vb, P.e.bt = bt, P.e.bs = bs;
-    return launch_gemv(h, stream, P, w_fp16, "qkv_rope_kvwrite");
+    return launch_gemv(h, stream, P, w_kind, "qkv_rope_kvwrite");
 }

@@ -343,14 +343,23 @@ def gemv(h: Handle, y, x, w, b=None, accum=False, stream=None):
                            ptr(b), n_in, n_out, int(accum)))
 
 
+def gemv_int8(h: Handle, y, x, w_packed, scales, b=None, accum=False, act_group=8, stream=None):
+    """gemv_int8 (llm.cu:226-316): `w_packed` int32 [n_in / 4][n_out], four consecutive input rows per word."""
+    n_in, n_out = w_packed.shape[0] * 4, w_packed.shape[1]
+    check(lib().mx230_gemv_int8(h._h, stream_ptr(stream), ptr(y), ptr(x), ptr(w_packed), ptr(scales), ptr(b),
+                                n_in, n_out, int(accum), act_group))
+
+
 def qkv_rope_kvwrite(h: Handle, qkv, x, w, b, pos, c: KvCache, n_head, n_kv_head, theta, pg: Paging | None = None,
-                     stream=None):
+                     stream=None, w_scales=None, act_group=8):
     """The qkv step of one decode token in one launch (gemv + rope + KV write of gpu.rs:2558-2646):
     `pos` is a host int or an int32 device tensor (the graph-captured form)."""
-    n_in = w.shape[0]
+    int8 = w.dtype == torch.int32   # packed int8 weights
+    n_in = w.shape[0] * (4 if int8 else 1)
+    kind = 2 if int8 else int(w.dtype == torch.float16)
     dyn = not isinstance(pos, int)
     caches = (None, None, *c.q8_args()) if c.quant else (ptr(c.k), ptr(c.v), None, None, None, None, None, None)
     check(lib().mx230_qkv_rope_kvwrite(h._h, stream_ptr(stream), ptr(qkv), ptr(x), ptr(w),
-                                       int(w.dtype == torch.float16), ptr(b), n_in, 0 if dyn else pos,
+                                       kind, ptr(w_scales), act_group, ptr(b), n_in, 0 if dyn else pos,
                                        ptr(pos) if dyn else None, n_head, n_kv_head, 64, theta, *caches,
                                        ptr(pg.table_dev) if pg else None, pg.block_size if pg else 0))

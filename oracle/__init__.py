@@ -301,3 +301,24 @@ def gemv(x, w, b=None, y=None, accum=False):
     lib().orc_gemv(_f(out), _f(x), _f(w), _f(None if b is None else np.ascontiguousarray(b, np.float32)),
                    n_in, n_out, 1 if accum else 0)
     return out
+
+
+def pack_int8_weights(w8):
+    """int8 [n_in][n_out] -> int32 words of four consecutive input rows, w32[(i/4)][o], byte j = row 4(i/4)+j
+    (the reference's load-time repacking, llm.cu:183-188)."""
+    w8 = np.ascontiguousarray(w8, np.int8)
+    n_in, n_out = w8.shape
+    u = w8.astype(np.uint8).astype(np.uint32).reshape(n_in // 4, 4, n_out)
+    return np.ascontiguousarray((u[:, 0] | (u[:, 1] << 8) | (u[:, 2] << 16) | (u[:, 3] << 24)).astype(np.uint32).view(np.int32))
+
+
+def gemv_int8(x, w32, scales, b=None, y=None, accum=False, ag=8):
+    """The reference gemv_int8 (llm.cu:226-316) on packed weights."""
+    x = np.ascontiguousarray(x, np.float32)
+    w32 = np.ascontiguousarray(w32, np.int32)
+    n_in, n_out = w32.shape[0] * 4, w32.shape[1]
+    out = np.zeros(n_out, np.float32) if y is None else np.ascontiguousarray(y, np.float32).copy()
+    lib().orc_gemv_int8(_f(out), _f(x), _i(w32), _f(np.ascontiguousarray(scales, np.float32)),
+                        _f(None if b is None else np.ascontiguousarray(b, np.float32)), n_in, n_out,
+                        1 if accum else 0, ag)
+    return out

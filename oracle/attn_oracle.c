@@ -671,3 +671,43 @@ void orc_gemv(float *y, const float *x, const float *w, const float *b, int n_in
         y[o] = accum ? y[o] + r : r;
     }
 }
+
+/* gemv_int8 (03-llm-engine/kernels/llm.cu:226-316): the activation row is quantised per group of `ag`
+ * values (absmax / 127, codes clamp(rne(x * (127 / amax)), +-127), group scale amax / 127, or 1 when the
+ * group is all zero); weights are int32 words of four consecutive input rows, w32[(i/4)*n_out + o];
+ * per output column: acc += (float)(integer dot of the group) * xs[g] over the groups in order, then
+ * y[o] (+)= acc * scales[o] + b[o]. */
+void orc_gemv_int8(float *y, const float *x, const int *w32, const float *scales, const float *b, int n_in,
+                   int n_out, int accum, int ag) {
+    int n_groups = n_in / ag;
+    signed char *xq = (signed char *)malloc((size_t)n_in);
+    float *xs = (float *)malloc(sizeof(float) * (size_t)n_groups);
+    for (int g = 0; g < n_groups; ++g) {
+        const float *xg = x + (size_t)g * ag;
+        float amax = 0.0f;
+        for (int j = 0; j < ag; ++j) amax = fmaxf(amax, fabsf(xg[j]));
+        float id = amax > 0.0f ? 127.0f / amax : 0.0f;
+        for (int j = 0; j < ag; ++j) {
+            int v = (int)nearbyintf(xg[j] * id);
+            v = v > 127 ? 127 : (v < -127 ? -127 : v);
+            xq[(size_t)g * ag + j] = (signed char)v;
+        }
+        xs[g] = amax > 0.0f ? amax / 127.0f : 1.0f;
+    }
+    for (int o = 0; o < n_out; ++o) {
+        float acc = 0.0f;
+        for (int g = 0; g < n_groups; ++g) {
+            int ig = 0;
+            for (int q = 0; q < ag / 4; ++q) {
+                int word = w32[(size_t)((ag / 4) * g + q) * n_out + o];
+                for (int j = 0; j < 4; ++j)
+                    ig += (int)(signed char)((word >> (8 * j)) & 0xFF) * (int)xq[(size_t)g * ag + 4 * q + j];
+            }
+            acc += (float)ig * xs[g];
+        }
+        float r = acc * scales[o] + (b ? b[o] : 0.0f);
+        y[o] = accum ? y[o] + r : r;
+    }
+    free(xq);
+    free(xs);
+}

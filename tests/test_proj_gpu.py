@@ -84,6 +84,46 @@ def test_fused_qkv_step(handle, quant, affine, paged, dyn):
         assert torch.isfinite(out).all()
 
 
+@pytest.mark.parametrize("n_in,n_out", [(896, 1152), (2048, 2560), (64, 8), (4864, 896)])
+@pytest.mark.parametrize("ag", [4, 8])
+def test_gemv_int8_matches_oracle(handle, n_in, n_out, ag):
+    rng = np.random.default_rng(n_in + ag)
+    x = oracle.normal((n_in,), 630, 0)
+    x[: 2 * ag] = 0.0                                   # an all-zero activation group (scale 1, codes 0)
+    w32 = oracle.pack_int8_weights(rng.integers(-127, 128, size=(n_in, n_out), dtype=np.int8))
+    scales = (np.abs(oracle.normal((n_out,), 631, 0)) * 0.01 + 0.001).astype(np.float32)
+    b = oracle.normal((n_out,), 632, 0)
+    y0 = oracle.normal((n_out,), 633, 0)
+    for accum, bias in ((False, True), (True, False)):
+        want = oracle.gemv_int8(x, w32, scales, b if bias else None, y0, accum, ag)
+        y = dev(y0)
+        la.gemv_int8(handle, y, dev(x), dev(w32), dev(scales), dev(b) if bias else None, accum, ag)
+        handle.check_status()
+        assert_close(y.cpu().numpy(), want, f"gemv_int8 ag={ag} accum={accum}", max_abs=2e-4 * max(1.0, float(np.abs(want).max())), mean_rel=2e-5)
+
+
+def test_fused_qkv_step_with_int8_weights(handle):
+    nh, nkv, n_in, theta, pos = 14, 2, 896, 1e6, 21
+    qd, kvd = nh * 64, nkv * 64
+    n_out = qd + 2 * kvd
+    rng = np.random.default_rng(7)
+    x = oracle.normal((n_in,), 640, 0)
+    w32 = oracle.pack_int8_weights(rng.integers(-127, 128, size=(n_in, n_out), dtype=np.int8))
+    scales = np.full(n_out, 0.002, np.float32)
+    b = oracle.normal((n_out,), 641, 0)
+    c = la.KvCache(64, nkv, 64, True)
+    qkv = torch.full((n_out,), float("nan"), device="cuda")
+    la.qkv_rope_kvwrite(handle, qkv, dev(x), dev(w32), dev(b), pos, c, nh, nkv, theta, w_scales=dev(scales), act_group=8)
+    handle.check_status()
+    got = qkv.cpu().numpy()
+    want = oracle.rope_qkv_row(oracle.gemv_int8(x, w32, scales, b, ag=8), pos, nh, nkv, 64, theta)
+    assert_close(got, want, "fused qkv row, int8 weights", max_abs=2e-4 * float(np.abs(want).max()), mean_rel=2e-5)
+    q8 = oracle.Q8Cache(64, nkv)
+    oracle.quantize_kv_row(q8, got, pos, qd)
+    assert np.array_equal(c.k[pos].cpu().numpy(), q8.kq[pos]) and np.array_equal(c.v[pos].cpu().numpy(), q8.vq[pos])
+    assert np.array_equal(c.ks[pos].cpu().numpy(), q8.ks[pos]) and np.array_equal(c.vb[pos].cpu().numpy(), q8.vb[pos])
+
+
 def test_gemv_rejects_bad_arguments(handle):
     from mx230_b200._lib import Mx230Error
     with pytest.raises(Mx230Error):
