@@ -299,6 +299,10 @@ int mx230_attn_decode_partial(mx230_handle *h, void *stream, float *part_m, floa
                               long long seq_rows, int qkv_stride);
 int mx230_merge_partials(mx230_handle *h, void *stream, float *out, const float *m,
                          const float *l, const float *acc, int parts, int rows, int head_dim);
+/* the same merge straight from the all-gathered buffer [parts][m[rows] | l[rows] | acc[rows][64]]
+ * (rows even, so that every part's accumulators stay 16-byte aligned) */
+int mx230_merge_partials_packed(mx230_handle *h, void *stream, float *out, const float *gathered,
+                                int parts, int rows, int head_dim);
 
 /* prefill attention of n_tok new rows at absolute positions pos0+qi over cache keys
  * 0..=pos0+qi: attn_prefill / _q8 / _paged / _q8_paged / _dp4a / _dp4a_paged

@@ -1122,20 +1122,23 @@ decode_f32_ring_kernel(const DecodeParams P) {
 }
 
 // Log-sum-exp merge of gathered partial triples: one thread per (row, 4 dims).
+// Part p keeps its maxima and sums at m + p*ml_stride, l + p*ml_stride and its accumulators at
+// acc + p*acc_stride (floats): rows / rows*64 for separate arrays, rows*66 for both when the parts
+// are the ranks' packed [m | l | acc] buffers as the all-gather leaves them.
 __global__ void merge_partials_kernel(float *out, const float *m, const float *l, const float *acc,
-                                      int parts, int rows) {
+                                      int parts, int rows, size_t ml_stride, size_t acc_stride) {
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * 16) return;
     int r = idx >> 4, d4 = (idx & 15) * 4;
     float mm = -CUDART_INF_F;
-    for (int p = 0; p < parts; ++p) mm = fmaxf(mm, m[(size_t)p * rows + r]);
+    for (int p = 0; p < parts; ++p) mm = fmaxf(mm, m[(size_t)p * ml_stride + r]);
     float ll = 0.0f;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < parts; ++p) {
-        float mp = m[(size_t)p * rows + r];
+        float mp = m[(size_t)p * ml_stride + r];
         float w = (mp == -CUDART_INF_F) ? 0.0f : __expf(mp - mm);
-        ll += l[(size_t)p * rows + r] * w;
-        float4 v = *(const float4 *)(acc + ((size_t)p * rows + r) * 64 + d4);
+        ll += l[(size_t)p * ml_stride + r] * w;
+        float4 v = *(const float4 *)(acc + (size_t)p * acc_stride + (size_t)r * 64 + d4);
         a.x += v.x * w, a.y += v.y * w, a.z += v.z * w, a.w += v.w * w;
     }
     float inv = 1.0f / ll;
@@ -1436,7 +1439,25 @@ extern "C" int mx230_merge_partials(mx230_handle *h, void *stream, float *out, c
     mx230_device_guard guard(h->device);
     cudaStream_t st = (cudaStream_t)stream;
     MX_LAUNCH(h, st, MX230_K_MERGE,
-              (merge_partials_kernel<<<(rows * 16 + 127) / 128, 128, 0, st>>>(out, m, l, acc, parts, rows)));
+              (merge_partials_kernel<<<(rows * 16 + 127) / 128, 128, 0, st>>>(out, m, l, acc, parts, rows, (size_t)rows,
+                                                                              (size_t)rows * 64)));
+    return MX230_OK;
+}
+
+extern "C" int mx230_merge_partials_packed(mx230_handle *h, void *stream, float *out, const float *gathered,
+                                           int parts, int rows, int head_dim) {
+    MX_REQUIRE(h && out && gathered, MX230_ERR_INVALID_ARG, "merge_partials_packed: null argument");
+    MX_REQUIRE(head_dim == 64, MX230_ERR_UNSUPPORTED, "merge_partials_packed: head_dim must be 64");
+    MX_REQUIRE(parts > 0 && rows >= 0, MX230_ERR_INVALID_ARG, "merge_partials_packed: bad sizes");
+    MX_REQUIRE(rows % 2 == 0 && (((uintptr_t)gathered) & 15) == 0, MX230_ERR_INVALID_ARG,
+               "merge_partials_packed: rows must be even and the buffer 16-byte aligned");
+    if (rows == 0) return MX230_OK;
+    mx230_device_guard guard(h->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t f = (size_t)rows * 66;   // floats per part: [m | l | acc]
+    MX_LAUNCH(h, st, MX230_K_MERGE,
+              (merge_partials_kernel<<<(rows * 16 + 127) / 128, 128, 0, st>>>(out, gathered, gathered + rows,
+                                                                              gathered + 2 * (size_t)rows, parts, rows, f, f)));
     return MX230_OK;
 }
 

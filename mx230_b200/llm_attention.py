@@ -235,6 +235,11 @@ def merge_partials(h: Handle, out, m, l, acc, parts, rows, head_dim=64, stream=N
                                      parts, rows, head_dim))
 
 
+def merge_partials_packed(h: Handle, out, gathered, parts, rows, head_dim=64, stream=None):
+    """Merge straight from the all-gathered buffer [parts][m | l | acc] (rows even)."""
+    check(lib().mx230_merge_partials_packed(h._h, stream_ptr(stream), ptr(out), ptr(gathered), parts, rows, head_dim))
+
+
 # ---------------------------------------------------------------- the step
 def decode_step(h: Handle, out, qkv, c: KvCache, pos: int, n_head, n_kv_head, head_dim, theta,
                 pg: Paging | None = None, host_table=None, use_rope=True, stream=None):

@@ -71,7 +71,8 @@ def gather_partials(plan: SplitKvPlan, local, gathered, group=None):
     into `gathered` [world, floats_per_rank].  One collective per decode step."""
     import torch.distributed as dist
     if plan.world == 1:
-        gathered[0].copy_(local)
+        if local.data_ptr() != gathered.data_ptr():
+            gathered[0].copy_(local)
         return gathered
     dist.all_gather_into_tensor(gathered.view(-1), local.view(-1), group=group)
     return gathered
@@ -84,8 +85,10 @@ class SplitKvDecoder:
     def __init__(self, handle, plan: SplitKvPlan, rank: int, device="cuda", group=None):
         import torch
         self.h, self.plan, self.rank, self.group = handle, plan, rank, group
-        self.local = torch.zeros(plan.floats_per_rank, dtype=torch.float32, device=device)
         self.gathered = torch.zeros(plan.world, plan.floats_per_rank, dtype=torch.float32, device=device)
+        # alone, the rank writes its partial straight into the gathered buffer
+        self.local = self.gathered[0] if plan.world == 1 else torch.zeros(
+            plan.floats_per_rank, dtype=torch.float32, device=device)
         self.out = torch.zeros(plan.rows, plan.head_dim, dtype=torch.float32, device=device)
         # packed views: [m | l | acc] of this rank, and contiguous gathered m / l / acc
         r = plan.rows
@@ -107,7 +110,10 @@ class SplitKvDecoder:
             self.l.zero_()
             self.acc.zero_()
         gather_partials(p, self.local, self.gathered, self.group)
-        m, l, acc = p.unpack(self.gathered)
-        self.gm.copy_(m), self.gl.copy_(l), self.ga.copy_(acc)
-        la.merge_partials(self.h, self.out, self.gm, self.gl, self.ga, p.world, p.rows, p.head_dim)
+        if p.rows % 2 == 0:   # merge straight from the gathered buffer
+            la.merge_partials_packed(self.h, self.out, self.gathered, p.world, p.rows, p.head_dim)
+        else:
+            m, l, acc = p.unpack(self.gathered)
+            self.gm.copy_(m), self.gl.copy_(l), self.ga.copy_(acc)
+            la.merge_partials(self.h, self.out, self.gm, self.gl, self.ga, p.world, p.rows, p.head_dim)
         return self.out

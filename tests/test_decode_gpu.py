@@ -265,6 +265,13 @@ def test_slab_batched_and_partial_merge(handle):
         assert_close(merged.cpu().numpy().reshape(n_seq, qd), full, "partial+merge", **TOL)
         om = oracle.merge_partials(pm.cpu().numpy(), pl.cpu().numpy(), pa.cpu().numpy())
         assert_close(merged.cpu().numpy(), om, "merge kernel vs oracle merge", **TOL)
+        # the same merge straight from the ranks' packed [m | l | acc] buffers
+        packed = torch.cat([pm, pl, pa.reshape(3, rows * 64)], dim=1).contiguous()
+        merged2 = torch.full((rows, 64), 7.0, device="cuda")
+        la.merge_partials_packed(handle, merged2, packed, 3, rows)
+        assert torch.equal(merged2, merged)
+        with pytest.raises(_lib.Mx230Error):   # odd row count: the parts would lose their alignment
+            la.merge_partials_packed(handle, merged2, packed, 3, rows - 1)
         # one partial of the oracle for rank 1 of sequence 2
         m, l, acc = oracle.gqa_partial(qs[2], cuts[1], cuts[2], nh, nkv, 64, cache=_slab(q8, 2, ctx))
         got_acc = pa[1].cpu().numpy().reshape(n_seq, nh, 64)[2]
