@@ -333,7 +333,8 @@ def run_ours(args):
         value = world * STEP_FLOP / (ms_step * 1e-3) / 1e12
         e2e_val = world * STEP_FLOP / (e2e_ms / e2e_steps * 1e-3) / 1e12
         kern = {}
-        for name, flop in (("flash_fwd_kernel", FWD_FLOP), ("bwd_dq_kernel", DQ_FLOP), ("bwd_dkv_kernel", DKV_FLOP)):
+        for name, flop in (("flash_fwd_kernel", FWD_FLOP), ("bwd_fused_kernel", BWD_FLOP), ("bwd_dq_kernel", DQ_FLOP),
+                           ("bwd_dkv_kernel", DKV_FLOP)):
             if name in prof:
                 cnt, tot = prof[name]
                 kern[name] = {"launches": cnt, "ms_per_launch": tot / cnt,
@@ -372,8 +373,8 @@ def run_ours(args):
                        "l2": "inputs larger than L2 (4 x 50 MB fp32 operands per step)",
                        "entry_points": "mx230_attn_flash_lse + mx230_attn_bwd_preprocess + mx230_attn_bwd_flash"},
             "fwd_tflops": world * FWD_FLOP / (kern["flash_fwd_kernel"]["ms_per_launch"] * 1e-3) / 1e12,
-            "bwd_tflops": world * BWD_FLOP / ((kern["bwd_dq_kernel"]["ms_per_launch"] +
-                                               kern["bwd_dkv_kernel"]["ms_per_launch"]) * 1e-3) / 1e12,
+            "bwd_tflops": world * BWD_FLOP / (sum(kern[k]["ms_per_launch"] for k in kern if k.startswith("bwd_") and
+                                                  "achieved_tflops" in kern[k]) * 1e-3) / 1e12,
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,

@@ -57,8 +57,12 @@ enum {
 enum {
     MX230_OPT_Q8_SCORE_MODE = 1, /* MX230_Q8_SCORE_* (default REF) */
     MX230_OPT_DECODE_CHUNK = 2,  /* keys per decode CTA; 0 = automatic */
-    MX230_OPT_DECODE_TENSOR = 3  /* int8 decode in the reference score mode: 1 (default) = the GQA group's two
+    MX230_OPT_DECODE_TENSOR = 3, /* int8 decode in the reference score mode: 1 (default) = the GQA group's two
                                     contractions on warp-level tensor-core tiles, 0 = CUDA cores only */
+    MX230_OPT_BWD_TWO_PASS = 4   /* mx230_attn_bwd_flash*: 0 (default) = one fused pass, dK/dV written once and dQ
+                                    summed with fp32 reductions (order of the partial sums not fixed);
+                                    1 = the reference's atomic-free split, a dQ pass and a dK/dV pass,
+                                    bit-reproducible */
 };
 
 /* kernel ids of the profiling interface */
@@ -76,7 +80,8 @@ enum {
     MX230_K_MERGE = 10,
     MX230_K_PREFILL = 11,
     MX230_K_GEMV = 12,
-    MX230_K_COUNT = 13
+    MX230_K_BWD_FUSED = 13,
+    MX230_K_COUNT = 14
 };
 
 typedef struct mx230_handle mx230_handle;

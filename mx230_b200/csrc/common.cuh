@@ -37,6 +37,7 @@ struct mx230_handle {
     int q8_score_mode;     // MX230_Q8_SCORE_*
     int decode_chunk;      // keys per decode CTA (0 = automatic)
     int decode_tensor;     // int8 decode, reference score mode: tensor-core tiles (1) or CUDA cores (0)
+    int bwd_two_pass;      // flash backward: two atomic-free passes (1) or one fused pass with dQ reductions (0)
     long long launches;    // kernels launched through this handle
     mx230_encode_tiled_fn encode_tiled;
     // per-kernel timing: event pairs recorded around launches while enabled
@@ -247,6 +248,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
+// 16 lanes x 32 columns of 32-bit in the 256-bit pattern: for each group k of 8 columns, thread i gets
+// columns 8k + 2(i%4) + {0,1} of lane base + i/4 in r[4k], r[4k+1] and of lane base + i/4 + 8 in
+// r[4k+2], r[4k+3] -- four threads share a 32-byte piece of one row.
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -287,6 +301,24 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
     d |= (uint64_t)1 << 46;                     // descriptor version of this architecture
     d |= (uint64_t)2 << 61;                     // 128-byte swizzle
     return d;
+}
+
+// The same tile layout read as an MN-major operand wider than one 64-element row: the next 64
+// elements of the MN axis start `mn_chunk_bytes` further on (a second tile of the same shape).
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t mn_chunk_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(mn_chunk_bytes >> 4) << 16;  // leading-dim byte offset: between 64-element chunks of the MN axis
+    d |= (uint64_t)(1024 >> 4) << 32;            // stride between 8-row groups of the contraction axis
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Vector fp32 reduction into global memory (no return value).  L2 works on 32-byte sectors: a warp
+// instruction should cover whole sectors (four neighbouring lanes with 8 bytes each).
+__device__ __forceinline__ void red_add_f32x2(float *dst, float a, float b) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(dst), "f"(a), "f"(b) : "memory");
 }
 
 // Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulation.

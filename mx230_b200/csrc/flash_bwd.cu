@@ -29,10 +29,11 @@
 // The 1/sqrt(d) factor of dS is applied to the fp32 accumulators in the epilogue (exact: 2^-3).
 #include <math_constants.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
-
 constexpr int HD = 64;
 constexpr int BT = 128;          // rows of the owned tile (queries in dQ, keys in dK/dV)
 constexpr int BS = 128;          // rows of a streamed tile
@@ -43,7 +44,7 @@ constexpr int STR_BYTES = BS * HD * 2;   // 16 KB
 constexpr int BWD_THREADS = 512;
 // warpgroups: compute left, compute right, {TMA, X, acc0, Y}, {acc1, 3 idle}.
 // setmaxnreg moves registers only inside the CTA's launch-time allocation (128 per thread for 512 threads)
-constexpr int REGS_COMPUTE = 216, REGS_SERVICE = 40;
+constexpr int REGS_COMPUTE = 208, REGS_SERVICE = 48;
 static_assert(8 * REGS_COMPUTE + 8 * REGS_SERVICE <= 16 * 128, "setmaxnreg budget exceeds the launch-time register allocation");
 
 // shared memory map (after 1024-byte alignment)
@@ -52,7 +53,12 @@ constexpr int SM_OWN_B = SM_OWN_A + OWN_BYTES;           // V (dK/dV pass)
 constexpr int SM_STR_A = SM_OWN_B + OWN_BYTES;           // STAGES x 16 KB: K / Q
 constexpr int SM_STR_B = SM_STR_A + STAGES * STR_BYTES;  // STAGES x 16 KB: V / dO
 constexpr int SM_LD = SM_STR_B + STAGES * STR_BYTES;     // STAGES x 2 x 128 floats: -L*log2e, -Delta (dK/dV)
-constexpr int SM_BAR = SM_LD + STAGES * 2 * BS * 4;
+constexpr int SM_DS = SM_LD + STAGES * 2 * BS * 4;        // fused pass: dS^T as bf16, two [128 keys][64 queries] tiles
+constexpr int DS_HALF_BYTES = BT * HS * 2;               // 16 KB
+constexpr int SM_DS1_A = SM_STR_A + (STAGES - 1) * STR_BYTES;   // second E buffer: the last stage's slots
+constexpr int SM_DS1_B = SM_STR_B + (STAGES - 1) * STR_BYTES;
+constexpr int SM_BAR = SM_DS + 2 * DS_HALF_BYTES;
+static_assert(SM_DS % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 constexpr int SM_TOTAL = SM_BAR + 256;
 constexpr int SM_ALLOC = SM_TOTAL + 1024;
 
@@ -63,13 +69,17 @@ constexpr int BAR_SDP_FULL = BAR_STR_EMPTY + STAGES;     // MMA -> compute: X, Y
 constexpr int BAR_SDP_FREE = BAR_SDP_FULL + 1;           // compute -> MMA: X, Y in registers
 constexpr int BAR_DS_READY = BAR_SDP_FREE + 1;           // compute -> MMA: E, P written
 constexpr int BAR_ACC_DONE = BAR_DS_READY + 1;
-constexpr int N_BARS = BAR_ACC_DONE + 1;
+constexpr int BAR_DQ_FULL = BAR_ACC_DONE + 1;            // fused pass: MMA -> drain warps
+constexpr int BAR_DQ_FREE = BAR_DQ_FULL + 1;             // drain warps -> MMA
+constexpr int N_BARS = BAR_DQ_FREE + 1;
 
 // tensor memory columns
 constexpr int TM_X = 0, TM_Y = 128, TM_E = 256, TM_P = 320;   // E, P: bf16 pairs, 64 columns each
 constexpr int TM_ACC0 = 384, TM_ACC1 = 448;
 // dQ pass only (no second accumulator there): the owned Q and dO tiles as bf16 A operands, 32 columns each
 constexpr int TM_OWN_A = 448, TM_OWN_B = 480;
+// fused pass: E lives in shared memory (the dQ contraction needs it there), which frees 64 columns for dQ's tile
+constexpr int TMF_P = 256, TMF_ACC0 = 320, TMF_ACC1 = 384, TMF_DQ = 448;
 constexpr int TM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -78,6 +88,7 @@ struct BwdParams {
     const float *Delta;  // [BH][N]
     float *out0;         // dQ (dQ pass) / dK (dK/dV pass)   [BH][N][64]
     float *out1;         // unused / dV
+    float *dq;           // fused pass: dQ, zeroed before the launch, summed into with fp32 reductions
     const uint4 *own_a;  // dQ pass: bf16 Q  [BH][N][64], read straight into tensor memory
     const uint4 *own_b;  // dQ pass: bf16 dO [BH][N][64]
     int n;
@@ -86,6 +97,8 @@ struct BwdParams {
 };
 
 // MODE 0: dQ pass (own = Q, dO; stream = K, V).  MODE 1: dK/dV pass (own = K, V; stream = Q, dO).
+// MODE 2: the dK/dV pass that also forms every tile's dQ contribution (dS K, a fifth MMA stream reading
+// dS^T from shared memory as an MN-major A operand) and adds it to dQ in global memory.
 template <int MODE>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ CUtensorMap tmOwnB,
@@ -112,17 +125,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
         else it_beg = own0 / BS;
     }
     const int n = it_end - it_beg;  // >= 1
+    constexpr bool FUSED = MODE == 2;
+    // the fused pass streams through three stages: the fourth one's two 16 KB slots hold its second E buffer
+    constexpr int NST = FUSED ? STAGES - 1 : STAGES;
+    constexpr int N_ACC = MODE == 0 ? 1 : 2;   // accumulate issuers: one commit each per tile
+    constexpr int tP = FUSED ? TMF_P : TM_P, tACC0 = FUSED ? TMF_ACC0 : TM_ACC0, tACC1 = FUSED ? TMF_ACC1 : TM_ACC1;
 
     if (tid == 0) {
         mx::mbar_init(bar(BAR_OWN_FULL), MODE == 0 ? 2 * BT / 32 : 1);  // dQ: every compute warp; dK/dV: TMA
         for (int s = 0; s < STAGES; ++s) {
-            mx::mbar_init(bar(BAR_STR_FULL + s), MODE == 1 ? 33 : 1);
-            mx::mbar_init(bar(BAR_STR_EMPTY + s), MODE == 1 ? 2 : 1);   // one commit per accumulate issuer
+            mx::mbar_init(bar(BAR_STR_FULL + s), MODE >= 1 ? 33 : 1);
+            mx::mbar_init(bar(BAR_STR_EMPTY + s), N_ACC);
         }
-        mx::mbar_init(bar(BAR_SDP_FULL), 2);              // the X and the Y issuer
+        mx::mbar_init(bar(BAR_SDP_FULL), FUSED ? 1 : 2);  // the X and the Y issuer (one thread in the fused pass)
+        mx::mbar_init(bar(BAR_DQ_FULL), 1);
+        mx::mbar_init(bar(BAR_DQ_FREE), 4);
         mx::mbar_init(bar(BAR_SDP_FREE), 2 * BT / 32);    // one elected lane per compute warp arrives
         mx::mbar_init(bar(BAR_DS_READY), 2 * BT / 32);
-        mx::mbar_init(bar(BAR_ACC_DONE), MODE == 1 ? 2 : 1);
+        mx::mbar_init(bar(BAR_ACC_DONE), N_ACC);
         *abort_flag = 0;
         mx::mbar_fence_init();
     }
@@ -139,7 +159,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             if (lane == 0) {
                 mx::tma_prefetch_desc(&tmStrA);
                 mx::tma_prefetch_desc(&tmStrB);
-                if (MODE == 1) {
+                if (MODE >= 1) {
                     mx::tma_prefetch_desc(&tmOwnA);
                     mx::tma_prefetch_desc(&tmOwnB);
                     mx::mbar_expect_tx(bar(BAR_OWN_FULL), 2 * OWN_BYTES);
@@ -149,11 +169,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             }
             bool ok = true;
             for (int y = 0; y < n; ++y) {
-                const int s = y % STAGES, r = y / STAGES;
+                const int s = y % NST, r = y / NST;
                 const int row0 = (it_beg + y) * BS;
                 // -L*log2(e) and -Delta of the streamed queries: fetched before the wait, stored after it
                 float lv[4], dv[4];
-                if (MODE == 1) {
+                if (MODE >= 1) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const int q = row0 + u * 32 + lane;
@@ -171,7 +191,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                     mx::tma_load_3d(smem_base + SM_STR_A + s * STR_BYTES, &tmStrA, bar(BAR_STR_FULL + s), 0, row0, bh);
                     mx::tma_load_3d(smem_base + SM_STR_B + s * STR_BYTES, &tmStrB, bar(BAR_STR_FULL + s), 0, row0, bh);
                 }
-                if (MODE == 1) {
+                if (MODE >= 1) {
                     float *ld = (float *)(smem + SM_LD + s * (2 * BS * 4));
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -182,7 +202,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 }
             }
             __syncwarp();
-        } else if (warp == 9 || warp == 11) {
+        } else if (!FUSED && (warp == 9 || warp == 11)) {
             // ------------------------- MMA issuers 1, 2: X (warp 9) and Y (warp 11) ---------
             // (the loops are kept free of run-time choices between instruction forms, which slow
             // the issuing thread down)
@@ -195,7 +215,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 const uint32_t dst = tmem + (is_y ? TM_Y : TM_X);
                 bool ok = mx::mbar_wait(bar(BAR_OWN_FULL), 0, abort_flag, P.status);
                 for (int y = 0; y < n && ok; ++y) {
-                    const int s = y % STAGES, r = y / STAGES;
+                    const int s = y % NST, r = y / NST;
                     ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
                     // as soon as both warpgroups hold the previous X, Y in registers
                     if (ok && y > 0) ok = mx::mbar_wait(bar(BAR_SDP_FREE), (y - 1) & 1, abort_flag, P.status);
@@ -213,7 +233,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 }
             }
             __syncwarp();
-        } else if (warp == 10 || (MODE == 1 && warp == 12)) {
+        } else if (!FUSED && (warp == 10 || (MODE == 1 && warp == 12))) {
             // ------------------------- MMA issuers 3, 4: accumulators ------------
             // warp 10: acc0 += E A_str (dQ += dS K | dK += dS^T Q); warp 12 (dK/dV pass): acc1 += P B_str
             // (dV += P^T dO).  One commit per tile and thread: it frees the stage for the producer and
@@ -226,8 +246,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 const uint32_t str_base = smem_base + (second ? SM_STR_B : SM_STR_A);
                 bool ok = true;
                 for (int y = 0; y < n && ok; ++y) {
-                    const int s = y % STAGES;
-                    const int r = y / STAGES;
+                    const int s = y % NST;
+                    const int r = y / NST;
                     // the streamed tile (read here as the MN-major B operand) and E, P
                     ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
                     if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), y & 1, abort_flag, P.status);
@@ -243,6 +263,155 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 }
             }
             __syncwarp();
+        } else if (FUSED && warp == 9) {
+            // ------------------------- fused pass, issuer 1: X = K Q^T, then Y = V dO^T ------------
+            // (the compute warps are busy with the previous tile for far longer than both take)
+            if (lane == 0) {
+                constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BT, BS, false, false);
+                const uint64_t own_k = mx::smem_desc_sw128(smem_base + SM_OWN_A);
+                const uint64_t own_v = mx::smem_desc_sw128(smem_base + SM_OWN_B);
+                bool ok = mx::mbar_wait(bar(BAR_OWN_FULL), 0, abort_flag, P.status);
+                for (int y = 0; y < n && ok; ++y) {
+                    const int s = y % NST, r = y / NST;
+                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
+                    if (ok && y > 0) ok = mx::mbar_wait(bar(BAR_SDP_FREE), (y - 1) & 1, abort_flag, P.status);
+                    if (!ok) break;
+                    mx::tc_fence_after();
+                    const uint64_t sq = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
+                    const uint64_t so = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
+#pragma unroll
+                    for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_X, own_k + 2 * k, sq + 2 * k, IDESC_S, k > 0);
+#pragma unroll
+                    for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_Y, own_v + 2 * k, so + 2 * k, IDESC_S, k > 0);
+                    mx::mma_commit(bar(BAR_SDP_FULL));
+                }
+            }
+            __syncwarp();
+        } else if (FUSED && warp == 10) {
+            // ------------------------- fused pass, issuer 2: dK += E Q, E (K-major) and Q from shared memory ----
+            if (lane == 0) {
+                constexpr uint32_t IDESC_G = mx::mma_idesc_bf16(BT, HD, false, true);
+                const uint64_t ds0 = mx::smem_desc_sw128(smem_base + SM_DS), ds1 = mx::smem_desc_sw128(smem_base + SM_DS1_A);
+                bool ok = true;
+                for (int y = 0; y < n && ok; ++y) {
+                    const int s = y % NST, r = y / NST;
+                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
+                    if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), y & 1, abort_flag, P.status);
+                    if (!ok) break;
+                    mx::tc_fence_after();
+                    const uint64_t sd = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
+                    // 16 queries of contraction = 32 B inside a row; queries 64.. are the second half tile
+                    const uint64_t lo = (y & 1) ? ds1 : ds0;
+                    const uint64_t hi = lo + (uint64_t)(((y & 1) ? SM_DS1_B - SM_DS1_A : DS_HALF_BYTES) >> 4);
+#pragma unroll
+                    for (int k = 0; k < BS / 16; ++k)
+                        mx::mma_ss(tmem + TMF_ACC0, (k >> 2 ? hi : lo) + (uint64_t)(2 * (k & 3)), sd + 128 * k, IDESC_G,
+                                   (y > 0 || k > 0));
+                    mx::mma_commit(bar(BAR_STR_EMPTY + s));
+                    if (y == n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                }
+            }
+            __syncwarp();
+        } else if (FUSED && warp == 11) {
+            // ------------------------- fused pass, issuer 3: dV += P dO, then this tile's dQ = E^T K ----------
+            // dQ: A = E read with the queries contiguous (MN-major; the second 64 queries in the other half
+            // tile), B = the owned K tile with its rows as the contraction; a fresh accumulator per tile,
+            // taken over by the drain warps.
+            if (lane == 0) {
+                constexpr uint32_t IDESC_G = mx::mma_idesc_bf16(BT, HD, false, true);
+                constexpr uint32_t IDESC_Q = mx::mma_idesc_bf16(BS, HD, true, true);
+                const uint64_t ad0 = mx::smem_desc_sw128_mn(smem_base + SM_DS, DS_HALF_BYTES);
+                const uint64_t ad1 = mx::smem_desc_sw128_mn(smem_base + SM_DS1_A, SM_DS1_B - SM_DS1_A);
+                const uint64_t bd = mx::smem_desc_sw128(smem_base + SM_OWN_A);
+                bool ok = true;
+                for (int y = 0; y < n && ok; ++y) {
+                    const int s = y % NST, r = y / NST;
+                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
+                    if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), y & 1, abort_flag, P.status);
+                    if (!ok) break;
+                    mx::tc_fence_after();
+                    const uint64_t sd = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BS / 16; ++k)
+                        mx::mma_ts(tmem + TMF_ACC1, tmem + TMF_P + 8 * k, sd + 128 * k, IDESC_G, (y > 0 || k > 0));
+                    // the drain warps hold the previous dQ tile in registers
+                    if (y > 0) ok = mx::mbar_wait(bar(BAR_DQ_FREE), (y - 1) & 1, abort_flag, P.status);
+                    if (!ok) break;
+                    mx::tc_fence_after();
+                    const uint64_t ad = (y & 1) ? ad1 : ad0;
+#pragma unroll
+                    for (int k = 0; k < BT / 16; ++k) mx::mma_ss(tmem + TMF_DQ, ad + 128 * k, bd + 128 * k, IDESC_Q, k > 0);
+                    mx::mma_commit(bar(BAR_DQ_FULL));
+                    mx::mma_commit(bar(BAR_STR_EMPTY + s));
+                    if (y == n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                }
+            }
+            __syncwarp();
+        } else if (FUSED && warp >= 12) {
+            // ------------------------- fused pass, drain warps: dQ tile -> global memory -------------------
+            // Warp 12 + j takes lanes 32j .. 32j+31 (queries) of the finished 128 x 64 tile and adds them, 0.125
+            // applied, to dQ with fp32 reductions.  The tile is read in the 256-bit pattern, where four lanes
+            // hold one 32-byte sector of a row: L2 performs reductions sector by sector.  These warps stall on
+            // the reductions' issue; the compute warps never do.
+            const uint32_t ta = tmem + ((uint32_t)((warp & 3) * 32) << 16) + TMF_DQ;
+            const int g_hi = lane >> 4, gl = (lane >> 2) & 3;
+            bool ok = true;
+            for (int y = 0; y < n; ++y) {
+                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_DQ_FULL), y & 1, abort_flag, P.status));
+                if (!ok) break;
+                mx::tc_fence_after();
+                const int qw = (it_beg + y) * BS + (warp & 3) * 32;   // first query of this warp's 32
+                float *dstw = P.dq + ((size_t)bh * N + qw) * HD + 8 * gl + 2 * (lane & 3);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t r0[16], r1[16];
+                    mx::tmem_ld_16x256b_x4(ta + half * 32, r0);
+                    mx::tmem_ld_16x256b_x4(ta + (16u << 16) + half * 32, r1);
+                    mx::tmem_wait_ld();
+                    if (half == 1) {  // the whole tile is in registers (or on its way to L2)
+                        mx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mx::mbar_arrive(bar(BAR_DQ_FREE));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            // lane (g, c) holds row 16j + 8hh + g, columns 8k + 2c + {0,1} in register pair k
+                            float v[4][2];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                v[k][0] = __uint_as_float(j ? r1[4 * k + 2 * hh] : r0[4 * k + 2 * hh]);
+                                v[k][1] = __uint_as_float(j ? r1[4 * k + 2 * hh + 1] : r0[4 * k + 2 * hh + 1]);
+                            }
+                            // 4 x 4 transpose between the register index k and the low two bits of g: afterwards
+                            // pair k holds row 16j + 8hh + 4 g_hi + k, columns 8 gl + 2c + {0,1}, so that the 16 lanes
+                            // of one g_hi cover 128 contiguous bytes of one row -- one full line per L2 request
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+#pragma unroll
+                                for (int m = 0; m < 2; ++m) {   // bit 0: pairs (2m, 2m+1), partner lane ^ 4
+                                    const bool up = gl & 1;
+                                    const float got = __shfl_xor_sync(0xFFFFFFFFu, up ? v[2 * m][e] : v[2 * m + 1][e], 4);
+                                    if (up) v[2 * m][e] = got; else v[2 * m + 1][e] = got;
+                                }
+#pragma unroll
+                                for (int m = 0; m < 2; ++m) {   // bit 1: pairs (m, m+2), partner lane ^ 8
+                                    const bool up = gl & 2;
+                                    const float got = __shfl_xor_sync(0xFFFFFFFFu, up ? v[m][e] : v[m + 2][e], 8);
+                                    if (up) v[m][e] = got; else v[m + 2][e] = got;
+                                }
+                            }
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const int rr = 16 * j + 8 * hh + 4 * g_hi + k;
+                                if (qw + rr < N)
+                                    mx::red_add_f32x2(dstw + rr * HD + half * 32, v[k][0] * 0.125f, v[k][1] * 0.125f);
+                            }
+                        }
+                    }
+                }
+            }
         }
     } else {
         // ------------------------- compute warpgroups -------------------
@@ -273,9 +442,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
         }
         bool ok = true;
         for (int y = 0; y < n; ++y) {
-            const int s = y % STAGES, r = y / STAGES;
+            const int s = y % NST, r = y / NST;
             ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_SDP_FULL), y & 1, abort_flag, P.status));
-            if (MODE == 1 && ok)  // the stage's L / Delta slices were written with plain stores
+            if (MODE >= 1 && ok)  // the stage's L / Delta slices were written with plain stores
                 ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status));
             if (!ok) break;
             mx::tc_fence_after();
@@ -302,10 +471,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                     if (!v0) xv[i] = 0xFF800000u;
                 }
             }
-            uint32_t pe[HS / 2], pp[MODE == 1 ? HS / 2 : 1];
+            uint32_t pe[HS / 2], pp[MODE >= 1 ? HS / 2 : 1];
+            // fused pass: E goes to shared memory as bf16, this thread's key row = one 128-byte swizzled line of
+            // 64 queries.  Two buffers: the MMAs of tile y-1 may still read the other one (those of y-2 are
+            // done: the previous iteration waited for them before its own tensor-memory stores).
+            unsigned char *dsrow = smem + ((y & 1) ? SM_DS1_A + h * (SM_DS1_B - SM_DS1_A) : SM_DS + h * DS_HALF_BYTES) +
+                                   (tid & 127) * 128;
 #pragma unroll
             for (int i = 0; i < HS; i += 2) {
-                if (MODE == 1) {
+                if (MODE >= 1) {
                     const float2 l2 = *(const float2 *)(ld + i), d2 = *(const float2 *)(ld + BS + i);
                     nl0 = l2.x, nl1 = l2.y, nd0 = d2.x, nd1 = d2.y;
                 }
@@ -314,16 +488,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 const float e0 = p0 * (__uint_as_float(yv[i]) + nd0);
                 const float e1 = p1 * (__uint_as_float(yv[i + 1]) + nd1);
                 pe[i >> 1] = mx::pack_bf16(e0, e1);
-                if (MODE == 1) pp[i >> 1] = mx::pack_bf16(p0, p1);
+                if (MODE >= 1) pp[i >> 1] = mx::pack_bf16(p0, p1);
+                if (FUSED && (i & 7) == 6) {  // eight values = one 16-byte piece of this key row's swizzled line
+                    const int cch = i >> 3;
+                    *(uint4 *)(dsrow + ((cch ^ (tid & 7)) << 4)) =
+                        make_uint4(pe[4 * cch], pe[4 * cch + 1], pe[4 * cch + 2], pe[4 * cch + 3]);
+                }
             }
             if (y > 0) {  // the accumulate MMAs of the previous tile have consumed E, P
-                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_EMPTY + (y - 1) % STAGES),
-                                                           ((y - 1) / STAGES) & 1, abort_flag, P.status));
+                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_EMPTY + (y - 1) % NST),
+                                                           ((y - 1) / NST) & 1, abort_flag, P.status));
                 if (!ok) break;
                 mx::tc_fence_after();
             }
-            mx::tmem_st32(tm_row + TM_E + h * (HS / 2), *(uint32_t(*)[32])(pe));
-            if (MODE == 1) mx::tmem_st32(tm_row + TM_P + h * (HS / 2), *(uint32_t(*)[32])(pp));
+            if (FUSED) mx::fence_proxy_async_smem();   // E went to shared memory inside the loop above
+            else mx::tmem_st32(tm_row + TM_E + h * (HS / 2), *(uint32_t(*)[32])(pe));
+            if (MODE >= 1) mx::tmem_st32(tm_row + tP + h * (HS / 2), *(uint32_t(*)[32])(pp));
             mx::tmem_wait_st();
             mx::tc_fence_before();
             __syncwarp();
@@ -352,7 +532,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
                     uint32_t v[32];
-                    mx::tmem_ld32(tm_row + (h == 0 ? TM_ACC0 : TM_ACC1) + cc * 32, v);
+                    mx::tmem_ld32(tm_row + (h == 0 ? tACC0 : tACC1) + cc * 32, v);
                     mx::tmem_wait_ld();
                     if (rv) {
 #pragma unroll
@@ -394,6 +574,7 @@ int set_attrs(int device) {
     if (!done[device]) {
         MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
         MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
+        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
         done[device] = true;
     }
     return MX230_OK;
@@ -418,7 +599,8 @@ int make_maps(mx230_handle *h, Maps &m, const void *Qb, const void *Kb, const vo
 
 int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dQ,
               int batch_heads, int n, int causal) {
-    BwdParams P{L, Delta, dQ, nullptr, (const uint4 *)m.ptr[0], (const uint4 *)m.ptr[3], n, causal ? 1 : 0, h->status_dev};
+    BwdParams P{L, Delta, dQ, nullptr, nullptr, (const uint4 *)m.ptr[0], (const uint4 *)m.ptr[3], n, causal ? 1 : 0,
+                h->status_dev};
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_DQ,
               (bwd_kernel<0><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[0], m.box128[3], m.box128[1],
@@ -428,10 +610,24 @@ int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, c
 
 int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dK,
                float *dV, int batch_heads, int n, int causal) {
-    BwdParams P{L, Delta, dK, dV, nullptr, nullptr, n, causal ? 1 : 0, h->status_dev};
+    BwdParams P{L, Delta, dK, dV, nullptr, nullptr, nullptr, n, causal ? 1 : 0, h->status_dev};
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_DKV,
               (bwd_kernel<1><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
+                                                                  m.box128[3], P)));
+    return MX230_OK;
+}
+
+// One pass over the (key tile, query tile) pairs for all three gradients: dK, dV written once by the
+// CTA that owns the key tile, dQ zeroed here and summed into by every CTA (fp32 reductions at L2, so
+// the order of dQ's partial sums is not fixed from run to run).
+int launch_fused(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dQ,
+                 float *dK, float *dV, int batch_heads, int n, int causal) {
+    MX_CHECK_CUDA(cudaMemsetAsync(dQ, 0, (size_t)batch_heads * n * HD * sizeof(float), st));
+    BwdParams P{L, Delta, dK, dV, dQ, nullptr, nullptr, n, causal ? 1 : 0, h->status_dev};
+    dim3 grid(batch_heads, (n + BT - 1) / BT);
+    MX_LAUNCH(h, st, MX230_K_BWD_FUSED,
+              (bwd_kernel<2><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
                                                                   m.box128[3], P)));
     return MX230_OK;
 }
@@ -457,6 +653,7 @@ int bwd_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb, cons
     Maps m;
     if ((rc = make_maps(h, m, Qb, Kb, Vb, dOb, batch_heads, n))) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    if (which == 3 && !h->bwd_two_pass) return launch_fused(h, st, m, L, Delta, dQ, dK, dV, batch_heads, n, causal);
     if ((which & 1) && (rc = launch_dq(h, st, m, L, Delta, dQ, batch_heads, n, causal))) return rc;
     if ((which & 2) && (rc = launch_dkv(h, st, m, L, Delta, dK, dV, batch_heads, n, causal))) return rc;
     return MX230_OK;

@@ -150,6 +150,11 @@ extern "C" int mx230_set_option(mx230_handle *h, int option, int value) {
                        "mx230_set_option: decode tensor switch must be 0 or 1");
             h->decode_tensor = value;
             return MX230_OK;
+        case MX230_OPT_BWD_TWO_PASS:
+            MX_REQUIRE(value == 0 || value == 1, MX230_ERR_INVALID_ARG,
+                       "mx230_set_option: backward two-pass switch must be 0 or 1");
+            h->bwd_two_pass = value;
+            return MX230_OK;
         default:
             return mx230_fail(MX230_ERR_INVALID_ARG, "mx230_set_option: unknown option %d", option);
     }
@@ -255,7 +260,7 @@ extern "C" const char *mx230_kernel_name(int kernel) {
         "cast_bf16_kernel", "flash_fwd_kernel", "bwd_preprocess_kernel", "bwd_dq_kernel",
         "bwd_dkv_kernel", "rope_kernel", "copy_kv_kernel", "quantize_kv_kernel",
         "decode_f32_kernel", "decode_q8_kernel", "merge_partials_kernel", "prefill_stage_kernels",
-        "gemv_heads_kernel"};
+        "gemv_heads_kernel", "bwd_fused_kernel"};
     return (kernel >= 0 && kernel < MX230_K_COUNT) ? names[kernel] : "?";
 }
 

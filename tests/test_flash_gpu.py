@@ -90,7 +90,16 @@ def test_forward_is_deterministic_and_bf16_entry_agrees(handle):
     assert np.array_equal(o.cpu().numpy(), a) and np.array_equal(l.cpu().numpy(), la_)
 
 
-def run_bwd(handle, q, k, v, do, causal):
+def run_bwd(handle, q, k, v, do, causal, two_pass=0):
+    """two_pass=0: the fused pass (dQ summed with fp32 reductions); 1: the atomic-free dQ and dK/dV passes."""
+    handle.set_option(_lib.OPT_BWD_TWO_PASS, two_pass)
+    try:
+        return _run_bwd(handle, q, k, v, do, causal)
+    finally:
+        handle.set_option(_lib.OPT_BWD_TWO_PASS, 0)
+
+
+def _run_bwd(handle, q, k, v, do, causal):
     n = q.shape[-2]
     dq_, dk_, dv_, ddo = dev(q), dev(k), dev(v), dev(do)
     o = nan_like(q.shape)
@@ -104,12 +113,13 @@ def run_bwd(handle, q, k, v, do, causal):
     return o.cpu().numpy(), delta.cpu().numpy(), gq.cpu().numpy(), gk.cpu().numpy(), gv.cpu().numpy()
 
 
+@pytest.mark.parametrize("two_pass", [0, 1])
 @pytest.mark.parametrize("causal", [False, True])
-def test_backward_reference_inputs(handle, causal):
+def test_backward_reference_inputs(handle, causal, two_pass):
     """run_verify_bwd: N=512, seeds 11..14 (02-flash-attention/src/main.rs:457-499)."""
     n = 512
     q, k, v, do = (oracle.pseudo_rand(n * 64, s).reshape(n, 64) for s in (11, 12, 13, 14))
-    o, delta, gq, gk, gv = run_bwd(handle, q, k, v, do, causal)
+    o, delta, gq, gk, gv = run_bwd(handle, q, k, v, do, causal, two_pass)
     wq, wk, wv = oracle.attn_bwd(q, k, v, do, causal)
     assert_close(delta, oracle.bwd_preprocess(do, o), "Delta", max_abs=1e-5, mean_rel=1e-5)
     assert_close(gq, wq, "dQ")
@@ -117,11 +127,12 @@ def test_backward_reference_inputs(handle, causal):
     assert_close(gv, wv, "dV")
 
 
+@pytest.mark.parametrize("two_pass", [0, 1])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("n", [1, 63, 64, 65, 128, 129, 191, 256, 257, 1000])
-def test_backward_odd_sizes(handle, n, causal):
+def test_backward_odd_sizes(handle, n, causal, two_pass):
     q, k, v, do = (oracle.normal((n, 64), 200 + n, i) for i in range(4))
-    _, _, gq, gk, gv = run_bwd(handle, q, k, v, do, causal)
+    _, _, gq, gk, gv = run_bwd(handle, q, k, v, do, causal, two_pass)
     wq, wk, wv = oracle.attn_bwd(q, k, v, do, causal)
     # with a single visible key the softmax is constant, so dQ and dK are exactly zero and a
     # relative error is undefined: only the absolute gate applies there
@@ -134,13 +145,23 @@ def test_backward_odd_sizes(handle, n, causal):
 def test_backward_batched_split_passes_and_determinism(handle):
     b, h, n = 2, 2, 520
     q, k, v, do = (oracle.normal((b, h, n, 64), 9, i) for i in range(4))
-    _, _, gq, gk, gv = run_bwd(handle, q, k, v, do, True)
     wq, wk, wv = oracle.attn_bwd(q, k, v, do, True)
+    # fused pass: dK, dV are written once by their owner; dQ is a sum of fp32 reductions in no fixed order
+    _, _, fq, fk, fv = run_bwd(handle, q, k, v, do, True)
+    _, _, fq2, fk2, fv2 = run_bwd(handle, q, k, v, do, True)
+    assert_close(fq, wq, "dQ fused")
+    assert_close(fk, wk, "dK fused")
+    assert_close(fv, wv, "dV fused")
+    assert np.array_equal(fk, fk2) and np.array_equal(fv, fv2)
+    assert_close(fq2, fq, "dQ fused, run to run", max_abs=1e-5, mean_rel=1e-6)
+    # the atomic-free split is bit-reproducible
+    _, _, gq, gk, gv = run_bwd(handle, q, k, v, do, True, two_pass=1)
     assert_close(gq, wq, "dQ")
     assert_close(gk, wk, "dK")
     assert_close(gv, wv, "dV")
-    _, _, gq2, gk2, gv2 = run_bwd(handle, q, k, v, do, True)
+    _, _, gq2, gk2, gv2 = run_bwd(handle, q, k, v, do, True, two_pass=1)
     assert np.array_equal(gq, gq2) and np.array_equal(gk, gk2) and np.array_equal(gv, gv2)
+    assert_close(fq, gq, "dQ fused vs split", max_abs=1e-3, mean_rel=1e-4)
     # the two passes are also callable on their own (attn_bwd_dq / attn_bwd_dkv)
     dq_, dk_, dv_, ddo = dev(q), dev(k), dev(v), dev(do)
     o, l, delta = nan_like(q.shape), nan_like(q.shape[:-1]), nan_like(q.shape[:-1])
