@@ -48,9 +48,9 @@ DQ_FLOP = BWD_FLOP * 2.0 / 5.0
 DKV_FLOP = BWD_FLOP * 3.0 / 5.0
 WORKLOAD = "causal flash-attention fwd+bwd, B=4 H=12 N=4096 d=64 (BASELINE.json configs[1])"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the three tensor kernels on this exact
-# workload, from the committed ncu capture (the operands, 4 x 25 MB bf16 + fp32 outputs, mostly stay in the 126 MB L2)
-NCU_DRAM_BYTES_PER_LAUNCH = {"flash_fwd_kernel": 80008960 + 15823872, "bwd_dq_kernel": 106645504 + 24320512,
-                             "bwd_dkv_kernel": 111527680 + 56352768}
+# workload, from the committed ncu captures (the operands, 4 x 25 MB bf16 + fp32 outputs, mostly stay in the 126 MB L2)
+NCU_DRAM_BYTES_PER_LAUNCH = {"flash_fwd_kernel": 80018432 + 15701504, "bwd_fused_kernel": 304081920 + 194913280,
+                             "bwd_dq_kernel": 106743296 + 25219328, "bwd_dkv_kernel": 111542272 + 58254080}
 NOMINAL_BF16_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
 
@@ -390,7 +390,7 @@ def run_ours(args):
 
 def run_case(args):
     """One kernel family on a fixed shape, a few launches and nothing else: the command that the
-    ncu captures under profiles/ wrap (`--case fwd|bwd|decode_c4|decode_long`)."""
+    ncu captures under profiles/ wrap (`--case fwd|bwd|bwd_two_pass|decode_c4|decode_long`)."""
     import torch
     from mx230_b200 import flash_attention as fa
     from mx230_b200 import llm_attention as la
@@ -398,7 +398,9 @@ def run_case(args):
     torch.cuda.set_device(0)
     h = Handle(0, 1 << 30)
     reps = max(1, args.steps)
-    if args.case in ("fwd", "bwd"):
+    if args.case in ("fwd", "bwd", "bwd_two_pass"):
+        from mx230_b200 import _lib
+        h.set_option(_lib.OPT_BWD_TWO_PASS, 1 if args.case == "bwd_two_pass" else 0)
         q, k, v, do = (torch.randn(BH, N, D, device="cuda") for _ in range(4))
         o = torch.empty_like(q)
         l = torch.empty(BH, N, device="cuda")
@@ -406,7 +408,7 @@ def run_case(args):
         dq, dk, dv = (torch.empty_like(q) for _ in range(3))
         for _ in range(reps):
             fa.run_flash_lse(h, q, k, v, o, l, N, True)
-            if args.case == "bwd":
+            if args.case != "fwd":
                 fa.run_preprocess(h, do, o, delta, N)
                 fa.run_bwd_flash(h, q, k, v, do, l, delta, dq, dk, dv, N, True)
     else:
@@ -648,7 +650,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "decode_c4", "decode_long", "splitkv", "configs", "proj"],
+    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "bwd_two_pass", "decode_c4", "decode_long", "splitkv", "configs", "proj"],
                     help="fwd|bwd|decode_*: profiling aid, runs one kernel family a few times and exits; "
                          "splitkv: long-context decode with keys split over the ranks (torchrun for N > 1); "
                          "configs: every BASELINE.json configuration on one GPU; "

@@ -7,26 +7,32 @@
 //   p_ij  = exp(scale * q_i.k_j - L_i),  dP_ij = dO_i . v_j
 //   dS_ij = p_ij (dP_ij - Delta_i) scale
 //   dQ_i += dS_ij k_j ;  dK_j += dS_ij q_i ;  dV_j += p_ij dO_i
-// The same atomic-free split is kept -- a dQ pass owned by query tiles and a dK/dV pass
-// owned by key tiles, each output element written exactly once -- with all contractions on
-// tcgen05 tensor cores (bf16 operands, fp32 accumulators in tensor memory).  Both passes are
-// one kernel template: a CTA owns ONE 128-row tile (queries for dQ, keys for dK/dV) and
-// streams 128-row tiles of the other axis through a TMA ring.  Per streamed tile:
+// Two ways through the same kernel template, all contractions on tcgen05 tensor cores (bf16 operands,
+// fp32 accumulators in tensor memory):
+//  * the reference's atomic-free split -- a dQ pass owned by query tiles (MODE 0) and a dK/dV pass owned
+//    by key tiles (MODE 1), each output element written exactly once, bit-reproducible;
+//  * one fused pass (MODE 2, the default of mx230_attn_bwd_flash): the dK/dV pass also forms every tile's
+//    dQ contribution and adds it to global memory with fp32 reductions, so S and dP are computed once.
+// A CTA owns ONE 128-row tile (queries for dQ, keys otherwise) and streams 128-row tiles of the other axis
+// through a TMA ring.  Per streamed tile:
 //
 //   X = A_own A_str^T, Y = B_own B_str^T      (S, dP   |  S^T, dP^T)   128 x 128, N = 128 MMAs
 //   P = exp2(X c - L), E = P o (Y - Delta)    one thread per owned row and column half
-//   acc0 += E A_str   (dQ += dS K | dK += dS^T Q),   acc1 += P B_str (dV += P^T dO)   TS MMAs
+//   acc0 += E A_str   (dQ += dS K | dK += dS^T Q),   acc1 += P B_str (dV += P^T dO)
+//   fused pass only:  dQ_tile = E^T K  (fresh accumulator), drained to global memory by four warps
 //
-// Every MMA stream (X, Y, acc0, acc1) has its own issuing thread: a thread issues an MMA about
+// Every MMA stream has its own issuing thread in the two-pass kernels: a thread issues an MMA about
 // every 60 cycles and stalls on each commit until its MMAs have drained, so one thread cannot
 // keep the tensor pipe busy with 32-cycle N = 64 MMAs.  The two compute warpgroups take the left
 // and right 64 columns of X, Y: X, Y of the next tile are issued as soon as both hold the current
 // ones in registers, and the accumulate MMAs of a tile run under the next tile's exponentials.
 // In the dQ pass the owned Q and dO tiles are read as A operands from tensor memory (written there
 // once by the compute threads), which leaves shared-memory bandwidth to the streamed operand; in
-// the dK/dV pass tensor memory is full and they stay in shared memory.  The recomputed tiles go back
-// to tensor memory as bf16 A operands; no operand is ever written to shared memory by a thread.
-// The 1/sqrt(d) factor of dS is applied to the fp32 accumulators in the epilogue (exact: 2^-3).
+// the other passes tensor memory is full and they stay in shared memory.  The recomputed tiles go back
+// to tensor memory as bf16 A operands; the fused pass has no columns left for E and keeps it in shared
+// memory (two swizzled buffers written inside the exp loop), where the dQ contraction needs it anyway:
+// the same bytes are read K-major for dK and MN-major (queries contiguous) for dQ.
+// The 1/sqrt(d) factor of dS is applied to the fp32 accumulators on their way out (exact: 2^-3).
 #include <math_constants.h>
 
 #include <type_traits>
@@ -42,7 +48,8 @@ constexpr int STAGES = 4;
 constexpr int OWN_BYTES = BT * HD * 2;   // 16 KB
 constexpr int STR_BYTES = BS * HD * 2;   // 16 KB
 constexpr int BWD_THREADS = 512;
-// warpgroups: compute left, compute right, {TMA, X, acc0, Y}, {acc1, 3 idle}.
+// warpgroups: compute left, compute right, {TMA, X, acc0, Y}, {acc1, 3 idle}; fused pass: {TMA, X+Y, dK, dV+dQ},
+// {4 drain warps}.
 // setmaxnreg moves registers only inside the CTA's launch-time allocation (128 per thread for 512 threads)
 constexpr int REGS_COMPUTE = 208, REGS_SERVICE = 48;
 static_assert(8 * REGS_COMPUTE + 8 * REGS_SERVICE <= 16 * 128, "setmaxnreg budget exceeds the launch-time register allocation");
@@ -392,14 +399,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
 #pragma unroll
                                 for (int m = 0; m < 2; ++m) {   // bit 0: pairs (2m, 2m+1), partner lane ^ 4
                                     const bool up = gl & 1;
-                                    const float got = __shfl_xor_sync(0xFFFFFFFFu, up ? v[2 * m][e] : v[2 * m + 1][e], 4);
-                                    if (up) v[2 * m][e] = got; else v[2 * m + 1][e] = got;
+                                    const float a = v[2 * m][e], b = v[2 * m + 1][e];
+                                    const float got = __shfl_xor_sync(0xFFFFFFFFu, up ? a : b, 4);
+                                    v[2 * m][e] = up ? got : a;
+                                    v[2 * m + 1][e] = up ? b : got;
                                 }
 #pragma unroll
                                 for (int m = 0; m < 2; ++m) {   // bit 1: pairs (m, m+2), partner lane ^ 8
                                     const bool up = gl & 2;
-                                    const float got = __shfl_xor_sync(0xFFFFFFFFu, up ? v[m][e] : v[m + 2][e], 8);
-                                    if (up) v[m][e] = got; else v[m + 2][e] = got;
+                                    const float a = v[m][e], b = v[m + 2][e];
+                                    const float got = __shfl_xor_sync(0xFFFFFFFFu, up ? a : b, 8);
+                                    v[m][e] = up ? got : a;
+                                    v[m + 2][e] = up ? b : got;
                                 }
                             }
 #pragma unroll
