@@ -108,6 +108,9 @@ struct mx230_device_guard {
 int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
                          uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes,
                          uint32_t box_rows);
+// fp32 tensor map over [outer][rows][64] with a {32, 32, 1} box (half rows of 128 bytes) and 128-byte swizzle.
+int mx230_make_tmap_f32_half_rows(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
+                                  uint64_t outer);
 
 // fp32 -> bf16 staging of up to four equally sized tensors in one launch (flash_fwd.cu).
 int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src, void *const *dst,
@@ -195,6 +198,24 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *tma
         "[%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z)
         : "memory");
+}
+// Tile in shared memory added (fp32) to the tensor in global memory; rows outside the tensor are
+// clipped.  x must keep the 16-byte rule; never start a reduce at a negative coordinate.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap *tmap, uint32_t src, int x, int y, int z) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(tmap), "r"(src), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest `N` groups of this thread have finished READING their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

@@ -64,10 +64,13 @@ constexpr int SM_DS = SM_LD + STAGES * 2 * BS * 4;        // fused pass: dS^T as
 constexpr int DS_HALF_BYTES = BT * HS * 2;               // 16 KB
 constexpr int SM_DS1_A = SM_STR_A + (STAGES - 1) * STR_BYTES;   // second E buffer: the last stage's slots
 constexpr int SM_DS1_B = SM_STR_B + (STAGES - 1) * STR_BYTES;
-constexpr int SM_BAR = SM_DS + 2 * DS_HALF_BYTES;
-static_assert(SM_DS % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+constexpr int SM_DQ = SM_DS + 2 * DS_HALF_BYTES;          // fused pass: 4 x 4 KB, one staging tile per drain warp
+constexpr int DQ_STAGE_BYTES = 32 * 32 * 4;              // 32 queries x 32 dims fp32, 128-byte rows
+constexpr int SM_BAR = SM_DQ + 4 * DQ_STAGE_BYTES;
+static_assert(SM_DS % 1024 == 0 && SM_DQ % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 constexpr int SM_TOTAL = SM_BAR + 256;
 constexpr int SM_ALLOC = SM_TOTAL + 1024;
+static_assert(SM_ALLOC <= 227 * 1024, "shared memory per CTA");
 
 constexpr int BAR_OWN_FULL = 0;
 constexpr int BAR_STR_FULL = 1;                          // [STAGES]
@@ -110,7 +113,7 @@ template <int MODE>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ CUtensorMap tmOwnB,
            const __grid_constant__ CUtensorMap tmStrA, const __grid_constant__ CUtensorMap tmStrB,
-           const BwdParams P) {
+           const __grid_constant__ CUtensorMap tmDQ, const BwdParams P) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t smem_base = (mx::smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char *smem = smem_dyn + (smem_base - mx::smem_u32(smem_dyn));
@@ -356,73 +359,49 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             __syncwarp();
         } else if (FUSED && warp >= 12) {
             // ------------------------- fused pass, drain warps: dQ tile -> global memory -------------------
-            // Warp 12 + j takes lanes 32j .. 32j+31 (queries) of the finished 128 x 64 tile and adds them, 0.125
-            // applied, to dQ with fp32 reductions.  The tile is read in the 256-bit pattern, where four lanes
-            // hold one 32-byte sector of a row: L2 performs reductions sector by sector.  These warps stall on
-            // the reductions' issue; the compute warps never do.
+            // Warp 12 + j takes lanes 32j .. 32j+31 (queries) of the finished 128 x 64 tile, 0.125 applied, through
+            // a 4 KB swizzled staging tile of its own (32 queries x 32 dims at a time) and hands it to the TMA
+            // unit, which adds it to dQ in global memory (fp32 reductions at L2, whole 128-byte lines, rows past
+            // the end of the sequence clipped).  Per-thread red instructions from the registers were slower: they
+            // stall their warp on issue and, in any lane layout a tensor-memory load gives directly, split lines.
             const uint32_t ta = tmem + ((uint32_t)((warp & 3) * 32) << 16) + TMF_DQ;
-            const int g_hi = lane >> 4, gl = (lane >> 2) & 3;
+            const uint32_t stage = smem_base + SM_DQ + (warp & 3) * DQ_STAGE_BYTES;
+            unsigned char *stage_row = smem + SM_DQ + (warp & 3) * DQ_STAGE_BYTES + lane * 128;
+            if (lane == 0) mx::tma_prefetch_desc(&tmDQ);
             bool ok = true;
             for (int y = 0; y < n; ++y) {
                 ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_DQ_FULL), y & 1, abort_flag, P.status));
                 if (!ok) break;
                 mx::tc_fence_after();
                 const int qw = (it_beg + y) * BS + (warp & 3) * 32;   // first query of this warp's 32
-                float *dstw = P.dq + ((size_t)bh * N + qw) * HD + 8 * gl + 2 * (lane & 3);
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    uint32_t r0[16], r1[16];
-                    mx::tmem_ld_16x256b_x4(ta + half * 32, r0);
-                    mx::tmem_ld_16x256b_x4(ta + (16u << 16) + half * 32, r1);
+                    uint32_t v[32];
+                    mx::tmem_ld32(ta + half * 32, v);
                     mx::tmem_wait_ld();
-                    if (half == 1) {  // the whole tile is in registers (or on its way to L2)
+                    if (half == 1) {  // the whole tile has left tensor memory
                         mx::tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mx::mbar_arrive(bar(BAR_DQ_FREE));
                     }
+                    // the previous reduction has finished reading the staging tile
+                    if (lane == 0) mx::bulk_wait_group_read<0>();
+                    __syncwarp();
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-#pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            // lane (g, c) holds row 16j + 8hh + g, columns 8k + 2c + {0,1} in register pair k
-                            float v[4][2];
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                v[k][0] = __uint_as_float(j ? r1[4 * k + 2 * hh] : r0[4 * k + 2 * hh]);
-                                v[k][1] = __uint_as_float(j ? r1[4 * k + 2 * hh + 1] : r0[4 * k + 2 * hh + 1]);
-                            }
-                            // 4 x 4 transpose between the register index k and the low two bits of g: afterwards
-                            // pair k holds row 16j + 8hh + 4 g_hi + k, columns 8 gl + 2c + {0,1}, so that the 16 lanes
-                            // of one g_hi cover 128 contiguous bytes of one row -- one full line per L2 request
-#pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-#pragma unroll
-                                for (int m = 0; m < 2; ++m) {   // bit 0: pairs (2m, 2m+1), partner lane ^ 4
-                                    const bool up = gl & 1;
-                                    const float a = v[2 * m][e], b = v[2 * m + 1][e];
-                                    const float got = __shfl_xor_sync(0xFFFFFFFFu, up ? a : b, 4);
-                                    v[2 * m][e] = up ? got : a;
-                                    v[2 * m + 1][e] = up ? b : got;
-                                }
-#pragma unroll
-                                for (int m = 0; m < 2; ++m) {   // bit 1: pairs (m, m+2), partner lane ^ 8
-                                    const bool up = gl & 2;
-                                    const float a = v[m][e], b = v[m + 2][e];
-                                    const float got = __shfl_xor_sync(0xFFFFFFFFu, up ? a : b, 8);
-                                    v[m][e] = up ? got : a;
-                                    v[m + 2][e] = up ? b : got;
-                                }
-                            }
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                const int rr = 16 * j + 8 * hh + 4 * g_hi + k;
-                                if (qw + rr < N)
-                                    mx::red_add_f32x2(dstw + rr * HD + half * 32, v[k][0] * 0.125f, v[k][1] * 0.125f);
-                            }
-                        }
+                    for (int cch = 0; cch < 8; ++cch)
+                        *(float4 *)(stage_row + ((cch ^ (lane & 7)) << 4)) =
+                            make_float4(__uint_as_float(v[4 * cch]) * 0.125f, __uint_as_float(v[4 * cch + 1]) * 0.125f,
+                                        __uint_as_float(v[4 * cch + 2]) * 0.125f, __uint_as_float(v[4 * cch + 3]) * 0.125f);
+                    mx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && qw < N) {   // a tile wholly past the end has nothing to add
+                        mx::tma_reduce_add_3d(&tmDQ, stage, half * 32, qw, bh);
+                        mx::bulk_commit_group();
                     }
                 }
             }
+            if (lane == 0) mx::bulk_wait_group<0>();   // shared memory must outlive the reads; dQ complete at exit
+            __syncwarp();
         }
     } else {
         // ------------------------- compute warpgroups -------------------
@@ -615,7 +594,7 @@ int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, c
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_DQ,
               (bwd_kernel<0><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[0], m.box128[3], m.box128[1],
-                                                                  m.box128[2], P)));
+                                                                  m.box128[2], m.box128[0], P)));
     return MX230_OK;
 }
 
@@ -625,7 +604,7 @@ int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, 
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_DKV,
               (bwd_kernel<1><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
-                                                                  m.box128[3], P)));
+                                                                  m.box128[3], m.box128[0], P)));
     return MX230_OK;
 }
 
@@ -634,12 +613,15 @@ int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, 
 // the order of dQ's partial sums is not fixed from run to run).
 int launch_fused(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dQ,
                  float *dK, float *dV, int batch_heads, int n, int causal) {
+    CUtensorMap tm_dq;
+    int rc = mx230_make_tmap_f32_half_rows(h, &tm_dq, dQ, n, batch_heads);
+    if (rc) return rc;
     MX_CHECK_CUDA(cudaMemsetAsync(dQ, 0, (size_t)batch_heads * n * HD * sizeof(float), st));
     BwdParams P{L, Delta, dK, dV, dQ, nullptr, nullptr, n, causal ? 1 : 0, h->status_dev};
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_FUSED,
               (bwd_kernel<2><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
-                                                                  m.box128[3], P)));
+                                                                  m.box128[3], tm_dq, P)));
     return MX230_OK;
 }
 

@@ -285,3 +285,22 @@ int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, ui
         return mx230_fail(MX230_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return MX230_OK;
 }
+
+// fp32 [outer][rows][64] seen as 128-byte half rows: boxes of 32 rows x 32 floats, 128-byte swizzle
+// (the staging layout of the fused backward's dQ reductions).
+int mx230_make_tmap_f32_half_rows(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
+                                  uint64_t outer) {
+    MX_REQUIRE(((uintptr_t)base & 15) == 0, MX230_ERR_INVALID_ARG,
+               "tensor map base %p is not 16-byte aligned", base);
+    cuuint64_t dims[3] = {64, rows, outer};
+    cuuint64_t strides[2] = {64 * sizeof(float), rows * 64 * sizeof(float)};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = h->encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(base),
+                                 dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return mx230_fail(MX230_ERR_CUDA, "cuTensorMapEncodeTiled (fp32) failed with CUresult %d", (int)r);
+    return MX230_OK;
+}
