@@ -336,6 +336,17 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t 
     return d;
 }
 
+// Unswizzled K-major operand of 16 bf16 columns: 8 x 16-byte core matrices, the 8-row groups of the first
+// 8 columns packed densely (128 B apart), the second 8 columns `k_chunk_bytes` after the first.
+__device__ __forceinline__ uint64_t smem_desc_kmajor_plain(uint32_t saddr, uint32_t k_chunk_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(k_chunk_bytes >> 4) << 16;   // leading-dim byte offset: between the core matrices of the K axis
+    d |= (uint64_t)(128 >> 4) << 32;             // stride between 8-row groups
+    d |= (uint64_t)1 << 46;
+    return d;                                    // swizzle field 0: none
+}
+
 // Vector fp32 reduction into global memory (no return value).  L2 works on 32-byte sectors: a warp
 // instruction should cover whole sectors (four neighbouring lanes with 8 bytes each).
 __device__ __forceinline__ void red_add_f32x2(float *dst, float a, float b) {

@@ -66,7 +66,16 @@ constexpr int SM_DS1_A = SM_STR_A + (STAGES - 1) * STR_BYTES;   // second E buff
 constexpr int SM_DS1_B = SM_STR_B + (STAGES - 1) * STR_BYTES;
 constexpr int SM_DQ = SM_DS + 2 * DS_HALF_BYTES;          // fused pass: 4 x 4 KB, one staging tile per drain warp
 constexpr int DQ_STAGE_BYTES = 32 * 32 * 4;              // 32 queries x 32 dims fp32, 128-byte rows
-constexpr int SM_BAR = SM_DQ + 4 * DQ_STAGE_BYTES;
+// fused pass: -8 L and -Delta of the streamed queries enter X and Y through a fifth K step of their MMAs
+// (three bf16 terms each, against columns of ones), so the compute threads load nothing per element.
+// Unswizzled K-major operands of 128 rows x 16 columns: the first 8 columns are a dense [128][8] bf16 tile,
+// the second 8 columns of every operand are one shared block of zeros.
+constexpr int AUG_BYTES = 128 * 16;                      // 2 KB
+constexpr int SM_AUG_B = SM_DQ + 4 * DQ_STAGE_BYTES;     // (STAGES - 1) tiles: row q = {Lh, Lm, Ll, Dh, Dm, Dl, 0, 0}
+constexpr int SM_AUG_AX = SM_AUG_B + (STAGES - 1) * AUG_BYTES;   // ones in columns 0..2
+constexpr int SM_AUG_AY = SM_AUG_AX + AUG_BYTES;                 // ones in columns 3..5
+constexpr int SM_AUG_Z = SM_AUG_AY + AUG_BYTES;                  // zeros (placed last: offsets to it are positive)
+constexpr int SM_BAR = SM_AUG_Z + AUG_BYTES;
 static_assert(SM_DS % 1024 == 0 && SM_DQ % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 constexpr int SM_TOTAL = SM_BAR + 256;
 constexpr int SM_ALLOC = SM_TOTAL + 1024;
@@ -177,6 +186,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                     mx::tma_load_3d(smem_base + SM_OWN_B, &tmOwnB, bar(BAR_OWN_FULL), 0, own0, bh);
                 }
             }
+            if (FUSED) {   // the constant operands: ones for X, ones for Y, zeros (ordered before the first arrive below)
+                uint4 *ax = (uint4 *)(smem + SM_AUG_AX), *ay = (uint4 *)(smem + SM_AUG_AY), *az = (uint4 *)(smem + SM_AUG_Z);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    ax[u * 32 + lane] = make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u);
+                    ay[u * 32 + lane] = make_uint4(0u, 0x3F800000u, 0x3F803F80u, 0u);
+                    az[u * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
             bool ok = true;
             for (int y = 0; y < n; ++y) {
                 const int s = y % NST, r = y / NST;
@@ -188,7 +206,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                     for (int u = 0; u < 4; ++u) {
                         const int q = row0 + u * 32 + lane;
                         const bool v = q < N;
-                        lv[u] = v ? -P.L[(size_t)bh * N + q] * LOG2E : 0.0f;
+                        // fused pass: X + lv is multiplied by 0.125 log2(e) afterwards, hence -8 L (exact)
+                        lv[u] = v ? -P.L[(size_t)bh * N + q] * (FUSED ? 8.0f : LOG2E) : 0.0f;
                         dv[u] = v ? -P.Delta[(size_t)bh * N + q] : 0.0f;
                     }
                 }
@@ -201,7 +220,25 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                     mx::tma_load_3d(smem_base + SM_STR_A + s * STR_BYTES, &tmStrA, bar(BAR_STR_FULL + s), 0, row0, bh);
                     mx::tma_load_3d(smem_base + SM_STR_B + s * STR_BYTES, &tmStrB, bar(BAR_STR_FULL + s), 0, row0, bh);
                 }
-                if (MODE >= 1) {
+                if (FUSED) {
+                    uint4 *aug = (uint4 *)(smem + SM_AUG_B + s * AUG_BYTES);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        // value = hi + mid + lo, each a bf16: what is left over is below 2^-24 of it
+                        const uint32_t lh = mx::pack_bf16(lv[u], 0.0f) & 0xFFFFu;
+                        const float l1 = lv[u] - __uint_as_float(lh << 16);
+                        const uint32_t lm = mx::pack_bf16(l1, 0.0f) & 0xFFFFu;
+                        const float l2 = l1 - __uint_as_float(lm << 16);
+                        const uint32_t dh = mx::pack_bf16(dv[u], 0.0f) & 0xFFFFu;
+                        const float d1 = dv[u] - __uint_as_float(dh << 16);
+                        const uint32_t dm = mx::pack_bf16(d1, 0.0f) & 0xFFFFu;
+                        const float d2 = d1 - __uint_as_float(dm << 16);
+                        aug[u * 32 + lane] = make_uint4(lh | (lm << 16), (mx::pack_bf16(l2, 0.0f) & 0xFFFFu) | (dh << 16),
+                                                        dm | (mx::pack_bf16(d2, 0.0f) << 16), 0u);
+                    }
+                    mx::fence_proxy_async_smem();   // read by the MMAs
+                    mx::mbar_arrive(bar(BAR_STR_FULL + s));
+                } else if (MODE >= 1) {
                     float *ld = (float *)(smem + SM_LD + s * (2 * BS * 4));
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -280,6 +317,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BT, BS, false, false);
                 const uint64_t own_k = mx::smem_desc_sw128(smem_base + SM_OWN_A);
                 const uint64_t own_v = mx::smem_desc_sw128(smem_base + SM_OWN_B);
+                const uint64_t aug_x = mx::smem_desc_kmajor_plain(smem_base + SM_AUG_AX, SM_AUG_Z - SM_AUG_AX);
+                const uint64_t aug_y = mx::smem_desc_kmajor_plain(smem_base + SM_AUG_AY, SM_AUG_Z - SM_AUG_AY);
                 bool ok = mx::mbar_wait(bar(BAR_OWN_FULL), 0, abort_flag, P.status);
                 for (int y = 0; y < n && ok; ++y) {
                     const int s = y % NST, r = y / NST;
@@ -291,8 +330,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                     const uint64_t so = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
 #pragma unroll
                     for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_X, own_k + 2 * k, sq + 2 * k, IDESC_S, k > 0);
+                    const uint64_t bq = mx::smem_desc_kmajor_plain(smem_base + SM_AUG_B + s * AUG_BYTES,
+                                                                   SM_AUG_Z - SM_AUG_B - s * AUG_BYTES);
+                    mx::mma_ss(tmem + TM_X, aug_x, bq, IDESC_S, 1);   // X -= 8 L of the query column
 #pragma unroll
                     for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_Y, own_v + 2 * k, so + 2 * k, IDESC_S, k > 0);
+                    mx::mma_ss(tmem + TM_Y, aug_y, bq, IDESC_S, 1);   // Y -= Delta of the query column
                     mx::mma_commit(bar(BAR_SDP_FULL));
                 }
             }
@@ -434,7 +477,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
         for (int y = 0; y < n; ++y) {
             const int s = y % NST, r = y / NST;
             ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_SDP_FULL), y & 1, abort_flag, P.status));
-            if (MODE >= 1 && ok)  // the stage's L / Delta slices were written with plain stores
+            if (MODE == 1 && ok)  // the stage's L / Delta slices were written with plain stores
                 ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status));
             if (!ok) break;
             mx::tc_fence_after();
@@ -469,14 +512,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                                    (tid & 127) * 128;
 #pragma unroll
             for (int i = 0; i < HS; i += 2) {
-                if (MODE >= 1) {
+                if (MODE == 1) {
                     const float2 l2 = *(const float2 *)(ld + i), d2 = *(const float2 *)(ld + BS + i);
                     nl0 = l2.x, nl1 = l2.y, nd0 = d2.x, nd1 = d2.y;
                 }
-                const float p0 = mx::ex2(fmaf(__uint_as_float(xv[i]), c, nl0));
-                const float p1 = mx::ex2(fmaf(__uint_as_float(xv[i + 1]), c, nl1));
-                const float e0 = p0 * (__uint_as_float(yv[i]) + nd0);
-                const float e1 = p1 * (__uint_as_float(yv[i + 1]) + nd1);
+                // (fused pass: X, Y arrive with -8 L and -Delta already added by the MMAs; nl, nd stay 0)
+                const float p0 = FUSED ? mx::ex2(__uint_as_float(xv[i]) * c) : mx::ex2(fmaf(__uint_as_float(xv[i]), c, nl0));
+                const float p1 = FUSED ? mx::ex2(__uint_as_float(xv[i + 1]) * c)
+                                       : mx::ex2(fmaf(__uint_as_float(xv[i + 1]), c, nl1));
+                const float e0 = FUSED ? p0 * __uint_as_float(yv[i]) : p0 * (__uint_as_float(yv[i]) + nd0);
+                const float e1 = FUSED ? p1 * __uint_as_float(yv[i + 1]) : p1 * (__uint_as_float(yv[i + 1]) + nd1);
                 pe[i >> 1] = mx::pack_bf16(e0, e1);
                 if (MODE >= 1) pp[i >> 1] = mx::pack_bf16(p0, p1);
                 if (FUSED && (i & 7) == 6) {  // eight values = one 16-byte piece of this key row's swizzled line
