@@ -112,9 +112,10 @@ int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, ui
 int mx230_make_tmap_f32_half_rows(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
                                   uint64_t outer);
 
-// fp32 -> bf16 staging of up to four equally sized tensors in one launch (flash_fwd.cu).
+// fp32 -> bf16 staging of up to four equally sized tensors in one launch (flash_fwd.cu); `zero`, if not
+// null, is a buffer of `count` floats cleared by the same launch.
 int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src, void *const *dst,
-                      int n_tensors, size_t count);
+                      int n_tensors, size_t count, float *zero);
 
 // tcgen05 flash forward over staged bf16 operands (flash_fwd.cu).  Q [heads][n_q][64]; K, V
 // [heads / kv_group][n_k][64]; causal row r sees keys <= r + q_off; output row r of head h at

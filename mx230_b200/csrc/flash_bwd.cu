@@ -657,11 +657,11 @@ int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, 
 // CTA that owns the key tile, dQ zeroed here and summed into by every CTA (fp32 reductions at L2, so
 // the order of dQ's partial sums is not fixed from run to run).
 int launch_fused(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dQ,
-                 float *dK, float *dV, int batch_heads, int n, int causal) {
+                 float *dK, float *dV, int batch_heads, int n, int causal, bool dq_is_zero) {
     CUtensorMap tm_dq;
     int rc = mx230_make_tmap_f32_half_rows(h, &tm_dq, dQ, n, batch_heads);
     if (rc) return rc;
-    MX_CHECK_CUDA(cudaMemsetAsync(dQ, 0, (size_t)batch_heads * n * HD * sizeof(float), st));
+    if (!dq_is_zero) MX_CHECK_CUDA(cudaMemsetAsync(dQ, 0, (size_t)batch_heads * n * HD * sizeof(float), st));
     BwdParams P{L, Delta, dK, dV, dQ, nullptr, nullptr, n, causal ? 1 : 0, h->status_dev};
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_FUSED,
@@ -680,7 +680,7 @@ int check_args(const char *who, mx230_handle *h, int batch_heads, int n) {
 // which: bit 0 = dQ pass, bit 1 = dK/dV pass
 int bwd_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb, const void *Vb, const void *dOb,
              const float *L, const float *Delta, float *dQ, float *dK, float *dV, int batch_heads, int n,
-             int causal, int which, const char *who) {
+             int causal, int which, const char *who, bool dq_is_zero = false) {
     MX_REQUIRE(Qb && Kb && Vb && dOb && L && Delta, MX230_ERR_INVALID_ARG, "%s: null input", who);
     MX_REQUIRE(!(which & 1) || dQ, MX230_ERR_INVALID_ARG, "%s: null dQ", who);
     MX_REQUIRE(!(which & 2) || (dK && dV), MX230_ERR_INVALID_ARG, "%s: null dK/dV", who);
@@ -691,7 +691,8 @@ int bwd_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb, cons
     Maps m;
     if ((rc = make_maps(h, m, Qb, Kb, Vb, dOb, batch_heads, n))) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    if (which == 3 && !h->bwd_two_pass) return launch_fused(h, st, m, L, Delta, dQ, dK, dV, batch_heads, n, causal);
+    if (which == 3 && !h->bwd_two_pass)
+        return launch_fused(h, st, m, L, Delta, dQ, dK, dV, batch_heads, n, causal, dq_is_zero);
     if ((which & 1) && (rc = launch_dq(h, st, m, L, Delta, dQ, batch_heads, n, causal))) return rc;
     if ((which & 2) && (rc = launch_dkv(h, st, m, L, Delta, dK, dV, batch_heads, n, causal))) return rc;
     return MX230_OK;
@@ -712,10 +713,13 @@ int bwd_fp32(mx230_handle *h, void *stream, const float *Q, const float *K, cons
     size_t count = (size_t)batch_heads * n * HD;
     void *dst[4] = {h->ws, (char *)h->ws + one, (char *)h->ws + 2 * one, (char *)h->ws + 3 * one};
     const float *src[4] = {Q, K, V, dO};
-    rc = mx230_launch_cast(h, (cudaStream_t)stream, src, dst, 4, count);
+    // the fused pass sums into dQ: the staging launch clears it on the way
+    const bool fused = which == 3 && !h->bwd_two_pass;
+    MX_REQUIRE(!fused || (dQ && ((uintptr_t)dQ & 15) == 0), MX230_ERR_INVALID_ARG, "%s: dQ null or not 16-byte aligned", who);
+    rc = mx230_launch_cast(h, (cudaStream_t)stream, src, dst, 4, count, fused ? dQ : nullptr);
     if (rc) return rc;
     return bwd_bf16(h, stream, dst[0], dst[1], dst[2], dst[3], L, Delta, dQ, dK, dV, batch_heads, n, causal,
-                    which, who);
+                    which, who, fused);
 }
 
 }  // namespace

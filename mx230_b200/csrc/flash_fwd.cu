@@ -367,28 +367,42 @@ struct CastParams {
     const float *src[4];
     __nv_bfloat16 *dst[4];
     size_t count;  // elements per tensor, multiple of 8
+    float4 *zero;  // optional: `count` floats set to zero by one more slice of the grid (blockIdx.y = n_tensors)
+    int n_tensors;
 };
 
-__global__ void cast_bf16_kernel(const CastParams P) {
-    const float *src = P.src[blockIdx.y];
-    __nv_bfloat16 *dst = P.dst[blockIdx.y];
-    size_t n8 = P.count / 8;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
-         i += (size_t)gridDim.x * blockDim.x) {
-        float4 a = ((const float4 *)src)[2 * i], b = ((const float4 *)src)[2 * i + 1];
-        uint4 o;
-        o.x = mx::pack_bf16(a.x, a.y);
-        o.y = mx::pack_bf16(a.z, a.w);
-        o.z = mx::pack_bf16(b.x, b.y);
-        o.w = mx::pack_bf16(b.z, b.w);
-        ((uint4 *)dst)[i] = o;
+// Four coalesced 16-byte loads in flight per thread (streaming: the fp32 operands are not needed again and
+// should not push the bf16 copies, which the attention kernels read next, out of L2), 8-byte stores.
+__global__ void __launch_bounds__(256) cast_bf16_kernel(const CastParams P) {
+    if ((int)blockIdx.y == P.n_tensors) {
+        const size_t n4 = P.count / 4;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x)
+            P.zero[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
+    }
+    const float4 *src = (const float4 *)P.src[blockIdx.y];
+    uint2 *dst = (uint2 *)P.dst[blockIdx.y];
+    const size_t n4 = P.count / 4;
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * step < n4; i += 4 * step) {
+        float4 a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) a[u] = __ldcs(src + i + u * step);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            dst[i + u * step] = make_uint2(mx::pack_bf16(a[u].x, a[u].y), mx::pack_bf16(a[u].z, a[u].w));
+    }
+    for (; i < n4; i += step) {
+        const float4 a = __ldcs(src + i);
+        dst[i] = make_uint2(mx::pack_bf16(a.x, a.y), mx::pack_bf16(a.z, a.w));
     }
 }
 
 }  // namespace
 
 int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src, void *const *dst,
-                      int n_tensors, size_t count) {
+                      int n_tensors, size_t count, float *zero) {
     MX_REQUIRE(count % 8 == 0, MX230_ERR_INVALID_ARG, "cast: element count must be a multiple of 8");
     if (count == 0 || n_tensors == 0) return MX230_OK;
     CastParams P;
@@ -399,11 +413,14 @@ int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src,
                    "cast: buffers must be 16-byte aligned");
     }
     P.count = count;
-    size_t n8 = count / 8;
-    unsigned bx = (unsigned)((n8 + 255) / 256);
+    P.zero = (float4 *)zero;
+    P.n_tensors = n_tensors;
+    MX_REQUIRE(((uintptr_t)zero & 15) == 0, MX230_ERR_INVALID_ARG, "cast: buffers must be 16-byte aligned");
+    size_t n16 = (count / 4 + 3) / 4;   // threads, at four 16-byte loads each
+    unsigned bx = (unsigned)((n16 + 255) / 256);
     unsigned cap = (unsigned)h->sm_count * 8;
     if (bx > cap) bx = cap;
-    MX_LAUNCH(h, st, MX230_K_CAST, (cast_bf16_kernel<<<dim3(bx, n_tensors), 256, 0, st>>>(P)));
+    MX_LAUNCH(h, st, MX230_K_CAST, (cast_bf16_kernel<<<dim3(bx, n_tensors + (zero ? 1 : 0)), 256, 0, st>>>(P)));
     return MX230_OK;
 }
 
@@ -462,7 +479,7 @@ extern "C" int mx230_cast_bf16(mx230_handle *h, void *stream, const float *src, 
     mx230_device_guard guard(h->device);
     const float *s[1] = {src};
     void *d[1] = {dst_bf16};
-    return mx230_launch_cast(h, (cudaStream_t)stream, s, d, 1, count);
+    return mx230_launch_cast(h, (cudaStream_t)stream, s, d, 1, count, nullptr);
 }
 
 extern "C" int mx230_attn_flash_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb,
@@ -493,7 +510,7 @@ static int flash_fp32(mx230_handle *h, void *stream, const float *Q, const float
     void *qb = h->ws, *kb = (char *)h->ws + one, *vb = (char *)h->ws + 2 * one;
     const float *src[3] = {Q, K, V};
     void *dst[3] = {qb, kb, vb};
-    rc = mx230_launch_cast(h, (cudaStream_t)stream, src, dst, 3, count);
+    rc = mx230_launch_cast(h, (cudaStream_t)stream, src, dst, 3, count, nullptr);
     if (rc) return rc;
     return mx230_launch_flash_fwd(h, (cudaStream_t)stream, qb, kb, vb, O, L, batch_heads, n, causal);
 }
