@@ -142,6 +142,26 @@ def test_backward_odd_sizes(handle, n, causal, two_pass):
     assert_close(gv, wv, f"dV n={n}")
 
 
+def test_backward_large_logits_and_large_delta(handle):
+    """Sharply peaked softmax (scores of a few hundred, so |L| is large) and dO of a few hundred (so
+    |Delta| is large): the fused pass carries -8 L and -Delta through the tensor cores as three bf16
+    terms each, which must not cost accuracy against the fp32 constants of the two-pass kernels.
+    The inputs are bf16-representable, so that the staging cast is exact and the oracle sees the
+    same numbers (at such scores the rounding of q and k alone would move the result by percents)."""
+    n = 384
+    bf = lambda x: torch.from_numpy(x).to(torch.bfloat16).float().numpy()
+    q, k, v, do = (oracle.normal((2, n, 64), 77, i) for i in range(4))
+    q, k, v, do = bf(4.0 * q), bf(4.0 * k), bf(v), bf(300.0 * do)
+    wq, wk, wv = oracle.attn_bwd(q, k, v, do, True)
+    _, _, fq, fk, fv = run_bwd(handle, q, k, v, do, True, 0)
+    _, _, gq, gk, gv = run_bwd(handle, q, k, v, do, True, 1)
+    for f, g, w, name in ((fq, gq, wq, "dQ"), (fk, gk, wk, "dK"), (fv, gv, wv, "dV")):
+        scale = max(1.0, float(np.abs(w).max()))   # the gradients are in the thousands here
+        assert_close(f, w, f"{name} fused", max_abs=2e-2 * scale, mean_rel=1e-2)
+        assert_close(g, w, f"{name} two-pass", max_abs=2e-2 * scale, mean_rel=1e-2)
+        assert_close(f, g, f"{name} fused vs two-pass", max_abs=2e-3 * scale, mean_rel=1e-3)
+
+
 def test_backward_batched_split_passes_and_determinism(handle):
     b, h, n = 2, 2, 520
     q, k, v, do = (oracle.normal((b, h, n, 64), 9, i) for i in range(4))
