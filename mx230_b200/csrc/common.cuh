@@ -111,6 +111,8 @@ int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, ui
 // fp32 tensor map over [outer][rows][64] with a {32, 32, 1} box (half rows of 128 bytes) and 128-byte swizzle.
 int mx230_make_tmap_f32_half_rows(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
                                   uint64_t outer);
+int mx230_make_tmap_f32_half_rows_strided(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
+                                          uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes);
 
 // fp32 -> bf16 staging of up to four equally sized tensors in one launch (flash_fwd.cu); `zero`, if not
 // null, is a buffer of `count` floats cleared by the same launch.
@@ -205,6 +207,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *tma
 __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap *tmap, uint32_t src, int x, int y, int z) {
     asm volatile(
         "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(tmap), "r"(src), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+// Tile in shared memory stored to the tensor in global memory (rows outside the tensor are clipped).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *tmap, uint32_t src, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
         ::"l"(tmap), "r"(src), "r"(x), "r"(y), "r"(z)
         : "memory");
 }

@@ -122,7 +122,8 @@ template <int MODE>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ CUtensorMap tmOwnB,
            const __grid_constant__ CUtensorMap tmStrA, const __grid_constant__ CUtensorMap tmStrB,
-           const __grid_constant__ CUtensorMap tmDQ, const BwdParams P) {
+           const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmOut0,
+           const __grid_constant__ CUtensorMap tmOut1, const BwdParams P) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t smem_base = (mx::smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char *smem = smem_dyn + (smem_base - mx::smem_u32(smem_dyn));
@@ -443,7 +444,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                     }
                 }
             }
-            if (lane == 0) mx::bulk_wait_group<0>();   // shared memory must outlive the reads; dQ complete at exit
+            // the staging tile must outlive the reads; the reductions themselves complete before the grid does
+            if (lane == 0) mx::bulk_wait_group_read<0>();
             __syncwarp();
         }
     } else {
@@ -560,6 +562,36 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                         *(float4 *)(dst + i) = make_float4(__uint_as_float(v[i]) * 0.125f, __uint_as_float(v[i + 1]) * 0.125f,
                                                            __uint_as_float(v[i + 2]) * 0.125f, __uint_as_float(v[i + 3]) * 0.125f);
                 }
+            } else if (FUSED) {
+                // the left warpgroup stores dK (scaled), the right one dV: each warp stages its 32 rows, 32 columns
+                // at a time, in a swizzled 4 KB tile (the stream stages are idle now: every MMA has completed) and
+                // hands it to the TMA unit -- 16-byte stores from lane = row registers would each touch a sector
+                // of their own and took 3.2 us per CTA
+                const float sc = h == 0 ? 0.125f : 1.0f;
+                const CUtensorMap *tm = h == 0 ? &tmOut0 : &tmOut1;
+                const int wrow0 = own0 + (warp & 3) * 32;
+                const int st_off = (h == 0 ? SM_STR_A : SM_STR_B) + (warp & 3) * (2 * DQ_STAGE_BYTES);
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t v[32];
+                    mx::tmem_ld32(tm_row + (h == 0 ? tACC0 : tACC1) + cc * 32, v);
+                    mx::tmem_wait_ld();
+                    unsigned char *srow = smem + st_off + cc * DQ_STAGE_BYTES + lane * 128;
+#pragma unroll
+                    for (int cch = 0; cch < 8; ++cch)
+                        *(float4 *)(srow + ((cch ^ (lane & 7)) << 4)) =
+                            make_float4(__uint_as_float(v[4 * cch]) * sc, __uint_as_float(v[4 * cch + 1]) * sc,
+                                        __uint_as_float(v[4 * cch + 2]) * sc, __uint_as_float(v[4 * cch + 3]) * sc);
+                }
+                mx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && wrow0 < N) {
+                    mx::tma_store_3d(tm, smem_base + st_off, 0, wrow0, bh);
+                    mx::tma_store_3d(tm, smem_base + st_off + DQ_STAGE_BYTES, 32, wrow0, bh);
+                    mx::bulk_commit_group();
+                    mx::bulk_wait_group_read<0>();   // the staging tiles must outlive the reads
+                }
+                __syncwarp();
             } else {
                 // the left warpgroup stores dK (scaled), the right one dV
                 const float sc = h == 0 ? 0.125f : 1.0f;
@@ -639,7 +671,7 @@ int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, c
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_DQ,
               (bwd_kernel<0><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[0], m.box128[3], m.box128[1],
-                                                                  m.box128[2], m.box128[0], P)));
+                                                                  m.box128[2], m.box128[0], m.box128[0], m.box128[0], P)));
     return MX230_OK;
 }
 
@@ -649,7 +681,7 @@ int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, 
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_DKV,
               (bwd_kernel<1><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
-                                                                  m.box128[3], m.box128[0], P)));
+                                                                  m.box128[3], m.box128[0], m.box128[0], m.box128[0], P)));
     return MX230_OK;
 }
 
@@ -658,15 +690,17 @@ int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, 
 // the order of dQ's partial sums is not fixed from run to run).
 int launch_fused(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dQ,
                  float *dK, float *dV, int batch_heads, int n, int causal, bool dq_is_zero) {
-    CUtensorMap tm_dq;
+    CUtensorMap tm_dq, tm_dk, tm_dv;
     int rc = mx230_make_tmap_f32_half_rows(h, &tm_dq, dQ, n, batch_heads);
+    if (!rc) rc = mx230_make_tmap_f32_half_rows(h, &tm_dk, dK, n, batch_heads);
+    if (!rc) rc = mx230_make_tmap_f32_half_rows(h, &tm_dv, dV, n, batch_heads);
     if (rc) return rc;
     if (!dq_is_zero) MX_CHECK_CUDA(cudaMemsetAsync(dQ, 0, (size_t)batch_heads * n * HD * sizeof(float), st));
     BwdParams P{L, Delta, dK, dV, dQ, nullptr, nullptr, n, causal ? 1 : 0, h->status_dev};
     dim3 grid(batch_heads, (n + BT - 1) / BT);
     MX_LAUNCH(h, st, MX230_K_BWD_FUSED,
               (bwd_kernel<2><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
-                                                                  m.box128[3], tm_dq, P)));
+                                                                  m.box128[3], tm_dq, tm_dk, tm_dv, P)));
     return MX230_OK;
 }
 

@@ -23,6 +23,8 @@
 // Operands are bf16 (rounded once by the cast pre-pass), accumulation is fp32.
 #include <math_constants.h>
 
+#include <cstring>
+
 #include "common.cuh"
 
 namespace {
@@ -78,6 +80,7 @@ struct FwdParams {
     int q_off;            // causal: query row r sees keys <= r + q_off (0 for self-attention)
     int kv_group;         // query heads per K/V head (K/V head of query head h is h / kv_group)
     int causal;
+    int tma_out;          // O leaves through staged TMA stores (strides and base 16-byte aligned) or per-thread stores
     int *status;
 };
 
@@ -89,7 +92,8 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const FwdParams P) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                 const FwdParams P) {
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t smem_base = (mx::smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char *smem = smem_dyn + (smem_base - mx::smem_u32(smem_dyn));
@@ -336,6 +340,33 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 mx::tc_fence_after();
                 const float inv = 1.0f / l;
                 float *orow = P.O + (size_t)bh * P.o_head_stride + (size_t)row * P.o_row_stride;
+                if (P.tma_out) {
+                    // each warp stages its 32 rows, 32 columns at a time, in a swizzled 4 KB piece of this tile's Q
+                    // buffer (its last Q K^T has completed) and hands it to the TMA unit, which clips rows past the
+                    // end: 16-byte stores from lane = row registers each touch a sector of their own
+                    const int wrow0 = q0 + t * BM + (warp & 3) * 32;
+                    const int st_off = SMEM_Q + t * TILE_BYTES + (warp & 3) * 4096;
+#pragma unroll
+                    for (int cc = 0; cc < HD / 32; ++cc) {
+                        uint32_t o[32];
+                        mx::tmem_ld32(tm_o + cc * 32, o);
+                        mx::tmem_wait_ld();
+                        unsigned char *srow = smem + st_off + lane * 128;
+#pragma unroll
+                        for (int cch = 0; cch < 8; ++cch)
+                            *(float4 *)(srow + ((cch ^ (lane & 7)) << 4)) =
+                                make_float4(__uint_as_float(o[4 * cch]) * inv, __uint_as_float(o[4 * cch + 1]) * inv,
+                                            __uint_as_float(o[4 * cch + 2]) * inv, __uint_as_float(o[4 * cch + 3]) * inv);
+                        mx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && wrow0 < NQ) {
+                            mx::tma_store_3d(&tmO, smem_base + st_off, cc * 32, wrow0, bh);
+                            mx::bulk_commit_group();
+                            mx::bulk_wait_group_read<0>();   // the piece is reused for the second half and must outlive the read
+                        }
+                        __syncwarp();
+                    }
+                } else
 #pragma unroll
                 for (int cc = 0; cc < HD / 32; ++cc) {
                     uint32_t o[32];
@@ -428,9 +459,18 @@ int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src,
 int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
                               const void *Vb, float *O, float *L, int heads, int n_q, int n_k, int q_off,
                               int kv_group, long long o_head_stride, long long o_row_stride, int causal) {
-    CUtensorMap tq, tk, tv;
+    CUtensorMap tq, tk, tv, to;
     uint64_t rs = HD * 2;
     int rc;
+    const bool tma_out = (((uintptr_t)O & 15) == 0) && o_row_stride % 4 == 0 && o_head_stride % 4 == 0 &&
+                         o_row_stride > 0 && o_head_stride > 0;
+    if (tma_out) {
+        if ((rc = mx230_make_tmap_f32_half_rows_strided(h, &to, O, n_q, heads, (uint64_t)o_row_stride * 4,
+                                                        (uint64_t)o_head_stride * 4)))
+            return rc;
+    } else {
+        memset(&to, 0, sizeof(to));
+    }
     if ((rc = mx230_make_tmap_bf16(h, &tq, Qb, n_q, heads, rs, (uint64_t)n_q * HD * 2, BM))) return rc;
     if ((rc = mx230_make_tmap_bf16(h, &tk, Kb, n_k, heads / kv_group, rs, (uint64_t)n_k * HD * 2, BN))) return rc;
     if ((rc = mx230_make_tmap_bf16(h, &tv, Vb, n_k, heads / kv_group, rs, (uint64_t)n_k * HD * 2, BN))) return rc;
@@ -452,10 +492,11 @@ int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, 
     P.q_off = q_off;
     P.kv_group = kv_group;
     P.causal = causal ? 1 : 0;
+    P.tma_out = tma_out ? 1 : 0;
     P.status = h->status_dev;
     dim3 grid(heads, (n_q + QT * BM - 1) / (QT * BM));
     MX_LAUNCH(h, st, MX230_K_FLASH_FWD,
-              (flash_fwd_kernel<<<grid, FWD_THREADS, SMEM_ALLOC, st>>>(tq, tk, tv, P)));
+              (flash_fwd_kernel<<<grid, FWD_THREADS, SMEM_ALLOC, st>>>(tq, tk, tv, to, P)));
     return MX230_OK;
 }
 

@@ -290,10 +290,19 @@ int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, ui
 // (the staging layout of the fused backward's dQ reductions).
 int mx230_make_tmap_f32_half_rows(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
                                   uint64_t outer) {
+    return mx230_make_tmap_f32_half_rows_strided(h, out, base, rows, outer, 64 * sizeof(float),
+                                                 rows * 64 * sizeof(float));
+}
+
+// the same with the row and outer strides given in bytes (multiples of 16)
+int mx230_make_tmap_f32_half_rows_strided(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
+                                          uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes) {
     MX_REQUIRE(((uintptr_t)base & 15) == 0, MX230_ERR_INVALID_ARG,
                "tensor map base %p is not 16-byte aligned", base);
+    MX_REQUIRE(row_stride_bytes % 16 == 0 && outer_stride_bytes % 16 == 0, MX230_ERR_INVALID_ARG,
+               "tensor map strides must be multiples of 16 bytes");
     cuuint64_t dims[3] = {64, rows, outer};
-    cuuint64_t strides[2] = {64 * sizeof(float), rows * 64 * sizeof(float)};
+    cuuint64_t strides[2] = {row_stride_bytes, outer_stride_bytes};
     cuuint32_t box[3] = {32, 32, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = h->encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(base),
