@@ -7,9 +7,13 @@
 // when causal, any N, natural-log L) and maps the two contractions onto the 5th-gen
 // tensor cores:
 //
-//   * one CTA owns 256 query rows of one head as two 128-row tiles;
-//   * warp 8 streams Q once and K/V tiles (128 keys) through a 4-stage shared-memory
-//     ring with plain per-CTA TMA tile loads (128-byte swizzle);
+//   * a work item is 256 query rows of one head as two 128-row tiles; the kernel is persistent:
+//     one CTA per SM walks a fixed share of the items (heaviest first, dealt out in snake order so
+//     that every CTA gets the same number of key tiles), and every role runs ahead into the next
+//     item on its own, so the next item's Q / K loads and first Q K^T run under the current
+//     item's last softmax and its epilogue;
+//   * warp 8 streams Q (two buffers, alternating by item) and K/V tiles (128 keys) through a
+//     4-stage shared-memory ring with plain per-CTA TMA tile loads (128-byte swizzle);
 //   * warp 9 issues the tcgen05.mma stream S_t = Q_t K^T into tensor memory (128 fp32 columns
 //     per tile), warp 10 the stream O_t += P_t V with P_t read from tensor memory as bf16 (a
 //     thread issues an MMA about every 60 cycles, so each stream has its own thread);
@@ -41,16 +45,18 @@ constexpr int FWD_THREADS = 384;        // 3 warpgroups: softmax 0, softmax 1, {
 // increase would block for ever.
 static_assert(8 * 216 + 4 * 72 <= 12 * 168, "setmaxnreg budget exceeds the launch-time register allocation");
 
+constexpr int Q_BUFS = 2;                // Q of the next item lands while the current one is in use
 constexpr int SMEM_Q = 0;
-constexpr int SMEM_K = SMEM_Q + QT * TILE_BYTES;
+constexpr int SMEM_K = SMEM_Q + Q_BUFS * QT * TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;
 constexpr int SMEM_BAR = SMEM_V + KV_STAGES * TILE_BYTES;
 constexpr int SMEM_TOTAL = SMEM_BAR + 256;
 constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;  // slack for 1024-byte alignment
 
 // barrier slots (8 bytes each) inside SMEM_BAR
-constexpr int BAR_Q_FULL = 0;
-constexpr int BAR_K_FULL = 1;                    // [KV_STAGES]
+constexpr int BAR_Q_FULL = 0;                    // [Q_BUFS]
+constexpr int BAR_Q_EMPTY = BAR_Q_FULL + Q_BUFS; // [Q_BUFS] softmax warps -> TMA: item done with its Q buffer
+constexpr int BAR_K_FULL = BAR_Q_EMPTY + Q_BUFS; // [KV_STAGES]
 constexpr int BAR_K_EMPTY = BAR_K_FULL + KV_STAGES;
 constexpr int BAR_V_FULL = BAR_K_EMPTY + KV_STAGES;
 constexpr int BAR_V_EMPTY = BAR_V_FULL + KV_STAGES;
@@ -58,7 +64,7 @@ constexpr int BAR_S_FULL = BAR_V_EMPTY + KV_STAGES;  // [QT] MMA -> softmax: S_t
 constexpr int BAR_S_FREE = BAR_S_FULL + QT;          // [QT] softmax -> MMA: S_t copied to registers
 constexpr int BAR_P_FULL = BAR_S_FREE + QT;          // [QT] softmax -> MMA: P_t written
 constexpr int BAR_O_DONE = BAR_P_FULL + QT;          // [QT] MMA -> softmax: O_t += P_t V complete
-constexpr int N_BARS = BAR_O_DONE + QT;              // 25
+constexpr int N_BARS = BAR_O_DONE + QT;              // 28
 
 // tensor-memory columns: nothing aliases, so S_t(j+1) can be produced while P_t(j) is consumed
 constexpr int TM_S = 0;     // S_t at TM_S + t*128, fp32
@@ -80,6 +86,9 @@ struct FwdParams {
     int q_off;            // causal: query row r sees keys <= r + q_off (0 for self-attention)
     int kv_group;         // query heads per K/V head (K/V head of query head h is h / kv_group)
     int causal;
+    int heads;            // query heads (items are (query block, head) pairs, heads fastest)
+    int n_qblocks;        // blocks of QT*BM query rows per head
+    int n_items;          // heads * n_qblocks
     int tma_out;          // O leaves through staged TMA stores (strides and base 16-byte aligned) or per-thread stores
     int *status;
 };
@@ -88,6 +97,25 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
+}
+
+// The CTA's `round`-th work item.  Items are listed heaviest first (when causal: the latest query block of
+// every head, then the one before, ...) and dealt to the CTAs forwards in even rounds, backwards in odd ones.
+__device__ __forceinline__ bool fwd_item(const FwdParams &P, int round, int &bh, int &q0) {
+    const int G = (int)gridDim.x, c = (int)blockIdx.x;
+    const int i = round * G + ((round & 1) ? G - 1 - c : c);
+    if (i >= P.n_items) return false;
+    const int rank = i / P.heads;
+    bh = i - rank * P.heads;
+    q0 = (P.causal ? P.n_qblocks - 1 - rank : rank) * (QT * BM);
+    return true;
+}
+// K/V tiles that query tile `t` of the block starting at row q0 has to see
+__device__ __forceinline__ int fwd_tile_iters(const FwdParams &P, int q0, int t) {
+    const int r0 = q0 + t * BM;
+    if (r0 >= P.n_q) return 0;
+    const int n_kv_total = (P.n_k + BN - 1) / BN;
+    return P.causal ? min(n_kv_total, (r0 + BM - 1 + P.q_off) / BN + 1) : n_kv_total;
 }
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
@@ -104,23 +132,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NQ = P.n_q, N = P.n_k;  // N: keys (bounds the K/V loop and the key mask)
-    // heads vary fastest in launch order and, when causal, the latest (heaviest) query
-    // blocks of every head are dispatched first
-    const int bh = blockIdx.x;
-    const int qb = P.causal ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
-    const int q0 = qb * (QT * BM);
-    const int n_kv_total = (N + BN - 1) / BN;
-    int n_it[QT];
-#pragma unroll
-    for (int t = 0; t < QT; ++t) {
-        int r0 = q0 + t * BM;
-        if (r0 >= NQ) n_it[t] = 0;
-        else n_it[t] = P.causal ? min(n_kv_total, (r0 + BM - 1 + P.q_off) / BN + 1) : n_kv_total;
-    }
-    const int n_max = max(n_it[0], n_it[1]);
 
     if (tid == 0) {
-        mx::mbar_init(bar(BAR_Q_FULL), 1);
+        for (int b = 0; b < Q_BUFS; ++b) {
+            mx::mbar_init(bar(BAR_Q_FULL + b), 1);
+            mx::mbar_init(bar(BAR_Q_EMPTY + b), QT * BM / 32);  // one elected lane per softmax warp arrives
+        }
         for (int s = 0; s < KV_STAGES; ++s) {
             mx::mbar_init(bar(BAR_K_FULL + s), 1);
             mx::mbar_init(bar(BAR_K_EMPTY + s), 1);
@@ -152,25 +169,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             mx::tma_prefetch_desc(&tmQ);
             mx::tma_prefetch_desc(&tmK);
             mx::tma_prefetch_desc(&tmV);
-            int nq = (n_it[1] > 0) ? 2 : 1;
-            mx::mbar_expect_tx(bar(BAR_Q_FULL), nq * TILE_BYTES);
-            for (int t = 0; t < nq; ++t)
-                mx::tma_load_3d(smem_base + SMEM_Q + t * TILE_BYTES, &tmQ, bar(BAR_Q_FULL), 0,
-                                q0 + t * BM, bh);
             bool ok = true;
-            const int kvh = bh / P.kv_group;
-            for (int j = 0; j < n_max && ok; ++j) {
-                int s = j % KV_STAGES, r = j / KV_STAGES;
-                if (r > 0) ok = mx::mbar_wait(bar(BAR_K_EMPTY + s), (r - 1) & 1, abort_flag, P.status);
+            uint32_t g = 0;  // K/V tiles loaded so far, over all items: ring slot g % KV_STAGES, use g / KV_STAGES
+            int bh, q0;
+            for (int it = 0; ok && fwd_item(P, it, bh, q0); ++it) {
+                const int n_it1 = fwd_tile_iters(P, q0, 1);
+                const int n_max = max(fwd_tile_iters(P, q0, 0), n_it1);
+                const int qbuf = it & 1;
+                // the buffer's previous item (two items ago) must have staged its last O piece out of it
+                if (it >= Q_BUFS) ok = mx::mbar_wait(bar(BAR_Q_EMPTY + qbuf), ((it >> 1) - 1) & 1, abort_flag, P.status);
                 if (!ok) break;
-                mx::mbar_expect_tx(bar(BAR_K_FULL + s), TILE_BYTES);
-                mx::tma_load_3d(smem_base + SMEM_K + s * TILE_BYTES, &tmK, bar(BAR_K_FULL + s), 0,
-                                j * BN, kvh);
-                if (r > 0) ok = mx::mbar_wait(bar(BAR_V_EMPTY + s), (r - 1) & 1, abort_flag, P.status);
-                if (!ok) break;
-                mx::mbar_expect_tx(bar(BAR_V_FULL + s), TILE_BYTES);
-                mx::tma_load_3d(smem_base + SMEM_V + s * TILE_BYTES, &tmV, bar(BAR_V_FULL + s), 0,
-                                j * BN, kvh);
+                const int nq = (n_it1 > 0) ? 2 : 1;
+                mx::mbar_expect_tx(bar(BAR_Q_FULL + qbuf), nq * TILE_BYTES);
+                for (int t = 0; t < nq; ++t)
+                    mx::tma_load_3d(smem_base + SMEM_Q + (qbuf * QT + t) * TILE_BYTES, &tmQ, bar(BAR_Q_FULL + qbuf), 0,
+                                    q0 + t * BM, bh);
+                const int kvh = bh / P.kv_group;
+                for (int j = 0; j < n_max; ++j, ++g) {
+                    const int s = g % KV_STAGES;
+                    const uint32_t r = g / KV_STAGES;
+                    if (r > 0) ok = mx::mbar_wait(bar(BAR_K_EMPTY + s), (r - 1) & 1, abort_flag, P.status);
+                    if (!ok) break;
+                    mx::mbar_expect_tx(bar(BAR_K_FULL + s), TILE_BYTES);
+                    mx::tma_load_3d(smem_base + SMEM_K + s * TILE_BYTES, &tmK, bar(BAR_K_FULL + s), 0,
+                                    j * BN, kvh);
+                    if (r > 0) ok = mx::mbar_wait(bar(BAR_V_EMPTY + s), (r - 1) & 1, abort_flag, P.status);
+                    if (!ok) break;
+                    mx::mbar_expect_tx(bar(BAR_V_FULL + s), TILE_BYTES);
+                    mx::tma_load_3d(smem_base + SMEM_V + s * TILE_BYTES, &tmV, bar(BAR_V_FULL + s), 0,
+                                    j * BN, kvh);
+                }
             }
         }
         __syncwarp();
@@ -180,35 +208,39 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // than a 128x64x16 MMA takes to execute, so the two MMA streams get a thread each)
         if (lane == 0) {
             constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BM, BN, false, false);
-            bool ok = mx::mbar_wait(bar(BAR_Q_FULL), 0, abort_flag, P.status);
-            auto issue_s = [&](int t, int stage) {
-                uint64_t a = mx::smem_desc_sw128(smem_base + SMEM_Q + t * TILE_BYTES);
-                uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_K + stage * TILE_BYTES);
+            bool ok = true;
+            uint32_t g = 0;            // K/V tiles consumed so far, over all items
+            uint32_t cs[QT] = {0, 0};  // score tiles issued so far per query tile, over all items
+            int bh, q0;
+            for (int it = 0; ok && fwd_item(P, it, bh, q0); ++it) {
+                int n_it[QT];
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k)  // 32 bytes per 16-element step inside the swizzle span
-                    mx::mma_ss(tmem + TM_S + t * BN, a + 2 * k, b + 2 * k, IDESC_S, k > 0);
-                mx::mma_commit(bar(BAR_S_FULL + t));
-            };
-            if (ok && n_max > 0) ok = mx::mbar_wait(bar(BAR_K_FULL + 0), 0, abort_flag, P.status);
-            if (ok && n_max > 0) {
-                mx::tc_fence_after();
-                for (int t = 0; t < QT; ++t)
-                    if (n_it[t] > 0) issue_s(t, 0);
-                mx::mma_commit(bar(BAR_K_EMPTY + 0));
-            }
-            // next scores as soon as the softmax groups hold the current ones in registers
-            for (int j = 0; j + 1 < n_max && ok; ++j) {
-                const int s1 = (j + 1) % KV_STAGES, r1 = (j + 1) / KV_STAGES;
-                ok = mx::mbar_wait(bar(BAR_K_FULL + s1), r1 & 1, abort_flag, P.status);
-                for (int t = 0; t < QT && ok; ++t) {
-                    if (j + 1 >= n_it[t]) continue;
-                    ok = mx::mbar_wait(bar(BAR_S_FREE + t), j & 1, abort_flag, P.status);
+                for (int t = 0; t < QT; ++t) n_it[t] = fwd_tile_iters(P, q0, t);
+                const int n_max = max(n_it[0], n_it[1]);
+                const int qbuf = it & 1;
+                ok = mx::mbar_wait(bar(BAR_Q_FULL + qbuf), (it >> 1) & 1, abort_flag, P.status);
+                for (int j = 0; j < n_max && ok; ++j, ++g) {
+                    const int s = g % KV_STAGES;
+                    ok = mx::mbar_wait(bar(BAR_K_FULL + s), (g / KV_STAGES) & 1, abort_flag, P.status);
+                    const uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_K + s * TILE_BYTES);
+#pragma unroll
+                    for (int t = 0; t < QT; ++t) {
+                        if (!ok || j >= n_it[t]) continue;
+                        // next scores as soon as the softmax group holds the previous ones in registers (the
+                        // previous ones may be the last of the item before: this is where the items overlap)
+                        if (cs[t] > 0) ok = mx::mbar_wait(bar(BAR_S_FREE + t), (cs[t] - 1) & 1, abort_flag, P.status);
+                        if (!ok) continue;
+                        mx::tc_fence_after();
+                        const uint64_t a = mx::smem_desc_sw128(smem_base + SMEM_Q + (qbuf * QT + t) * TILE_BYTES);
+#pragma unroll
+                        for (int k = 0; k < HD / 16; ++k)  // 32 bytes per 16-element step inside the swizzle span
+                            mx::mma_ss(tmem + TM_S + t * BN, a + 2 * k, b + 2 * k, IDESC_S, k > 0);
+                        mx::mma_commit(bar(BAR_S_FULL + t));
+                        ++cs[t];
+                    }
                     if (!ok) break;
-                    mx::tc_fence_after();
-                    issue_s(t, s1);
+                    mx::mma_commit(bar(BAR_K_EMPTY + s));
                 }
-                if (!ok) break;
-                mx::mma_commit(bar(BAR_K_EMPTY + s1));
             }
         }
         __syncwarp();
@@ -217,23 +249,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) {
             constexpr uint32_t IDESC_O = mx::mma_idesc_bf16(BM, HD, false, true);
             bool ok = true;
-            for (int j = 0; j < n_max && ok; ++j) {
-                const int s = j % KV_STAGES, r = j / KV_STAGES;
-                ok = mx::mbar_wait(bar(BAR_V_FULL + s), r & 1, abort_flag, P.status);
-                const uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_V + s * TILE_BYTES);
-                for (int t = 0; t < QT && ok; ++t) {
-                    if (j >= n_it[t]) continue;
-                    ok = mx::mbar_wait(bar(BAR_P_FULL + t), j & 1, abort_flag, P.status);
-                    if (!ok) break;
-                    mx::tc_fence_after();
+            uint32_t g = 0;            // K/V tiles consumed so far, over all items
+            uint32_t cp[QT] = {0, 0};  // P tiles consumed so far per query tile, over all items
+            int bh, q0;
+            for (int it = 0; ok && fwd_item(P, it, bh, q0); ++it) {
+                int n_it[QT];
 #pragma unroll
-                    for (int k = 0; k < BN / 16; ++k)  // 16 keys: 8 packed columns of P, 2048 bytes of V
-                        mx::mma_ts(tmem + TM_O + t * HD, tmem + TM_P + t * (BN / 2) + 8 * k, b + 128 * k,
-                                   IDESC_O, (j > 0 || k > 0));
-                    mx::mma_commit(bar(BAR_O_DONE + t));
+                for (int t = 0; t < QT; ++t) n_it[t] = fwd_tile_iters(P, q0, t);
+                const int n_max = max(n_it[0], n_it[1]);
+                for (int j = 0; j < n_max && ok; ++j, ++g) {
+                    const int s = g % KV_STAGES;
+                    ok = mx::mbar_wait(bar(BAR_V_FULL + s), (g / KV_STAGES) & 1, abort_flag, P.status);
+                    const uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_V + s * TILE_BYTES);
+#pragma unroll
+                    for (int t = 0; t < QT; ++t) {
+                        if (!ok || j >= n_it[t]) continue;
+                        // an item's first P_t is written after the softmax group has taken the previous item's
+                        // O_t out of tensor memory, so overwriting O_t (j == 0) needs no barrier of its own
+                        ok = mx::mbar_wait(bar(BAR_P_FULL + t), cp[t] & 1, abort_flag, P.status);
+                        if (!ok) continue;
+                        mx::tc_fence_after();
+#pragma unroll
+                        for (int k = 0; k < BN / 16; ++k)  // 16 keys: 8 packed columns of P, 2048 bytes of V
+                            mx::mma_ts(tmem + TM_O + t * HD, tmem + TM_P + t * (BN / 2) + 8 * k, b + 128 * k,
+                                       IDESC_O, (j > 0 || k > 0));
+                        mx::mma_commit(bar(BAR_O_DONE + t));
+                        ++cp[t];
+                    }
+                    if (!ok) break;
+                    mx::mma_commit(bar(BAR_V_EMPTY + s));
                 }
-                if (!ok) break;
-                mx::mma_commit(bar(BAR_V_EMPTY + s));
             }
         }
         __syncwarp();
@@ -243,17 +288,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         const int t = warp >> 2;             // query tile of this group
         const int row_in_tile = tid & 127;
-        const int row = q0 + t * BM + row_in_tile;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tm_s = tmem + lane_off + TM_S + t * BN;
         const uint32_t tm_p = tmem + lane_off + TM_P + t * (BN / 2);
         const uint32_t tm_o = tmem + lane_off + TM_O + t * HD;
         const float c = 0.125f * 1.4426950408889634f;  // scale * log2(e)
-        const int n_t = n_it[t];
-        float m = -CUDART_INF_F, l = 0.0f;
         bool ok = true;
-        for (int j = 0; j < n_t; ++j) {
-            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), j & 1, abort_flag, P.status));
+        uint32_t cnt = 0;  // score tiles this group has taken so far, over all items
+        int bh, q0;
+        for (int it = 0; ok && fwd_item(P, it, bh, q0); ++it) {
+        const int n_t = fwd_tile_iters(P, q0, t);
+        const int row = q0 + t * BM + row_in_tile;
+        const int qbuf = it & 1;
+        float m = -CUDART_INF_F, l = 0.0f;
+        for (int j = 0; j < n_t; ++j, ++cnt) {
+            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), cnt & 1, abort_flag, P.status));
             if (!ok) break;
             mx::tc_fence_after();
             // the whole score row into registers with one round trip, then S_t is free again
@@ -294,7 +343,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 // P_t and O_t are stable once the previous P V has completed (issued a whole
                 // softmax ago, so this wait is normally already satisfied)
                 ok = __all_sync(0xFFFFFFFFu,
-                                mx::mbar_wait(bar(BAR_O_DONE + t), (j - 1) & 1, abort_flag, P.status));
+                                mx::mbar_wait(bar(BAR_O_DONE + t), (cnt - 1) & 1, abort_flag, P.status));
                 if (!ok) break;
                 mx::tc_fence_after();
                 if (__any_sync(0xFFFFFFFFu, raise)) {
@@ -335,7 +384,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // epilogue: O / l and the log-sum-exp
         if (ok && n_t > 0) {
             ok = __all_sync(0xFFFFFFFFu,
-                            mx::mbar_wait(bar(BAR_O_DONE + t), (n_t - 1) & 1, abort_flag, P.status));
+                            mx::mbar_wait(bar(BAR_O_DONE + t), (cnt - 1) & 1, abort_flag, P.status));
             if (ok) {
                 mx::tc_fence_after();
                 const float inv = 1.0f / l;
@@ -345,7 +394,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     // buffer (its last Q K^T has completed) and hands it to the TMA unit, which clips rows past the
                     // end: 16-byte stores from lane = row registers each touch a sector of their own
                     const int wrow0 = q0 + t * BM + (warp & 3) * 32;
-                    const int st_off = SMEM_Q + t * TILE_BYTES + (warp & 3) * 4096;
+                    const int st_off = SMEM_Q + (qbuf * QT + t) * TILE_BYTES + (warp & 3) * 4096;
 #pragma unroll
                     for (int cc = 0; cc < HD / 32; ++cc) {
                         uint32_t o[32];
@@ -384,6 +433,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (P.L != nullptr && row < NQ) P.L[(size_t)bh * NQ + row] = m * 0.125f + __logf(l);
             }
         }
+        // this warp no longer touches the item's Q buffer (operand of its tile's Q K^T, then staging space)
+        __syncwarp();
+        if (ok && lane == 0) mx::mbar_arrive(bar(BAR_Q_EMPTY + qbuf));
+        }  // items
     }
 
     // ------------------------- teardown ---------------------------------
@@ -492,9 +545,14 @@ int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, 
     P.q_off = q_off;
     P.kv_group = kv_group;
     P.causal = causal ? 1 : 0;
+    P.heads = heads;
+    P.n_qblocks = (n_q + QT * BM - 1) / (QT * BM);
+    MX_REQUIRE((long long)heads * P.n_qblocks <= 0x7FFFFFFF, MX230_ERR_UNSUPPORTED, "flash forward: too many query blocks");
+    P.n_items = heads * P.n_qblocks;
     P.tma_out = tma_out ? 1 : 0;
     P.status = h->status_dev;
-    dim3 grid(heads, (n_q + QT * BM - 1) / (QT * BM));
+    // persistent: one CTA per SM (the kernel holds all of an SM's tensor memory), each walking its share of the items
+    dim3 grid((unsigned)(P.n_items < h->sm_count ? P.n_items : h->sm_count));
     MX_LAUNCH(h, st, MX230_K_FLASH_FWD,
               (flash_fwd_kernel<<<grid, FWD_THREADS, SMEM_ALLOC, st>>>(tq, tk, tv, to, P)));
     return MX230_OK;
