@@ -113,7 +113,37 @@ struct BwdParams {
     int n;
     int causal;
     int *status;
+    int heads;           // batch_heads
+    int n_tiles;         // owned tiles per head
+    int n_items;         // heads * n_tiles work items (owned tile, head), heads fastest, heaviest tiles first
 };
+
+// One CTA's `round`-th work item: an owned 128-row tile of one head and the range of streamed tiles it sees.
+// Items are listed heaviest first (dQ: late query tiles see the most keys; dK/dV: early key tiles see the most
+// queries) and dealt to the CTAs forwards in even rounds, backwards in odd ones, so that a persistent grid of
+// one CTA per SM ends up with equal shares; a grid of n_items CTAs gives every CTA exactly one item.
+struct BwdItem {
+    int bh, own0, it_beg, n;   // head, first owned row, first streamed tile, streamed tiles (>= 1)
+};
+template <int MODE>
+__device__ __forceinline__ bool bwd_item(const BwdParams &P, int round, BwdItem &I) {
+    const int G = (int)gridDim.x, c = (int)blockIdx.x;
+    const int i = round * G + ((round & 1) ? G - 1 - c : c);
+    if (i >= P.n_items) return false;
+    const int rank = i / P.heads;
+    I.bh = i - rank * P.heads;
+    const int tile = (MODE == 0 && P.causal) ? P.n_tiles - 1 - rank : rank;
+    I.own0 = tile * BT;
+    const int n_str_total = (P.n + BS - 1) / BS;
+    int it_beg = 0, it_end = n_str_total;
+    if (P.causal) {
+        if (MODE == 0) it_end = min(n_str_total, (I.own0 + BT - 1) / BS + 1);
+        else it_beg = I.own0 / BS;
+    }
+    I.it_beg = it_beg;
+    I.n = it_end - it_beg;
+    return true;
+}
 
 // MODE 0: dQ pass (own = Q, dO; stream = K, V).  MODE 1: dK/dV pass (own = K, V; stream = Q, dO).
 // MODE 2: the dK/dV pass that also forms every tile's dQ contribution (dS K, a fifth MMA stream reading
@@ -133,18 +163,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
     volatile int *abort_flag = (volatile int *)(smem + SM_BAR + 8 * N_BARS + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int N = P.n, bh = blockIdx.x;
-    const int n_str_total = (N + BS - 1) / BS;
-    // dQ: late query tiles see the most keys; dK/dV: early key tiles see the most queries.
-    // Either way the heaviest tiles of every head are dispatched first.
-    const int tile = (MODE == 0 && P.causal) ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
-    const int own0 = tile * BT;
-    int it_beg = 0, it_end = n_str_total;
-    if (P.causal) {
-        if (MODE == 0) it_end = min(n_str_total, (own0 + BT - 1) / BS + 1);
-        else it_beg = own0 / BS;
-    }
-    const int n = it_end - it_beg;  // >= 1
+    const int N = P.n;
     constexpr bool FUSED = MODE == 2;
     // the fused pass streams through three stages: the fourth one's two 16 KB slots hold its second E buffer
     constexpr int NST = FUSED ? STAGES - 1 : STAGES;
@@ -182,9 +201,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 if (MODE >= 1) {
                     mx::tma_prefetch_desc(&tmOwnA);
                     mx::tma_prefetch_desc(&tmOwnB);
-                    mx::mbar_expect_tx(bar(BAR_OWN_FULL), 2 * OWN_BYTES);
-                    mx::tma_load_3d(smem_base + SM_OWN_A, &tmOwnA, bar(BAR_OWN_FULL), 0, own0, bh);
-                    mx::tma_load_3d(smem_base + SM_OWN_B, &tmOwnB, bar(BAR_OWN_FULL), 0, own0, bh);
                 }
             }
             if (FUSED) {   // the constant operands: ones for X, ones for Y, zeros (ordered before the first arrive below)
@@ -197,56 +213,72 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 }
             }
             bool ok = true;
-            for (int y = 0; y < n; ++y) {
-                const int s = y % NST, r = y / NST;
-                const int row0 = (it_beg + y) * BS;
-                // -L*log2(e) and -Delta of the streamed queries: fetched before the wait, stored after it
-                float lv[4], dv[4];
+            uint32_t g = 0;   // streamed tiles so far, over all items: ring slot g % NST, use g / NST
+            BwdItem I;
+            for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
+                const int bh = I.bh;
                 if (MODE >= 1) {
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int q = row0 + u * 32 + lane;
-                        const bool v = q < N;
-                        // fused pass: X + lv is multiplied by 0.125 log2(e) afterwards, hence -8 L (exact)
-                        lv[u] = v ? -P.L[(size_t)bh * N + q] * (FUSED ? 8.0f : LOG2E) : 0.0f;
-                        dv[u] = v ? -P.Delta[(size_t)bh * N + q] : 0.0f;
+                    // the owned tiles are single-buffered: every MMA of the previous item must have completed
+                    if (it > 0) ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_ACC_DONE), (it - 1) & 1, abort_flag, P.status));
+                    if (!ok) break;
+                    if (lane == 0) {
+                        mx::mbar_expect_tx(bar(BAR_OWN_FULL), 2 * OWN_BYTES);
+                        mx::tma_load_3d(smem_base + SM_OWN_A, &tmOwnA, bar(BAR_OWN_FULL), 0, I.own0, bh);
+                        mx::tma_load_3d(smem_base + SM_OWN_B, &tmOwnB, bar(BAR_OWN_FULL), 0, I.own0, bh);
                     }
                 }
-                if (r > 0)
-                    ok = __all_sync(0xFFFFFFFFu,
-                                    mx::mbar_wait(bar(BAR_STR_EMPTY + s), (r - 1) & 1, abort_flag, P.status));
-                if (!ok) break;
-                if (lane == 0) {
-                    mx::mbar_expect_tx(bar(BAR_STR_FULL + s), 2 * STR_BYTES);
-                    mx::tma_load_3d(smem_base + SM_STR_A + s * STR_BYTES, &tmStrA, bar(BAR_STR_FULL + s), 0, row0, bh);
-                    mx::tma_load_3d(smem_base + SM_STR_B + s * STR_BYTES, &tmStrB, bar(BAR_STR_FULL + s), 0, row0, bh);
-                }
-                if (FUSED) {
-                    uint4 *aug = (uint4 *)(smem + SM_AUG_B + s * AUG_BYTES);
+                for (int y = 0; y < I.n; ++y, ++g) {
+                    const int s = g % NST;
+                    const uint32_t r = g / NST;
+                    const int row0 = (I.it_beg + y) * BS;
+                    // -L*log2(e) and -Delta of the streamed queries: fetched before the wait, stored after it
+                    float lv[4], dv[4];
+                    if (MODE >= 1) {
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        // value = hi + mid + lo, each a bf16: what is left over is below 2^-24 of it
-                        const uint32_t lh = mx::pack_bf16(lv[u], 0.0f) & 0xFFFFu;
-                        const float l1 = lv[u] - __uint_as_float(lh << 16);
-                        const uint32_t lm = mx::pack_bf16(l1, 0.0f) & 0xFFFFu;
-                        const float l2 = l1 - __uint_as_float(lm << 16);
-                        const uint32_t dh = mx::pack_bf16(dv[u], 0.0f) & 0xFFFFu;
-                        const float d1 = dv[u] - __uint_as_float(dh << 16);
-                        const uint32_t dm = mx::pack_bf16(d1, 0.0f) & 0xFFFFu;
-                        const float d2 = d1 - __uint_as_float(dm << 16);
-                        aug[u * 32 + lane] = make_uint4(lh | (lm << 16), (mx::pack_bf16(l2, 0.0f) & 0xFFFFu) | (dh << 16),
-                                                        dm | (mx::pack_bf16(d2, 0.0f) << 16), 0u);
+                        for (int u = 0; u < 4; ++u) {
+                            const int q = row0 + u * 32 + lane;
+                            const bool v = q < N;
+                            // fused pass: X + lv is multiplied by 0.125 log2(e) afterwards, hence -8 L (exact)
+                            lv[u] = v ? -P.L[(size_t)bh * N + q] * (FUSED ? 8.0f : LOG2E) : 0.0f;
+                            dv[u] = v ? -P.Delta[(size_t)bh * N + q] : 0.0f;
+                        }
                     }
-                    mx::fence_proxy_async_smem();   // read by the MMAs
-                    mx::mbar_arrive(bar(BAR_STR_FULL + s));
-                } else if (MODE >= 1) {
-                    float *ld = (float *)(smem + SM_LD + s * (2 * BS * 4));
+                    if (r > 0)
+                        ok = __all_sync(0xFFFFFFFFu,
+                                        mx::mbar_wait(bar(BAR_STR_EMPTY + s), (r - 1) & 1, abort_flag, P.status));
+                    if (!ok) break;
+                    if (lane == 0) {
+                        mx::mbar_expect_tx(bar(BAR_STR_FULL + s), 2 * STR_BYTES);
+                        mx::tma_load_3d(smem_base + SM_STR_A + s * STR_BYTES, &tmStrA, bar(BAR_STR_FULL + s), 0, row0, bh);
+                        mx::tma_load_3d(smem_base + SM_STR_B + s * STR_BYTES, &tmStrB, bar(BAR_STR_FULL + s), 0, row0, bh);
+                    }
+                    if (FUSED) {
+                        uint4 *aug = (uint4 *)(smem + SM_AUG_B + s * AUG_BYTES);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        ld[u * 32 + lane] = lv[u];
-                        ld[BS + u * 32 + lane] = dv[u];
+                        for (int u = 0; u < 4; ++u) {
+                            // value = hi + mid + lo, each a bf16: what is left over is below 2^-24 of it
+                            const uint32_t lh = mx::pack_bf16(lv[u], 0.0f) & 0xFFFFu;
+                            const float l1 = lv[u] - __uint_as_float(lh << 16);
+                            const uint32_t lm = mx::pack_bf16(l1, 0.0f) & 0xFFFFu;
+                            const float l2 = l1 - __uint_as_float(lm << 16);
+                            const uint32_t dh = mx::pack_bf16(dv[u], 0.0f) & 0xFFFFu;
+                            const float d1 = dv[u] - __uint_as_float(dh << 16);
+                            const uint32_t dm = mx::pack_bf16(d1, 0.0f) & 0xFFFFu;
+                            const float d2 = d1 - __uint_as_float(dm << 16);
+                            aug[u * 32 + lane] = make_uint4(lh | (lm << 16), (mx::pack_bf16(l2, 0.0f) & 0xFFFFu) | (dh << 16),
+                                                            dm | (mx::pack_bf16(d2, 0.0f) << 16), 0u);
+                        }
+                        mx::fence_proxy_async_smem();   // read by the MMAs
+                        mx::mbar_arrive(bar(BAR_STR_FULL + s));
+                    } else if (MODE >= 1) {
+                        float *ld = (float *)(smem + SM_LD + s * (2 * BS * 4));
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            ld[u * 32 + lane] = lv[u];
+                            ld[BS + u * 32 + lane] = dv[u];
+                        }
+                        mx::mbar_arrive(bar(BAR_STR_FULL + s));
                     }
-                    mx::mbar_arrive(bar(BAR_STR_FULL + s));
                 }
             }
             __syncwarp();
@@ -261,23 +293,28 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 const uint32_t own_t = tmem + (is_y ? TM_OWN_B : TM_OWN_A);
                 const uint32_t str_base = smem_base + (is_y ? SM_STR_B : SM_STR_A);
                 const uint32_t dst = tmem + (is_y ? TM_Y : TM_X);
-                bool ok = mx::mbar_wait(bar(BAR_OWN_FULL), 0, abort_flag, P.status);
-                for (int y = 0; y < n && ok; ++y) {
-                    const int s = y % NST, r = y / NST;
-                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
-                    // as soon as both warpgroups hold the previous X, Y in registers
-                    if (ok && y > 0) ok = mx::mbar_wait(bar(BAR_SDP_FREE), (y - 1) & 1, abort_flag, P.status);
-                    if (!ok) break;
-                    mx::tc_fence_after();
-                    const uint64_t sd = mx::smem_desc_sw128(str_base + s * STR_BYTES);
-                    if (MODE == 0) {
+                bool ok = true;
+                uint32_t g = 0;
+                BwdItem I;
+                for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
+                    ok = mx::mbar_wait(bar(BAR_OWN_FULL), it & 1, abort_flag, P.status);
+                    for (int y = 0; y < I.n && ok; ++y, ++g) {
+                        const int s = g % NST;
+                        ok = mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status);
+                        // as soon as both warpgroups hold the previous X, Y in registers
+                        if (ok && g > 0) ok = mx::mbar_wait(bar(BAR_SDP_FREE), (g - 1) & 1, abort_flag, P.status);
+                        if (!ok) break;
+                        mx::tc_fence_after();
+                        const uint64_t sd = mx::smem_desc_sw128(str_base + s * STR_BYTES);
+                        if (MODE == 0) {
 #pragma unroll
-                        for (int k = 0; k < HD / 16; ++k) mx::mma_ts(dst, own_t + 8 * k, sd + 2 * k, IDESC_S, k > 0);
-                    } else {
+                            for (int k = 0; k < HD / 16; ++k) mx::mma_ts(dst, own_t + 8 * k, sd + 2 * k, IDESC_S, k > 0);
+                        } else {
 #pragma unroll
-                        for (int k = 0; k < HD / 16; ++k) mx::mma_ss(dst, own + 2 * k, sd + 2 * k, IDESC_S, k > 0);
+                            for (int k = 0; k < HD / 16; ++k) mx::mma_ss(dst, own + 2 * k, sd + 2 * k, IDESC_S, k > 0);
+                        }
+                        mx::mma_commit(bar(BAR_SDP_FULL));
                     }
-                    mx::mma_commit(bar(BAR_SDP_FULL));
                 }
             }
             __syncwarp();
@@ -293,21 +330,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 const uint32_t a = tmem + (second ? TM_P : TM_E);
                 const uint32_t str_base = smem_base + (second ? SM_STR_B : SM_STR_A);
                 bool ok = true;
-                for (int y = 0; y < n && ok; ++y) {
-                    const int s = y % NST;
-                    const int r = y / NST;
-                    // the streamed tile (read here as the MN-major B operand) and E, P
-                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
-                    if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), y & 1, abort_flag, P.status);
-                    if (!ok) break;
-                    mx::tc_fence_after();
-                    const uint64_t sd = mx::smem_desc_sw128(str_base + s * STR_BYTES);
+                uint32_t g = 0;
+                BwdItem I;
+                for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
+                    for (int y = 0; y < I.n && ok; ++y, ++g) {
+                        const int s = g % NST;
+                        // the streamed tile (read here as the MN-major B operand) and E, P
+                        ok = mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status);
+                        if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), g & 1, abort_flag, P.status);
+                        if (!ok) break;
+                        mx::tc_fence_after();
+                        const uint64_t sd = mx::smem_desc_sw128(str_base + s * STR_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BS / 16; ++k) mx::mma_ts(acc, a + 8 * k, sd + 128 * k, IDESC_G, (y > 0 || k > 0));
-                    // X, Y of this tile were complete before its E, P could be formed, so this commit
-                    // also covers every read of the stage
-                    mx::mma_commit(bar(BAR_STR_EMPTY + s));
-                    if (y == n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                        for (int k = 0; k < BS / 16; ++k) mx::mma_ts(acc, a + 8 * k, sd + 128 * k, IDESC_G, (y > 0 || k > 0));
+                        // X, Y of this tile were complete before its E, P could be formed, so this commit
+                        // also covers every read of the stage
+                        mx::mma_commit(bar(BAR_STR_EMPTY + s));
+                        if (y == I.n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                    }
                 }
             }
             __syncwarp();
@@ -320,24 +360,29 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 const uint64_t own_v = mx::smem_desc_sw128(smem_base + SM_OWN_B);
                 const uint64_t aug_x = mx::smem_desc_kmajor_plain(smem_base + SM_AUG_AX, SM_AUG_Z - SM_AUG_AX);
                 const uint64_t aug_y = mx::smem_desc_kmajor_plain(smem_base + SM_AUG_AY, SM_AUG_Z - SM_AUG_AY);
-                bool ok = mx::mbar_wait(bar(BAR_OWN_FULL), 0, abort_flag, P.status);
-                for (int y = 0; y < n && ok; ++y) {
-                    const int s = y % NST, r = y / NST;
-                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
-                    if (ok && y > 0) ok = mx::mbar_wait(bar(BAR_SDP_FREE), (y - 1) & 1, abort_flag, P.status);
-                    if (!ok) break;
-                    mx::tc_fence_after();
-                    const uint64_t sq = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
-                    const uint64_t so = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
+                bool ok = true;
+                uint32_t g = 0;
+                BwdItem I;
+                for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
+                    ok = mx::mbar_wait(bar(BAR_OWN_FULL), it & 1, abort_flag, P.status);
+                    for (int y = 0; y < I.n && ok; ++y, ++g) {
+                        const int s = g % NST;
+                        ok = mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status);
+                        if (ok && g > 0) ok = mx::mbar_wait(bar(BAR_SDP_FREE), (g - 1) & 1, abort_flag, P.status);
+                        if (!ok) break;
+                        mx::tc_fence_after();
+                        const uint64_t sq = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
+                        const uint64_t so = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
 #pragma unroll
-                    for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_X, own_k + 2 * k, sq + 2 * k, IDESC_S, k > 0);
-                    const uint64_t bq = mx::smem_desc_kmajor_plain(smem_base + SM_AUG_B + s * AUG_BYTES,
-                                                                   SM_AUG_Z - SM_AUG_B - s * AUG_BYTES);
-                    mx::mma_ss(tmem + TM_X, aug_x, bq, IDESC_S, 1);   // X -= 8 L of the query column
+                        for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_X, own_k + 2 * k, sq + 2 * k, IDESC_S, k > 0);
+                        const uint64_t bq = mx::smem_desc_kmajor_plain(smem_base + SM_AUG_B + s * AUG_BYTES,
+                                                                       SM_AUG_Z - SM_AUG_B - s * AUG_BYTES);
+                        mx::mma_ss(tmem + TM_X, aug_x, bq, IDESC_S, 1);   // X -= 8 L of the query column
 #pragma unroll
-                    for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_Y, own_v + 2 * k, so + 2 * k, IDESC_S, k > 0);
-                    mx::mma_ss(tmem + TM_Y, aug_y, bq, IDESC_S, 1);   // Y -= Delta of the query column
-                    mx::mma_commit(bar(BAR_SDP_FULL));
+                        for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_Y, own_v + 2 * k, so + 2 * k, IDESC_S, k > 0);
+                        mx::mma_ss(tmem + TM_Y, aug_y, bq, IDESC_S, 1);   // Y -= Delta of the query column
+                        mx::mma_commit(bar(BAR_SDP_FULL));
+                    }
                 }
             }
             __syncwarp();
@@ -347,22 +392,26 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 constexpr uint32_t IDESC_G = mx::mma_idesc_bf16(BT, HD, false, true);
                 const uint64_t ds0 = mx::smem_desc_sw128(smem_base + SM_DS), ds1 = mx::smem_desc_sw128(smem_base + SM_DS1_A);
                 bool ok = true;
-                for (int y = 0; y < n && ok; ++y) {
-                    const int s = y % NST, r = y / NST;
-                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
-                    if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), y & 1, abort_flag, P.status);
-                    if (!ok) break;
-                    mx::tc_fence_after();
-                    const uint64_t sd = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
-                    // 16 queries of contraction = 32 B inside a row; queries 64.. are the second half tile
-                    const uint64_t lo = (y & 1) ? ds1 : ds0;
-                    const uint64_t hi = lo + (uint64_t)(((y & 1) ? SM_DS1_B - SM_DS1_A : DS_HALF_BYTES) >> 4);
+                uint32_t g = 0;
+                BwdItem I;
+                for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
+                    for (int y = 0; y < I.n && ok; ++y, ++g) {
+                        const int s = g % NST;
+                        ok = mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status);
+                        if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), g & 1, abort_flag, P.status);
+                        if (!ok) break;
+                        mx::tc_fence_after();
+                        const uint64_t sd = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
+                        // 16 queries of contraction = 32 B inside a row; queries 64.. are the second half tile
+                        const uint64_t lo = (g & 1) ? ds1 : ds0;
+                        const uint64_t hi = lo + (uint64_t)(((g & 1) ? SM_DS1_B - SM_DS1_A : DS_HALF_BYTES) >> 4);
 #pragma unroll
-                    for (int k = 0; k < BS / 16; ++k)
-                        mx::mma_ss(tmem + TMF_ACC0, (k >> 2 ? hi : lo) + (uint64_t)(2 * (k & 3)), sd + 128 * k, IDESC_G,
-                                   (y > 0 || k > 0));
-                    mx::mma_commit(bar(BAR_STR_EMPTY + s));
-                    if (y == n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                        for (int k = 0; k < BS / 16; ++k)
+                            mx::mma_ss(tmem + TMF_ACC0, (k >> 2 ? hi : lo) + (uint64_t)(2 * (k & 3)), sd + 128 * k, IDESC_G,
+                                       (y > 0 || k > 0));
+                        mx::mma_commit(bar(BAR_STR_EMPTY + s));
+                        if (y == I.n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                    }
                 }
             }
             __syncwarp();
@@ -378,26 +427,30 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 const uint64_t ad1 = mx::smem_desc_sw128_mn(smem_base + SM_DS1_A, SM_DS1_B - SM_DS1_A);
                 const uint64_t bd = mx::smem_desc_sw128(smem_base + SM_OWN_A);
                 bool ok = true;
-                for (int y = 0; y < n && ok; ++y) {
-                    const int s = y % NST, r = y / NST;
-                    ok = mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status);
-                    if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), y & 1, abort_flag, P.status);
-                    if (!ok) break;
-                    mx::tc_fence_after();
-                    const uint64_t sd = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
+                uint32_t g = 0;
+                BwdItem I;
+                for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
+                    for (int y = 0; y < I.n && ok; ++y, ++g) {
+                        const int s = g % NST;
+                        ok = mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status);
+                        if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), g & 1, abort_flag, P.status);
+                        if (!ok) break;
+                        mx::tc_fence_after();
+                        const uint64_t sd = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BS / 16; ++k)
-                        mx::mma_ts(tmem + TMF_ACC1, tmem + TMF_P + 8 * k, sd + 128 * k, IDESC_G, (y > 0 || k > 0));
-                    // the drain warps hold the previous dQ tile in registers
-                    if (y > 0) ok = mx::mbar_wait(bar(BAR_DQ_FREE), (y - 1) & 1, abort_flag, P.status);
-                    if (!ok) break;
-                    mx::tc_fence_after();
-                    const uint64_t ad = (y & 1) ? ad1 : ad0;
+                        for (int k = 0; k < BS / 16; ++k)
+                            mx::mma_ts(tmem + TMF_ACC1, tmem + TMF_P + 8 * k, sd + 128 * k, IDESC_G, (y > 0 || k > 0));
+                        // the drain warps hold the previous dQ tile in registers
+                        if (g > 0) ok = mx::mbar_wait(bar(BAR_DQ_FREE), (g - 1) & 1, abort_flag, P.status);
+                        if (!ok) break;
+                        mx::tc_fence_after();
+                        const uint64_t ad = (g & 1) ? ad1 : ad0;
 #pragma unroll
-                    for (int k = 0; k < BT / 16; ++k) mx::mma_ss(tmem + TMF_DQ, ad + 128 * k, bd + 128 * k, IDESC_Q, k > 0);
-                    mx::mma_commit(bar(BAR_DQ_FULL));
-                    mx::mma_commit(bar(BAR_STR_EMPTY + s));
-                    if (y == n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                        for (int k = 0; k < BT / 16; ++k) mx::mma_ss(tmem + TMF_DQ, ad + 128 * k, bd + 128 * k, IDESC_Q, k > 0);
+                        mx::mma_commit(bar(BAR_DQ_FULL));
+                        mx::mma_commit(bar(BAR_STR_EMPTY + s));
+                        if (y == I.n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                    }
                 }
             }
             __syncwarp();
@@ -413,34 +466,38 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             unsigned char *stage_row = smem + SM_DQ + (warp & 3) * DQ_STAGE_BYTES + lane * 128;
             if (lane == 0) mx::tma_prefetch_desc(&tmDQ);
             bool ok = true;
-            for (int y = 0; y < n; ++y) {
-                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_DQ_FULL), y & 1, abort_flag, P.status));
-                if (!ok) break;
-                mx::tc_fence_after();
-                const int qw = (it_beg + y) * BS + (warp & 3) * 32;   // first query of this warp's 32
+            uint32_t g = 0;
+            BwdItem I;
+            for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
+                for (int y = 0; y < I.n; ++y, ++g) {
+                    ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_DQ_FULL), g & 1, abort_flag, P.status));
+                    if (!ok) break;
+                    mx::tc_fence_after();
+                    const int qw = (I.it_beg + y) * BS + (warp & 3) * 32;   // first query of this warp's 32
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t v[32];
-                    mx::tmem_ld32(ta + half * 32, v);
-                    mx::tmem_wait_ld();
-                    if (half == 1) {  // the whole tile has left tensor memory
-                        mx::tc_fence_before();
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t v[32];
+                        mx::tmem_ld32(ta + half * 32, v);
+                        mx::tmem_wait_ld();
+                        if (half == 1) {  // the whole tile has left tensor memory
+                            mx::tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mx::mbar_arrive(bar(BAR_DQ_FREE));
+                        }
+                        // the previous reduction has finished reading the staging tile
+                        if (lane == 0) mx::bulk_wait_group_read<0>();
                         __syncwarp();
-                        if (lane == 0) mx::mbar_arrive(bar(BAR_DQ_FREE));
-                    }
-                    // the previous reduction has finished reading the staging tile
-                    if (lane == 0) mx::bulk_wait_group_read<0>();
-                    __syncwarp();
 #pragma unroll
-                    for (int cch = 0; cch < 8; ++cch)
-                        *(float4 *)(stage_row + ((cch ^ (lane & 7)) << 4)) =
-                            make_float4(__uint_as_float(v[4 * cch]) * 0.125f, __uint_as_float(v[4 * cch + 1]) * 0.125f,
-                                        __uint_as_float(v[4 * cch + 2]) * 0.125f, __uint_as_float(v[4 * cch + 3]) * 0.125f);
-                    mx::fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0 && qw < N) {   // a tile wholly past the end has nothing to add
-                        mx::tma_reduce_add_3d(&tmDQ, stage, half * 32, qw, bh);
-                        mx::bulk_commit_group();
+                        for (int cch = 0; cch < 8; ++cch)
+                            *(float4 *)(stage_row + ((cch ^ (lane & 7)) << 4)) =
+                                make_float4(__uint_as_float(v[4 * cch]) * 0.125f, __uint_as_float(v[4 * cch + 1]) * 0.125f,
+                                            __uint_as_float(v[4 * cch + 2]) * 0.125f, __uint_as_float(v[4 * cch + 3]) * 0.125f);
+                        mx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && qw < N) {   // a tile wholly past the end has nothing to add
+                            mx::tma_reduce_add_3d(&tmDQ, stage, half * 32, qw, I.bh);
+                            mx::bulk_commit_group();
+                        }
                     }
                 }
             }
@@ -452,10 +509,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
         // ------------------------- compute warpgroups -------------------
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_COMPUTE));
         const int h = warp >> 2;                        // column half of this warpgroup
-        const int row = own0 + (tid & 127);             // owned row (query | key) of this thread
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tm_row = tmem + lane_off;
         const float c = 0.125f * LOG2E;
+        bool ok = true;
+        uint32_t g = 0;   // streamed tiles so far, over all items
+        BwdItem I;
+        for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
+        const int bh = I.bh, own0 = I.own0, n = I.n, it_beg = I.it_beg;
+        const int row = own0 + (tid & 127);             // owned row (query | key) of this thread
         const bool rv = row < N;
         float nl0 = 0.0f, nl1 = 0.0f, nd0 = 0.0f, nd1 = 0.0f;  // -L*log2e and -Delta (MODE 0: of this row)
         if (MODE == 0) {
@@ -475,10 +537,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             __syncwarp();
             if (lane == 0) mx::mbar_arrive(bar(BAR_OWN_FULL));
         }
-        bool ok = true;
-        for (int y = 0; y < n; ++y) {
-            const int s = y % NST, r = y / NST;
-            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_SDP_FULL), y & 1, abort_flag, P.status));
+        for (int y = 0; y < n; ++y, ++g) {
+            const int s = g % NST;
+            const uint32_t r = g / NST;
+            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_SDP_FULL), g & 1, abort_flag, P.status));
             if (MODE == 1 && ok)  // the stage's L / Delta slices were written with plain stores
                 ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_FULL + s), r & 1, abort_flag, P.status));
             if (!ok) break;
@@ -510,7 +572,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             // fused pass: E goes to shared memory as bf16, this thread's key row = one 128-byte swizzled line of
             // 64 queries.  Two buffers: the MMAs of tile y-1 may still read the other one (those of y-2 are
             // done: the previous iteration waited for them before its own tensor-memory stores).
-            unsigned char *dsrow = smem + ((y & 1) ? SM_DS1_A + h * (SM_DS1_B - SM_DS1_A) : SM_DS + h * DS_HALF_BYTES) +
+            unsigned char *dsrow = smem + ((g & 1) ? SM_DS1_A + h * (SM_DS1_B - SM_DS1_A) : SM_DS + h * DS_HALF_BYTES) +
                                    (tid & 127) * 128;
 #pragma unroll
             for (int i = 0; i < HS; i += 2) {
@@ -532,9 +594,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                         make_uint4(pe[4 * cch], pe[4 * cch + 1], pe[4 * cch + 2], pe[4 * cch + 3]);
                 }
             }
-            if (y > 0) {  // the accumulate MMAs of the previous tile have consumed E, P
-                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_EMPTY + (y - 1) % NST),
-                                                           ((y - 1) / NST) & 1, abort_flag, P.status));
+            if (g > 0) {  // the accumulate MMAs of the previous tile (of the previous item, at y == 0) have consumed E, P
+                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_EMPTY + (g - 1) % NST),
+                                                           ((g - 1) / NST) & 1, abort_flag, P.status));
                 if (!ok) break;
                 mx::tc_fence_after();
             }
@@ -547,7 +609,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             if (lane == 0) mx::mbar_arrive(bar(BAR_DS_READY));
         }
         // ---- epilogue: accumulators -> global, dS's 1/sqrt(d) applied here ----
-        if (ok) ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag, P.status));
+        if (ok) ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_ACC_DONE), it & 1, abort_flag, P.status));
         if (ok) {
             mx::tc_fence_after();
             if (MODE == 0) {
@@ -564,19 +626,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 }
             } else if (FUSED) {
                 // the left warpgroup stores dK (scaled), the right one dV: each warp stages its 32 rows, 32 columns
-                // at a time, in a swizzled 4 KB tile (the stream stages are idle now: every MMA has completed) and
-                // hands it to the TMA unit -- 16-byte stores from lane = row registers would each touch a sector
-                // of their own and took 3.2 us per CTA
+                // at a time, in a swizzled 4 KB tile and hands it to the TMA unit -- 16-byte stores from lane = row
+                // registers would each touch a sector of their own and took 3.2 us per CTA.  The two staging tiles
+                // are this warp's own 32 rows of the two E buffers (every MMA of the item has completed, and no other
+                // warp writes there), so the stream stages and the owned tiles are free for the next item's loads
+                // meanwhile.
                 const float sc = h == 0 ? 0.125f : 1.0f;
                 const CUtensorMap *tm = h == 0 ? &tmOut0 : &tmOut1;
                 const int wrow0 = own0 + (warp & 3) * 32;
-                const int st_off = (h == 0 ? SM_STR_A : SM_STR_B) + (warp & 3) * (2 * DQ_STAGE_BYTES);
+                const int st_off[2] = {SM_DS + h * DS_HALF_BYTES + (warp & 3) * DQ_STAGE_BYTES,
+                                       SM_DS1_A + h * (SM_DS1_B - SM_DS1_A) + (warp & 3) * DQ_STAGE_BYTES};
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
                     uint32_t v[32];
                     mx::tmem_ld32(tm_row + (h == 0 ? tACC0 : tACC1) + cc * 32, v);
                     mx::tmem_wait_ld();
-                    unsigned char *srow = smem + st_off + cc * DQ_STAGE_BYTES + lane * 128;
+                    unsigned char *srow = smem + st_off[cc] + lane * 128;
 #pragma unroll
                     for (int cch = 0; cch < 8; ++cch)
                         *(float4 *)(srow + ((cch ^ (lane & 7)) << 4)) =
@@ -586,8 +651,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 mx::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0 && wrow0 < N) {
-                    mx::tma_store_3d(tm, smem_base + st_off, 0, wrow0, bh);
-                    mx::tma_store_3d(tm, smem_base + st_off + DQ_STAGE_BYTES, 32, wrow0, bh);
+                    mx::tma_store_3d(tm, smem_base + st_off[0], 0, wrow0, bh);
+                    mx::tma_store_3d(tm, smem_base + st_off[1], 32, wrow0, bh);
                     mx::bulk_commit_group();
                     mx::bulk_wait_group_read<0>();   // the staging tiles must outlive the reads
                 }
@@ -611,6 +676,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 }
             }
         }
+        }  // items
     }
     mx::tc_fence_before();
     __syncthreads();
@@ -664,11 +730,19 @@ int make_maps(mx230_handle *h, Maps &m, const void *Qb, const void *Kb, const vo
     return MX230_OK;
 }
 
+// work-item fields of the parameters; returns the number of items
+int set_items(BwdParams &P, int batch_heads, int n) {
+    P.heads = batch_heads;
+    P.n_tiles = (n + BT - 1) / BT;
+    P.n_items = batch_heads * P.n_tiles;
+    return P.n_items;
+}
+
 int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dQ,
               int batch_heads, int n, int causal) {
     BwdParams P{L, Delta, dQ, nullptr, nullptr, (const uint4 *)m.ptr[0], (const uint4 *)m.ptr[3], n, causal ? 1 : 0,
                 h->status_dev};
-    dim3 grid(batch_heads, (n + BT - 1) / BT);
+    dim3 grid((unsigned)set_items(P, batch_heads, n));   // one item per CTA
     MX_LAUNCH(h, st, MX230_K_BWD_DQ,
               (bwd_kernel<0><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[0], m.box128[3], m.box128[1],
                                                                   m.box128[2], m.box128[0], m.box128[0], m.box128[0], P)));
@@ -678,7 +752,7 @@ int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, c
 int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dK,
                float *dV, int batch_heads, int n, int causal) {
     BwdParams P{L, Delta, dK, dV, nullptr, nullptr, nullptr, n, causal ? 1 : 0, h->status_dev};
-    dim3 grid(batch_heads, (n + BT - 1) / BT);
+    dim3 grid((unsigned)set_items(P, batch_heads, n));   // one item per CTA
     MX_LAUNCH(h, st, MX230_K_BWD_DKV,
               (bwd_kernel<1><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
                                                                   m.box128[3], m.box128[0], m.box128[0], m.box128[0], P)));
@@ -697,7 +771,10 @@ int launch_fused(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L
     if (rc) return rc;
     if (!dq_is_zero) MX_CHECK_CUDA(cudaMemsetAsync(dQ, 0, (size_t)batch_heads * n * HD * sizeof(float), st));
     BwdParams P{L, Delta, dK, dV, dQ, nullptr, nullptr, n, causal ? 1 : 0, h->status_dev};
-    dim3 grid(batch_heads, (n + BT - 1) / BT);
+    // persistent: one CTA per SM (the kernel holds all of an SM's tensor memory) walks its share of the items, the
+    // next item's owned and first streamed tiles loading while the compute warps store the current item's dK, dV
+    const int n_items = set_items(P, batch_heads, n);
+    dim3 grid((unsigned)(n_items < h->sm_count ? n_items : h->sm_count));
     MX_LAUNCH(h, st, MX230_K_BWD_FUSED,
               (bwd_kernel<2><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
                                                                   m.box128[3], tm_dq, tm_dk, tm_dv, P)));
