@@ -71,7 +71,17 @@ class ClockSampler:
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        # `index` is the CUDA device ordinal of this process; nvidia-smi numbers the physical GPUs, which
+        # differs under CUDA_VISIBLE_DEVICES, so the GPU is named by its UUID when torch can give it
+        self.index, self.rows, self.proc = str(index), [], None
+        try:
+            import torch
+            name = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+            if subprocess.run(["nvidia-smi", f"--id={name}", "--query-gpu=index", "--format=csv,noheader"],
+                              capture_output=True, timeout=20).returncode == 0:
+                self.index = name
+        except Exception:
+            pass
 
     def start(self):
         try:
