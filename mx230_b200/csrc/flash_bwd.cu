@@ -13,8 +13,12 @@
 //    by key tiles (MODE 1), each output element written exactly once, bit-reproducible;
 //  * one fused pass (MODE 2, the default of mx230_attn_bwd_flash): the dK/dV pass also forms every tile's
 //    dQ contribution and adds it to global memory with fp32 reductions, so S and dP are computed once.
-// A CTA owns ONE 128-row tile (queries for dQ, keys otherwise) and streams 128-row tiles of the other axis
-// through a TMA ring.  Per streamed tile:
+// A work item is ONE owned 128-row tile of one head (queries for dQ, keys otherwise) against the 128-row tiles
+// of the other axis, streamed through a TMA ring.  The two-pass kernels run one item per CTA; the fused pass is
+// persistent: one CTA per SM walks its share of the items (heaviest first, dealt out in snake order), ring
+// positions and barrier parities run on from item to item, and the next item's owned and first streamed tiles
+// are requested as soon as the current item's last MMAs have completed, while its dK / dV are still being stored.
+// Per streamed tile:
 //
 //   X = A_own A_str^T, Y = B_own B_str^T      (S, dP   |  S^T, dP^T)   128 x 128, N = 128 MMAs
 //   P = exp2(X c - L), E = P o (Y - Delta)    one thread per owned row and column half
