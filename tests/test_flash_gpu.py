@@ -195,6 +195,34 @@ def test_backward_batched_split_passes_and_determinism(handle):
     assert np.array_equal(c.cpu().numpy(), gv)
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_more_items_than_sms_every_head_equals_itself_alone(handle, causal):
+    """The forward and the fused backward walk their (tile, head) work items with one CTA per SM: with
+    37 heads of 1100 rows there are 185 forward items and 333 backward items, i.e. a full round, a
+    reversed one and a partial one on 148 SMs.  Heads are independent units (the reference kernels are
+    per head, 02-flash-attention/src/main.rs:68-88,179-210), so every sampled head of the batched call
+    must equal the same head run alone, whatever CTA and round it fell into."""
+    bh, n = 37, 1100
+    q, k, v, do = (oracle.normal((bh, n, 64), 31, i) for i in range(4))
+    o, delta, dq, dk, dv = run_bwd(handle, q, k, v, do, causal)
+    o_again, l = run_fwd(handle, q, k, v, causal)
+    assert np.array_equal(o_again, o)
+    assert np.isfinite(o).all() and np.isfinite(dq).all() and np.isfinite(dk).all() and np.isfinite(dv).all()
+    for h_ in (0, 1, 17, 35, 36):
+        o1, delta1, dq1, dk1, dv1 = run_bwd(handle, q[h_], k[h_], v[h_], do[h_], causal)
+        assert np.array_equal(o1.reshape(n, 64), o[h_]) and np.array_equal(delta1.reshape(n), delta[h_])
+        assert np.array_equal(dk1.reshape(n, 64), dk[h_]) and np.array_equal(dv1.reshape(n, 64), dv[h_])
+        assert_close(dq[h_], dq1.reshape(n, 64), f"dQ head {h_}, batched vs alone", max_abs=1e-4, mean_rel=1e-5)
+    # one head against the oracle as well
+    wo, wl = oracle.attn_fwd(q[36], k[36], v[36], causal)
+    wq, wk, wv = oracle.attn_bwd(q[36], k[36], v[36], do[36], causal)
+    assert_close(o[36], wo, "O")
+    assert_close(l[36], wl, "L")
+    assert_close(dq[36], wq, "dQ")
+    assert_close(dk[36], wk, "dK")
+    assert_close(dv[36], wv, "dV")
+
+
 def test_linearity_in_v_and_do_at_full_length(handle):
     """Size-independent properties at N=4096 (the benchmark's sequence length), where the
     oracle would take minutes: O is linear in V; dV is linear in dO; row sums of softmax
