@@ -59,10 +59,21 @@ enum {
     MX230_OPT_DECODE_CHUNK = 2,  /* keys per decode CTA; 0 = automatic */
     MX230_OPT_DECODE_TENSOR = 3, /* int8 decode in the reference score mode: 1 (default) = the GQA group's two
                                     contractions on warp-level tensor-core tiles, 0 = CUDA cores only */
-    MX230_OPT_BWD_TWO_PASS = 4   /* mx230_attn_bwd_flash*: 0 (default) = one fused pass, dK/dV written once and dQ
+    MX230_OPT_BWD_TWO_PASS = 4,  /* mx230_attn_bwd_flash*: 0 (default) = one fused pass, dK/dV written once and dQ
                                     summed with fp32 reductions (order of the partial sums not fixed);
                                     1 = the reference's atomic-free split, a dQ pass and a dK/dV pass,
                                     bit-reproducible */
+    MX230_OPT_BWD_REUSE_STAGED = 5, /* mx230_attn_bwd_{dq,dkv,flash}: 1 = when the workspace still holds the bf16 copies
+                                    of Q, K, V that mx230_attn_flash[_lse] staged for the SAME pointers and shape
+                                    (no other workspace-using call in between, same stream, tensor contents
+                                    unchanged -- the caller's promise), stage only dO.  0 (default) = always
+                                    stage all four */
+    MX230_OPT_WAIT_LIMIT = 6,    /* bound of every device-side barrier wait, in thousands of SM cycles (default
+                                    4000000 = 4e9 cycles, about 2 s); on expiry the kernel records a status and
+                                    returns (mx230_check_status -> MX230_ERR_DEVICE_STATUS).  Synchronises the device */
+    MX230_OPT_TEST_DROP_TILE = 7 /* test hook, default -1 = off: while set, the TMA producer of CTA 0 of a flash forward /
+                                    fused backward launch never requests its value-th streamed tile, so that the
+                                    bounded wait of its consumer runs out and the abort path executes */
 };
 
 /* kernel ids of the profiling interface */
@@ -398,6 +409,10 @@ int mx230_kv_pool_insert(mx230_kv_pool *p, const uint32_t *tokens, int n, const 
  * step 4 (the tree takes over the new full chunks, the request's borrow is released). */
 int mx230_kv_pool_begin_request(mx230_kv_pool *p, const uint32_t *tokens, int n, int *reused_tokens);
 int mx230_kv_pool_end_request(mx230_kv_pool *p, const uint32_t *tokens, int n);
+/* Gives the open request up instead of ending it (its attention step failed to enqueue): the borrow of
+ * every table block is released and the tree adopts nothing, so the never-written blocks cannot be matched
+ * by a later request.  The reference panics at this point (gpu.rs:2273-2345). */
+int mx230_kv_pool_abort_request(mx230_kv_pool *p);
 int mx230_kv_pool_audit(const mx230_kv_pool *p);                        /* Paging::audit, gpu.rs:476 */
 
 /* ---- continuous-batching scheduler over batched decode ---------------------------------------

@@ -18,6 +18,7 @@ OK = 0
 ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_STATUS, ERR_NO_DEVICE = range(1, 7)
 Q8_SCORE_REF, Q8_SCORE_EXACT = 0, 1
 OPT_Q8_SCORE_MODE, OPT_DECODE_CHUNK, OPT_DECODE_TENSOR, OPT_BWD_TWO_PASS = 1, 2, 3, 4
+OPT_BWD_REUSE_STAGED, OPT_WAIT_LIMIT, OPT_TEST_DROP_TILE = 5, 6, 7
 K_COUNT = 14
 
 

@@ -31,13 +31,22 @@ struct mx230_handle {
     int sm_count;
     void *ws;              // workspace: bf16 operand staging / split-KV partials
     size_t ws_bytes;
-    int *status_dev;       // [4] device status words (0 = ok)
+    int *status_dev;       // [8] device words: [0..3] status (0 = ok), [4..5] the wait limit in SM cycles (64-bit)
+    int test_drop_tile;    // test hook: streamed tile that CTA 0's producer never requests (-1 = off)
     unsigned *counters;    // split-KV arrival counters (self-resetting)
     size_t n_counters;
     int q8_score_mode;     // MX230_Q8_SCORE_*
     int decode_chunk;      // keys per decode CTA (0 = automatic)
     int decode_tensor;     // int8 decode, reference score mode: tensor-core tiles (1) or CUDA cores (0)
     int bwd_two_pass;      // flash backward: two atomic-free passes (1) or one fused pass with dQ reductions (0)
+    int bwd_reuse_staged;  // flash backward: skip re-staging Q, K, V when the workspace still holds the forward's copies
+    // which fp32 tensors the workspace's staged bf16 Q (pre-scaled), K, V currently belong to; cleared by every
+    // entry point that writes the workspace for something else
+    struct {
+        const void *q, *k, *v;
+        int batch_heads, n;
+        int valid;
+    } staged;
     long long launches;    // kernels launched through this handle
     mx230_encode_tiled_fn encode_tiled;
     // per-kernel timing: event pairs recorded around launches while enabled
@@ -114,17 +123,37 @@ int mx230_make_tmap_f32_half_rows(mx230_handle *h, CUtensorMap *out, const void 
 int mx230_make_tmap_f32_half_rows_strided(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
                                           uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes);
 
-// fp32 -> bf16 staging of up to four equally sized tensors in one launch (flash_fwd.cu); `zero`, if not
-// null, is a buffer of `count` floats cleared by the same launch.
+// fp32 -> bf16 staging of up to four equally sized tensors of `heads` x `per_head` elements in one launch
+// (flash_fwd.cu).  `zero`, if not null, is a buffer of the same size cleared by the same launch.  Tensor 0 is
+// multiplied by `scale0` before rounding (1 = plain cast).  norm2[t] (t = 0, 1; may be null): receives, per head
+// and grid part, the largest squared row norm (rows of 64 values) of tensor t as given, [heads][MX230_NORM_PARTS]
+// floats with unused parts set to 0 -- what the forward kernel needs for its bound on |q . k|.
+constexpr int MX230_NORM_PARTS = 32;
 int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src, void *const *dst,
-                      int n_tensors, size_t count, float *zero);
+                      int n_tensors, int heads, size_t per_head, float *zero, float scale0, float *const *norm2);
+// 1/sqrt(64) * log2(e): Q staged times this gives scores in log2 units
+#define MX230_QK_LOG2_SCALE (0.125f * 1.4426950408889634f)
+// layout of the flash entry points' workspace: `k` staged bf16 tensors of mx230_flash_stage_bytes each, then the
+// row-norm partials of Q and K
+inline size_t mx230_flash_stage_bytes(int batch_heads, int n) {
+    size_t one = (size_t)batch_heads * (size_t)n * 64 * 2;
+    return (one + 1023) & ~(size_t)1023;
+}
+inline size_t mx230_flash_norm_bytes(int batch_heads) {
+    size_t b = (size_t)2 * batch_heads * MX230_NORM_PARTS * sizeof(float);
+    return (b + 1023) & ~(size_t)1023;
+}
 
 // tcgen05 flash forward over staged bf16 operands (flash_fwd.cu).  Q [heads][n_q][64]; K, V
 // [heads / kv_group][n_k][64]; causal row r sees keys <= r + q_off; output row r of head h at
-// O + h*o_head_stride + r*o_row_stride.
+// O + h*o_head_stride + r*o_row_stride.  q_prescaled: Qb holds Q * MX230_QK_LOG2_SCALE.  q_norm2 / k_norm2 (both or
+// neither): largest squared row norm per head of the unscaled Q [heads][MX230_NORM_PARTS] and of K
+// [heads / kv_group][MX230_NORM_PARTS]; with them (and q_prescaled) a head whose scores are provably small takes the
+// kernel's max-free softmax loop.
 int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
                               const void *Vb, float *O, float *L, int heads, int n_q, int n_k, int q_off,
-                              int kv_group, long long o_head_stride, long long o_row_stride, int causal);
+                              int kv_group, long long o_head_stride, long long o_row_stride, int causal,
+                              int q_prescaled, const float *q_norm2, const float *k_norm2);
 
 // ---------------------------------------------------------------------------
 // device
@@ -133,7 +162,8 @@ int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, 
 
 namespace mx {
 
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s of SM cycles per wait
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // default bound of a wait: about 2 s of SM cycles
+constexpr int STATUS_LIMIT_WORD = 4;                   // status[4..5]: the bound in force (64-bit), set by the host
 constexpr int STATUS_WAIT_TIMEOUT = 1;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -184,13 +214,43 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((++polls & 255u) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (clock64() - t0 > *(const volatile long long *)(status + STATUS_LIMIT_WORD)) {
                 *abort_flag = 1;
                 atomicExch(status, STATUS_WAIT_TIMEOUT);
                 return false;
             }
         }
     }
+}
+
+// One lane of the (converged) warp: the branch it guards leaves the rest of the warp's code warp-uniform, so
+// that operands of the guarded instructions (descriptors, addresses) can live on the uniform datapath.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+// Non-blocking look at a barrier phase (no suspend, no retry): costs a fraction of a try_wait that passes.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait with the cheap look first: for phases that have normally completed long before.
+__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status) {
+    if (mbar_test(bar, parity)) return true;
+    return mbar_wait(bar, parity, abort_flag, status);
 }
 
 // ---- TMA: plain (per-CTA) tiled loads into this CTA's shared memory ----

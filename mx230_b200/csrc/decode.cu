@@ -1253,6 +1253,7 @@ int launch_decode(mx230_handle *h, void *stream, DecodeParams P, int n_seq, int 
                    "attn_decode: workspace %zu B < %zu B needed for %d key splits", h->ws_bytes, need,
                    n_splits);
         size_t rows = (size_t)n_seq * P.n_head * n_splits;
+        h->staged.valid = 0;   // the workspace is about to hold something else
         P.ws_acc = (float *)h->ws;
         P.ws_m = P.ws_acc + rows * 64;
         P.ws_l = P.ws_m + rows;

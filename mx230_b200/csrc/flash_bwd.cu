@@ -120,6 +120,7 @@ struct BwdParams {
     int heads;           // batch_heads
     int n_tiles;         // owned tiles per head
     int n_items;         // heads * n_tiles work items (owned tile, head), heads fastest, heaviest tiles first
+    int test_drop_tile;  // test hook (fused pass): streamed tile (counted over the CTA's items) that CTA 0's producer never requests; -1 = off
 };
 
 // One CTA's `round`-th work item: an owned 128-row tile of one head and the range of streamed tiles it sees.
@@ -152,7 +153,10 @@ __device__ __forceinline__ bool bwd_item(const BwdParams &P, int round, BwdItem 
 // MODE 0: dQ pass (own = Q, dO; stream = K, V).  MODE 1: dK/dV pass (own = K, V; stream = Q, dO).
 // MODE 2: the dK/dV pass that also forms every tile's dQ contribution (dS K, a fifth MMA stream reading
 // dS^T from shared memory as an MN-major A operand) and adds it to dQ in global memory.
-template <int MODE>
+// PRE: the bf16 Q holds Q * scale * log2(e) (what the fp32 entry points stage, and what the forward used for L): the
+// scores X arrive in log2 units, and dK, a product with that Q, is scaled back on its way out.  The caller-staged
+// bf16 entry point passes plain Q (PRE = false).
+template <int MODE, bool PRE>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ CUtensorMap tmOwnB,
            const __grid_constant__ CUtensorMap tmStrA, const __grid_constant__ CUtensorMap tmStrB,
@@ -242,8 +246,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                         for (int u = 0; u < 4; ++u) {
                             const int q = row0 + u * 32 + lane;
                             const bool v = q < N;
-                            // fused pass: X + lv is multiplied by 0.125 log2(e) afterwards, hence -8 L (exact)
-                            lv[u] = v ? -P.L[(size_t)bh * N + q] * (FUSED ? 8.0f : LOG2E) : 0.0f;
+                            // fused pass over a plain Q: X + lv is multiplied by 0.125 log2(e) afterwards, hence -8 L (exact)
+                            lv[u] = v ? -P.L[(size_t)bh * N + q] * ((FUSED && !PRE) ? 8.0f : LOG2E) : 0.0f;
                             dv[u] = v ? -P.Delta[(size_t)bh * N + q] : 0.0f;
                         }
                     }
@@ -251,6 +255,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                         ok = __all_sync(0xFFFFFFFFu,
                                         mx::mbar_wait(bar(BAR_STR_EMPTY + s), (r - 1) & 1, abort_flag, P.status));
                     if (!ok) break;
+                    if (FUSED && P.test_drop_tile == (int)g && blockIdx.x == 0) continue;   // test hook: this tile never arrives
                     if (lane == 0) {
                         mx::mbar_expect_tx(bar(BAR_STR_FULL + s), 2 * STR_BYTES);
                         mx::tma_load_3d(smem_base + SM_STR_A + s * STR_BYTES, &tmStrA, bar(BAR_STR_FULL + s), 0, row0, bh);
@@ -516,6 +521,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tm_row = tmem + lane_off;
         const float c = 0.125f * LOG2E;
+        // dK = scale * dS^T Q; with Q staged as Q * scale * log2(e) that is dS^T Q' / log2(e)
+        constexpr float DK_SCALE = PRE ? 0.6931471805599453f : 0.125f;
         bool ok = true;
         uint32_t g = 0;   // streamed tiles so far, over all items
         BwdItem I;
@@ -585,9 +592,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                     nl0 = l2.x, nl1 = l2.y, nd0 = d2.x, nd1 = d2.y;
                 }
                 // (fused pass: X, Y arrive with -8 L and -Delta already added by the MMAs; nl, nd stay 0)
-                const float p0 = FUSED ? mx::ex2(__uint_as_float(xv[i]) * c) : mx::ex2(fmaf(__uint_as_float(xv[i]), c, nl0));
-                const float p1 = FUSED ? mx::ex2(__uint_as_float(xv[i + 1]) * c)
-                                       : mx::ex2(fmaf(__uint_as_float(xv[i + 1]), c, nl1));
+                float p0, p1;
+                if (FUSED) {
+                    p0 = PRE ? mx::ex2(__uint_as_float(xv[i])) : mx::ex2(__uint_as_float(xv[i]) * c);
+                    p1 = PRE ? mx::ex2(__uint_as_float(xv[i + 1])) : mx::ex2(__uint_as_float(xv[i + 1]) * c);
+                } else {
+                    p0 = PRE ? mx::ex2(__uint_as_float(xv[i]) + nl0) : mx::ex2(fmaf(__uint_as_float(xv[i]), c, nl0));
+                    p1 = PRE ? mx::ex2(__uint_as_float(xv[i + 1]) + nl1) : mx::ex2(fmaf(__uint_as_float(xv[i + 1]), c, nl1));
+                }
                 const float e0 = FUSED ? p0 * __uint_as_float(yv[i]) : p0 * (__uint_as_float(yv[i]) + nd0);
                 const float e1 = FUSED ? p1 * __uint_as_float(yv[i + 1]) : p1 * (__uint_as_float(yv[i + 1]) + nd1);
                 pe[i >> 1] = mx::pack_bf16(e0, e1);
@@ -635,7 +647,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 // are this warp's own 32 rows of the two E buffers (every MMA of the item has completed, and no other
                 // warp writes there), so the stream stages and the owned tiles are free for the next item's loads
                 // meanwhile.
-                const float sc = h == 0 ? 0.125f : 1.0f;
+                const float sc = h == 0 ? DK_SCALE : 1.0f;
                 const CUtensorMap *tm = h == 0 ? &tmOut0 : &tmOut1;
                 const int wrow0 = own0 + (warp & 3) * 32;
                 const int st_off[2] = {SM_DS + h * DS_HALF_BYTES + (warp & 3) * DQ_STAGE_BYTES,
@@ -663,7 +675,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 __syncwarp();
             } else {
                 // the left warpgroup stores dK (scaled), the right one dV
-                const float sc = h == 0 ? 0.125f : 1.0f;
+                const float sc = h == 0 ? DK_SCALE : 1.0f;
                 float *dst = (h == 0 ? P.out0 : P.out1) + ((size_t)bh * N + row) * HD;
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
@@ -709,9 +721,12 @@ int set_attrs(int device) {
     static bool done[64] = {};
     MX_REQUIRE(device >= 0 && device < 64, MX230_ERR_UNSUPPORTED, "flash backward: device index %d", device);
     if (!done[device]) {
-        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
-        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
-        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
+        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
+        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
+        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
+        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
+        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
+        MX_CHECK_CUDA(cudaFuncSetAttribute(bwd_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_ALLOC));
         done[device] = true;
     }
     return MX230_OK;
@@ -736,6 +751,7 @@ int make_maps(mx230_handle *h, Maps &m, const void *Qb, const void *Kb, const vo
 
 // work-item fields of the parameters; returns the number of items
 int set_items(BwdParams &P, int batch_heads, int n) {
+    P.test_drop_tile = -1;
     P.heads = batch_heads;
     P.n_tiles = (n + BT - 1) / BT;
     P.n_items = batch_heads * P.n_tiles;
@@ -743,23 +759,33 @@ int set_items(BwdParams &P, int batch_heads, int n) {
 }
 
 int launch_dq(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dQ,
-              int batch_heads, int n, int causal) {
+              int batch_heads, int n, int causal, bool pre) {
     BwdParams P{L, Delta, dQ, nullptr, nullptr, (const uint4 *)m.ptr[0], (const uint4 *)m.ptr[3], n, causal ? 1 : 0,
                 h->status_dev};
     dim3 grid((unsigned)set_items(P, batch_heads, n));   // one item per CTA
-    MX_LAUNCH(h, st, MX230_K_BWD_DQ,
-              (bwd_kernel<0><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[0], m.box128[3], m.box128[1],
-                                                                  m.box128[2], m.box128[0], m.box128[0], m.box128[0], P)));
+    if (pre)
+        MX_LAUNCH(h, st, MX230_K_BWD_DQ,
+                  (bwd_kernel<0, true><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[0], m.box128[3], m.box128[1], m.box128[2],
+                                                                            m.box128[0], m.box128[0], m.box128[0], P)));
+    else
+        MX_LAUNCH(h, st, MX230_K_BWD_DQ,
+                  (bwd_kernel<0, false><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[0], m.box128[3], m.box128[1], m.box128[2],
+                                                                             m.box128[0], m.box128[0], m.box128[0], P)));
     return MX230_OK;
 }
 
 int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dK,
-               float *dV, int batch_heads, int n, int causal) {
+               float *dV, int batch_heads, int n, int causal, bool pre) {
     BwdParams P{L, Delta, dK, dV, nullptr, nullptr, nullptr, n, causal ? 1 : 0, h->status_dev};
     dim3 grid((unsigned)set_items(P, batch_heads, n));   // one item per CTA
-    MX_LAUNCH(h, st, MX230_K_BWD_DKV,
-              (bwd_kernel<1><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
-                                                                  m.box128[3], m.box128[0], m.box128[0], m.box128[0], P)));
+    if (pre)
+        MX_LAUNCH(h, st, MX230_K_BWD_DKV,
+                  (bwd_kernel<1, true><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0], m.box128[3],
+                                                                            m.box128[0], m.box128[0], m.box128[0], P)));
+    else
+        MX_LAUNCH(h, st, MX230_K_BWD_DKV,
+                  (bwd_kernel<1, false><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0], m.box128[3],
+                                                                             m.box128[0], m.box128[0], m.box128[0], P)));
     return MX230_OK;
 }
 
@@ -767,7 +793,7 @@ int launch_dkv(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, 
 // CTA that owns the key tile, dQ zeroed here and summed into by every CTA (fp32 reductions at L2, so
 // the order of dQ's partial sums is not fixed from run to run).
 int launch_fused(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L, const float *Delta, float *dQ,
-                 float *dK, float *dV, int batch_heads, int n, int causal, bool dq_is_zero) {
+                 float *dK, float *dV, int batch_heads, int n, int causal, bool dq_is_zero, bool pre) {
     CUtensorMap tm_dq, tm_dk, tm_dv;
     int rc = mx230_make_tmap_f32_half_rows(h, &tm_dq, dQ, n, batch_heads);
     if (!rc) rc = mx230_make_tmap_f32_half_rows(h, &tm_dk, dK, n, batch_heads);
@@ -778,10 +804,16 @@ int launch_fused(mx230_handle *h, cudaStream_t st, const Maps &m, const float *L
     // persistent: one CTA per SM (the kernel holds all of an SM's tensor memory) walks its share of the items, the
     // next item's owned and first streamed tiles loading while the compute warps store the current item's dK, dV
     const int n_items = set_items(P, batch_heads, n);
+    P.test_drop_tile = h->test_drop_tile;
     dim3 grid((unsigned)(n_items < h->sm_count ? n_items : h->sm_count));
-    MX_LAUNCH(h, st, MX230_K_BWD_FUSED,
-              (bwd_kernel<2><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0],
-                                                                  m.box128[3], tm_dq, tm_dk, tm_dv, P)));
+    if (pre)
+        MX_LAUNCH(h, st, MX230_K_BWD_FUSED,
+                  (bwd_kernel<2, true><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0], m.box128[3],
+                                                                            tm_dq, tm_dk, tm_dv, P)));
+    else
+        MX_LAUNCH(h, st, MX230_K_BWD_FUSED,
+                  (bwd_kernel<2, false><<<grid, BWD_THREADS, SM_ALLOC, st>>>(m.box128[1], m.box128[2], m.box128[0], m.box128[3],
+                                                                             tm_dq, tm_dk, tm_dv, P)));
     return MX230_OK;
 }
 
@@ -795,7 +827,7 @@ int check_args(const char *who, mx230_handle *h, int batch_heads, int n) {
 // which: bit 0 = dQ pass, bit 1 = dK/dV pass
 int bwd_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb, const void *Vb, const void *dOb,
              const float *L, const float *Delta, float *dQ, float *dK, float *dV, int batch_heads, int n,
-             int causal, int which, const char *who, bool dq_is_zero = false) {
+             int causal, int which, const char *who, bool dq_is_zero = false, bool pre = false) {
     MX_REQUIRE(Qb && Kb && Vb && dOb && L && Delta, MX230_ERR_INVALID_ARG, "%s: null input", who);
     MX_REQUIRE(!(which & 1) || dQ, MX230_ERR_INVALID_ARG, "%s: null dQ", who);
     MX_REQUIRE(!(which & 2) || (dK && dV), MX230_ERR_INVALID_ARG, "%s: null dK/dV", who);
@@ -807,9 +839,9 @@ int bwd_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb, cons
     if ((rc = make_maps(h, m, Qb, Kb, Vb, dOb, batch_heads, n))) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     if (which == 3 && !h->bwd_two_pass)
-        return launch_fused(h, st, m, L, Delta, dQ, dK, dV, batch_heads, n, causal, dq_is_zero);
-    if ((which & 1) && (rc = launch_dq(h, st, m, L, Delta, dQ, batch_heads, n, causal))) return rc;
-    if ((which & 2) && (rc = launch_dkv(h, st, m, L, Delta, dK, dV, batch_heads, n, causal))) return rc;
+        return launch_fused(h, st, m, L, Delta, dQ, dK, dV, batch_heads, n, causal, dq_is_zero, pre);
+    if ((which & 1) && (rc = launch_dq(h, st, m, L, Delta, dQ, batch_heads, n, causal, pre))) return rc;
+    if ((which & 2) && (rc = launch_dkv(h, st, m, L, Delta, dK, dV, batch_heads, n, causal, pre))) return rc;
     return MX230_OK;
 }
 
@@ -824,17 +856,28 @@ int bwd_fp32(mx230_handle *h, void *stream, const float *Q, const float *K, cons
     MX_REQUIRE(h->ws && need <= h->ws_bytes, MX230_ERR_WORKSPACE,
                "%s: workspace %zu B < %zu B needed (call mx230_reserve)", who, h->ws_bytes, need);
     mx230_device_guard guard(h->device);
-    size_t one = need / 4;
-    size_t count = (size_t)batch_heads * n * HD;
+    size_t one = mx230_flash_stage_bytes(batch_heads, n);
     void *dst[4] = {h->ws, (char *)h->ws + one, (char *)h->ws + 2 * one, (char *)h->ws + 3 * one};
     const float *src[4] = {Q, K, V, dO};
     // the fused pass sums into dQ: the staging launch clears it on the way
     const bool fused = which == 3 && !h->bwd_two_pass;
     MX_REQUIRE(!fused || (dQ && ((uintptr_t)dQ & 15) == 0), MX230_ERR_INVALID_ARG, "%s: dQ null or not 16-byte aligned", who);
-    rc = mx230_launch_cast(h, (cudaStream_t)stream, src, dst, 4, count, fused ? dQ : nullptr);
+    // Q is staged as Q * scale * log2(e), bit for bit what the forward staged and took L from: the recomputed
+    // probabilities then sum to one over a row whatever the rounding did to a single score.
+    if (h->bwd_reuse_staged && h->staged.valid && h->staged.q == Q && h->staged.k == K && h->staged.v == V &&
+        h->staged.batch_heads == batch_heads && h->staged.n == n) {
+        // the forward's bf16 copies of these very tensors are still in the workspace: only dO is staged
+        rc = mx230_launch_cast(h, (cudaStream_t)stream, src + 3, dst + 3, 1, batch_heads, (size_t)n * HD,
+                               fused ? dQ : nullptr, 1.0f, nullptr);
+    } else {
+        h->staged.valid = 0;
+        rc = mx230_launch_cast(h, (cudaStream_t)stream, src, dst, 4, batch_heads, (size_t)n * HD, fused ? dQ : nullptr,
+                               MX230_QK_LOG2_SCALE, nullptr);
+        if (!rc) h->staged = {Q, K, V, batch_heads, n, 1};
+    }
     if (rc) return rc;
     return bwd_bf16(h, stream, dst[0], dst[1], dst[2], dst[3], L, Delta, dQ, dK, dV, batch_heads, n, causal,
-                    which, who, fused);
+                    which, who, fused, true);
 }
 
 }  // namespace

@@ -28,6 +28,7 @@
 #include <math_constants.h>
 
 #include <cstring>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -43,7 +44,36 @@ constexpr int FWD_THREADS = 384;        // 3 warpgroups: softmax 0, softmax 1, {
 // setmaxnreg moves registers only inside the CTA's launch-time allocation (168 per thread for 384
 // threads): what the softmax warps gain must have been released by the third warpgroup, or the
 // increase would block for ever.
-static_assert(8 * 216 + 4 * 72 <= 12 * 168, "setmaxnreg budget exceeds the launch-time register allocation");
+#ifndef FWD_REGS_SOFTMAX
+#define FWD_REGS_SOFTMAX 216
+#define FWD_REGS_SERVICE 72
+#endif
+static_assert(8 * FWD_REGS_SOFTMAX + 4 * FWD_REGS_SERVICE <= 12 * 168, "setmaxnreg budget exceeds the launch-time register allocation");
+
+// build-time knobs of the softmax loop
+#ifndef FWD_FAST
+#define FWD_FAST 1        // fixed-reference mode (no row max, no subtraction) while the sums stay in range
+#endif
+#ifndef FWD_POLY
+#define FWD_POLY 2        // of every FWD_POLY_DEN column pairs, how many take 2^x from the FMA-pipe polynomial
+#endif
+#ifndef FWD_POLY_DEN
+#define FWD_POLY_DEN 4
+#endif
+#ifndef FWD_ADD2
+#define FWD_ADD2 1        // row sums with packed f32x2 adds
+#endif
+
+#ifndef FWD_UNIFORM_ISSUE
+#define FWD_UNIFORM_ISSUE 1   // MMA issuer warps run warp-uniform with one elected lane (0: a lone lane in a divergent branch)
+#endif
+#if FWD_UNIFORM_ISSUE
+#define ISSUER_WAIT(w) __all_sync(0xFFFFFFFFu, (w))
+#define ISSUER_LANE mx::elect_one()
+#else
+#define ISSUER_WAIT(w) (w)
+#define ISSUER_LANE true
+#endif
 
 constexpr int Q_BUFS = 2;                // Q of the next item lands while the current one is in use
 constexpr int SMEM_Q = 0;
@@ -90,6 +120,10 @@ struct FwdParams {
     int n_qblocks;        // blocks of QT*BM query rows per head
     int n_items;          // heads * n_qblocks
     int tma_out;          // O leaves through staged TMA stores (strides and base 16-byte aligned) or per-thread stores
+    int prescaled;        // Q was staged multiplied by scale * log2(e): the scores arrive in log2 units
+    const float *q_norm2; // [heads][MX230_NORM_PARTS] largest squared row norm of the unscaled Q per head and part, or null
+    const float *k_norm2; // [heads / kv_group][MX230_NORM_PARTS] the same for K
+    int test_drop_tile;   // test hook: K/V tile (counted over the CTA's items) that CTA 0's producer never requests; -1 = off
     int *status;
 };
 
@@ -97,6 +131,58 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
+}
+
+// Packed pairs of fp32 (one 64-bit register pair per operand): half the instructions of the scalar forms.
+__device__ __forceinline__ uint64_t pk2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float &a, float &b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2_rm(uint64_t a, uint64_t b) {   // round towards minus infinity
+    uint64_t r;
+    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// a += lo(w), b += hi(w) for a packed pair of bf16 (fp32 sums of the ROUNDED probabilities)
+__device__ __forceinline__ void add_bf16x2(uint32_t w, float &a, float &b) {
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\t"
+        "add.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %1, hi, %1;\n\t}"
+        : "+f"(a), "+f"(b)
+        : "r"(w));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// 2^x for two values on the FMA and integer pipes, leaving the exp unit to the other columns: x = n + f
+// with n = floor(x) (the magic-number add, rounded down, leaves n in the low mantissa bits), 2^f by a
+// degree-3 polynomial (relative error 7.9e-5, far below the bf16 rounding of the probabilities), and n
+// added to the exponent field.  Valid for -126 <= x < 128 and nothing else (no clamp): the caller uses it
+// only where the scores are bounded, and never on masked (-inf) entries.
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float &p0, float &p1) {
+    const uint64_t x = pk2(x0, x1);
+    const uint64_t t = add2_rm(x, pk2(12582912.0f, 12582912.0f));          // 1.5 * 2^23 + floor(x)
+    const uint64_t fl = add2(t, pk2(-12582912.0f, -12582912.0f));         // floor(x), exact
+    const uint64_t f = fma2(fl, pk2(-1.0f, -1.0f), x);                    // x - floor(x) in [0, 1)
+    uint64_t p = fma2(pk2(0.07806939631700516f, 0.07806939631700516f), f, pk2(0.22593535482883453f, 0.22593535482883453f));
+    p = fma2(p, f, pk2(0.6959162950515747f, 0.6959162950515747f));
+    p = fma2(p, f, pk2(0.9999210238456726f, 0.9999210238456726f));
+    float a, b, ta, tb;
+    upk2(p, a, b);
+    upk2(t, ta, tb);
+    p0 = __int_as_float(__float_as_int(a) + (__float_as_int(ta) << 23));
+    p1 = __int_as_float(__float_as_int(b) + (__float_as_int(tb) << 23));
 }
 
 // The CTA's `round`-th work item.  Items are listed heaviest first (when causal: the latest query block of
@@ -162,7 +248,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // register budget: the softmax warpgroups hold a 128-value score row per thread, the
     // third warpgroup (TMA, two MMA issuers, one idle warp) needs few
     if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FWD_REGS_SERVICE));
         if (warp == 8) {
         // ------------------------- TMA producer -------------------------
         if (lane == 0) {
@@ -190,6 +276,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     const uint32_t r = g / KV_STAGES;
                     if (r > 0) ok = mx::mbar_wait(bar(BAR_K_EMPTY + s), (r - 1) & 1, abort_flag, P.status);
                     if (!ok) break;
+                    if (P.test_drop_tile == (int)g && blockIdx.x == 0) continue;   // test hook: this tile never arrives
                     mx::mbar_expect_tx(bar(BAR_K_FULL + s), TILE_BYTES);
                     mx::tma_load_3d(smem_base + SMEM_K + s * TILE_BYTES, &tmK, bar(BAR_K_FULL + s), 0,
                                     j * BN, kvh);
@@ -204,9 +291,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __syncwarp();
         } else if (warp == 9) {
         // ------------------------- MMA issuer 1: S_t = Q_t K^T ----------
-        // (issuing one tcgen05.mma costs the issuing thread ~65 cycles whatever its size, more
-        // than a 128x64x16 MMA takes to execute, so the two MMA streams get a thread each)
-        if (lane == 0) {
+        // The whole warp runs the loop and the waits; one elected lane issues.  Control flow and descriptor
+        // arithmetic stay warp-uniform that way (a lone thread inside a divergent branch pays several dependent
+        // instructions per tcgen05.mma to move its operands to the uniform registers the instruction reads).
+        if (FWD_UNIFORM_ISSUE || lane == 0) {
             constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BM, BN, false, false);
             bool ok = true;
             uint32_t g = 0;            // K/V tiles consumed so far, over all items
@@ -218,35 +306,37 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 for (int t = 0; t < QT; ++t) n_it[t] = fwd_tile_iters(P, q0, t);
                 const int n_max = max(n_it[0], n_it[1]);
                 const int qbuf = it & 1;
-                ok = mx::mbar_wait(bar(BAR_Q_FULL + qbuf), (it >> 1) & 1, abort_flag, P.status);
+                ok = ISSUER_WAIT(mx::mbar_wait(bar(BAR_Q_FULL + qbuf), (it >> 1) & 1, abort_flag, P.status));
                 for (int j = 0; j < n_max && ok; ++j, ++g) {
                     const int s = g % KV_STAGES;
-                    ok = mx::mbar_wait(bar(BAR_K_FULL + s), (g / KV_STAGES) & 1, abort_flag, P.status);
+                    ok = ISSUER_WAIT(mx::mbar_wait(bar(BAR_K_FULL + s), (g / KV_STAGES) & 1, abort_flag, P.status));
                     const uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_K + s * TILE_BYTES);
 #pragma unroll
                     for (int t = 0; t < QT; ++t) {
                         if (!ok || j >= n_it[t]) continue;
                         // next scores as soon as the softmax group holds the previous ones in registers (the
                         // previous ones may be the last of the item before: this is where the items overlap)
-                        if (cs[t] > 0) ok = mx::mbar_wait(bar(BAR_S_FREE + t), (cs[t] - 1) & 1, abort_flag, P.status);
+                        if (cs[t] > 0) ok = ISSUER_WAIT(mx::mbar_wait(bar(BAR_S_FREE + t), (cs[t] - 1) & 1, abort_flag, P.status));
                         if (!ok) continue;
                         mx::tc_fence_after();
                         const uint64_t a = mx::smem_desc_sw128(smem_base + SMEM_Q + (qbuf * QT + t) * TILE_BYTES);
+                        if (ISSUER_LANE) {
 #pragma unroll
-                        for (int k = 0; k < HD / 16; ++k)  // 32 bytes per 16-element step inside the swizzle span
-                            mx::mma_ss(tmem + TM_S + t * BN, a + 2 * k, b + 2 * k, IDESC_S, k > 0);
-                        mx::mma_commit(bar(BAR_S_FULL + t));
+                            for (int k = 0; k < HD / 16; ++k)  // 32 bytes per 16-element step inside the swizzle span
+                                mx::mma_ss(tmem + TM_S + t * BN, a + 2 * k, b + 2 * k, IDESC_S, k > 0);
+                            mx::mma_commit(bar(BAR_S_FULL + t));
+                        }
                         ++cs[t];
                     }
                     if (!ok) break;
-                    mx::mma_commit(bar(BAR_K_EMPTY + s));
+                    if (ISSUER_LANE) mx::mma_commit(bar(BAR_K_EMPTY + s));
                 }
             }
         }
         __syncwarp();
         } else if (warp == 10) {
         // ------------------------- MMA issuer 2: O_t += P_t V -----------
-        if (lane == 0) {
+        if (FWD_UNIFORM_ISSUE || lane == 0) {
             constexpr uint32_t IDESC_O = mx::mma_idesc_bf16(BM, HD, false, true);
             bool ok = true;
             uint32_t g = 0;            // K/V tiles consumed so far, over all items
@@ -259,25 +349,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const int n_max = max(n_it[0], n_it[1]);
                 for (int j = 0; j < n_max && ok; ++j, ++g) {
                     const int s = g % KV_STAGES;
-                    ok = mx::mbar_wait(bar(BAR_V_FULL + s), (g / KV_STAGES) & 1, abort_flag, P.status);
+                    ok = ISSUER_WAIT(mx::mbar_wait(bar(BAR_V_FULL + s), (g / KV_STAGES) & 1, abort_flag, P.status));
                     const uint64_t b = mx::smem_desc_sw128(smem_base + SMEM_V + s * TILE_BYTES);
 #pragma unroll
                     for (int t = 0; t < QT; ++t) {
                         if (!ok || j >= n_it[t]) continue;
                         // an item's first P_t is written after the softmax group has taken the previous item's
                         // O_t out of tensor memory, so overwriting O_t (j == 0) needs no barrier of its own
-                        ok = mx::mbar_wait(bar(BAR_P_FULL + t), cp[t] & 1, abort_flag, P.status);
+                        ok = ISSUER_WAIT(mx::mbar_wait(bar(BAR_P_FULL + t), cp[t] & 1, abort_flag, P.status));
                         if (!ok) continue;
                         mx::tc_fence_after();
+                        if (ISSUER_LANE) {
 #pragma unroll
-                        for (int k = 0; k < BN / 16; ++k)  // 16 keys: 8 packed columns of P, 2048 bytes of V
-                            mx::mma_ts(tmem + TM_O + t * HD, tmem + TM_P + t * (BN / 2) + 8 * k, b + 128 * k,
-                                       IDESC_O, (j > 0 || k > 0));
-                        mx::mma_commit(bar(BAR_O_DONE + t));
+                            for (int k = 0; k < BN / 16; ++k)  // 16 keys: 8 packed columns of P, 2048 bytes of V
+                                mx::mma_ts(tmem + TM_O + t * HD, tmem + TM_P + t * (BN / 2) + 8 * k, b + 128 * k,
+                                           IDESC_O, (j > 0 || k > 0));
+                            mx::mma_commit(bar(BAR_O_DONE + t));
+                        }
                         ++cp[t];
                     }
                     if (!ok) break;
-                    mx::mma_commit(bar(BAR_V_EMPTY + s));
+                    if (ISSUER_LANE) mx::mma_commit(bar(BAR_V_EMPTY + s));
                 }
             }
         }
@@ -285,14 +377,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
     } else {
         // ------------------------- softmax groups -----------------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FWD_REGS_SOFTMAX));
         const int t = warp >> 2;             // query tile of this group
         const int row_in_tile = tid & 127;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tm_s = tmem + lane_off + TM_S + t * BN;
         const uint32_t tm_p = tmem + lane_off + TM_P + t * (BN / 2);
         const uint32_t tm_o = tmem + lane_off + TM_O + t * HD;
-        const float c = 0.125f * 1.4426950408889634f;  // scale * log2(e)
+        // Scores arrive in log2 units when Q was staged pre-multiplied by scale * log2(e) (c = 1), else raw (c = scale * log2(e)).
+        const float c = P.prescaled ? 1.0f : 0.125f * 1.4426950408889634f;
+        const float l_scale = P.prescaled ? 0.6931471805599453f : 0.125f;   // running max -> natural-log units
         bool ok = true;
         uint32_t cnt = 0;  // score tiles this group has taken so far, over all items
         int bh, q0;
@@ -300,7 +394,146 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int n_t = fwd_tile_iters(P, q0, t);
         const int row = q0 + t * BM + row_in_tile;
         const int qbuf = it & 1;
-        float m = -CUDART_INF_F, l = 0.0f;
+        const int last = P.causal ? min(N - 1, row + P.q_off) : N - 1;  // last visible key of this row
+        // Fixed-reference mode, chosen per head: when |q . k| * scale * log2(e) <= 80 for every row pair of the head --
+        // by Cauchy-Schwarz from the largest row norms of Q and K that the staging pass left -- the probabilities are
+        // taken as 2^s against the reference 0: no row max, no subtraction, no rescale of O.  bf16 probabilities and
+        // fp32 sums carry the same relative precision at 2^-80 .. 2^80 as around 1, every row sum stays inside
+        // [2^-80, N 2^80], and the result is that of the max-subtracted form.  Heads with larger scores (and calls
+        // without the norms) take the general path: running max, lazy rescale.
+        bool fast = false;
+        if (FWD_FAST && P.q_norm2 != nullptr) {
+            float nq = 0.0f, nk = 0.0f;
+            if (lane < MX230_NORM_PARTS) {
+                nq = P.q_norm2[(size_t)bh * MX230_NORM_PARTS + lane];
+                nk = P.k_norm2[(size_t)(bh / P.kv_group) * MX230_NORM_PARTS + lane];
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                nq = fmaxf(nq, __shfl_xor_sync(0xFFFFFFFFu, nq, o));
+                nk = fmaxf(nk, __shfl_xor_sync(0xFFFFFFFFu, nk, o));
+            }
+            // the norms are those of the fp32 values; rounding to bf16 moves a norm by less than 0.4 %
+            fast = nq * nk * (MX230_QK_LOG2_SCALE * MX230_QK_LOG2_SCALE) <= 80.0f * 80.0f;
+        }
+        float m = fast ? 0.0f : -CUDART_INF_F, l = 0.0f;
+        float l_norm = 0.0f;   // what O is divided by (fast mode: see below; general mode: l)
+        if (fast) {
+        // ---- max-free loop, software-pipelined over the row halves: the second half of a score row lands under the
+        // first half's exponentials, and the first half of the NEXT row is requested (once its barrier is seen
+        // complete, without waiting) before the last quarter of this one is exponentiated
+        uint32_t va[BN / 2], vb[BN / 2];
+        uint64_t rs2[2] = {0ull, 0ull};
+        float rs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        auto exp32 = [&](const uint32_t *src, uint32_t *pk, int key_base, bool need_mask) {
+            uint32_t x[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = src[i];
+            if (need_mask) {   // diagonal and ragged tiles only (a warp-uniform branch: full tiles pay nothing)
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (key_base + i > last) x[i] = (FWD_POLY > 0) ? 0xC2FC0000u : 0xFF800000u;  // -126 (2^-126 against sums >= 2^-80) | -inf
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float p0, p1;
+                if (((i >> 1) % FWD_POLY_DEN) < FWD_POLY) {
+                    ex2_poly2(__uint_as_float(x[i]), __uint_as_float(x[i + 1]), p0, p1);
+                } else {
+                    p0 = mx::ex2(__uint_as_float(x[i]));
+                    p1 = mx::ex2(__uint_as_float(x[i + 1]));
+                }
+                pk[i >> 1] = mx::pack_bf16(p0, p1);
+                if (FWD_ADD2) {
+                    rs2[(i >> 1) & 1] = add2(rs2[(i >> 1) & 1], pk2(p0, p1));
+                } else {
+                    rs[i & 2] += p0;
+                    rs[(i & 2) + 1] += p1;
+                }
+            }
+        };
+        // First key tile only: the sum of the ROUNDED probabilities as well.  Rows that see a handful of keys live
+        // there (the first rows of a causal head), and for them the output has to be normalised by what the tensor
+        // core actually multiplies with V -- a row with one visible key must return that row of V, not V times
+        // bf16(p) / p, or dO . O stops cancelling against dP in the backward.  Everywhere else a row sums so many
+        // terms that the two sums differ far below the rounding of V itself, and the fp32 sum serves both uses.
+        float rb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float l_first = 0.0f;   // fp32 sum of the first tile
+        auto sum_rounded16 = [&](const uint32_t *pk) {
+#pragma unroll
+            for (int w = 0; w < 16; ++w) add_bf16x2(pk[w], rb[(w & 1) * 2], rb[(w & 1) * 2 + 1]);
+        };
+        auto sum_now = [&]() {
+            if (FWD_ADD2) {
+                float a0, a1, a2, a3;
+                upk2(rs2[0], a0, a1);
+                upk2(rs2[1], a2, a3);
+                return (a0 + a1) + (a2 + a3);
+            }
+            return (rs[0] + rs[1]) + (rs[2] + rs[3]);
+        };
+        // one score tile; FIRST (a compile-time flag: the loop below stays free of the first tile's extra work) also
+        // takes the sums of the rounded probabilities
+        auto tile = [&](auto first_c, int j) -> bool {
+            constexpr bool FIRST = decltype(first_c)::value;
+            bool good = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), cnt & 1, abort_flag, P.status));
+            if (!good) return false;
+            mx::tc_fence_after();
+            mx::tmem_ld32(tm_s, *(uint32_t(*)[32])(va));
+            mx::tmem_ld32(tm_s + 32, *(uint32_t(*)[32])(va + 32));
+            mx::tmem_wait_ld();                                       // va is in registers
+            mx::tmem_ld32(tm_s + 64, *(uint32_t(*)[32])(vb));        // lands under the first exponentials
+            mx::tmem_ld32(tm_s + 96, *(uint32_t(*)[32])(vb + 32));
+            const int key0 = j * BN;
+            const bool need_mask = (key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM + P.q_off);
+            uint32_t pk01[32], pk23[16];
+            exp32(va, pk01, key0, need_mask);
+            mx::tmem_wait_ld();                                       // the whole row has left S_t
+            mx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mx::mbar_arrive(bar(BAR_S_FREE + t));
+            exp32(va + 32, pk01 + 16, key0 + 32, need_mask);
+            if (!FIRST) {
+                // P_t is free once the previous P V has completed: that takes several hundred cycles from the end of the
+                // previous softmax, which is why half a row is exponentiated before the first store
+                good = __all_sync(0xFFFFFFFFu,
+                                  mx::mbar_wait_fast(bar(BAR_O_DONE + t), (cnt - 1) & 1, abort_flag, P.status));
+                if (!good) return false;
+                mx::tc_fence_after();
+            }
+            mx::tmem_st16(tm_p, *(uint32_t(*)[16])(pk01));
+            mx::tmem_st16(tm_p + 16, *(uint32_t(*)[16])(pk01 + 16));
+            if (FIRST) {
+                sum_rounded16(pk01);
+                sum_rounded16(pk01 + 16);
+            }
+            exp32(vb, pk23, key0 + 64, need_mask);
+            mx::tmem_st16(tm_p + 32, pk23);
+            if (FIRST) sum_rounded16(pk23);
+            exp32(vb + 32, pk23, key0 + 96, need_mask);
+            mx::tmem_st16(tm_p + 48, pk23);
+            if (FIRST) {
+                sum_rounded16(pk23);
+                l_first = sum_now();
+            }
+            mx::tmem_wait_st();
+            mx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mx::mbar_arrive(bar(BAR_P_FULL + t));
+            return true;
+        };
+        if (n_t > 0) {
+            ok = tile(std::true_type{}, 0);
+            ++cnt;
+            for (int j = 1; ok && j < n_t; ++j) {
+                ok = tile(std::false_type{}, j);
+                ++cnt;
+            }
+        }
+        l = sum_now();
+        l_norm = l - l_first + ((rb[0] + rb[1]) + (rb[2] + rb[3]));
+        } else {
+        // ---- general loop: running row max, raised lazily
         for (int j = 0; j < n_t; ++j, ++cnt) {
             ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), cnt & 1, abort_flag, P.status));
             if (!ok) break;
@@ -316,7 +549,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
             const int key0 = j * BN;
             if ((key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM + P.q_off)) {
-                const int last = P.causal ? min(N - 1, row + P.q_off) : N - 1;  // last visible key
 #pragma unroll
                 for (int i = 0; i < BN; ++i)
                     if (key0 + i > last) v[i] = 0xFF800000u;  // -inf
@@ -340,8 +572,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float alpha = (raise && j > 0) ? mx::ex2((m - m_new) * c) : 1.0f;
             const float nmc = -m_new * c;
             if (j > 0) {
-                // P_t and O_t are stable once the previous P V has completed (issued a whole
-                // softmax ago, so this wait is normally already satisfied)
+                // P_t and O_t are stable once the previous P V has completed
                 ok = __all_sync(0xFFFFFFFFu,
                                 mx::mbar_wait(bar(BAR_O_DONE + t), (cnt - 1) & 1, abort_flag, P.status));
                 if (!ok) break;
@@ -358,8 +589,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     }
                 }
             }
-            // scalar fma / ex2 / add: measured on B200, the packed f32x2 forms issue slower than
-            // two scalar instructions, and cvt.rn.bf16x2 costs no more than an integer-pipe pack
             float rs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int cc = 0; cc < BN / 32; ++cc) {
@@ -381,13 +610,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             __syncwarp();
             if (lane == 0) mx::mbar_arrive(bar(BAR_P_FULL + t));
         }
+        }
         // epilogue: O / l and the log-sum-exp
         if (ok && n_t > 0) {
             ok = __all_sync(0xFFFFFFFFu,
                             mx::mbar_wait(bar(BAR_O_DONE + t), (cnt - 1) & 1, abort_flag, P.status));
             if (ok) {
                 mx::tc_fence_after();
-                const float inv = 1.0f / l;
+                const float inv = 1.0f / (fast ? l_norm : l);
                 float *orow = P.O + (size_t)bh * P.o_head_stride + (size_t)row * P.o_row_stride;
                 if (P.tma_out) {
                     // each warp stages its 32 rows, 32 columns at a time, in a swizzled 4 KB piece of this tile's Q
@@ -430,7 +660,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         }
                     }
                 }
-                if (P.L != nullptr && row < NQ) P.L[(size_t)bh * NQ + row] = m * 0.125f + __logf(l);
+                if (P.L != nullptr && row < NQ) P.L[(size_t)bh * NQ + row] = m * l_scale + __logf(l);
             }
         }
         // this warp no longer touches the item's Q buffer (operand of its tile's Q K^T, then staging space)
@@ -446,49 +676,83 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (warp == 9) mx::tmem_dealloc(tmem, TM_COLS);
 }
 
-// fp32 -> bf16 (round to nearest even) for up to four equally sized tensors.
+// fp32 -> bf16 (round to nearest even) for up to four equally sized tensors of `heads` x `per_head4` float4s.
 struct CastParams {
     const float *src[4];
     __nv_bfloat16 *dst[4];
-    size_t count;  // elements per tensor, multiple of 8
-    float4 *zero;  // optional: `count` floats set to zero by one more slice of the grid (blockIdx.y = n_tensors)
+    size_t per_head4;   // float4s per head (the whole tensor when heads == 1)
+    float4 *zero;       // optional: a buffer of the tensors' size set to zero by one more slice of the grid (blockIdx.y = n_tensors)
+    float *norm2[2];    // optional, tensors 0 and 1: [heads][MX230_NORM_PARTS] largest squared row norm seen by each grid part
     int n_tensors;
+    float scale0;       // tensor 0 is multiplied by this before rounding (1 = plain cast)
 };
 
-// Four coalesced 16-byte loads in flight per thread (streaming: the fp32 operands are not needed again and
-// should not push the bf16 copies, which the attention kernels read next, out of L2), 8-byte stores.
+// Grid (parts, tensors [+ 1], heads): a block converts every gridDim.x-th group of 256 float4s of its head.  Four
+// coalesced 16-byte loads in flight per thread (streaming: the fp32 operands are not needed again and should not push
+// the bf16 copies, which the attention kernels read next, out of L2), 8-byte stores.  A row of 64 values is 16
+// neighbouring lanes, so its squared norm costs four shuffles on a kernel that waits for memory anyway.
 __global__ void __launch_bounds__(256) cast_bf16_kernel(const CastParams P) {
-    if ((int)blockIdx.y == P.n_tensors) {
-        const size_t n4 = P.count / 4;
-        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x)
-            P.zero[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        return;
-    }
-    const float4 *src = (const float4 *)P.src[blockIdx.y];
-    uint2 *dst = (uint2 *)P.dst[blockIdx.y];
-    const size_t n4 = P.count / 4;
+    const size_t n4 = P.per_head4;
+    const size_t base = (size_t)blockIdx.z * n4;
     const size_t step = (size_t)gridDim.x * blockDim.x;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if ((int)blockIdx.y == P.n_tensors) {
+        for (; i < n4; i += step) P.zero[base + i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
+    }
+    const float4 *src = (const float4 *)P.src[blockIdx.y] + base;
+    uint2 *dst = (uint2 *)P.dst[blockIdx.y] + base;
+    const float sc = blockIdx.y == 0 ? P.scale0 : 1.0f;   // one rounding either way: fp32 product -> bf16
+    float *norm_out = blockIdx.y < 2 ? P.norm2[blockIdx.y] : nullptr;
+    const unsigned half_mask = 0xFFFFu << (threadIdx.x & 16);   // the 16 lanes that hold one row
+    float mx = 0.0f;
+    auto row_norm = [&](const float4 &a) {
+        float q = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) q += __shfl_xor_sync(half_mask, q, o);
+        mx = fmaxf(mx, q);
+    };
     for (; i + 3 * step < n4; i += 4 * step) {
         float4 a[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) a[u] = __ldcs(src + i + u * step);
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-            dst[i + u * step] = make_uint2(mx::pack_bf16(a[u].x, a[u].y), mx::pack_bf16(a[u].z, a[u].w));
+            dst[i + u * step] = make_uint2(mx::pack_bf16(a[u].x * sc, a[u].y * sc), mx::pack_bf16(a[u].z * sc, a[u].w * sc));
+        if (norm_out != nullptr) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) row_norm(a[u]);
+        }
     }
     for (; i < n4; i += step) {
         const float4 a = __ldcs(src + i);
-        dst[i] = make_uint2(mx::pack_bf16(a.x, a.y), mx::pack_bf16(a.z, a.w));
+        dst[i] = make_uint2(mx::pack_bf16(a.x * sc, a.y * sc), mx::pack_bf16(a.z * sc, a.w * sc));
+        if (norm_out != nullptr) row_norm(a);
+    }
+    if (norm_out != nullptr) {   // block maximum -> this part's slot (parts the grid does not have are set to 0)
+        __shared__ float red[8];
+        __syncwarp();
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
+            norm_out[(size_t)blockIdx.z * MX230_NORM_PARTS + blockIdx.x] = mx;
+            if (blockIdx.x == 0)
+                for (int q = (int)gridDim.x; q < MX230_NORM_PARTS; ++q) norm_out[(size_t)blockIdx.z * MX230_NORM_PARTS + q] = 0.0f;
+        }
     }
 }
 
 }  // namespace
 
 int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src, void *const *dst,
-                      int n_tensors, size_t count, float *zero) {
-    MX_REQUIRE(count % 8 == 0, MX230_ERR_INVALID_ARG, "cast: element count must be a multiple of 8");
-    if (count == 0 || n_tensors == 0) return MX230_OK;
+                      int n_tensors, int heads, size_t per_head, float *zero, float scale0, float *const *norm2) {
+    MX_REQUIRE(per_head % 8 == 0, MX230_ERR_INVALID_ARG, "cast: element count must be a multiple of 8");
+    MX_REQUIRE(norm2 == nullptr || per_head % 64 == 0, MX230_ERR_INVALID_ARG, "cast: row norms need rows of 64 values");
+    if (per_head == 0 || n_tensors == 0 || heads == 0) return MX230_OK;
+    MX_REQUIRE(heads > 0 && heads <= 65535, MX230_ERR_UNSUPPORTED, "cast: %d heads", heads);
     CastParams P;
     for (int i = 0; i < 4; ++i) {
         P.src[i] = src[i < n_tensors ? i : 0];
@@ -496,22 +760,30 @@ int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src,
         MX_REQUIRE((((uintptr_t)P.src[i] | (uintptr_t)P.dst[i]) & 15) == 0, MX230_ERR_INVALID_ARG,
                    "cast: buffers must be 16-byte aligned");
     }
-    P.count = count;
+    P.per_head4 = per_head / 4;
     P.zero = (float4 *)zero;
     P.n_tensors = n_tensors;
+    P.scale0 = scale0;
+    P.norm2[0] = norm2 ? norm2[0] : nullptr;
+    P.norm2[1] = norm2 && n_tensors > 1 ? norm2[1] : nullptr;
     MX_REQUIRE(((uintptr_t)zero & 15) == 0, MX230_ERR_INVALID_ARG, "cast: buffers must be 16-byte aligned");
-    size_t n16 = (count / 4 + 3) / 4;   // threads, at four 16-byte loads each
-    unsigned bx = (unsigned)((n16 + 255) / 256);
-    unsigned cap = (unsigned)h->sm_count * 8;
-    if (bx > cap) bx = cap;
-    MX_LAUNCH(h, st, MX230_K_CAST, (cast_bf16_kernel<<<dim3(bx, n_tensors + (zero ? 1 : 0)), 256, 0, st>>>(P)));
+    // parts per head: every thread gets at least one round of four loads, the whole grid about eight blocks per SM
+    const int slices = n_tensors + (zero ? 1 : 0);
+    size_t want = (P.per_head4 + 1023) / 1024;
+    size_t cap = ((size_t)h->sm_count * 8 + (size_t)slices * heads - 1) / ((size_t)slices * heads);
+    size_t parts = want < cap ? want : cap;
+    if (parts < 1) parts = 1;
+    if (norm2 != nullptr && parts > MX230_NORM_PARTS) parts = MX230_NORM_PARTS;
+    if (parts > 65535) parts = 65535;
+    MX_LAUNCH(h, st, MX230_K_CAST, (cast_bf16_kernel<<<dim3((unsigned)parts, slices, heads), 256, 0, st>>>(P)));
     return MX230_OK;
 }
 
 // General launcher.  Q: bf16 [heads][n_q][64]; K, V: bf16 [heads / kv_group][n_k][64].
 int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
                               const void *Vb, float *O, float *L, int heads, int n_q, int n_k, int q_off,
-                              int kv_group, long long o_head_stride, long long o_row_stride, int causal) {
+                              int kv_group, long long o_head_stride, long long o_row_stride, int causal,
+                              int q_prescaled, const float *q_norm2, const float *k_norm2) {
     CUtensorMap tq, tk, tv, to;
     uint64_t rs = HD * 2;
     int rc;
@@ -550,6 +822,10 @@ int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, 
     MX_REQUIRE((long long)heads * P.n_qblocks <= 0x7FFFFFFF, MX230_ERR_UNSUPPORTED, "flash forward: too many query blocks");
     P.n_items = heads * P.n_qblocks;
     P.tma_out = tma_out ? 1 : 0;
+    P.prescaled = q_prescaled ? 1 : 0;
+    P.q_norm2 = (q_prescaled && q_norm2 && k_norm2) ? q_norm2 : nullptr;
+    P.k_norm2 = P.q_norm2 ? k_norm2 : nullptr;
+    P.test_drop_tile = h->test_drop_tile;
     P.status = h->status_dev;
     // persistent: one CTA per SM (the kernel holds all of an SM's tensor memory), each walking its share of the items
     dim3 grid((unsigned)(P.n_items < h->sm_count ? P.n_items : h->sm_count));
@@ -559,9 +835,10 @@ int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, 
 }
 
 int mx230_launch_flash_fwd(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
-                           const void *Vb, float *O, float *L, int batch_heads, int n, int causal) {
+                           const void *Vb, float *O, float *L, int batch_heads, int n, int causal,
+                           int q_prescaled, const float *q_norm2, const float *k_norm2) {
     return mx230_launch_flash_fwd_ex(h, st, Qb, Kb, Vb, O, L, batch_heads, n, n, 0, 1, (long long)n * HD, HD,
-                                     causal);
+                                     causal, q_prescaled, q_norm2, k_norm2);
 }
 
 static int check_flash_args(const char *who, mx230_handle *h, int batch_heads, int n) {
@@ -578,7 +855,7 @@ extern "C" int mx230_cast_bf16(mx230_handle *h, void *stream, const float *src, 
     mx230_device_guard guard(h->device);
     const float *s[1] = {src};
     void *d[1] = {dst_bf16};
-    return mx230_launch_cast(h, (cudaStream_t)stream, s, d, 1, count, nullptr);
+    return mx230_launch_cast(h, (cudaStream_t)stream, s, d, 1, 1, count, nullptr, 1.0f, nullptr);
 }
 
 extern "C" int mx230_attn_flash_bf16(mx230_handle *h, void *stream, const void *Qb, const void *Kb,
@@ -591,7 +868,7 @@ extern "C" int mx230_attn_flash_bf16(mx230_handle *h, void *stream, const void *
     MX_REQUIRE((((uintptr_t)O) & 15) == 0, MX230_ERR_INVALID_ARG, "attn_flash_bf16: O must be 16-byte aligned");
     mx230_device_guard guard(h->device);
     return mx230_launch_flash_fwd(h, (cudaStream_t)stream, Qb, Kb, Vb, O, L_or_null, batch_heads, n,
-                                  causal);
+                                  causal, 0, nullptr, nullptr);
 }
 
 static int flash_fp32(mx230_handle *h, void *stream, const float *Q, const float *K, const float *V,
@@ -604,14 +881,21 @@ static int flash_fp32(mx230_handle *h, void *stream, const float *Q, const float
     MX_REQUIRE(h->ws && need <= h->ws_bytes, MX230_ERR_WORKSPACE,
                "%s: workspace %zu B < %zu B needed (call mx230_reserve)", who, h->ws_bytes, need);
     mx230_device_guard guard(h->device);
-    size_t one = need / 3;
-    size_t count = (size_t)batch_heads * n * HD;
+    const size_t one = mx230_flash_stage_bytes(batch_heads, n);
     void *qb = h->ws, *kb = (char *)h->ws + one, *vb = (char *)h->ws + 2 * one;
+    float *qn = (float *)((char *)h->ws + 3 * one), *kn = qn + (size_t)batch_heads * MX230_NORM_PARTS;
     const float *src[3] = {Q, K, V};
     void *dst[3] = {qb, kb, vb};
-    rc = mx230_launch_cast(h, (cudaStream_t)stream, src, dst, 3, count, nullptr);
+    float *norms[2] = {qn, kn};
+    // Q is staged as Q * (scale * log2 e), rounded once from the fp32 product: the kernel's scores are then
+    // already in log2 units.  The same launch leaves the largest row norms of Q and K per head, from which the
+    // kernel bounds |q . k| and, where the bound allows, runs its softmax loop without a row max.
+    h->staged.valid = 0;
+    rc = mx230_launch_cast(h, (cudaStream_t)stream, src, dst, 3, batch_heads, (size_t)n * HD, nullptr,
+                           MX230_QK_LOG2_SCALE, norms);
     if (rc) return rc;
-    return mx230_launch_flash_fwd(h, (cudaStream_t)stream, qb, kb, vb, O, L, batch_heads, n, causal);
+    h->staged = {Q, K, V, batch_heads, n, 1};
+    return mx230_launch_flash_fwd(h, (cudaStream_t)stream, qb, kb, vb, O, L, batch_heads, n, causal, 1, qn, kn);
 }
 
 extern "C" int mx230_attn_flash(mx230_handle *h, void *stream, const float *Q, const float *K,

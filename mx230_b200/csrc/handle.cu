@@ -79,12 +79,17 @@ extern "C" int mx230_create(mx230_handle **out, int device, size_t workspace_byt
     }
     h->encode_tiled = (mx230_encode_tiled_fn)fn;
 
-    if (cudaMalloc(&h->status_dev, 4 * sizeof(int)) != cudaSuccess ||
+    if (cudaMalloc(&h->status_dev, 8 * sizeof(int)) != cudaSuccess ||
         cudaMalloc(&h->counters, N_COUNTERS * sizeof(unsigned)) != cudaSuccess) {
         delete h;
         return mx230_fail(MX230_ERR_CUDA, "mx230_create: cudaMalloc of status words failed");
     }
-    cudaMemset(h->status_dev, 0, 4 * sizeof(int));
+    cudaMemset(h->status_dev, 0, 8 * sizeof(int));
+    {
+        const long long limit = 4000000000ll;   // bound of a device-side wait in SM cycles (mx::WAIT_LIMIT_CYCLES)
+        cudaMemcpy(h->status_dev + 4, &limit, sizeof(limit), cudaMemcpyHostToDevice);
+    }
+    h->test_drop_tile = -1;
     cudaMemset(h->counters, 0, N_COUNTERS * sizeof(unsigned));
     if (workspace_bytes > 0) {
         if (cudaMalloc(&h->ws, workspace_bytes) != cudaSuccess) {
@@ -155,6 +160,23 @@ extern "C" int mx230_set_option(mx230_handle *h, int option, int value) {
                        "mx230_set_option: backward two-pass switch must be 0 or 1");
             h->bwd_two_pass = value;
             return MX230_OK;
+        case MX230_OPT_BWD_REUSE_STAGED:
+            MX_REQUIRE(value == 0 || value == 1, MX230_ERR_INVALID_ARG,
+                       "mx230_set_option: backward staging-reuse switch must be 0 or 1");
+            h->bwd_reuse_staged = value;
+            return MX230_OK;
+        case MX230_OPT_WAIT_LIMIT: {
+            MX_REQUIRE(value >= 1, MX230_ERR_INVALID_ARG, "mx230_set_option: wait limit must be at least 1 (thousand cycles)");
+            mx230_device_guard guard(h->device);
+            MX_CHECK_CUDA(cudaDeviceSynchronize());
+            const long long limit = 1000ll * value;
+            MX_CHECK_CUDA(cudaMemcpy(h->status_dev + 4, &limit, sizeof(limit), cudaMemcpyHostToDevice));
+            return MX230_OK;
+        }
+        case MX230_OPT_TEST_DROP_TILE:
+            MX_REQUIRE(value >= -1, MX230_ERR_INVALID_ARG, "mx230_set_option: tile index %d", value);
+            h->test_drop_tile = value;
+            return MX230_OK;
         default:
             return mx230_fail(MX230_ERR_INVALID_ARG, "mx230_set_option: unknown option %d", option);
     }
@@ -162,9 +184,7 @@ extern "C" int mx230_set_option(mx230_handle *h, int option, int value) {
 
 extern "C" size_t mx230_flash_workspace_bytes(int batch_heads, int n, int with_backward) {
     if (batch_heads <= 0 || n <= 0) return 0;
-    size_t one = (size_t)batch_heads * (size_t)n * 64 * sizeof(__nv_bfloat16);
-    one = (one + 1023) & ~(size_t)1023;
-    return one * (with_backward ? 4 : 3);
+    return mx230_flash_stage_bytes(batch_heads, n) * (with_backward ? 4 : 3) + mx230_flash_norm_bytes(batch_heads);
 }
 
 extern "C" size_t mx230_decode_workspace_bytes(int n_seq, int n_head, int max_splits) {

@@ -311,6 +311,21 @@ extern "C" int mx230_kv_pool_end_request(mx230_kv_pool *p, const uint32_t *token
     return MX230_OK;
 }
 
+// The open request is given up (its attention step could not be enqueued): every table block loses the
+// request's reference and NOTHING is handed to the tree -- the fresh blocks were never written, and a later
+// request with the same prefix must not find them.  The reference has no such path: it panics
+// (03-llm-engine/src/gpu.rs:2273-2345).
+extern "C" int mx230_kv_pool_abort_request(mx230_kv_pool *p) {
+    MX_REQUIRE(p && p->prefix_cache, MX230_ERR_INVALID_ARG, "kv_pool_abort_request: bad argument or pool without a prefix tree");
+    MX_REQUIRE(p->req_log_blocks > 0, MX230_ERR_INVALID_ARG, "kv_pool_abort_request: no open request");
+    for (int j = 0; j < p->req_log_blocks; ++j) {
+        decref(p, p->table[j]);
+        p->table[j] = -1;
+    }
+    p->req_log_blocks = 0;
+    return MX230_OK;
+}
+
 // No block owned by two tree nodes, every tree block referenced, the free list a duplicate-free
 // set of unreferenced blocks disjoint from the tree.
 extern "C" int mx230_kv_pool_audit(const mx230_kv_pool *p) {

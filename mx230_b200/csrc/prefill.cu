@@ -20,7 +20,8 @@ namespace {
 
 constexpr int HD = 64;
 
-// out[h][r][0..63] (bf16) <- qkv[r*stride + h*64 + 0..63]; 8 elements per thread
+// out[h][r][0..63] (bf16) <- qkv[r*stride + h*64 + 0..63] * 1/sqrt(64) * log2(e), so that the attention
+// kernel's scores arrive in log2 units (one rounding, from the fp32 product); 8 elements per thread
 __global__ void stage_q_kernel(__nv_bfloat16 *out, const float *qkv, int n_tok, int n_head, int stride) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // over n_head*n_tok*8
     size_t total = (size_t)n_head * n_tok * 8;
@@ -31,11 +32,12 @@ __global__ void stage_q_kernel(__nv_bfloat16 *out, const float *qkv, int n_tok, 
     int h = (int)(hr / n_tok);
     const float4 *src = (const float4 *)(qkv + (size_t)r * stride + h * HD + c * 8);
     float4 a = src[0], b = src[1];
+    const float sc = MX230_QK_LOG2_SCALE;
     uint4 o;
-    o.x = mx::pack_bf16(a.x, a.y);
-    o.y = mx::pack_bf16(a.z, a.w);
-    o.z = mx::pack_bf16(b.x, b.y);
-    o.w = mx::pack_bf16(b.z, b.w);
+    o.x = mx::pack_bf16(a.x * sc, a.y * sc);
+    o.y = mx::pack_bf16(a.z * sc, a.w * sc);
+    o.z = mx::pack_bf16(b.x * sc, b.y * sc);
+    o.w = mx::pack_bf16(b.z * sc, b.w * sc);
     *(uint4 *)(out + ((size_t)h * n_tok + r) * HD + c * 8) = o;
 }
 
@@ -120,6 +122,7 @@ int prefill(mx230_handle *h, void *stream, float *out, const float *qkv, const f
                "%s: workspace %zu B < %zu B needed (call mx230_reserve)", who, h->ws_bytes, need);
     mx230_device_guard guard(h->device);
     cudaStream_t st = (cudaStream_t)stream;
+    h->staged.valid = 0;   // the workspace is about to hold something else
     __nv_bfloat16 *qb = (__nv_bfloat16 *)h->ws;
     __nv_bfloat16 *kbuf = (__nv_bfloat16 *)((char *)h->ws + qbytes);
     __nv_bfloat16 *vbuf = (__nv_bfloat16 *)((char *)h->ws + qbytes + kbytes);
@@ -130,7 +133,7 @@ int prefill(mx230_handle *h, void *stream, float *out, const float *qkv, const f
     size_t tk = (size_t)n_keys * n_kv_head * 8;
     MX_LAUNCH(h, st, MX230_K_PREFILL, (stage_kv_kernel<<<(unsigned)((tk + 255) / 256), 256, 0, st>>>(S)));
     return mx230_launch_flash_fwd_ex(h, st, qb, kbuf, vbuf, out, nullptr, n_head, n_tok, n_keys, pos0,
-                                     n_head / n_kv_head, HD, out_stride, 1);
+                                     n_head / n_kv_head, HD, out_stride, 1, 1, nullptr, nullptr);
 }
 
 }  // namespace

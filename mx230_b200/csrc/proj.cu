@@ -254,6 +254,7 @@ int launch_gemv(mx230_handle *h, void *stream, GemvParams P, int w_kind, const c
                    h->ws_bytes, need);
         MX_REQUIRE((size_t)n_blocks <= h->n_counters, MX230_ERR_UNSUPPORTED, "%s: %d column blocks exceed %zu counters",
                    who, n_blocks, h->n_counters);
+        h->staged.valid = 0;   // the workspace is about to hold something else
         P.partials = (float *)h->ws;
         P.counters = h->counters;
     }

@@ -125,6 +125,10 @@ class KvPool:
         a, pa = _tok(tokens)
         check(lib().mx230_kv_pool_end_request(self._p, pa, a.size))
 
+    def abort_request(self) -> None:
+        """Drops the open request without letting the tree adopt its (unwritten) blocks."""
+        check(lib().mx230_kv_pool_abort_request(self._p))
+
 
 def prefill_cached(h, pool: KvPool, cache, tokens, qkv_rows, out, n_head, n_kv_head, theta,
                    table_dev, use_rope=True, stream=None) -> PrefixStats:
@@ -145,6 +149,10 @@ def prefill_cached(h, pool: KvPool, cache, tokens, qkv_rows, out, n_head, n_kv_h
         stride = rows.shape[-1]
         la.prefill_step(h, out, rows, cache, k, n - k, n_head, n_kv_head, 64, theta, stride, out.shape[-1],
                         pg, use_rope, stream)
-    finally:
-        pool.end_request(tokens)
+    except BaseException:
+        # the KV rows of the fresh blocks were not (all) enqueued: the tree must not adopt them
+        pool.abort_request()
+        raise
+    # only now, with RoPE -> KV write -> attention enqueued, may the tree take over the new full chunks
+    pool.end_request(tokens)
     return PrefixStats(n, k, k // pool.block_size)

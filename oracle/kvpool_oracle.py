@@ -149,6 +149,13 @@ class PoolOracle:
         for j in range(n_log):
             self.decref(self.table[j])
 
+    def abort_request(self, tokens):
+        """A request that failed after begin_request: its borrow is released, the tree adopts nothing."""
+        n_log = -(-len(tokens) // self.bs)
+        for j in range(n_log):
+            self.decref(self.table[j])
+            self.table[j] = -1
+
     def audit(self):
         owner = {}
         for i, nd in enumerate(self.nodes):

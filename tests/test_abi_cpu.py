@@ -36,7 +36,8 @@ def test_status_strings_and_errors(lib_built):
     # null out-pointer is rejected before any CUDA call
     assert L.mx230_create(None, 0, 0) == _lib.ERR_INVALID_ARG
     assert b"null" in L.mx230_last_error()
-    assert L.mx230_flash_workspace_bytes(48, 4096, 1) == 4 * 48 * 4096 * 64 * 2
+    # four staged bf16 tensors plus the row-norm partials of Q and K (2 x 48 heads x 32 parts floats)
+    assert L.mx230_flash_workspace_bytes(48, 4096, 1) == 4 * 48 * 4096 * 64 * 2 + 2 * 48 * 32 * 4
     assert L.mx230_flash_workspace_bytes(0, 4096, 1) == 0
 
 

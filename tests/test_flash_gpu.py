@@ -87,7 +87,41 @@ def test_forward_is_deterministic_and_bf16_entry_agrees(handle):
     l = nan_like((4, n))
     fa.run_flash_bf16(handle, qb, kb, vb, o, l, n, True)
     handle.check_status()
-    assert np.array_equal(o.cpu().numpy(), a) and np.array_equal(l.cpu().numpy(), la_)
+    o2 = nan_like((4, n, 64))
+    l2 = nan_like((4, n))
+    fa.run_flash_bf16(handle, qb, kb, vb, o2, l2, n, True)
+    assert torch.equal(o, o2) and torch.equal(l, l2)
+    # The fp32 entry stages Q pre-multiplied by scale * log2(e) (one rounding of the product) and may take the
+    # max-free softmax loop; the bf16 entry gets the caller's unscaled bf16 Q and takes the running-max loop: the
+    # same attention from two roundings of Q, each inside the parity bar against the oracle and close to each other.
+    wo, wl = oracle.attn_fwd(q, k, v, True)
+    assert_close(o.cpu().numpy(), wo, "O, bf16 entry")
+    assert_close(l.cpu().numpy(), wl, "L, bf16 entry")
+    assert_close(o.cpu().numpy(), a, "O, bf16 entry vs fp32 entry", max_abs=2e-2, mean_rel=5e-3)
+
+
+def test_forward_large_scores_take_the_running_max_path(handle):
+    """Scores far outside the window of the max-free loop (|q . k| / 8 * log2 e > 80 for some pair, here several hundred):
+    the staging pass's row norms send the head down the running-max path, and heads with small scores in the same
+    call keep the max-free one.  K and V are bf16-representable and q is chosen so that q * scale * log2(e), the
+    product the staging pass rounds, is too: the device and the oracle then see the same numbers and only the softmax
+    arithmetic is compared (at such scores one rounding of q would move single probabilities by percents)."""
+    n = 700
+    bf = lambda x: torch.from_numpy(np.ascontiguousarray(x, np.float32)).to(torch.bfloat16).float().numpy()
+    c = np.float32(0.125 * 1.4426950408889634)
+    q, k, v = (oracle.normal((3, n, 64), 81, i) for i in range(3))
+    q[1] *= 8.0
+    k[1] *= 8.0          # head 1: scores up to several hundred; heads 0 and 2: ordinary
+    q = (bf(q * c) / c).astype(np.float32)
+    assert np.array_equal(bf(q * c), (q * c).astype(np.float32)) or np.abs(bf(q * c) - q * c).max() < 1e-6
+    k, v = bf(k), bf(v)
+    for causal in (True, False):
+        o, l = run_fwd(handle, q, k, v, causal)
+        wo, wl = oracle.attn_fwd(q, k, v, causal)
+        assert np.isfinite(o).all() and np.isfinite(l).all()
+        for h_ in range(3):
+            assert_close(o[h_], wo[h_], f"O head {h_}")
+            assert_close(l[h_], wl[h_], f"L head {h_}", max_abs=2e-2 if h_ != 1 else 5e-2)
 
 
 def run_bwd(handle, q, k, v, do, causal, two_pass=0):
@@ -146,12 +180,14 @@ def test_backward_large_logits_and_large_delta(handle):
     """Sharply peaked softmax (scores of a few hundred, so |L| is large) and dO of a few hundred (so
     |Delta| is large): the fused pass carries -8 L and -Delta through the tensor cores as three bf16
     terms each, which must not cost accuracy against the fp32 constants of the two-pass kernels.
-    The inputs are bf16-representable, so that the staging cast is exact and the oracle sees the
+    The inputs are bf16-representable as staged, so that the staging cast is exact and the oracle sees the
     same numbers (at such scores the rounding of q and k alone would move the result by percents)."""
     n = 384
-    bf = lambda x: torch.from_numpy(x).to(torch.bfloat16).float().numpy()
+    bf = lambda x: torch.from_numpy(np.ascontiguousarray(x, np.float32)).to(torch.bfloat16).float().numpy()
     q, k, v, do = (oracle.normal((2, n, 64), 77, i) for i in range(4))
-    q, k, v, do = bf(4.0 * q), bf(4.0 * k), bf(v), bf(300.0 * do)
+    # (q is staged as q * scale * log2(e): it is that product which has to be bf16-representable)
+    c = np.float32(0.125 * 1.4426950408889634)
+    q, k, v, do = (bf(4.0 * q * c) / c).astype(np.float32), bf(4.0 * k), bf(v), bf(300.0 * do)
     wq, wk, wv = oracle.attn_bwd(q, k, v, do, True)
     _, _, fq, fk, fv = run_bwd(handle, q, k, v, do, True, 0)
     _, _, gq, gk, gv = run_bwd(handle, q, k, v, do, True, 1)

@@ -126,3 +126,65 @@ def test_primitives_alloc_insert_lookup_evict():
     assert p.evict() == o.evict() == 3
     assert p.free_blocks == 4 and p.cached_blocks == 0 and p.evictions == 3
     p.audit()
+
+
+def test_aborted_request_leaves_no_trace_in_the_tree():
+    """A request whose attention step fails after begin_request is aborted: the fresh blocks were never
+    written, so the tree must not adopt them and a later request with the same prefix must compute it."""
+    bs = 4
+    p = KvPool(6 * bs, bs)
+    o = PoolOracle(6 * bs, bs)
+    a = [1, 2, 3, 4, 5, 6, 7, 8, 9]
+    assert p.begin_request(a) == 0 and o.begin_request(a) == 0
+    p.abort_request()
+    o.abort_request(a)
+    p.audit()
+    o.audit()
+    assert p.cached_blocks == 0 and p.free_blocks == 6 and p.lookup(a) == [] and o.lookup(a) == []
+    assert all(p.refcount(b) == 0 for b in range(6))
+    with pytest.raises(Mx230Error):
+        p.abort_request()                      # nothing open any more
+    # the same prompt again: nothing is reused; after a successful end the prefix is there
+    assert p.begin_request(a) == 0
+    p.end_request(a)
+    assert p.lookup(a) == p.table(2).tolist() and p.cached_blocks == 2
+    # an abort on top of a borrowed prefix releases the borrow but keeps the tree's own reference
+    b = [1, 2, 3, 4, 5, 6, 7, 8, 50, 51]
+    assert p.begin_request(b) == 8
+    held = p.table(2).tolist()
+    assert [p.refcount(x) for x in held] == [2, 2]
+    p.abort_request()
+    assert [p.refcount(x) for x in held] == [1, 1] and p.cached_blocks == 2 and p.free_blocks == 4
+    p.audit()
+
+
+def test_prefill_cached_aborts_when_the_attention_step_raises():
+    """paging.prefill_cached: a failure between begin_request and the enqueue of the attention step must not
+    let the tree adopt the request's blocks (host logic only: the step is made to fail before any launch)."""
+    from mx230_b200 import paging
+
+    bs = 4
+    p = KvPool(6 * bs, bs)
+    tokens = list(range(1, 10))
+
+    class Boom(RuntimeError):
+        pass
+
+    def qkv_rows(k):
+        raise Boom("suffix rows unavailable")
+
+    class FakeTable:
+        shape = (8,)
+
+        def __getitem__(self, sl):
+            return self
+
+        def copy_(self, src, non_blocking=False):
+            return self
+
+    with pytest.raises(Boom):
+        paging.prefill_cached(None, p, None, tokens, qkv_rows, None, 2, 1, 1e4, FakeTable())
+    p.audit()
+    assert p.cached_blocks == 0 and p.free_blocks == 6 and p.lookup(tokens) == []
+    assert p.begin_request(tokens) == 0        # the pool accepts a new request: nothing was left open
+    p.end_request(tokens)

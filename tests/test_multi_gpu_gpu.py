@@ -40,8 +40,12 @@ def _worker(rank, world, port, ctx, n_seq, nh, nkv, ret):
     from mx230_b200 import _lib, flash_attention as fa, llm_attention as la
     from mx230_b200.common import Handle
     from mx230_b200.multi_gpu import SplitKvDecoder, SplitKvPlan, shard_range
+    import datetime
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    # a short collective timeout: if the peer fails, this rank's next collective ends with an error
+    # instead of spinning on the GPU
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=60))
     try:
         h = Handle(rank, 64 << 20)
         dev = f"cuda:{rank}"
@@ -86,8 +90,8 @@ def _worker(rank, world, port, ctx, n_seq, nh, nkv, ret):
         both = [torch.zeros_like(chk) for _ in range(world)]
         dist.all_gather(both, chk)
         ret[rank] = (err_dec, rel_dec, err_fwd, [float(b) for b in both], (lo, hi))
+        dist.barrier()   # success path only: a rank that raised must not enter a collective its peer is not in
     finally:
-        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -100,12 +104,20 @@ def test_split_kv_decode_and_sharded_forward_two_gpus(ctx):
     ctxm = mp.get_context("spawn")
     ret = ctxm.Manager().dict()
     port = _free_port()
-    procs = [ctxm.Process(target=_worker, args=(r, world, port, ctx, n_seq, nh, nkv, ret)) for r in range(world)]
+    procs = [ctxm.Process(target=_worker, args=(r, world, port, ctx, n_seq, nh, nkv, ret), daemon=True)
+             for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
         p.join(300)
-        assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+    codes = [p.exitcode for p in procs]
+    for p in procs:   # never leave a rank behind on the GPUs
+        if p.is_alive():
+            p.terminate()
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+    assert codes == [0] * world, f"rank exit codes {codes}"
     assert sorted(ret.keys()) == [0, 1]
     for r in range(world):
         err_dec, rel_dec, err_fwd, sums, _ = ret[r]
@@ -147,6 +159,8 @@ def test_two_handles_in_one_process():
             outs.append((o.cpu().numpy(), dq.cpu().numpy(), dk.cpu().numpy(), dv.cpu().numpy(), od.cpu().numpy()))
     for o, dq, dk, dv, od in outs:
         assert np.abs(o - wo).max() < TOL["max_abs"] and np.isfinite(od).all()
-    # both devices ran the same kernels on the same inputs
-    for a, b in zip(outs[0][:4], outs[1][:4]):
-        np.testing.assert_array_equal(a, b)
+    # both devices ran the same kernels on the same inputs: O, dK, dV are written once by their owner and
+    # must agree bit for bit; dQ of the fused backward is a sum of fp32 reductions in no fixed order
+    for i in (0, 2, 3):
+        np.testing.assert_array_equal(outs[0][i], outs[1][i])
+    assert np.abs(outs[0][1] - outs[1][1]).max() <= 1e-4
