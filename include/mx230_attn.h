@@ -283,8 +283,11 @@ int mx230_attn_decode_q8_batched(mx230_handle *h, void *stream, float *out, cons
  * allowed to enqueue on a stream they were handed -- the split-KV scratch lives in a fixed
  * 1 MiB + 4 KiB __device__ array inside the library image (resident per GPU until exit).
  * Single sequence, contiguous cache, keys 0..=t_cur, reference score mode, current device.
+ * It runs the CUDA-core decode kernel, not the tensor-core one that mx230_attn_decode_q8 defaults to:
+ * the same result to rounding, at a fraction of the bandwidth for GQA groups.
  * Shapes needing more than n_head * n_splits * 264 B <= 1 MiB are refused (MX230_ERR_WORKSPACE).
- * The first call on a device resolves the array's address: make it before any stream capture.
+ * The first call on a device resolves the array's address (serialised against other host threads'
+ * first calls): make it before any stream capture.
  * Calls share the array; calls that overlap on the GPU race on it. */
 int mx230_attn_decode_q8_noalloc(void *stream, float *out, const float *qkv, const int8_t *kq,
                                  const int8_t *vq, const float *ks, const float *vs, const float *kb,

@@ -87,6 +87,19 @@ int mx230_fail(int code, const char *fmt, ...);
         if (!(cond)) return mx230_fail(code, __VA_ARGS__); \
     } while (0)
 
+// Raises a kernel's dynamic shared-memory limit once per device and call site (function attributes are per
+// device; setting one costs a driver call, which has no place in front of every launch of a microsecond kernel).
+#define MX_SMEM_ATTR_ONCE(device, kernel, bytes)                                                         \
+    do {                                                                                                 \
+        static bool _done[64] = {};                                                                      \
+        const int _d = (device);                                                                         \
+        if (_d < 0 || _d >= 64 || !_done[_d]) {                                                          \
+            MX_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                               (int)(bytes)));                                           \
+            if (_d >= 0 && _d < 64) _done[_d] = true;                                                    \
+        }                                                                                                \
+    } while (0)
+
 // Checks the launch and counts it on the handle.
 #define MX_LAUNCHED(h)                                                                      \
     do {                                                                                    \
@@ -212,7 +225,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     unsigned polls = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++polls & 255u) == 0) {
+        // A poll that finds the phase incomplete may have been parked by the hardware for up to the suspend hint,
+        // so the abort flag and the clock are first looked at after 8 polls, then after 16, 32, ... (every 256 from
+        // there on): early for a wait that is going to run out, rare for the short waits of the steady state, whose
+        // polling warps share a scheduler with the compute warps.
+        ++polls;
+        if (polls >= 8u && (polls < 256u ? (polls & (polls - 1u)) == 0u : (polls & 255u) == 0u)) {
             if (*abort_flag) return false;
             if (clock64() - t0 > *(const volatile long long *)(status + STATUS_LIMIT_WORD)) {
                 *abort_flag = 1;
@@ -466,6 +484,64 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Packed pairs of fp32 (one 64-bit register pair per operand): half the instructions of the scalar forms.
+__device__ __forceinline__ uint64_t pk2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float &a, float &b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2_rm(uint64_t a, uint64_t b) {   // round towards minus infinity
+    uint64_t r;
+    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// a += lo(w), b += hi(w) for a packed pair of bf16 (fp32 sums of the ROUNDED probabilities)
+__device__ __forceinline__ void add_bf16x2(uint32_t w, float &a, float &b) {
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\t"
+        "add.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %1, hi, %1;\n\t}"
+        : "+f"(a), "+f"(b)
+        : "r"(w));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// 2^x for two values on the FMA and integer pipes, leaving the exp unit to the other columns: x = n + f
+// with n = floor(x) (the magic-number add, rounded down, leaves n in the low mantissa bits), 2^f by a
+// degree-3 polynomial (relative error 7.9e-5, far below the bf16 rounding of the probabilities), and n
+// added to the exponent field.  Valid for -126 <= x < 128 and nothing else (no clamp): the caller uses it
+// only where the scores are bounded, and never on masked (-inf) entries; CLAMP_LOW lifts the lower restriction
+// (two more instructions per pair).
+template <bool CLAMP_LOW>
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float &p0, float &p1) {
+    if (CLAMP_LOW) {   // for callers whose arguments are bounded above but not below (-inf included)
+        x0 = fmaxf(x0, -126.0f);
+        x1 = fmaxf(x1, -126.0f);
+    }
+    const uint64_t x = pk2(x0, x1);
+    const uint64_t t = add2_rm(x, pk2(12582912.0f, 12582912.0f));          // 1.5 * 2^23 + floor(x)
+    const uint64_t fl = add2(t, pk2(-12582912.0f, -12582912.0f));         // floor(x), exact
+    const uint64_t f = fma2(fl, pk2(-1.0f, -1.0f), x);                    // x - floor(x) in [0, 1)
+    uint64_t p = fma2(pk2(0.07806939631700516f, 0.07806939631700516f), f, pk2(0.22593535482883453f, 0.22593535482883453f));
+    p = fma2(p, f, pk2(0.6959162950515747f, 0.6959162950515747f));
+    p = fma2(p, f, pk2(0.9999210238456726f, 0.9999210238456726f));
+    float a, b, ta, tb;
+    upk2(p, a, b);
+    upk2(t, ta, tb);
+    p0 = __int_as_float(__float_as_int(a) + (__float_as_int(ta) << 23));
+    p1 = __int_as_float(__float_as_int(b) + (__float_as_int(tb) << 23));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

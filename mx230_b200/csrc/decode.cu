@@ -16,6 +16,8 @@
 // cache with the GQA group on warp-level tensor-core tiles (reference score mode).
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -1156,34 +1158,28 @@ int launch_g(mx230_handle *h, cudaStream_t st, const DecodeParams &P, dim3 grid,
         // reference score mode: the tensor-core kernel serves any group size up to 8 per CTA
         size_t sm = (size_t)Q8MmaSmem::TOTAL;
         if (P.tables) {
-            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_mma_kernel<true>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_SMEM_ATTR_ONCE(h->device, (decode_q8_mma_kernel<true>), sm);
             MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_mma_kernel<true><<<grid, Q8_THREADS, sm, st>>>(P)));
         } else {
-            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_mma_kernel<false>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_SMEM_ATTR_ONCE(h->device, (decode_q8_mma_kernel<false>), sm);
             MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_mma_kernel<false><<<grid, Q8_THREADS, sm, st>>>(P)));
         }
     } else if (q8) {
         size_t sm = q8_smem_bytes<G>();
         if (P.tables) {
-            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_kernel<G, true>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_SMEM_ATTR_ONCE(h->device, (decode_q8_kernel<G, true>), sm);
             MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_kernel<G, true><<<grid, Q8_THREADS, sm, st>>>(P)));
         } else {
-            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_kernel<G, false>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_SMEM_ATTR_ONCE(h->device, (decode_q8_kernel<G, false>), sm);
             MX_LAUNCH(h, st, MX230_K_DECODE_Q8, (decode_q8_kernel<G, false><<<grid, Q8_THREADS, sm, st>>>(P)));
         }
     } else {
         size_t sm = (size_t)F32Smem<G>::TOTAL;
         if (P.tables) {
-            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_f32_ring_kernel<G, true>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_SMEM_ATTR_ONCE(h->device, (decode_f32_ring_kernel<G, true>), sm);
             MX_LAUNCH(h, st, MX230_K_DECODE_F32, (decode_f32_ring_kernel<G, true><<<grid, F32_THREADS, sm, st>>>(P)));
         } else {
-            MX_CHECK_CUDA(cudaFuncSetAttribute(decode_f32_ring_kernel<G, false>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
+            MX_SMEM_ATTR_ONCE(h->device, (decode_f32_ring_kernel<G, false>), sm);
             MX_LAUNCH(h, st, MX230_K_DECODE_F32, (decode_f32_ring_kernel<G, false><<<grid, F32_THREADS, sm, st>>>(P)));
         }
     }
@@ -1476,10 +1472,12 @@ extern "C" int mx230_merge_partials_packed(mx230_handle *h, void *stream, float 
 //  * The array is NOALLOC_SCRATCH_BYTES (1 MiB + 4 KiB) per GPU that loads the library and stays
 //    resident until the process exits.  A call needs n_head * n_splits * 264 bytes of it
 //    (n_splits <= 64) plus n_kv_head counters; a shape that does not fit is refused with
-//    MX230_ERR_WORKSPACE.  Single sequence, contiguous cache, reference score mode.
+//    MX230_ERR_WORKSPACE.  Single sequence, contiguous cache, reference score mode.  It always runs the
+//    CUDA-core kernel (decode_q8_kernel), not the tensor-core one that handle-based calls default to: the same
+//    results as mx230_attn_decode_q8 to rounding, but for GQA groups a fraction of its bandwidth.
 //  * The first call on each device resolves the array's device address (the name of a __device__
-//    array is not a device pointer in host code) and reads the SM count; make that first call
-//    outside of any stream capture.
+//    array is not a device pointer in host code) and reads the SM count, under a process-wide lock, so
+//    first calls from several host threads are safe; make that first call outside of any stream capture.
 //  * All calls on a device share the array.  It keeps what the previous call left there: the
 //    counters are cleared on the stream before every launch, the partials are always rewritten
 //    before they are read.  Two calls that overlap on the GPU (different streams) race on it.
@@ -1498,12 +1496,12 @@ struct NoallocDevice {
     int sm_count;
 };
 NoallocDevice g_noalloc_dev[NOALLOC_MAX_DEVICES];  // zero-initialised: scratch == nullptr means "not set up"
+std::mutex g_noalloc_mutex;                       // guards the one-time set-up of an entry above
 
 template <int G>
-int noalloc_launch(cudaStream_t st, const DecodeParams &P, dim3 grid) {
+int noalloc_launch(int device, cudaStream_t st, const DecodeParams &P, dim3 grid) {
     const size_t sm = q8_smem_bytes<G>();
-    MX_CHECK_CUDA(cudaFuncSetAttribute(decode_q8_kernel<G, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)sm));
+    MX_SMEM_ATTR_ONCE(device, (decode_q8_kernel<G, false>), sm);
     decode_q8_kernel<G, false><<<grid, Q8_THREADS, sm, st>>>(P);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)
@@ -1532,19 +1530,23 @@ extern "C" int mx230_attn_decode_q8_noalloc(void *stream, float *out, const floa
     MX_CHECK_CUDA(cudaGetDevice(&dev));
     MX_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, MX230_ERR_UNSUPPORTED, "%s: device %d out of range", who, dev);
     NoallocDevice &nd = g_noalloc_dev[dev];
-    if (nd.scratch == nullptr) {
-        // one-time set-up for this device, with this device current
-        void *p = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-        if (e != cudaSuccess || p == nullptr)
-            return mx230_fail(MX230_ERR_CUDA, "%s: cudaGetSymbolAddress failed: %s", who, cudaGetErrorString(e));
-        int sms = 0;
-        MX_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        int major = 0;
-        MX_CHECK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
-        MX_REQUIRE(major == 10, MX230_ERR_NO_DEVICE, "%s: device %d is not sm_100", who, dev);
-        nd.sm_count = sms;
-        nd.scratch = p;
+    {
+        // one-time set-up for this device, with this device current; host threads making their first calls
+        // at the same time are serialised here (later calls only take the uncontended lock)
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (nd.scratch == nullptr) {
+            int major = 0;
+            MX_CHECK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+            MX_REQUIRE(major == 10, MX230_ERR_NO_DEVICE, "%s: device %d is not sm_100", who, dev);
+            int sms = 0;
+            MX_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            void *p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess || p == nullptr)
+                return mx230_fail(MX230_ERR_CUDA, "%s: cudaGetSymbolAddress failed: %s", who, cudaGetErrorString(e));
+            nd.sm_count = sms;
+            nd.scratch = p;
+        }
     }
 
     DecodeParams P;
@@ -1587,9 +1589,9 @@ extern "C" int mx230_attn_decode_q8_noalloc(void *stream, float *out, const floa
     MX_CHECK_CUDA(cudaMemsetAsync(P.counters, 0, (size_t)gy * sizeof(unsigned), st));
     dim3 grid(n_splits, gy, 1);
     const int g = P.group > 8 ? 8 : P.group;
-    if (g == 1) return noalloc_launch<1>(st, P, grid);
-    if (g == 2) return noalloc_launch<2>(st, P, grid);
-    if (g <= 4) return noalloc_launch<4>(st, P, grid);
-    if (g <= 7) return noalloc_launch<7>(st, P, grid);
-    return noalloc_launch<8>(st, P, grid);
+    if (g == 1) return noalloc_launch<1>(dev, st, P, grid);
+    if (g == 2) return noalloc_launch<2>(dev, st, P, grid);
+    if (g <= 4) return noalloc_launch<4>(dev, st, P, grid);
+    if (g <= 7) return noalloc_launch<7>(dev, st, P, grid);
+    return noalloc_launch<8>(dev, st, P, grid);
 }

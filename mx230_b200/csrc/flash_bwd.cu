@@ -55,7 +55,14 @@ constexpr int BWD_THREADS = 512;
 // warpgroups: compute left, compute right, {TMA, X, acc0, Y}, {acc1, 3 idle}; fused pass: {TMA, X+Y, dK, dV+dQ},
 // {4 drain warps}.
 // setmaxnreg moves registers only inside the CTA's launch-time allocation (128 per thread for 512 threads)
-constexpr int REGS_COMPUTE = 208, REGS_SERVICE = 48;
+#ifndef BWD_REGS_COMPUTE
+#define BWD_REGS_COMPUTE 192
+#define BWD_REGS_SERVICE 64
+#endif
+#ifndef BWD_POLY
+#define BWD_POLY 0         // fused pass: of every four column pairs, how many take 2^x from the FMA-pipe polynomial
+#endif
+constexpr int REGS_COMPUTE = BWD_REGS_COMPUTE, REGS_SERVICE = BWD_REGS_SERVICE;
 static_assert(8 * REGS_COMPUTE + 8 * REGS_SERVICE <= 16 * 128, "setmaxnreg budget exceeds the launch-time register allocation");
 
 // shared memory map (after 1024-byte alignment)
@@ -363,7 +370,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
         } else if (FUSED && warp == 9) {
             // ------------------------- fused pass, issuer 1: X = K Q^T, then Y = V dO^T ------------
             // (the compute warps are busy with the previous tile for far longer than both take)
-            if (lane == 0) {
+            {
                 constexpr uint32_t IDESC_S = mx::mma_idesc_bf16(BT, BS, false, false);
                 const uint64_t own_k = mx::smem_desc_sw128(smem_base + SM_OWN_A);
                 const uint64_t own_v = mx::smem_desc_sw128(smem_base + SM_OWN_B);
@@ -373,31 +380,33 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 uint32_t g = 0;
                 BwdItem I;
                 for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
-                    ok = mx::mbar_wait(bar(BAR_OWN_FULL), it & 1, abort_flag, P.status);
+                    ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_OWN_FULL), it & 1, abort_flag, P.status));
                     for (int y = 0; y < I.n && ok; ++y, ++g) {
                         const int s = g % NST;
-                        ok = mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status);
-                        if (ok && g > 0) ok = mx::mbar_wait(bar(BAR_SDP_FREE), (g - 1) & 1, abort_flag, P.status);
+                        ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status));
+                        if (ok && g > 0) ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_SDP_FREE), (g - 1) & 1, abort_flag, P.status));
                         if (!ok) break;
                         mx::tc_fence_after();
                         const uint64_t sq = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
                         const uint64_t so = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
-#pragma unroll
-                        for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_X, own_k + 2 * k, sq + 2 * k, IDESC_S, k > 0);
                         const uint64_t bq = mx::smem_desc_kmajor_plain(smem_base + SM_AUG_B + s * AUG_BYTES,
                                                                        SM_AUG_Z - SM_AUG_B - s * AUG_BYTES);
-                        mx::mma_ss(tmem + TM_X, aug_x, bq, IDESC_S, 1);   // X -= 8 L of the query column
+                        if (mx::elect_one()) {
 #pragma unroll
-                        for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_Y, own_v + 2 * k, so + 2 * k, IDESC_S, k > 0);
-                        mx::mma_ss(tmem + TM_Y, aug_y, bq, IDESC_S, 1);   // Y -= Delta of the query column
-                        mx::mma_commit(bar(BAR_SDP_FULL));
+                            for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_X, own_k + 2 * k, sq + 2 * k, IDESC_S, k > 0);
+                            mx::mma_ss(tmem + TM_X, aug_x, bq, IDESC_S, 1);   // X -= L (in the units of X) of the query column
+#pragma unroll
+                            for (int k = 0; k < HD / 16; ++k) mx::mma_ss(tmem + TM_Y, own_v + 2 * k, so + 2 * k, IDESC_S, k > 0);
+                            mx::mma_ss(tmem + TM_Y, aug_y, bq, IDESC_S, 1);   // Y -= Delta of the query column
+                            mx::mma_commit(bar(BAR_SDP_FULL));
+                        }
                     }
                 }
             }
             __syncwarp();
         } else if (FUSED && warp == 10) {
             // ------------------------- fused pass, issuer 2: dK += E Q, E (K-major) and Q from shared memory ----
-            if (lane == 0) {
+            {
                 constexpr uint32_t IDESC_G = mx::mma_idesc_bf16(BT, HD, false, true);
                 const uint64_t ds0 = mx::smem_desc_sw128(smem_base + SM_DS), ds1 = mx::smem_desc_sw128(smem_base + SM_DS1_A);
                 bool ok = true;
@@ -406,20 +415,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
                     for (int y = 0; y < I.n && ok; ++y, ++g) {
                         const int s = g % NST;
-                        ok = mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status);
-                        if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), g & 1, abort_flag, P.status);
+                        ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status));
+                        if (ok) ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_DS_READY), g & 1, abort_flag, P.status));
                         if (!ok) break;
                         mx::tc_fence_after();
                         const uint64_t sd = mx::smem_desc_sw128(smem_base + SM_STR_A + s * STR_BYTES);
                         // 16 queries of contraction = 32 B inside a row; queries 64.. are the second half tile
                         const uint64_t lo = (g & 1) ? ds1 : ds0;
                         const uint64_t hi = lo + (uint64_t)(((g & 1) ? SM_DS1_B - SM_DS1_A : DS_HALF_BYTES) >> 4);
+                        if (mx::elect_one()) {
 #pragma unroll
-                        for (int k = 0; k < BS / 16; ++k)
-                            mx::mma_ss(tmem + TMF_ACC0, (k >> 2 ? hi : lo) + (uint64_t)(2 * (k & 3)), sd + 128 * k, IDESC_G,
-                                       (y > 0 || k > 0));
-                        mx::mma_commit(bar(BAR_STR_EMPTY + s));
-                        if (y == I.n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                            for (int k = 0; k < BS / 16; ++k)
+                                mx::mma_ss(tmem + TMF_ACC0, (k >> 2 ? hi : lo) + (uint64_t)(2 * (k & 3)), sd + 128 * k, IDESC_G,
+                                           (y > 0 || k > 0));
+                            mx::mma_commit(bar(BAR_STR_EMPTY + s));
+                            if (y == I.n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                        }
                     }
                 }
             }
@@ -429,7 +440,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             // dQ: A = E read with the queries contiguous (MN-major; the second 64 queries in the other half
             // tile), B = the owned K tile with its rows as the contraction; a fresh accumulator per tile,
             // taken over by the drain warps.
-            if (lane == 0) {
+            {
                 constexpr uint32_t IDESC_G = mx::mma_idesc_bf16(BT, HD, false, true);
                 constexpr uint32_t IDESC_Q = mx::mma_idesc_bf16(BS, HD, true, true);
                 const uint64_t ad0 = mx::smem_desc_sw128_mn(smem_base + SM_DS, DS_HALF_BYTES);
@@ -441,24 +452,28 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 for (int it = 0; ok && bwd_item<MODE>(P, it, I); ++it) {
                     for (int y = 0; y < I.n && ok; ++y, ++g) {
                         const int s = g % NST;
-                        ok = mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status);
-                        if (ok) ok = mx::mbar_wait(bar(BAR_DS_READY), g & 1, abort_flag, P.status);
+                        ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_STR_FULL + s), (g / NST) & 1, abort_flag, P.status));
+                        if (ok) ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_DS_READY), g & 1, abort_flag, P.status));
                         if (!ok) break;
                         mx::tc_fence_after();
                         const uint64_t sd = mx::smem_desc_sw128(smem_base + SM_STR_B + s * STR_BYTES);
+                        if (mx::elect_one()) {
 #pragma unroll
-                        for (int k = 0; k < BS / 16; ++k)
-                            mx::mma_ts(tmem + TMF_ACC1, tmem + TMF_P + 8 * k, sd + 128 * k, IDESC_G, (y > 0 || k > 0));
+                            for (int k = 0; k < BS / 16; ++k)
+                                mx::mma_ts(tmem + TMF_ACC1, tmem + TMF_P + 8 * k, sd + 128 * k, IDESC_G, (y > 0 || k > 0));
+                        }
                         // the drain warps hold the previous dQ tile in registers
-                        if (g > 0) ok = mx::mbar_wait(bar(BAR_DQ_FREE), (g - 1) & 1, abort_flag, P.status);
+                        if (g > 0) ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_DQ_FREE), (g - 1) & 1, abort_flag, P.status));
                         if (!ok) break;
                         mx::tc_fence_after();
                         const uint64_t ad = (g & 1) ? ad1 : ad0;
+                        if (mx::elect_one()) {
 #pragma unroll
-                        for (int k = 0; k < BT / 16; ++k) mx::mma_ss(tmem + TMF_DQ, ad + 128 * k, bd + 128 * k, IDESC_Q, k > 0);
-                        mx::mma_commit(bar(BAR_DQ_FULL));
-                        mx::mma_commit(bar(BAR_STR_EMPTY + s));
-                        if (y == I.n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                            for (int k = 0; k < BT / 16; ++k) mx::mma_ss(tmem + TMF_DQ, ad + 128 * k, bd + 128 * k, IDESC_Q, k > 0);
+                            mx::mma_commit(bar(BAR_DQ_FULL));
+                            mx::mma_commit(bar(BAR_STR_EMPTY + s));
+                            if (y == I.n - 1) mx::mma_commit(bar(BAR_ACC_DONE));
+                        }
                     }
                 }
             }
@@ -593,7 +608,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                 }
                 // (fused pass: X, Y arrive with -8 L and -Delta already added by the MMAs; nl, nd stay 0)
                 float p0, p1;
-                if (FUSED) {
+                if (FUSED && PRE && ((i >> 1) & 3) < BWD_POLY) {
+                    // a share of the exponentials on the FMA pipe (the exp unit is what the two compute warps of a
+                    // scheduler queue for); the arguments are <= ~0 but unbounded below, masked ones -inf
+                    mx::ex2_poly2<true>(__uint_as_float(xv[i]), __uint_as_float(xv[i + 1]), p0, p1);
+                } else if (FUSED) {
                     p0 = PRE ? mx::ex2(__uint_as_float(xv[i])) : mx::ex2(__uint_as_float(xv[i]) * c);
                     p1 = PRE ? mx::ex2(__uint_as_float(xv[i + 1])) : mx::ex2(__uint_as_float(xv[i + 1]) * c);
                 } else {

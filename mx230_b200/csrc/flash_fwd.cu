@@ -117,7 +117,8 @@ struct FwdParams {
     int kv_group;         // query heads per K/V head (K/V head of query head h is h / kv_group)
     int causal;
     int heads;            // query heads (items are (query block, head) pairs, heads fastest)
-    int n_qblocks;        // blocks of QT*BM query rows per head
+    int item_tiles;       // query tiles per work item: QT, or 1 when two-tile items would leave SMs without work
+    int n_qblocks;        // blocks of item_tiles*BM query rows per head
     int n_items;          // heads * n_qblocks
     int tma_out;          // O leaves through staged TMA stores (strides and base 16-byte aligned) or per-thread stores
     int prescaled;        // Q was staged multiplied by scale * log2(e): the scores arrive in log2 units
@@ -133,58 +134,6 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return r;
 }
 
-// Packed pairs of fp32 (one 64-bit register pair per operand): half the instructions of the scalar forms.
-__device__ __forceinline__ uint64_t pk2(float a, float b) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void upk2(uint64_t v, float &a, float &b) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-    uint64_t r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ uint64_t add2_rm(uint64_t a, uint64_t b) {   // round towards minus infinity
-    uint64_t r;
-    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-// a += lo(w), b += hi(w) for a packed pair of bf16 (fp32 sums of the ROUNDED probabilities)
-__device__ __forceinline__ void add_bf16x2(uint32_t w, float &a, float &b) {
-    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\t"
-        "add.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %1, hi, %1;\n\t}"
-        : "+f"(a), "+f"(b)
-        : "r"(w));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-
-// 2^x for two values on the FMA and integer pipes, leaving the exp unit to the other columns: x = n + f
-// with n = floor(x) (the magic-number add, rounded down, leaves n in the low mantissa bits), 2^f by a
-// degree-3 polynomial (relative error 7.9e-5, far below the bf16 rounding of the probabilities), and n
-// added to the exponent field.  Valid for -126 <= x < 128 and nothing else (no clamp): the caller uses it
-// only where the scores are bounded, and never on masked (-inf) entries.
-__device__ __forceinline__ void ex2_poly2(float x0, float x1, float &p0, float &p1) {
-    const uint64_t x = pk2(x0, x1);
-    const uint64_t t = add2_rm(x, pk2(12582912.0f, 12582912.0f));          // 1.5 * 2^23 + floor(x)
-    const uint64_t fl = add2(t, pk2(-12582912.0f, -12582912.0f));         // floor(x), exact
-    const uint64_t f = fma2(fl, pk2(-1.0f, -1.0f), x);                    // x - floor(x) in [0, 1)
-    uint64_t p = fma2(pk2(0.07806939631700516f, 0.07806939631700516f), f, pk2(0.22593535482883453f, 0.22593535482883453f));
-    p = fma2(p, f, pk2(0.6959162950515747f, 0.6959162950515747f));
-    p = fma2(p, f, pk2(0.9999210238456726f, 0.9999210238456726f));
-    float a, b, ta, tb;
-    upk2(p, a, b);
-    upk2(t, ta, tb);
-    p0 = __int_as_float(__float_as_int(a) + (__float_as_int(ta) << 23));
-    p1 = __int_as_float(__float_as_int(b) + (__float_as_int(tb) << 23));
-}
-
 // The CTA's `round`-th work item.  Items are listed heaviest first (when causal: the latest query block of
 // every head, then the one before, ...) and dealt to the CTAs forwards in even rounds, backwards in odd ones.
 __device__ __forceinline__ bool fwd_item(const FwdParams &P, int round, int &bh, int &q0) {
@@ -193,13 +142,13 @@ __device__ __forceinline__ bool fwd_item(const FwdParams &P, int round, int &bh,
     if (i >= P.n_items) return false;
     const int rank = i / P.heads;
     bh = i - rank * P.heads;
-    q0 = (P.causal ? P.n_qblocks - 1 - rank : rank) * (QT * BM);
+    q0 = (P.causal ? P.n_qblocks - 1 - rank : rank) * (P.item_tiles * BM);
     return true;
 }
 // K/V tiles that query tile `t` of the block starting at row q0 has to see
 __device__ __forceinline__ int fwd_tile_iters(const FwdParams &P, int q0, int t) {
     const int r0 = q0 + t * BM;
-    if (r0 >= P.n_q) return 0;
+    if (r0 >= P.n_q || t >= P.item_tiles) return 0;
     const int n_kv_total = (P.n_k + BN - 1) / BN;
     return P.causal ? min(n_kv_total, (r0 + BM - 1 + P.q_off) / BN + 1) : n_kv_total;
 }
@@ -438,14 +387,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int i = 0; i < 32; i += 2) {
                 float p0, p1;
                 if (((i >> 1) % FWD_POLY_DEN) < FWD_POLY) {
-                    ex2_poly2(__uint_as_float(x[i]), __uint_as_float(x[i + 1]), p0, p1);
+                    mx::ex2_poly2<false>(__uint_as_float(x[i]), __uint_as_float(x[i + 1]), p0, p1);
                 } else {
                     p0 = mx::ex2(__uint_as_float(x[i]));
                     p1 = mx::ex2(__uint_as_float(x[i + 1]));
                 }
                 pk[i >> 1] = mx::pack_bf16(p0, p1);
                 if (FWD_ADD2) {
-                    rs2[(i >> 1) & 1] = add2(rs2[(i >> 1) & 1], pk2(p0, p1));
+                    rs2[(i >> 1) & 1] = mx::add2(rs2[(i >> 1) & 1], mx::pk2(p0, p1));
                 } else {
                     rs[i & 2] += p0;
                     rs[(i & 2) + 1] += p1;
@@ -461,13 +410,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         float l_first = 0.0f;   // fp32 sum of the first tile
         auto sum_rounded16 = [&](const uint32_t *pk) {
 #pragma unroll
-            for (int w = 0; w < 16; ++w) add_bf16x2(pk[w], rb[(w & 1) * 2], rb[(w & 1) * 2 + 1]);
+            for (int w = 0; w < 16; ++w) mx::add_bf16x2(pk[w], rb[(w & 1) * 2], rb[(w & 1) * 2 + 1]);
         };
         auto sum_now = [&]() {
             if (FWD_ADD2) {
                 float a0, a1, a2, a3;
-                upk2(rs2[0], a0, a1);
-                upk2(rs2[1], a2, a3);
+                mx::upk2(rs2[0], a0, a1);
+                mx::upk2(rs2[1], a2, a3);
                 return (a0 + a1) + (a2 + a3);
             }
             return (rs[0] + rs[1]) + (rs[2] + rs[3]);
@@ -818,7 +767,10 @@ int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, 
     P.kv_group = kv_group;
     P.causal = causal ? 1 : 0;
     P.heads = heads;
-    P.n_qblocks = (n_q + QT * BM - 1) / (QT * BM);
+    // Two query tiles per item keep both softmax groups of a CTA busy; a call too small to give every SM such an
+    // item is cut into single-tile items instead (the second group idles, but twice as many SMs work).
+    P.item_tiles = ((long long)heads * ((n_q + QT * BM - 1) / (QT * BM)) < h->sm_count) ? 1 : QT;
+    P.n_qblocks = (n_q + P.item_tiles * BM - 1) / (P.item_tiles * BM);
     MX_REQUIRE((long long)heads * P.n_qblocks <= 0x7FFFFFFF, MX230_ERR_UNSUPPORTED, "flash forward: too many query blocks");
     P.n_items = heads * P.n_qblocks;
     P.tma_out = tma_out ? 1 : 0;

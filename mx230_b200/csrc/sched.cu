@@ -46,12 +46,12 @@ extern "C" int mx230_sched_create(mx230_sched **out, mx230_kv_pool *pool, int n_
                                   const int *prompt_len, const int *max_new, int n_requests) {
     MX_REQUIRE(out && pool && n_ctx > 0 && max_batch >= 1 && n_requests >= 0 && (n_requests == 0 || (prompt_len && max_new)),
                MX230_ERR_INVALID_ARG, "sched_create: bad argument");
+    int n_blocks = mx230_kv_pool_n_blocks(pool);
+    MX_REQUIRE(n_blocks > 0, MX230_ERR_INVALID_ARG, "sched_create: empty pool");   // (before anything is allocated)
     mx230_sched *s = new mx230_sched();
     s->pool = pool;
     s->n_ctx = n_ctx;
     s->max_batch = max_batch;
-    int n_blocks = mx230_kv_pool_n_blocks(pool);
-    MX_REQUIRE(n_blocks > 0, MX230_ERR_INVALID_ARG, "sched_create: empty pool");
     s->block = mx230_kv_pool_block_size(pool);
     s->n_log = (n_ctx + s->block - 1) / s->block;
     for (int r = 0; r < n_requests; ++r) {
