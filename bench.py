@@ -5,8 +5,8 @@
 
 Workload (one "step"): the causal forward + backward of B=4, H=12, N=4096, d=64 through
 the fp32-in / fp32-out C-ABI entry points -- attn_flash_lse, attn_bwd_preprocess,
-attn_bwd_flash -- on seeded synthetic N(0,1) tensors.  Operands are rounded to bf16 by
-the library's own staging kernel inside the timed region; accumulation is fp32.
+attn_bwd_flash -- on seeded synthetic N(0,1) tensors (the library's own generator).  Operands are
+rounded to bf16 by the library's staging kernel inside the timed region; accumulation is fp32.
 Algorithmic work per step: forward 2*B*H*N^2*d = 103.08 GFLOP, backward 2.5x = 257.70 GFLOP
 (the two recomputed matmuls of the atomic-free split are not counted).
 
@@ -15,14 +15,18 @@ Algorithmic work per step: forward 2*B*H*N^2*d = 103.08 GFLOP, backward 2.5x = 2
           host->device and O, L, dQ, dK, dV device->host inside the timed region.
 `roofline` per-launch achieved TFLOP/s of the dominant kernel, from event pairs the library
           records around each launch during the timed steps, against the measured dense
-          bf16 peak of MEASURED_PEAKS.json.
+          bf16 peak of this pool (read from the driver-written peaks file when present).
 `cpu_baseline` the CPU restatement of the reference's attention (oracle/) on a bounded sample.
-`decode`  HBM GB/s of the int8-KV GQA decode step (14q/2kv, ctx 2048, batch 64) and of its
-          fp32-KV control, caches rotated through > L2 worth of copies.
+`decode`  HBM GB/s of the int8-KV GQA decode step (14q/2kv, ctx 2048, batch 64; 32q/4kv, ctx 131072,
+          batch 8) and of the fp32-KV control, launches replayed from a CUDA graph over rotated caches.
+`prefill` TFLOP/s of the per-layer prefill attention (staging + kernel), 512 new tokens.
 
 With N > 1 GPUs (torchrun) every rank runs the same per-GPU workload on its own (batch, head)
 units -- no data-path collective -- and the job value is N * units / max-over-ranks time
-(weak scaling).  `--impl reference` times the CPU oracle with all host threads instead.
+(weak scaling); `multi_gpu` then adds the partitioned configurations: the long-context decode with
+its key axis split over the ranks (partial attention, one all-gather, log-sum-exp merge), the
+32768-token forward with its heads over the ranks and the batch-64 decode with its sequences over
+the ranks (strong scaling).  `--impl reference` times the CPU oracle with all host threads instead.
 """
 from __future__ import annotations
 
@@ -46,9 +50,9 @@ STEP_FLOP = FWD_FLOP + BWD_FLOP
 # 2, and the two shared ones (S, dP) are split evenly
 DQ_FLOP = BWD_FLOP * 2.0 / 5.0
 DKV_FLOP = BWD_FLOP * 3.0 / 5.0
-WORKLOAD = "causal flash-attention fwd+bwd, B=4 H=12 N=4096 d=64 (BASELINE.json configs[1])"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the three tensor kernels on this exact
-# workload, from the committed ncu captures (the operands, 4 x 25 MB bf16 + fp32 outputs, mostly stay in the 126 MB L2)
+WORKLOAD = "causal flash-attention fwd+bwd, B=4 H=12 N=4096 d=64, fp32 in/out, bf16 operands"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the tensor kernels on this exact workload, from one
+# ncu capture each (the operands, 4 x 25 MB bf16 + fp32 outputs, mostly stay in the 126 MB L2)
 NCU_DRAM_BYTES_PER_LAUNCH = {"flash_fwd_kernel": 84055808 + 19096576, "bwd_fused_kernel": 319950336 + 200664064,
                              "bwd_dq_kernel": 106472960 + 25134592, "bwd_dkv_kernel": 108812800 + 60150016}
 NOMINAL_BF16_TFLOPS = 2250.0
@@ -143,26 +147,39 @@ def cpu_sample(heads: int, threads: int):
 
 
 def run_reference(args):
-    """The reference's CPU attention path (C restatement: the Rust sources cannot be built
-    here) with all host threads, each step a bounded sample of the workload."""
+    """The reference's CPU attention path (C restatement: the Rust sources cannot be built here) with all
+    host threads.  A step is the whole workload -- all B*H heads, forward + backward -- as in the GPU arm."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
     import oracle
     threads = oracle.max_threads()
-    heads = threads  # one head of B*H per thread and step
-    for _ in range(args.warmup if args.warmup < 2 else 1):
-        cpu_sample(min(heads, 2), threads)
-    times = [cpu_sample(heads, threads) for _ in range(args.steps)]
+    q, k, v, do = (oracle.normal((BH, N, D), 1234, i) for i in range(4))
+
+    def step():
+        t0 = time.perf_counter()
+        oracle.attn_fwd(q, k, v, True, threads=threads)
+        oracle.attn_bwd(q, k, v, do, True, threads=threads)
+        return time.perf_counter() - t0
+
+    if args.warmup > 0:
+        cpu_sample(min(threads, 4), threads)   # one short untimed pass: page in the library, spin up the thread pool
+    # every step is the full workload; on a box whose cores would need more than about four minutes for the
+    # requested steps the run is cut to as many whole steps as fit (at least one) and `steps` reports that number
+    times, budget = [], 240.0
+    for _ in range(max(1, args.steps)):
+        times.append(step())
+        if sum(times) + times[-1] > budget:
+            break
     sec = sum(times) / len(times)
-    tflops = STEP_FLOP * heads / BH / sec / 1e12
+    tflops = STEP_FLOP / sec / 1e12
     line = {
         "impl": "reference", "metric": "attn_fwd_bwd_tflops", "value": tflops, "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": f"{heads} of {BH} (batch, head) units per step"},
+        "data": "synthetic", "config": {"workload": WORKLOAD, "per_gpu_units": f"{BH} (batch, head) units"},
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                         "sample": f"{heads} of {BH} heads, N={N}, forward+backward, {threads} OpenMP threads"},
+                         "sample": f"all {BH} heads, N={N}, forward+backward, {threads} OpenMP threads, {len(times)} steps"},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -170,9 +187,11 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------- GPU arm
-def decode_bench(h, torch, la, n_seq=64, nh=14, nkv=2, ctx=2048, iters=40, quants=(True, False), graph=False):
-    """int8-KV GQA decode (and fp32 control): GB/s of algorithmic bytes, caches rotated so that
-    consecutive launches never hit L2-resident data."""
+def decode_bench(h, torch, la, n_seq=64, nh=14, nkv=2, ctx=2048, quants=(True, False), replays=5):
+    """int8-KV GQA decode (and fp32 control): GB/s of algorithmic bytes.  A launch of a few microseconds cannot be
+    timed by an event pair around it (that measures the host's submission gap), so a sequence of launches over
+    rotated caches -- consecutive launches never touch L2-resident data -- is captured in a CUDA graph once and
+    replayed; the figure is the graph's device time per launch."""
     out = {}
     qd, kvd = nh * 64, nkv * 64
     for quant in quants:
@@ -191,24 +210,120 @@ def decode_bench(h, torch, la, n_seq=64, nh=14, nkv=2, ctx=2048, iters=40, quant
         q = torch.randn(n_seq, qd, device="cuda")
         o = torch.empty(n_seq, qd, device="cuda")
         pos = torch.full((n_seq,), ctx - 1, dtype=torch.int32, device="cuda")
-        for i in range(copies):
-            la.attn_decode_slab(h, o, q, caches[i], pos, n_seq, nh, nkv, 64, ctx, qd, qd)
-        torch.cuda.synchronize()
-        h.profile_reset()
-        h.profile_enable(True)
-        for i in range(iters):
-            la.attn_decode_slab(h, o, q, caches[i % copies], pos, n_seq, nh, nkv, 64, ctx, qd, qd)
-        h.profile_enable(False)
-        prof = h.profile_read()
-        name = "decode_q8_kernel" if quant else "decode_f32_kernel"
-        cnt, ms = prof[name]
-        g_us = graph_time_us(torch, [(lambda cc=cc: la.attn_decode_slab(h, o, q, cc, pos, n_seq, nh, nkv, 64, ctx, qd, qd))
-                                     for cc in (caches * 3)[:max(copies, 12)]]) if graph else None
+        launches = [(lambda cc=cc: la.attn_decode_slab(h, o, q, cc, pos, n_seq, nh, nkv, 64, ctx, qd, qd))
+                    for cc in (caches * 12)[:max(copies, 12)]]
+        g_us = graph_time_us(torch, launches, replays)
         out["int8_kv" if quant else "fp32_kv"] = {
-            "gbs": nbytes / (ms / cnt) / 1e6, "us_per_launch": 1e3 * ms / cnt, "bytes_per_launch": nbytes,
-            **({"graph_us_per_launch": g_us, "graph_gbs": nbytes / g_us / 1e3} if graph else {}),
+            "gbs": nbytes / g_us / 1e3, "us_per_launch": g_us, "bytes_per_launch": nbytes,
+            "timing": f"CUDA graph of {len(launches)} launches over {copies} rotated caches, {replays} replays",
             "batch": n_seq, "ctx": ctx, "heads": f"{nh}q/{nkv}kv", "cache_copies_rotated": copies}
         del caches
+    return out
+
+
+def prefill_bench(h, torch, la, n_tok=512, nh=14, nkv=2, reps=10):
+    """Per-layer prefill attention (Qwen2.5-0.5B layout): `n_tok` new rows at positions pos0.. over the cache,
+    staging kernels + attention kernel, fp32 and int8 cache, at pos0 = 0 and 1536.  Algorithmic FLOPs: 4 * 64 per
+    (query, visible key) pair and head."""
+    out = {}
+    qd, kvd = nh * 64, nkv * 64
+    stride = qd + 2 * kvd
+    for quant in (False, True):
+        for pos0 in (0, 1536):
+            n_keys = pos0 + n_tok
+            h.reserve(la.prefill_workspace_bytes(n_tok, n_keys, nh, nkv))
+            c = la.KvCache(n_keys, nkv, 64, quant)
+            if quant:
+                c.k.random_(-128, 128), c.v.random_(-128, 128)
+                c.ks.uniform_(0.01, 0.03), c.vs.uniform_(0.01, 0.03), c.kb.normal_(), c.vb.normal_()
+            else:
+                c.k.normal_(), c.v.normal_()
+            qkv = torch.randn(n_tok, stride, device="cuda")
+            o = torch.empty(n_tok, qd, device="cuda")
+            f = lambda: la.attn_prefill(h, o, qkv, c, pos0, n_tok, nh, nkv, stride, qd)
+            for _ in range(3):
+                f()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                f()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            pairs = n_tok * pos0 + n_tok * (n_tok + 1) // 2
+            out[f"{'int8' if quant else 'fp32'}_kv_pos0_{pos0}"] = {
+                "us": us, "tflops": 4.0 * 64 * pairs * nh / us / 1e6, "n_tok": n_tok, "n_keys": n_keys,
+                "heads": f"{nh}q/{nkv}kv", "launches_per_call": 3}
+    return out
+
+
+def multi_gpu_bench(h, torch, dist, la, fa, rank, world, local, steps):
+    """The partitioned configurations at N > 1 (strong scaling: the total problem is fixed), each timed on the
+    device between a barrier and all-ranks-done, max over ranks:
+      splitkv   32q/4kv, ctx 131072, 8 sequences, int8 cache: keys split over the ranks, one all-gather of the
+                (m, l, acc) triples, log-sum-exp merge on every rank;
+      fwd_32768 non-causal forward, 8 heads of 32768 tokens, heads over the ranks (no collective);
+      decode_b64 14q/2kv, ctx 2048, batch 64, int8 cache: sequences over the ranks (no collective)."""
+    from mx230_b200.multi_gpu import SplitKvDecoder, SplitKvPlan, shard_range
+    out = {}
+
+    def timed(fn, n, warm=3):
+        for _ in range(warm):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    # ---- split-KV decode
+    nh, nkv, ctx, n_seq = 32, 4, 131072, 8
+    plan = SplitKvPlan(ctx=ctx, world=world, n_seq=n_seq, n_head=nh)
+    t0, t1 = plan.key_range(rank)
+    span = max(1, t1 - t0)
+    caches = []
+    for _ in range(2):   # two copies of this rank's share: together larger than L2
+        c = la.KvCache(n_seq * span, nkv, 64, True)
+        c.k.random_(-128, 128), c.v.random_(-128, 128), c.ks.uniform_(0.01, 0.03), c.vs.uniform_(0.01, 0.03)
+        caches.append(c)
+    q = torch.randn(n_seq, nh * 64, device="cuda")
+    dec = SplitKvDecoder(h, plan, rank, device=f"cuda:{local}")
+    ms = timed(lambda i=0: dec.step(q, caches[i % 2], nkv, span, nh * 64), max(steps, 10))
+    total = n_seq * ctx * nkv * (128 + 16)
+    out["splitkv"] = {"ms_per_step": ms, "aggregate_gbs": total / ms / 1e6, "kv_bytes_total": total,
+                      "exchange_bytes_per_rank": plan.bytes_per_rank(), "scaling": "strong",
+                      "workload": "int8-KV GQA decode 32q/4kv ctx 131072 x 8 sequences, keys split over ranks, "
+                                  "ncclAllGather of the partial triples, merge on every rank"}
+    del caches, dec
+    # ---- 32768-token forward, heads over ranks
+    n, heads = 32768, 8
+    lo, hi = shard_range(heads, rank, world)
+    mine = max(1, hi - lo)
+    h.reserve(fa.workspace_bytes(mine, n, False))
+    qq, kk, vv = (torch.randn(mine, n, 64, device="cuda") for _ in range(3))
+    oo, ll = torch.empty_like(qq), torch.empty(mine, n, device="cuda")
+    ms = timed(lambda i=0: fa.run_flash_lse(h, qq, kk, vv, oo, ll, n, False), 3, warm=2)
+    out["fwd_32768"] = {"ms_per_step": ms, "aggregate_tflops": 4.0 * heads * n * n * 64 / ms / 1e9,
+                        "heads_per_rank": hi - lo, "scaling": "strong",
+                        "workload": "non-causal forward B=1 H=8 N=32768 d=64 (cast + kernel), heads over ranks"}
+    del qq, kk, vv, oo
+    # ---- batch-64 decode, sequences over ranks
+    nh, nkv, ctx, batch = 14, 2, 2048, 64
+    lo, hi = shard_range(batch, rank, world)
+    mine = max(1, hi - lo)
+    d = decode_bench(h, torch, la, n_seq=mine, nh=nh, nkv=nkv, ctx=ctx, quants=(True,))["int8_kv"]
+    t = torch.tensor([d["us_per_launch"]], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    tot = batch * (ctx * nkv * 64 * 2 + ctx * nkv * 16 + nh * 64 * 8)
+    out["decode_b64"] = {"us_per_step": float(t[0]), "aggregate_gbs": tot / float(t[0]) / 1e3, "seqs_per_rank": hi - lo,
+                         "scaling": "strong", "workload": "int8-KV GQA decode 14q/2kv ctx 2048 batch 64, sequences over ranks"}
     return out
 
 
@@ -232,9 +347,14 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    from mx230_b200 import _lib
+    from mx230_b200.common import normal
     h = Handle(local, fa.workspace_bytes(BH, N, True))
-    gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
-    q, k, v, do = (torch.randn(B, H, N, D, device="cuda", generator=gen) for _ in range(4))
+    # the training step keeps Q, K, V unchanged between its forward and backward: the backward then reuses the bf16
+    # copies the forward staged (an option of the library, documented in its header) and stages only dO
+    h.set_option(_lib.OPT_BWD_REUSE_STAGED, 1)
+    # seeded N(0,1) inputs from the library's generator (seed 1000 + rank, tensor index 0..3), uploaded once
+    q, k, v, do = (torch.from_numpy(normal((B, H, N, D), 1000 + rank, i)).cuda() for i in range(4))
     o = torch.empty_like(q)
     lse = torch.empty(B, H, N, device="cuda")
     delta = torch.empty_like(lse)
@@ -269,6 +389,20 @@ def run_ours(args):
     h.profile_enable(False)
     launches = h.launches - l0
     prof = h.profile_read()
+    h.check_status()
+
+    # the reference's atomic-free split (a dQ pass and a dK/dV pass, bit-reproducible) on the same step
+    h.set_option(_lib.OPT_BWD_TWO_PASS, 1)
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    h.profile_reset()
+    h.profile_enable(True)
+    for _ in range(5):
+        step()
+    h.profile_enable(False)
+    prof2 = h.profile_read()
+    h.set_option(_lib.OPT_BWD_TWO_PASS, 0)
     h.check_status()
 
     # ---- end to end: pinned host tensors in, results out, every step ----
@@ -333,10 +467,11 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
 
+    multi = multi_gpu_bench(h, torch, dist, la, fa, rank, world, local, args.steps) if world > 1 else None
     dec = decode_bench(h, torch, la) if rank == 0 else None
-    if dec is not None:  # BASELINE.json configs[4]: 32q/4kv, ctx 131072, 8 sequences, int8 cache (604 MB per launch)
-        dec["int8_kv_long"] = decode_bench(h, torch, la, n_seq=8, nh=32, nkv=4, ctx=131072, iters=10,
-                                           quants=(True,))["int8_kv"]
+    pre = prefill_bench(h, torch, la) if rank == 0 else None
+    if dec is not None:  # the long-context configuration: 32q/4kv, ctx 131072, 8 sequences, int8 cache (604 MB per launch)
+        dec["int8_kv_long"] = decode_bench(h, torch, la, n_seq=8, nh=32, nkv=4, ctx=131072, quants=(True,))["int8_kv"]
     if rank == 0:
         peaks = measured_peaks()
         ms_step = ms / args.steps
@@ -359,13 +494,13 @@ def run_ours(args):
         roofline = {"bound": "tensor", "kernel": dom, "achieved": kern[dom]["achieved_tflops"], "peak": peak,
                     "unit": "TFLOP/s", "frac": kern[dom]["achieved_tflops"] / peak,
                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(dom), "traffic_unit": "bytes per launch (dram read + write)",
-                    "traffic_source": "one ncu --set full capture of this workload: profiles/flash_fwd_bwd_c2_ncu_full.md",
-                    "peak_source": f"{peaks['source']} dense bf16 burst (MEASURED_PEAKS.json)",
+                    "traffic_source": "one ncu --set full capture of this kernel on this workload (not re-measured by this run)",
+                    "peak_source": f"{peaks['source']} dense bf16 burst",
                     "frac_of_nominal": kern[dom]["achieved_tflops"] / NOMINAL_BF16_TFLOPS,
                     "per_kernel": kern}
         import oracle
         cores = oracle.max_threads()
-        heads = max(1, min(cores, 8))
+        heads = max(1, min(cores, BH))   # one head per thread: every core busy
         sec = cpu_sample(heads, cores)
         sec1 = cpu_sample(1, 1)   # what the reference itself does: one head on one thread
         cpu = {"value": STEP_FLOP * heads / BH / sec / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
@@ -381,15 +516,19 @@ def run_ours(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_units": f"{BH} (batch, head) units",
                        "l2": "inputs larger than L2 (4 x 50 MB fp32 operands per step)",
-                       "entry_points": "mx230_attn_flash_lse + mx230_attn_bwd_preprocess + mx230_attn_bwd_flash"},
+                       "entry_points": "mx230_attn_flash_lse + mx230_attn_bwd_preprocess + mx230_attn_bwd_flash",
+                       "options": "MX230_OPT_BWD_REUSE_STAGED = 1 (the backward reuses the forward's staged Q, K, V)",
+                       "inputs": "N(0,1), library generator, seed 1000 + rank"},
             "fwd_tflops": world * FWD_FLOP / (kern["flash_fwd_kernel"]["ms_per_launch"] * 1e-3) / 1e12,
             "bwd_tflops": world * BWD_FLOP / (sum(kern[k]["ms_per_launch"] for k in kern if k.startswith("bwd_") and
                                                   "achieved_tflops" in kern[k]) * 1e-3) / 1e12,
+            "bwd_two_pass_tflops": world * BWD_FLOP / (sum(prof2[k][1] / prof2[k][0] for k in ("bwd_dq_kernel", "bwd_dkv_kernel")
+                                                            if k in prof2) * 1e-3) / 1e12 if "bwd_dq_kernel" in prof2 else None,
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
                     "pipeline": "3 streams, 2 buffer sets: the copies of steps i+1 / i-1 overlap the kernels of step i"},
-            "gpu_launches": launches, "clocks": clocks, "decode": dec,
+            "gpu_launches": launches, "clocks": clocks, "decode": dec, "prefill": pre, "multi_gpu": multi,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -400,7 +539,7 @@ def run_ours(args):
 
 def run_case(args):
     """One kernel family on a fixed shape, a few launches and nothing else: the command that the
-    ncu captures under profiles/ wrap (`--case fwd|bwd|bwd_two_pass|decode_c4|decode_long`)."""
+    ncu captures wrap (`--case fwd|bwd|bwd_two_pass|decode_c4|decode_long`)."""
     import torch
     from mx230_b200 import flash_attention as fa
     from mx230_b200 import llm_attention as la
@@ -440,7 +579,7 @@ def run_case(args):
 
 
 def run_splitkv(args):
-    """Long-context int8-KV decode (BASELINE.json configs[4]: 32q/4kv, ctx 131072, 8 sequences) with the
+    """Long-context int8-KV decode (32q/4kv, ctx 131072, 8 sequences) with the
     key axis split over the ranks: partial attention on this rank's keys, one all-gather of the
     (m, l, acc) triples, log-sum-exp merge on every rank.  Strong scaling: the total context is fixed.
     Run under torchrun for N > 1; prints one JSON line on rank 0."""
@@ -499,6 +638,7 @@ def graph_time_us(torch, launches, replays=5):
     kernels of a few microseconds the host cannot submit launches fast enough for an event pair around
     each one to measure anything but the submission gap."""
     side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())   # the caller's tensors (positions, caches) were filled on its stream
     with torch.cuda.stream(side):
         for f in launches:
             f()
@@ -519,7 +659,7 @@ def graph_time_us(torch, launches, replays=5):
 
 
 def run_configs(args):
-    """Every BASELINE.json configuration on one GPU, kernel time from the library's own event pairs
+    """Every benchmark configuration on one GPU, kernel time from the library's own event pairs
     (median-free mean over `--steps` launches after warm-up): C1 and C3 forward through the fp32 entry
     point (cast + kernel), C4 decode at batch 1 / 16 / 64 (int8 affine cache and fp32 control), C5 decode.
     One JSON line per configuration."""
@@ -557,11 +697,11 @@ def run_configs(args):
     fwd_config("C2-forward", 48, 4096, True)
     fwd_config("C3", 8, 32768, False)
     for b in (1, 16, 64):
-        d = decode_bench(h, torch, la, n_seq=b, iters=reps, graph=True)
+        d = decode_bench(h, torch, la, n_seq=b)
         for kname, v in d.items():
             v["frac_of_measured_hbm"] = v["gbs"] / peaks["hbm_gbs"]
             print(json.dumps({"config": f"C4 batch {b} {kname}", **v}), flush=True)
-    d = decode_bench(h, torch, la, n_seq=8, nh=32, nkv=4, ctx=131072, iters=reps, quants=(True,))["int8_kv"]
+    d = decode_bench(h, torch, la, n_seq=8, nh=32, nkv=4, ctx=131072, quants=(True,))["int8_kv"]
     d["frac_of_measured_hbm"] = d["gbs"] / peaks["hbm_gbs"]
     print(json.dumps({"config": "C5 one GPU int8_kv", **d}), flush=True)
     h.check_status()
@@ -663,7 +803,7 @@ def main():
     ap.add_argument("--case", default=None, choices=["fwd", "bwd", "bwd_two_pass", "decode_c4", "decode_long", "splitkv", "configs", "proj"],
                     help="fwd|bwd|decode_*: profiling aid, runs one kernel family a few times and exits; "
                          "splitkv: long-context decode with keys split over the ranks (torchrun for N > 1); "
-                         "configs: every BASELINE.json configuration on one GPU; "
+                         "configs: every benchmark configuration on one GPU; "
                          "proj: the projections either side of attention for one decode token")
     args = ap.parse_args()
     if args.case == "splitkv":

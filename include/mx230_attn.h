@@ -118,6 +118,14 @@ int mx230_check_status(mx230_handle *h, void *stream);
 /* Number of kernels launched through this handle so far. */
 long long mx230_launch_count(const mx230_handle *h);
 
+/* Seeded host-side input generators (no CUDA call; `out_host` is host memory).
+ * mx230_pseudo_rand: pseudo_rand of common/src/lib.rs:67-78 -- xorshift64* from `seed`, uniform in [-1, 1).
+ * mx230_fill_normal: N(0,1) values for benchmark and test inputs (the reference has no normal generator): the same
+ * xorshift64* stream, started at splitmix64(seed * 16 + tensor_index) (0 is a fixed point of xorshift, so a seed
+ * cannot be the state itself), through a Box-Muller transform in double precision, rounded to float. */
+int mx230_pseudo_rand(float *out_host, size_t n, uint64_t seed);
+int mx230_fill_normal(float *out_host, size_t n, uint64_t seed, uint64_t tensor_index);
+
 /* Per-kernel device timing (the role of the reference's opt-in prof_attn_us attribution,
  * 03-llm-engine/src/gpu.rs:1922-1928): while enabled, every launch is bracketed by a CUDA
  * event pair on the caller's stream.  mx230_profile_read synchronises the recorded events

@@ -30,6 +30,7 @@ class Mx230Error(RuntimeError):
 
 _CTYPE = {
     "int": C.c_int, "float": C.c_float, "size_t": C.c_size_t, "long long": C.c_longlong, "void": None, "uint32_t": C.c_uint32,
+    "uint64_t": C.c_uint64,
 }
 
 

@@ -109,18 +109,19 @@ def allclose_err(got, want, rtol: float, atol: float) -> float:
 
 
 def pseudo_rand(n: int, seed: int) -> np.ndarray:
-    """common/src/lib.rs:67-78: xorshift64* uniform in [-1, 1)."""
-    mask = (1 << 64) - 1
+    """common/src/lib.rs:67-78: xorshift64* uniform in [-1, 1) (host code of the library)."""
     out = np.empty(n, np.float32)
-    s = seed & mask
-    for i in range(n):
-        s ^= s >> 12
-        s ^= (s << 25) & mask
-        s ^= s >> 27
-        r = (s * 0x2545F4914F6CDD1D) & mask
-        out[i] = np.float32(r >> 40) / np.float32(1 << 23) - np.float32(1.0)
+    check(lib().mx230_pseudo_rand(out.ctypes.data_as(C.c_void_p), n, seed))
     return out
 
 
-__all__ = ["Handle", "stream_ptr", "time_median_ms", "max_rel_err", "allclose_err", "pseudo_rand",
+def normal(shape, seed: int, tensor_index: int) -> np.ndarray:
+    """Seeded N(0,1) inputs for benchmarks and tests: the xorshift64* stream of `pseudo_rand`, started at
+    splitmix64(seed * 16 + tensor_index), through Box-Muller in double precision."""
+    out = np.empty(int(np.prod(shape)), np.float32)
+    check(lib().mx230_fill_normal(out.ctypes.data_as(C.c_void_p), out.size, seed, tensor_index))
+    return out.reshape(shape)
+
+
+__all__ = ["Handle", "stream_ptr", "time_median_ms", "max_rel_err", "allclose_err", "pseudo_rand", "normal",
            "_lib"]

@@ -43,6 +43,7 @@ struct DecodeParams {
     const int *tables;  // block tables; kind 2: row s of n_log entries; null = linear
     int bs, n_log;
     long long seq_rows;  // linear batched slabs: sequence s starts at row s*seq_rows
+    int max_keys;        // capacity of one sequence (slab rows, or table entries x block) when positions come from the device; 0 = unknown
     int n_head, n_kv_head, group, head_groups;
     int score_mode;
 };
@@ -84,6 +85,9 @@ __device__ __forceinline__ void key_range(const DecodeParams &P, int s, int &kbe
         kend = P.t1;
     } else {
         int p = P.pos_kind == 0 ? P.pos : (P.pos_kind == 1 ? *P.pos_dev : P.pos_dev[s]);
+        // a position read from device memory cannot be validated by the host: where the capacity of a sequence is
+        // known, a wild value (a caller's ordering bug) is kept inside it rather than turned into wild addresses
+        if (P.pos_kind == 2 && P.max_keys > 0) p = min(max(p, 0), P.max_keys - 1);
         kbeg = 0;
         kend = p + 1;
     }
@@ -1219,6 +1223,7 @@ int launch_decode(mx230_handle *h, void *stream, DecodeParams P, int n_seq, int 
     P.group = P.n_head / P.n_kv_head;
     P.head_groups = (P.group + 7) / 8;
     P.score_mode = h->q8_score_mode;
+    P.max_keys = (P.pos_kind == 2 && known_keys > 0 && known_keys < 0x7FFFFFFF) ? (int)known_keys : 0;
     int gy = P.n_kv_head * P.head_groups;
     MX_REQUIRE((size_t)n_seq * gy <= h->n_counters, MX230_ERR_UNSUPPORTED,
                "attn_decode: n_seq*n_kv_head %lld exceeds %zu", (long long)n_seq * gy, h->n_counters);

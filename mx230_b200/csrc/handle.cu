@@ -5,6 +5,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <math.h>
+
 #include "common.cuh"
 
 static thread_local char g_err[512] = "";
@@ -202,6 +204,39 @@ extern "C" int mx230_check_status(mx230_handle *h, void *stream) {
         cudaMemset(h->status_dev, 0, sizeof(st));
         return mx230_fail(MX230_ERR_DEVICE_STATUS,
                           "device status %d (1 = bounded wait timed out), detail %d", st[0], st[1]);
+    }
+    return MX230_OK;
+}
+
+// ---- seeded input generators (host code) ----
+static inline uint64_t xorshift64star(uint64_t &s) {
+    s ^= s >> 12;
+    s ^= s << 25;
+    s ^= s >> 27;
+    return s * 0x2545F4914F6CDD1DULL;
+}
+
+extern "C" int mx230_pseudo_rand(float *out_host, size_t n, uint64_t seed) {
+    MX_REQUIRE(out_host != nullptr || n == 0, MX230_ERR_INVALID_ARG, "pseudo_rand: null output");
+    uint64_t s = seed;
+    for (size_t i = 0; i < n; ++i) out_host[i] = (float)(xorshift64star(s) >> 40) / (float)(1ULL << 23) - 1.0f;
+    return MX230_OK;
+}
+
+extern "C" int mx230_fill_normal(float *out_host, size_t n, uint64_t seed, uint64_t tensor_index) {
+    MX_REQUIRE(out_host != nullptr || n == 0, MX230_ERR_INVALID_ARG, "fill_normal: null output");
+    uint64_t s = seed * 16u + tensor_index;   // splitmix64 step: the generator's state must not be zero
+    s += 0x9E3779B97F4A7C15ULL;
+    s = (s ^ (s >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    s = (s ^ (s >> 27)) * 0x94D049BB133111EBULL;
+    s ^= s >> 31;
+    if (s == 0) s = 0x9E3779B97F4A7C15ULL;
+    for (size_t i = 0; i < n; i += 2) {
+        const double u1 = ((double)(xorshift64star(s) >> 11) + 1.0) / 9007199254740992.0;   // (0, 1]
+        const double u2 = ((double)(xorshift64star(s) >> 11) + 1.0) / 9007199254740992.0;
+        const double r = sqrt(-2.0 * log(u1)), a = 6.283185307179586476925 * u2;
+        out_host[i] = (float)(r * cos(a));
+        if (i + 1 < n) out_host[i + 1] = (float)(r * sin(a));
     }
     return MX230_OK;
 }

@@ -18,6 +18,17 @@ def test_pseudo_rand_matches_golden_and_host(golden):
     assert np.array_equal(common.pseudo_rand(257, 5), oracle.pseudo_rand(257, 5))
 
 
+def test_library_generators_equal_the_oracle_generators():
+    """The library's host-side generators (what the benchmark draws its inputs from) against the oracle's,
+    bit for bit: the uniform stream of common/src/lib.rs:67-78 and the N(0,1) stream built on it."""
+    for seed in (0, 1, 42, 1234):
+        assert np.array_equal(common.pseudo_rand(1000, seed + 1), oracle.pseudo_rand(1000, seed + 1))
+        for idx in (0, 3):
+            assert np.array_equal(common.normal((7, 143), seed, idx), oracle.normal((7, 143), seed, idx))
+    z = common.normal((200000,), 0, 0)
+    assert abs(float(z.mean())) < 0.01 and abs(float(z.std()) - 1.0) < 0.01
+
+
 def test_pseudo_rand_is_deterministic_and_bounded():
     a, b = oracle.pseudo_rand(1000, 42), oracle.pseudo_rand(1000, 42)
     assert np.array_equal(a, b)
