@@ -336,8 +336,11 @@ int mx230_merge_partials_packed(mx230_handle *h, void *stream, float *out, const
  * (llm.cu:3806-3872).  q row qi of head h is read at qkv[qi*qkv_stride + h*64], the result
  * goes to out[qi*out_stride + h*64]; K and V come only from the cache, which must already
  * hold positions pos0..pos0+n_tok-1 (the reference writes them first, gpu.rs:3243-3320).
- * Operands are rounded to bf16 (int8 codes after dequantisation) for the tensor cores.
- * The _dp4a forms (the reference's opt-in int8-score approximation) use the exact scores. */
+ * Operands are rounded to bf16 for the tensor cores.  Over an int8 cache MX230_OPT_Q8_SCORE_MODE selects the score
+ * arithmetic as for decode: REF (default) quantises q per (row, head) to int8 and rebuilds the score from the exact
+ * integer dot as attn_prefill_q8 does (llm.cu:3700-3716,3774-3782; the codes pass through the tensor cores exactly);
+ * EXACT scores with fp32 q on the dequantised K.  The _dp4a forms are the reference's opt-in int8-score
+ * approximation over an fp32 cache: every K row quantised on the fly, symmetric absmax (llm.cu:3737-3754). */
 size_t mx230_prefill_workspace_bytes(int n_tok, int n_keys, int n_head, int n_kv_head);
 int mx230_attn_prefill(mx230_handle *h, void *stream, float *out, const float *qkv,
                        const float *kcache, const float *vcache, int pos0, int n_tok, int n_head,

@@ -162,11 +162,14 @@ inline size_t mx230_flash_norm_bytes(int batch_heads) {
 // O + h*o_head_stride + r*o_row_stride.  q_prescaled: Qb holds Q * MX230_QK_LOG2_SCALE.  q_norm2 / k_norm2 (both or
 // neither): largest squared row norm per head of the unscaled Q [heads][MX230_NORM_PARTS] and of K
 // [heads / kv_group][MX230_NORM_PARTS]; with them (and q_prescaled) a head whose scores are provably small takes the
-// kernel's max-free softmax loop.
+// kernel's max-free softmax loop.  row_a / row_qsum / col_kskb (all or none; with them q_prescaled must be 0 and Qb, Kb
+// hold int8 codes as bf16): the int8 score mode -- score = row_a[h][i] * (dot * ks[j] + row_qsum[h][i] * kb[j]), with
+// col_kskb [heads / kv_group][n_k rounded up to 128] pairs (ks, kb).
 int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
                               const void *Vb, float *O, float *L, int heads, int n_q, int n_k, int q_off,
                               int kv_group, long long o_head_stride, long long o_row_stride, int causal,
-                              int q_prescaled, const float *q_norm2, const float *k_norm2);
+                              int q_prescaled, const float *q_norm2, const float *k_norm2, const float *row_a,
+                              const float *row_qsum, const float *col_kskb);
 
 // ---------------------------------------------------------------------------
 // device

@@ -597,34 +597,6 @@ decode_q8_mma_kernel(const DecodeParams P) {
     const bool affine = P.kb != nullptr;
     const float scale = 0.125f * LOG2E;  // scores are kept in the log2 domain
 
-    // ---- q: per-head int8 codes as the reference kernel forms them (padding heads: zeros) ----
-    const float *qrow = P.qkv + (size_t)s * P.qkv_stride + head0 * 64;
-    for (int i = tid; i < MG * 64; i += Q8_THREADS) qf[i] = (i / 64 < gc) ? qrow[i] : 0.0f;
-    __syncthreads();
-    {
-        const int g = warp;  // Q8_WARPS == MG
-        float a = qf[g * 64 + lane], b = qf[g * 64 + 32 + lane];
-        float qmax = warp_max_f(fmaxf(fabsf(a), fabsf(b)));
-        float qid = qmax > 0.0f ? __fdiv_rn(127.0f, qmax) : 0.0f;
-        int ca = max(-127, min(127, __float2int_rn(a * qid)));
-        int cb = max(-127, min(127, __float2int_rn(b * qid)));
-        int8_t *qb = (int8_t *)(qq + g * 16);
-        qb[lane] = (int8_t)ca;
-        qb[32 + lane] = (int8_t)cb;
-        float qsum = warp_sum_f((float)(ca + cb));  // exact: small integers
-        if (lane == 0) {
-            hq[g] = (qmax > 0.0f ? __fdiv_rn(qmax, 127.0f) : 0.0f) * scale;
-            hq[MG + g] = qsum;
-        }
-    }
-    __syncthreads();
-    static_assert(Q8_WARPS == MG, "one warp quantises one head");
-
-    // fragment coordinates: g = head row (and key / value-dim column of the B fragments), j = k group
-    const int g = lane >> 2, j = lane & 3;
-    const int4 qa = *(const int4 *)(qq + g * 16 + 4 * j);   // bytes 16j .. 16j+15 of head g
-    const float hq_g = hq[g], qsum_g = hq[MG + g];
-
     // ---- this warp's key sub-range ----
     const int n_keys = kb_ - ka;
     int per_w = (n_keys + Q8_WARPS - 1) / Q8_WARPS;
@@ -692,17 +664,47 @@ decode_q8_mma_kernel(const DecodeParams P) {
         }
     };
 
+    // the first tiles are requested before anything else: their HBM latency then covers the q prologue below
+#pragma unroll
+    for (int t = 0; t < MMA_STAGES - 1; ++t) {
+        if (t < n_tiles) issue(t);
+        cp_async_commit();
+    }
+
+    // ---- q: per-head int8 codes as the reference kernel forms them (padding heads: zeros) ----
+    const float *qrow = P.qkv + (size_t)s * P.qkv_stride + head0 * 64;
+    for (int i = tid; i < MG * 64; i += Q8_THREADS) qf[i] = (i / 64 < gc) ? qrow[i] : 0.0f;
+    __syncthreads();
+    {
+        const int g = warp;  // Q8_WARPS == MG
+        float a = qf[g * 64 + lane], b = qf[g * 64 + 32 + lane];
+        float qmax = warp_max_f(fmaxf(fabsf(a), fabsf(b)));
+        float qid = qmax > 0.0f ? __fdiv_rn(127.0f, qmax) : 0.0f;
+        int ca = max(-127, min(127, __float2int_rn(a * qid)));
+        int cb = max(-127, min(127, __float2int_rn(b * qid)));
+        int8_t *qb = (int8_t *)(qq + g * 16);
+        qb[lane] = (int8_t)ca;
+        qb[32 + lane] = (int8_t)cb;
+        float qsum = warp_sum_f((float)(ca + cb));  // exact: small integers
+        if (lane == 0) {
+            hq[g] = (qmax > 0.0f ? __fdiv_rn(qmax, 127.0f) : 0.0f) * scale;
+            hq[MG + g] = qsum;
+        }
+    }
+    __syncthreads();
+    static_assert(Q8_WARPS == MG, "one warp quantises one head");
+
+    // fragment coordinates: g = head row (and key / value-dim column of the B fragments), j = k group
+    const int g = lane >> 2, j = lane & 3;
+    const int4 qa = *(const int4 *)(qq + g * 16 + 4 * j);   // bytes 16j .. 16j+15 of head g
+    const float hq_g = hq[g], qsum_g = hq[MG + g];
+
     float m_run = -CUDART_INF_F, l_thr = 0.0f, b_thr = 0.0f;
     float oacc[8][2];
     float z0 = 0.0f, z1 = 0.0f;   // rows 8..15 of the output tiles: stay zero
 #pragma unroll
     for (int t = 0; t < 8; ++t) oacc[t][0] = oacc[t][1] = 0.0f;
 
-#pragma unroll
-    for (int t = 0; t < MMA_STAGES - 1; ++t) {
-        if (t < n_tiles) issue(t);
-        cp_async_commit();
-    }
     const uint32_t MAGIC = 0x64646464u, BIAS = 0x64806480u;  // f16 1024 | byte, minus 1152
     for (int tile = 0; tile < n_tiles; ++tile) {
         if (tile + MMA_STAGES - 1 < n_tiles) issue(tile + MMA_STAGES - 1);

@@ -125,6 +125,13 @@ struct FwdParams {
     const float *q_norm2; // [heads][MX230_NORM_PARTS] largest squared row norm of the unscaled Q per head and part, or null
     const float *k_norm2; // [heads / kv_group][MX230_NORM_PARTS] the same for K
     int test_drop_tile;   // test hook: K/V tile (counted over the CTA's items) that CTA 0's producer never requests; -1 = off
+    // int8 score mode (prefill over an int8 cache with the reference kernel's arithmetic): Q and K hold int8 CODES
+    // (exact in bf16), so the MMA returns exact integer dots, and the score is rebuilt per element as
+    // row_a[i] * (dot * ks[j] + row_qsum[i] * kb[j]) in log2 units (03-llm-engine/kernels/llm.cu:3774-3782)
+    const float *row_a;      // [heads][n_q]   q scale * 1/sqrt(64) * log2(e), or null = mode off
+    const float *row_qsum;   // [heads][n_q]   sum of the row's q codes
+    const float2 *col_kskb;  // [heads / kv_group][n_k_pad] (scale, offset) of every key
+    int n_k_pad;             // n_k rounded up to a multiple of BN
     int *status;
 };
 
@@ -334,8 +341,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t tm_p = tmem + lane_off + TM_P + t * (BN / 2);
         const uint32_t tm_o = tmem + lane_off + TM_O + t * HD;
         // Scores arrive in log2 units when Q was staged pre-multiplied by scale * log2(e) (c = 1), else raw (c = scale * log2(e)).
-        const float c = P.prescaled ? 1.0f : 0.125f * 1.4426950408889634f;
-        const float l_scale = P.prescaled ? 0.6931471805599453f : 0.125f;   // running max -> natural-log units
+        const bool i8_scores = P.row_a != nullptr;   // scores rebuilt from integer dots: already in log2 units
+        const float c = (P.prescaled || i8_scores) ? 1.0f : 0.125f * 1.4426950408889634f;
+        const float l_scale = (P.prescaled || i8_scores) ? 0.6931471805599453f : 0.125f;   // running max -> natural-log units
         bool ok = true;
         uint32_t cnt = 0;  // score tiles this group has taken so far, over all items
         int bh, q0;
@@ -483,6 +491,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         l_norm = l - l_first + ((rb[0] + rb[1]) + (rb[2] + rb[3]));
         } else {
         // ---- general loop: running row max, raised lazily
+        float row_a = 0.0f, row_qsum = 0.0f;
+        if (i8_scores && row < NQ) {
+            row_a = P.row_a[(size_t)bh * NQ + row];
+            row_qsum = P.row_qsum[(size_t)bh * NQ + row];
+        }
         for (int j = 0; j < n_t; ++j, ++cnt) {
             ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), cnt & 1, abort_flag, P.status));
             if (!ok) break;
@@ -497,6 +510,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (lane == 0) mx::mbar_arrive(bar(BAR_S_FREE + t));
 
             const int key0 = j * BN;
+            if (i8_scores) {
+                // the tile holds exact integer dots of int8 codes: the reference kernel's score for them
+                const float2 *cs = P.col_kskb + (size_t)(bh / P.kv_group) * P.n_k_pad + key0;
+#pragma unroll
+                for (int i = 0; i < BN; ++i) {
+                    const float2 kk = __ldg(cs + i);
+                    v[i] = __float_as_uint(row_a * fmaf(__uint_as_float(v[i]), kk.x, row_qsum * kk.y));
+                }
+            }
             if ((key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM + P.q_off)) {
 #pragma unroll
                 for (int i = 0; i < BN; ++i)
@@ -732,7 +754,8 @@ int mx230_launch_cast(mx230_handle *h, cudaStream_t st, const float *const *src,
 int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, const void *Kb,
                               const void *Vb, float *O, float *L, int heads, int n_q, int n_k, int q_off,
                               int kv_group, long long o_head_stride, long long o_row_stride, int causal,
-                              int q_prescaled, const float *q_norm2, const float *k_norm2) {
+                              int q_prescaled, const float *q_norm2, const float *k_norm2, const float *row_a,
+                              const float *row_qsum, const float *col_kskb) {
     CUtensorMap tq, tk, tv, to;
     uint64_t rs = HD * 2;
     int rc;
@@ -778,6 +801,10 @@ int mx230_launch_flash_fwd_ex(mx230_handle *h, cudaStream_t st, const void *Qb, 
     P.q_norm2 = (q_prescaled && q_norm2 && k_norm2) ? q_norm2 : nullptr;
     P.k_norm2 = P.q_norm2 ? k_norm2 : nullptr;
     P.test_drop_tile = h->test_drop_tile;
+    P.row_a = (row_a && row_qsum && col_kskb) ? row_a : nullptr;
+    P.row_qsum = P.row_a ? row_qsum : nullptr;
+    P.col_kskb = P.row_a ? (const float2 *)col_kskb : nullptr;
+    P.n_k_pad = (n_k + BN - 1) / BN * BN;
     P.status = h->status_dev;
     // persistent: one CTA per SM (the kernel holds all of an SM's tensor memory), each walking its share of the items
     dim3 grid((unsigned)(P.n_items < h->sm_count ? P.n_items : h->sm_count));
@@ -790,7 +817,7 @@ int mx230_launch_flash_fwd(mx230_handle *h, cudaStream_t st, const void *Qb, con
                            const void *Vb, float *O, float *L, int batch_heads, int n, int causal,
                            int q_prescaled, const float *q_norm2, const float *k_norm2) {
     return mx230_launch_flash_fwd_ex(h, st, Qb, Kb, Vb, O, L, batch_heads, n, n, 0, 1, (long long)n * HD, HD,
-                                     causal, q_prescaled, q_norm2, k_norm2);
+                                     causal, q_prescaled, q_norm2, k_norm2, nullptr, nullptr, nullptr);
 }
 
 static int check_flash_args(const char *who, mx230_handle *h, int batch_heads, int n) {

@@ -279,7 +279,9 @@ def gqa_decode_batched(qkv, pos, n_head, n_kv_head, head_dim=64, kcache=None, vc
 
 
 def prefill(qkv, pos0, n_tok, n_head, n_kv_head, qkv_stride, out_stride, kcache=None, vcache=None,
-            cache=None, table=None, block_size=16, threads=0):
+            cache=None, table=None, block_size=16, threads=0, mode=0):
+    """mode 0: exact scores (fp32 cache, or int8 cache dequantised).  mode 1: the reference kernels' int8 score
+    arithmetic -- over an int8 cache its attn_prefill_q8, over an fp32 cache its opt-in attn_prefill_dp4a."""
     qkv = np.ascontiguousarray(qkv, np.float32)
     out = np.zeros((n_tok, out_stride), np.float32)
     c = cache
@@ -287,7 +289,7 @@ def prefill(qkv, pos0, n_tok, n_head, n_kv_head, qkv_stride, out_stride, kcache=
                       _b(c.vq) if c else None, _f(c.ks) if c else None, _f(c.vs) if c else None,
                       _f(c.kb) if c else None, _f(c.vb) if c else None, pos0, n_tok, n_head,
                       n_kv_head, qkv_stride, out_stride, _i(table), block_size,
-                      1 if c is not None else 0, threads)
+                      (2 if mode else 1) if c is not None else (3 if mode else 0), threads)
     return out
 
 

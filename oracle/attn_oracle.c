@@ -635,11 +635,61 @@ void orc_gqa_decode_batched(float *out, const float *qkv, const float *kcache, c
     }
 }
 
+/* One query row over an fp32 cache with int8 scores formed on the fly: KIND 2 of attn_prefill_body
+ * (03-llm-engine/kernels/llm.cu:3700-3716 for q, :3737-3754 for K, :3774-3782 for the score).  q is quantised per
+ * (row, head): id = 127/amax, codes clamp(rne(q*id), +-127), qs = amax/127; every K row symmetrically the same way
+ * (Ks = amax/127, no offset); s = qs * scale * ((float)dot * Ks).  V stays fp32; softmax per row as in cpu.rs. */
+static void orc_gqa_row_dp4a(float *out, const float *q, const float *kcache, const float *vcache, int t_cur,
+                             int n_head, int n_kv_head, const int *table, int block_size) {
+    int kvd = n_kv_head * HD;
+    int group = n_head / n_kv_head;
+    float scale = 1.0f / sqrtf((float)HD);
+    float *s = (float *)malloc((size_t)(t_cur + 1) * sizeof(float));
+    for (int h = 0; h < n_head; ++h) {
+        int kvh = h / group;
+        const float *qh = q + h * HD;
+        float *o = out + h * HD;
+        int qq[HD];
+        float amax = 0.0f;
+        for (int d = 0; d < HD; ++d) amax = fmaxf(amax, fabsf(qh[d]));
+        float id = amax > 0.0f ? 127.0f / amax : 0.0f;
+        for (int d = 0; d < HD; ++d) qq[d] = rne_clamp(qh[d] * id, -127, 127);
+        float qs = amax > 0.0f ? amax / 127.0f : 0.0f;
+        float m = -INFINITY;
+        for (int j = 0; j <= t_cur; ++j) {
+            const float *kr = kcache + kv_row(table, block_size, j) * kvd + kvh * HD;
+            float kmax = 0.0f;
+            for (int d = 0; d < HD; ++d) kmax = fmaxf(kmax, fabsf(kr[d]));
+            float kid = kmax > 0.0f ? 127.0f / kmax : 0.0f;
+            int dot = 0;
+            for (int d = 0; d < HD; ++d) dot += qq[d] * rne_clamp(kr[d] * kid, -127, 127);
+            float ksj = kmax > 0.0f ? kmax / 127.0f : 0.0f;
+            s[j] = qs * scale * ((float)dot * ksj + 0.0f);
+            m = fmaxf(m, s[j]);
+        }
+        float sum = 0.0f;
+        for (int j = 0; j <= t_cur; ++j) {
+            s[j] = expf(s[j] - m);
+            sum += s[j];
+        }
+        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+        for (int j = 0; j <= t_cur; ++j) {
+            float p = s[j] / sum;
+            const float *vr = vcache + kv_row(table, block_size, j) * kvd + kvh * HD;
+            for (int d = 0; d < HD; ++d) o[d] += p * vr[d];
+        }
+    }
+    free(s);
+}
+
 /* Prefill attention of n_tok new rows at absolute positions pos0+qi over cache
  * keys 0..=pos0+qi: the semantics of attn_prefill_body,
  * 03-llm-engine/kernels/llm.cu:3674-3804, evaluated with the cpu.rs per-row
  * softmax (max, exp/sum, normalise, PV) instead of the kernel's online form.
- * kind 0: fp32 cache.  kind 1: int8 cache, dequant-exact (K^, V^ as above).
+ * kind 0: fp32 cache, fp32 scores (KIND 0).  kind 1: int8 cache, dequant-exact (K^, V^ as above).
+ * kind 2: int8 cache with the reference kernel's own score arithmetic (its KIND 1: q quantised per (row, head),
+ * integer dots, llm.cu:3700-3716,3774-3782 -- the same arithmetic as its decode kernel).
+ * kind 3: fp32 cache, K quantised on the fly (the reference's opt-in KIND 2, attn_prefill_dp4a).
  * q rows are read at qkv[qi*qkv_stride + h*64 ..], out at out[qi*out_stride + h*64 ..]. */
 void orc_prefill(float *out, const float *qkv, const float *kcache, const float *vcache,
                  const int8_t *kq, const int8_t *vq, const float *ks, const float *vs,
@@ -653,10 +703,13 @@ void orc_prefill(float *out, const float *qkv, const float *kcache, const float 
         if (kind == 0)
             orc_gqa_decode_f32(out + (size_t)qi * out_stride, qkv + (size_t)qi * qkv_stride, kcache,
                                vcache, pos0 + qi, n_head, n_kv_head, HD, table, block_size);
+        else if (kind == 3)
+            orc_gqa_row_dp4a(out + (size_t)qi * out_stride, qkv + (size_t)qi * qkv_stride, kcache, vcache,
+                             pos0 + qi, n_head, n_kv_head, table, block_size);
         else
             orc_gqa_decode_q8(out + (size_t)qi * out_stride, qkv + (size_t)qi * qkv_stride, kq, vq,
                               ks, vs, kb, vb, pos0 + qi, n_head, n_kv_head, HD, table, block_size,
-                              0);
+                              kind == 2 ? 1 : 0);
     }
 }
 

@@ -44,7 +44,7 @@ class RefModule:
             self._fn[sym] = f
         return self._fn[sym]
 
-    def launch(self, sym: str, grid, block, args, stream=None):
+    def launch(self, sym: str, grid, block, args, stream=None, smem: int = 0):
         """args: torch CUDA tensors (passed as device pointers), Python ints (int32) or floats (f32)."""
         import torch
         store, ptrs = [], []
@@ -62,6 +62,6 @@ class RefModule:
         b = tuple(block) + (1,) * (3 - len(block))
         s = stream if stream is not None else torch.cuda.current_stream()
         rc = self.cu.cuLaunchKernel(self.function(sym), *[C.c_uint(x) for x in g],
-                                    *[C.c_uint(x) for x in b], C.c_uint(0),
+                                    *[C.c_uint(x) for x in b], C.c_uint(smem),
                                     C.c_void_p(s.cuda_stream), arr, None)
         self._check(rc, f"cuLaunchKernel({sym})")

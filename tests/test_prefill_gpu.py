@@ -2,15 +2,20 @@
 
 Operands go through the tensor cores in bf16, so the gate is the floating-point parity bar:
 max-abs 2e-2, norm-wise mean-rel 5e-3 against the oracle's fp32 result -- cpu.rs attention
-over the fp32 cache, and attention over the dequantised codes for the int8 cache, with the
-codes themselves produced by the (bit-exact) quantize-on-write kernel.
+over the fp32 cache; over the int8 cache both score modes, each against its own oracle on the same
+(bit-exact) codes: the reference kernel's int8 scores (default, attn_prefill_q8's arithmetic) and
+exact scores over the dequantised codes; and the reference's opt-in int8-score approximation over an
+fp32 cache (attn_prefill_dp4a).
 """
 import numpy as np
 import pytest
 import torch
 
 import oracle
+from mx230_b200 import _lib
 from mx230_b200 import llm_attention as la
+from mx230_b200._lib import check, lib, ptr
+from mx230_b200.common import stream_ptr
 from tests.conftest import assert_close
 
 pytestmark = pytest.mark.gpu
@@ -49,22 +54,40 @@ def test_prefill_matches_oracle(handle, nh, nkv, pos0, n_tok, quant, paged):
         oracle.copy_kv_row(kc, vc, rows[t], t, qd, kvd, table, bs)
         oracle.quantize_kv_row(q8, rows[t], t, qd, table, bs)
     c = la.KvCache(slots, nkv, 64, quant)
+    new = np.ascontiguousarray(rows[pos0:])
+    pg = la.Paging(i32(table), bs) if paged else None
+    okw = dict(table=table, block_size=bs)
     if quant:
         c.k.copy_(dev(q8.kq)), c.v.copy_(dev(q8.vq)), c.ks.copy_(dev(q8.ks)), c.vs.copy_(dev(q8.vs))
         c.kb.copy_(dev(q8.kb)), c.vb.copy_(dev(q8.vb))
-        want = oracle.prefill(rows[pos0:], pos0, n_tok, nh, nkv, stride, out_stride, cache=q8, table=table,
-                              block_size=bs)
+        modes = [(_lib.Q8_SCORE_REF, oracle.prefill(new, pos0, n_tok, nh, nkv, stride, out_stride, cache=q8, mode=1, **okw)),
+                 (_lib.Q8_SCORE_EXACT, oracle.prefill(new, pos0, n_tok, nh, nkv, stride, out_stride, cache=q8, mode=0, **okw))]
     else:
         c.k.copy_(dev(kc)), c.v.copy_(dev(vc))
-        want = oracle.prefill(rows[pos0:], pos0, n_tok, nh, nkv, stride, out_stride, kcache=kc, vcache=vc,
-                              table=table, block_size=bs)
-    out = torch.zeros(n_tok, out_stride, device="cuda")
-    pg = la.Paging(i32(table), bs) if paged else None
-    la.attn_prefill(handle, out, dev(rows[pos0:]), c, pos0, n_tok, nh, nkv, stride, out_stride, pg)
-    handle.check_status()
-    got = out.cpu().numpy()
-    assert_close(got[:, :qd], want[:, :qd], "prefill")
-    assert (got[:, qd:] == 0).all()  # the padding columns of the output rows are not touched
+        modes = [(_lib.Q8_SCORE_REF, oracle.prefill(new, pos0, n_tok, nh, nkv, stride, out_stride, kcache=kc, vcache=vc, **okw))]
+    try:
+        for mode, want in modes:
+            handle.set_option(_lib.OPT_Q8_SCORE_MODE, mode)
+            out = torch.zeros(n_tok, out_stride, device="cuda")
+            la.attn_prefill(handle, out, dev(new), c, pos0, n_tok, nh, nkv, stride, out_stride, pg)
+            handle.check_status()
+            got = out.cpu().numpy()
+            assert_close(got[:, :qd], want[:, :qd], f"prefill, score mode {mode}")
+            assert (got[:, qd:] == 0).all()  # the padding columns of the output rows are not touched
+    finally:
+        handle.set_option(_lib.OPT_Q8_SCORE_MODE, _lib.Q8_SCORE_REF)
+    if not quant:
+        # attn_prefill_dp4a[_paged]: int8 scores with K quantised on the fly, over the same fp32 cache
+        want = oracle.prefill(new, pos0, n_tok, nh, nkv, stride, out_stride, kcache=kc, vcache=vc, mode=1, **okw)
+        out = torch.zeros(n_tok, out_stride, device="cuda")
+        args = [handle._h, stream_ptr(None), ptr(out), ptr(dev(new)), ptr(c.k), ptr(c.v), pos0, n_tok, nh, nkv, stride,
+                out_stride]
+        if paged:
+            check(lib().mx230_attn_prefill_dp4a_paged(*args, ptr(pg.table_dev), bs))
+        else:
+            check(lib().mx230_attn_prefill_dp4a(*args))
+        handle.check_status()
+        assert_close(out.cpu().numpy()[:, :qd], want[:, :qd], "prefill dp4a")
 
 
 def test_prefill_step_writes_cache_then_attends(handle):
@@ -86,14 +109,9 @@ def test_prefill_step_writes_cache_then_attends(handle):
     for t in range(pos0 + n_tok):
         oracle.quantize_kv_row(w, roped[t], t, qd)
     assert np.array_equal(c.k.cpu().numpy(), w.kq) and np.array_equal(c.v.cpu().numpy(), w.vq)
-    want = oracle.prefill(roped[pos0:], pos0, n_tok, nh, nkv, stride, qd, cache=w)
+    want = oracle.prefill(roped[pos0:], pos0, n_tok, nh, nkv, stride, qd, cache=w, mode=1)
     assert_close(out.cpu().numpy(), want, "prefill step")
-    # the last prefill row equals a decode step at the same position (exact-score mode)
-    from mx230_b200 import _lib
-    handle.set_option(_lib.OPT_Q8_SCORE_MODE, _lib.Q8_SCORE_EXACT)
-    try:
-        o1 = torch.zeros(qd, device="cuda")
-        la.attn_decode(handle, o1, d[pos0 + n_tok - 1], c, pos0 + n_tok - 1, nh, nkv, 64)
-    finally:
-        handle.set_option(_lib.OPT_Q8_SCORE_MODE, _lib.Q8_SCORE_REF)
+    # the last prefill row equals a decode step at the same position: both use the reference's int8 score arithmetic
+    o1 = torch.zeros(qd, device="cuda")
+    la.attn_decode(handle, o1, d[pos0 + n_tok - 1], c, pos0 + n_tok - 1, nh, nkv, 64)
     assert_close(out[-1].cpu().numpy(), o1.cpu().numpy(), "prefill row vs decode")

@@ -65,7 +65,8 @@ def test_reused_prefix_gives_the_cold_result(handle, quant):
         oracle.rope_qkv_row(rows[t], t, NH, NKV, 64, THETA)
         oracle.copy_kv_row(kc, vc, rows[t], t, QD, KVD)
         oracle.quantize_kv_row(q8, rows[t], t, QD)
-    kw = dict(cache=q8) if quant else dict(kcache=kc, vcache=vc)
+    # (over the int8 cache the default score mode is the reference kernel's int8 arithmetic: oracle mode 1)
+    kw = dict(cache=q8, mode=1) if quant else dict(kcache=kc, vcache=vc)
     want = oracle.prefill(rows[32:], 32, len(b) - 32, NH, NKV, STRIDE, QD, **kw)
     assert_close(out_b, want, "prefix-cached prefill vs oracle")
 
