@@ -301,7 +301,27 @@ def multi_gpu_bench(h, torch, dist, la, fa, rank, world, local, steps):
                       "exchange_bytes_per_rank": plan.bytes_per_rank(), "scaling": "strong",
                       "workload": "int8-KV GQA decode 32q/4kv ctx 131072 x 8 sequences, keys split over ranks, "
                                   "ncclAllGather of the partial triples, merge on every rank"}
-    del caches, dec
+    # the same step with the exchange and the merge in one kernel over peer memory (no collective call per step),
+    # host-launched like the line above and replayed from a CUDA graph of 16 steps (the reference captures its
+    # decode step in a graph, 03-llm-engine/src/gpu.rs:4024-4054; the exchange's step numbers live in device memory)
+    fdec = SplitKvDecoder(h, plan, rank, device=f"cuda:{local}", fused=True)
+    try:
+        ms_f = timed(lambda i=0: fdec.step(q, caches[i % 2], nkv, span, nh * 64), max(steps, 10))
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(16):
+                fdec.step(q, caches[i % 2], nkv, span, nh * 64)
+        ms_g = timed(lambda i=0: g.replay(), 8) / 16
+        h.check_status()
+    finally:
+        fdec.close()
+    out["splitkv_fused"] = {"ms_per_step": ms_f, "aggregate_gbs": total / ms_f / 1e6, "scaling": "strong",
+                            "ms_per_step_graph": ms_g, "aggregate_gbs_graph": total / ms_g / 1e6,
+                            "workload": "the same step; triples stored to every rank's exchange region over NVLink, "
+                                        "step flags, merge: one kernel after the partial-attention kernel"}
+    del caches, dec, fdec
     # ---- 32768-token forward, heads over ranks
     n, heads = 32768, 8
     lo, hi = shard_range(heads, rank, world)
@@ -604,7 +624,7 @@ def run_splitkv(args):
         c.k.random_(-128, 128), c.v.random_(-128, 128), c.ks.uniform_(0.01, 0.03), c.vs.uniform_(0.01, 0.03)
         caches.append(c)
     q = torch.randn(n_seq, nh * 64, device="cuda")
-    dec = SplitKvDecoder(h, plan, rank)
+    dec = SplitKvDecoder(h, plan, rank, fused=bool(args.fused))
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     steps, warm = max(1, args.steps), max(3, args.warmup)
     for i in range(warm):
@@ -623,10 +643,11 @@ def run_splitkv(args):
     h.check_status()
     total_bytes = n_seq * ctx * nkv * (128 + 16)
     if rank == 0:
-        print(json.dumps({"case": "splitkv", "n_gpus": world, "ms_per_step": float(ms), "steps": steps,
+        print(json.dumps({"case": "splitkv", "fused_exchange": bool(args.fused), "n_gpus": world, "ms_per_step": float(ms), "steps": steps,
                           "kv_bytes_total": total_bytes, "aggregate_gbs": total_bytes / float(ms) / 1e6,
                           "scaling": "strong", "exchange_bytes_per_rank": plan.bytes_per_rank(),
                           "config": {"workload": "int8-KV GQA decode 32q/4kv ctx 131072 x 8 sequences, keys split over ranks"}}))
+    dec.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -800,6 +821,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--fused", type=int, default=0, help="--case splitkv: 1 = exchange + merge in one kernel over peer memory")
     ap.add_argument("--case", default=None, choices=["fwd", "bwd", "bwd_two_pass", "decode_c4", "decode_long", "splitkv", "configs", "proj"],
                     help="fwd|bwd|decode_*: profiling aid, runs one kernel family a few times and exits; "
                          "splitkv: long-context decode with keys split over the ranks (torchrun for N > 1); "

@@ -331,6 +331,51 @@ int mx230_merge_partials(mx230_handle *h, void *stream, float *out, const float 
 int mx230_merge_partials_packed(mx230_handle *h, void *stream, float *out, const float *gathered,
                                 int parts, int rows, int head_dim);
 
+/* Split-KV exchange and merge in ONE kernel over peer memory (no reference counterpart: the reference
+ * runs on one device).  Each rank (one process, one GPU) creates a communicator for `rows` =
+ * n_seq * n_head rows; the library allocates an exchange region with cudaMalloc and exports it as a
+ * 64-byte CUDA IPC handle, which the host passes to the other ranks by its own transport
+ * (`_export` on the owner, `_import` on every other rank; `_attach` instead of `_import` for a region
+ * whose device address is already valid in this process).  After mx230_attn_decode_partial has
+ * written the rank's packed triples [m | l | acc] to `local`, mx230_splitkv_exchange_merge launches
+ * one kernel that stores them into every rank's region over NVLink, publishes a step number, waits
+ * (bounded by MX230_OPT_WAIT_LIMIT; expiry -> device status, the output is then not written) for the
+ * other ranks' step numbers and merges all triples into out[rows][64].  Every rank must call it the
+ * same number of times; ranks must not share a GPU (their kernels wait on one another).  Teardown in
+ * two phases with a host barrier between them: every rank calls `_disconnect` (synchronises the
+ * device, closes its imports), then, once all have, `_destroy` (frees its own region). */
+typedef struct mx230_splitkv_comm mx230_splitkv_comm;
+int mx230_splitkv_comm_create(mx230_handle *h, int rank, int world, int rows, int head_dim,
+                              mx230_splitkv_comm **out);
+int mx230_splitkv_comm_export(mx230_splitkv_comm *c, unsigned char *handle64);
+int mx230_splitkv_comm_import(mx230_splitkv_comm *c, int peer, const unsigned char *handle64);
+int mx230_splitkv_comm_region(mx230_splitkv_comm *c, void **base, size_t *bytes);
+int mx230_splitkv_comm_attach(mx230_splitkv_comm *c, int peer, void *region);
+int mx230_splitkv_exchange_merge(mx230_splitkv_comm *c, void *stream, float *out, const float *local);
+/* The same step with the stores issued by the partial-attention kernel itself: the CTA that finishes a
+ * (sequence, KV head) group stores its triples into every rank's region at once (arguments as
+ * mx230_attn_decode_partial, n_seq * n_head = the communicator's rows; an empty range t1 <= t0 stores the
+ * neutral triple), and mx230_splitkv_wait_merge, on the same stream, waits for all ranks' triples and merges
+ * them into out[rows][64].  One _partial_push and one _wait_merge make a step. */
+int mx230_attn_decode_partial_push(mx230_handle *h, void *stream, mx230_splitkv_comm *c, const float *qkv,
+                                   const float *kcache, const float *vcache, const int8_t *kq,
+                                   const int8_t *vq, const float *ks, const float *vs, const float *kb,
+                                   const float *vb, int t0, int t1, int n_seq, int n_head, int n_kv_head,
+                                   int head_dim, long long seq_rows, int qkv_stride);
+int mx230_splitkv_wait_merge(mx230_splitkv_comm *c, void *stream, float *out);
+/* The whole step in ONE kernel: the CTA that finishes a (sequence, KV head) group stores the group's triples
+ * into every other rank's region, waits (bounded, as above) for their triples of the same rows and writes the
+ * merged, normalised rows to out[rows][64].  The three forms of a step (_exchange_merge, _partial_push +
+ * _wait_merge, _decode_splitkv) give bit-identical results and may be mixed from step to step, as long as every
+ * rank makes one step per step. */
+int mx230_attn_decode_splitkv(mx230_handle *h, void *stream, mx230_splitkv_comm *c, float *out,
+                              const float *qkv, const float *kcache, const float *vcache, const int8_t *kq,
+                              const int8_t *vq, const float *ks, const float *vs, const float *kb,
+                              const float *vb, int t0, int t1, int n_seq, int n_head, int n_kv_head,
+                              int head_dim, long long seq_rows, int qkv_stride);
+int mx230_splitkv_comm_disconnect(mx230_splitkv_comm *c);
+void mx230_splitkv_comm_destroy(mx230_splitkv_comm *c);
+
 /* prefill attention of n_tok new rows at absolute positions pos0+qi over cache keys
  * 0..=pos0+qi: attn_prefill / _q8 / _paged / _q8_paged / _dp4a / _dp4a_paged
  * (llm.cu:3806-3872).  q row qi of head h is read at qkv[qi*qkv_stride + h*64], the result

@@ -125,6 +125,20 @@ struct mx230_device_guard {
     }
 };
 
+// Split-KV exchange over peer memory (splitkv.cu; the partial-attention kernels of decode.cu push into it).
+// A region holds, per step parity and source rank, rows*66 words {value, step number} in the packed order
+// [m (rows) | l (rows) | acc (rows x 64)], then one step number per 16-row slice.
+constexpr int MX230_SPLITKV_MAX_WORLD = 16;
+struct mx230_splitkv_comm {
+    mx230_handle *h;
+    int rank, world, rows, slices;
+    size_t part_words, step_offset_words, region_bytes;
+    uint2 *region[MX230_SPLITKV_MAX_WORLD];   // [rank] is the own allocation, the others are peers' regions mapped here
+    bool imported[MX230_SPLITKV_MAX_WORLD];   // opened from an IPC handle (closed again on disconnect)
+    uint2 **region_dev;                       // the same table in device memory, for kernels that take it by pointer
+    float *local;                             // packed triples of this rank, kept beside what is pushed
+};
+
 // 2-D/3-D bf16 tensor map over [outer][rows][64] with a {64, box_rows, 1} box and
 // 128-byte swizzle (one 64-element bf16 row is exactly one 128-byte swizzle span).
 int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
@@ -549,6 +563,30 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
+}
+
+// ---- {value, step} words of the split-KV exchange: 8-byte accesses are single-copy atomic, so a reader that
+// finds the current step number in a word also has that word's value ----
+__device__ __forceinline__ void st_words2(uint2 *p, float a, float b, unsigned step) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(p), "r"(__float_as_uint(a)), "r"(step),
+                 "r"(__float_as_uint(b))
+                 : "memory");
+}
+__device__ __forceinline__ void st_word(uint2 *p, float a, unsigned step) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(a)), "r"(step) : "memory");
+}
+__device__ __forceinline__ uint4 ld_words2(const uint2 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 ld_word(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
 }
 
 }  // namespace mx

@@ -46,6 +46,14 @@ struct DecodeParams {
     int max_keys;        // capacity of one sequence (slab rows, or table entries x block) when positions come from the device; 0 = unknown
     int n_head, n_kv_head, group, head_groups;
     int score_mode;
+    // partial mode with a push: the finished triples also go, as {value, step} words, into slot `push_rank` of every
+    // rank's split-KV exchange region (table of `push_world` region bases in device memory)
+    uint2 *const *push_regions;
+    unsigned *push_steps;        // [rows] the number of the last finished exchange step of every row (own region)
+    float *push_out;             // [rows][64]: the finishing CTA also waits for the other ranks' triples and merges; else null
+    int *push_status;            // where a wait that ran out is recorded
+    size_t push_part_words;      // rows * 66
+    int push_rank, push_world, push_rows;
 };
 
 __device__ __forceinline__ float warp_max_f(float v) {
@@ -132,11 +140,105 @@ __device__ void merge_and_store(const DecodeParams &P, int s, int head0, int gc,
                 P.fin_m[o] = mm;
                 P.fin_l[o] = ll;
             }
+            if (P.push_regions) {
+                // the row's step number: read by the row's 16 threads here, advanced (by the kernel that merges the row)
+                // only after a CTA-wide barrier
+                const unsigned step = *(const volatile unsigned *)(P.push_steps + o) + 1u;
+                const size_t parity = (size_t)(step & 1u) * P.push_world * P.push_part_words;
+                const size_t acc_word = 2 * (size_t)P.push_rows + o * 64 + d4;
+                // every other rank first, starting at a different peer on every rank; the own region last, and not
+                // at all when this CTA merges the row itself (it has the own triple in registers)
+                for (int i = 0; i < P.push_world - (P.push_out ? 1 : 0); ++i) {
+                    uint2 *dst = P.push_regions[(P.push_rank + 1 + i) % P.push_world] + parity + P.push_rank * P.push_part_words;
+                    mx::st_words2(dst + acc_word, a.x, a.y, step);
+                    mx::st_words2(dst + acc_word + 2, a.z, a.w, step);
+                    if (d4 == 0) mx::st_word(dst + o, mm, step);
+                    if (d4 == 4) mx::st_word(dst + P.push_rows + o, ll, step);
+                }
+                if (P.push_out) {
+                    // wait (bounded) for the other ranks' triples of this row and merge all of them in rank order
+                    const uint2 *gsrc = P.push_regions[P.push_rank] + parity;
+                    const long long t_start = clock64();
+                    const long long limit = *(const volatile long long *)(P.push_status + mx::STATUS_LIMIT_WORD);
+                    unsigned polls = 0;
+                    bool ok = true;
+                    auto give_up = [&]() {
+                        if ((++polls & 31u) != 0u) return false;
+                        if (clock64() - t_start > limit) {
+                            atomicExch(P.push_status, mx::STATUS_WAIT_TIMEOUT);
+                            return true;
+                        }
+                        return false;
+                    };
+                    auto wait_word = [&](const uint2 *p) {
+                        uint2 w = mx::ld_word(p);
+                        while (w.y != step) {
+                            if (give_up()) {
+                                ok = false;
+                                break;
+                            }
+                            w = mx::ld_word(p);
+                        }
+                        return w;
+                    };
+                    auto wait_words2 = [&](const uint2 *p) {
+                        uint4 v = mx::ld_words2(p);
+                        while (v.y != step || v.w != step) {
+                            if (give_up()) {
+                                ok = false;
+                                break;
+                            }
+                            v = mx::ld_words2(p);
+                        }
+                        return v;
+                    };
+                    float mp[MX230_SPLITKV_MAX_WORLD];
+                    float gm = -CUDART_INF_F;
+#pragma unroll
+                    for (int p = 0; p < MX230_SPLITKV_MAX_WORLD; ++p) {
+                        mp[p] = -CUDART_INF_F;
+                        if (p < P.push_world && ok) {
+                            mp[p] = p == P.push_rank ? mm : __uint_as_float(wait_word(gsrc + (size_t)p * P.push_part_words + o).x);
+                            gm = fmaxf(gm, mp[p]);
+                        }
+                    }
+                    float gl = 0.0f;
+                    float4 ga = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int p = 0; p < MX230_SPLITKV_MAX_WORLD; ++p) {
+                        if (p < P.push_world && ok) {
+                            float lp = ll;
+                            float4 v = a;
+                            if (p != P.push_rank) {
+                                const uint2 *gp = gsrc + (size_t)p * P.push_part_words;
+                                lp = __uint_as_float(wait_word(gp + P.push_rows + o).x);
+                                const uint4 v0 = wait_words2(gp + acc_word);
+                                const uint4 v1 = wait_words2(gp + acc_word + 2);
+                                v = make_float4(__uint_as_float(v0.x), __uint_as_float(v0.z), __uint_as_float(v1.x),
+                                                __uint_as_float(v1.z));
+                            }
+                            const float w = (mp[p] == -CUDART_INF_F) ? 0.0f : __expf(mp[p] - gm);
+                            gl += lp * w;
+                            ga.x += v.x * w, ga.y += v.y * w, ga.z += v.z * w, ga.w += v.w * w;
+                        }
+                    }
+                    if (ok) {   // after a wait that ran out the row is not written
+                        const float inv = 1.0f / gl;
+                        *(float4 *)(P.push_out + o * 64 + d4) = make_float4(ga.x * inv, ga.y * inv, ga.z * inv, ga.w * inv);
+                    }
+                }
+            }
         } else {
             float inv = 1.0f / ll;
             *(float4 *)(P.out + (size_t)s * P.out_stride + h * 64 + d4) =
                 make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
         }
+    }
+    if (P.push_out) {
+        // this CTA finished the step of its rows: their step numbers move on (also after a wait that ran out, so
+        // that the ranks stay on the same step count)
+        __syncthreads();
+        if (threadIdx.x < gc) P.push_steps[(size_t)s * P.n_head + head0 + threadIdx.x] += 1u;
     }
 }
 
@@ -1195,7 +1297,7 @@ int launch_g(mx230_handle *h, cudaStream_t st, const DecodeParams &P, dim3 grid,
 // `known_keys`: host-known upper bound of keys per sequence (<= 0 when the position
 // lives on the device); only steers how many key splits are launched.
 int launch_decode(mx230_handle *h, void *stream, DecodeParams P, int n_seq, int head_dim,
-                  long long known_keys) {
+                  long long known_keys, mx230_splitkv_comm *comm = nullptr) {
     MX_REQUIRE(h && P.qkv, MX230_ERR_INVALID_ARG, "attn_decode: null argument");
     MX_REQUIRE(head_dim == 64, MX230_ERR_UNSUPPORTED, "attn_decode: head_dim %d unsupported (must be 64)",
                head_dim);
@@ -1235,6 +1337,12 @@ int launch_decode(mx230_handle *h, void *stream, DecodeParams P, int n_seq, int 
     // (rounded down so that the whole grid is resident at once: a partial second wave would
     // nearly double the time)
     long long base_ctas = (long long)n_seq * gy;
+    // One-kernel split-KV step: the CTA that finishes a group waits there for the other ranks.  At most one CTA per
+    // group ever waits, so with fewer groups than SMs a slot always stays free for the CTAs that still have keys to
+    // stream, on every rank, and no rank's waiting CTAs can keep another rank's pushes from happening.  With more
+    // groups the wait moves into a kernel of its own behind this one.
+    float *merge_after = nullptr;
+    if (P.push_out && base_ctas >= h->sm_count) merge_after = P.push_out, P.push_out = nullptr;
     int want = (int)(((q8 ? 2LL : 3LL) * h->sm_count) / base_ctas);
     int n_splits;
     if (h->decode_chunk > 0 && known_keys > 0) {
@@ -1267,11 +1375,14 @@ int launch_decode(mx230_handle *h, void *stream, DecodeParams P, int n_seq, int 
     dim3 grid(n_splits, gy, n_seq);
     cudaStream_t st = (cudaStream_t)stream;
     int g = P.group > 8 ? 8 : P.group;
-    if (g == 1) return launch_g<1>(h, st, P, grid, q8);
-    if (g == 2) return launch_g<2>(h, st, P, grid, q8);
-    if (g <= 4) return launch_g<4>(h, st, P, grid, q8);
-    if (g <= 7) return launch_g<7>(h, st, P, grid, q8);
-    return launch_g<8>(h, st, P, grid, q8);
+    int rc;
+    if (g == 1) rc = launch_g<1>(h, st, P, grid, q8);
+    else if (g == 2) rc = launch_g<2>(h, st, P, grid, q8);
+    else if (g <= 4) rc = launch_g<4>(h, st, P, grid, q8);
+    else if (g <= 7) rc = launch_g<7>(h, st, P, grid, q8);
+    else rc = launch_g<8>(h, st, P, grid, q8);
+    if (rc == MX230_OK && merge_after) rc = mx230_splitkv_wait_merge(comm, stream, merge_after);
+    return rc;
 }
 
 DecodeParams base_params(float *out, int out_stride, const float *qkv, int qkv_stride, int n_head,
@@ -1431,6 +1542,55 @@ extern "C" int mx230_attn_decode_partial(mx230_handle *h, void *stream, float *p
     P.fin_m = part_m, P.fin_l = part_l, P.fin_acc = part_acc;
     P.range_mode = 1, P.t0 = t0, P.t1 = t1, P.seq_rows = seq_rows;
     return launch_decode(h, stream, P, n_seq, head_dim, (long long)t1 - t0);
+}
+
+int mx230_splitkv_push_neutral(mx230_splitkv_comm *c, void *stream, float *out);   // splitkv.cu
+
+static int decode_push(mx230_handle *h, void *stream, mx230_splitkv_comm *c, float *out, const float *qkv,
+                       const float *kcache, const float *vcache, const int8_t *kq, const int8_t *vq, const float *ks,
+                       const float *vs, const float *kb, const float *vb, int t0, int t1, int n_seq, int n_head,
+                       int n_kv_head, int head_dim, long long seq_rows, int qkv_stride) {
+    MX_REQUIRE(h && c, MX230_ERR_INVALID_ARG, "split-KV decode: null argument");
+    MX_REQUIRE(c->h == h, MX230_ERR_INVALID_ARG, "split-KV decode: the communicator belongs to another handle");
+    MX_REQUIRE((long long)n_seq * n_head == c->rows, MX230_ERR_INVALID_ARG,
+               "split-KV decode: n_seq * n_head = %lld, the communicator was made for %d rows",
+               (long long)n_seq * n_head, c->rows);
+    for (int p = 0; p < c->world; ++p)
+        MX_REQUIRE(c->region[p], MX230_ERR_INVALID_ARG, "split-KV decode: rank %d is not connected", p);
+    if (t1 <= t0) return mx230_splitkv_push_neutral(c, stream, out);   // an empty key range contributes (-inf, 0, 0)
+    MX_REQUIRE(seq_rows > 0 || n_seq == 1, MX230_ERR_INVALID_ARG, "split-KV decode: bad seq_rows");
+    DecodeParams P = base_params(nullptr, 0, qkv, qkv_stride, n_head, n_kv_head);
+    P.kcache = kcache, P.vcache = vcache;
+    set_q8(P, Q8_ARGS);
+    P.fin_m = c->local, P.fin_l = c->local + c->rows, P.fin_acc = c->local + 2 * (size_t)c->rows;
+    P.range_mode = 1, P.t0 = t0, P.t1 = t1, P.seq_rows = seq_rows;
+    P.push_regions = c->region_dev;
+    P.push_steps = (unsigned *)(c->region[c->rank] + c->step_offset_words);
+    P.push_out = out;
+    P.push_status = h->status_dev;
+    P.push_part_words = c->part_words;
+    P.push_rank = c->rank, P.push_world = c->world, P.push_rows = c->rows;
+    return launch_decode(h, stream, P, n_seq, head_dim, (long long)t1 - t0, c);
+}
+
+extern "C" int mx230_attn_decode_partial_push(mx230_handle *h, void *stream, mx230_splitkv_comm *c, const float *qkv,
+                                              const float *kcache, const float *vcache, const int8_t *kq,
+                                              const int8_t *vq, const float *ks, const float *vs, const float *kb,
+                                              const float *vb, int t0, int t1, int n_seq, int n_head, int n_kv_head,
+                                              int head_dim, long long seq_rows, int qkv_stride) {
+    return decode_push(h, stream, c, nullptr, qkv, kcache, vcache, Q8_ARGS, t0, t1, n_seq, n_head, n_kv_head, head_dim,
+                       seq_rows, qkv_stride);
+}
+
+extern "C" int mx230_attn_decode_splitkv(mx230_handle *h, void *stream, mx230_splitkv_comm *c, float *out,
+                                         const float *qkv, const float *kcache, const float *vcache, const int8_t *kq,
+                                         const int8_t *vq, const float *ks, const float *vs, const float *kb,
+                                         const float *vb, int t0, int t1, int n_seq, int n_head, int n_kv_head,
+                                         int head_dim, long long seq_rows, int qkv_stride) {
+    MX_REQUIRE(out && (((uintptr_t)out) & 15) == 0, MX230_ERR_INVALID_ARG,
+               "attn_decode_splitkv: out must be a 16-byte aligned device pointer");
+    return decode_push(h, stream, c, out, qkv, kcache, vcache, Q8_ARGS, t0, t1, n_seq, n_head, n_kv_head, head_dim,
+                       seq_rows, qkv_stride);
 }
 
 extern "C" int mx230_merge_partials(mx230_handle *h, void *stream, float *out, const float *m,

@@ -230,6 +230,22 @@ def attn_decode_partial(h: Handle, part_m, part_l, part_acc, qkv, c: KvCache, t0
                                           n_head, n_kv_head, head_dim, seq_rows, qkv_stride))
 
 
+def attn_decode_partial_push(h: Handle, comm, qkv, c: KvCache, t0, t1, n_seq, n_head, n_kv_head, head_dim, seq_rows,
+                             qkv_stride, stream=None):
+    """attn_decode_partial whose finishing CTAs store the triples into every rank's split-KV exchange region
+    (`comm`: the mx230_splitkv_comm of `multi_gpu.PeerExchange`)."""
+    check(lib().mx230_attn_decode_partial_push(h._h, stream_ptr(stream), comm, ptr(qkv), *_cache_args(c), t0, t1,
+                                               n_seq, n_head, n_kv_head, head_dim, seq_rows, qkv_stride))
+
+
+def attn_decode_splitkv(h: Handle, comm, out, qkv, c: KvCache, t0, t1, n_seq, n_head, n_kv_head, head_dim, seq_rows,
+                        qkv_stride, stream=None):
+    """A whole split-KV step in one kernel: partial attention over keys [t0, t1), stores to every other rank's
+    exchange region, wait for their triples, merged rows to out[n_seq * n_head][64]."""
+    check(lib().mx230_attn_decode_splitkv(h._h, stream_ptr(stream), comm, ptr(out), ptr(qkv), *_cache_args(c), t0, t1,
+                                          n_seq, n_head, n_kv_head, head_dim, seq_rows, qkv_stride))
+
+
 def merge_partials(h: Handle, out, m, l, acc, parts, rows, head_dim=64, stream=None):
     check(lib().mx230_merge_partials(h._h, stream_ptr(stream), ptr(out), ptr(m), ptr(l), ptr(acc),
                                      parts, rows, head_dim))

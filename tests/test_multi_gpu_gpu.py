@@ -1,7 +1,9 @@
 """Two GPUs, one process each, NCCL: split-KV decode (partial attention on each rank's key
 range, one all-gather, log-sum-exp merge) and (batch, head) sharding of the flash forward.
 Skipped on a box with fewer than two GPUs.  NVLS is switched off for these short-lived
-child processes; the kernels use no peer memory at all."""
+child processes.  The same decode step is then repeated with the all-gather and the merge fused into
+one kernel over peer memory (plain peer stores and flags, no multimem): its output must equal the
+NCCL path's bit for bit, since both merge the same triples in the same order."""
 import os
 import socket
 
@@ -70,6 +72,19 @@ def _worker(rank, world, port, ctx, n_seq, nh, nkv, ret):
             out = dec.step(q_dev, c, nkv, span, nh * 64)
         torch.cuda.synchronize()
         h.check_status()
+        # the same step with exchange + merge in one kernel over peer memory; three steps walk both
+        # halves of the double-buffered exchange region
+        fused_equal = True
+        for how in ("exchange", "push", "one"):   # stores by the merge kernel / by the attention kernel / all in one kernel
+            fdec = SplitKvDecoder(h, plan, rank, device=dev, fused=how)
+            try:
+                for _ in range(3):
+                    fout = fdec.step(q_dev, c, nkv, span, nh * 64)
+                torch.cuda.synchronize()
+                h.check_status()
+                fused_equal = fused_equal and bool(torch.equal(fout, out))
+            finally:
+                fdec.close()
         want = oracle.gqa_decode_batched(qs, [ctx - 1] * n_seq, nh, nkv, cache=q8, seq_rows=ctx, mode=0)
         got = out.cpu().numpy().reshape(n_seq, nh * 64)
         err_dec = float(np.abs(got - want).max())
@@ -89,7 +104,7 @@ def _worker(rank, world, port, ctx, n_seq, nh, nkv, ret):
         chk = torch.tensor([float(out.double().sum())], device=dev)
         both = [torch.zeros_like(chk) for _ in range(world)]
         dist.all_gather(both, chk)
-        ret[rank] = (err_dec, rel_dec, err_fwd, [float(b) for b in both], (lo, hi))
+        ret[rank] = (err_dec, rel_dec, err_fwd, [float(b) for b in both], (lo, hi), fused_equal)
         dist.barrier()   # success path only: a rank that raised must not enter a collective its peer is not in
     finally:
         dist.destroy_process_group()
@@ -120,7 +135,8 @@ def test_split_kv_decode_and_sharded_forward_two_gpus(ctx):
     assert codes == [0] * world, f"rank exit codes {codes}"
     assert sorted(ret.keys()) == [0, 1]
     for r in range(world):
-        err_dec, rel_dec, err_fwd, sums, _ = ret[r]
+        err_dec, rel_dec, err_fwd, sums, _, fused_equal = ret[r]
+        assert fused_equal, f"rank {r}: fused exchange+merge differs from all-gather + merge"
         assert err_dec < TOL["max_abs"] and rel_dec < TOL["mean_rel"], (r, err_dec, rel_dec)
         assert err_fwd < TOL["max_abs"], (r, err_fwd)
         assert abs(sums[0] - sums[1]) <= 1e-6 * max(1.0, abs(sums[0]))
