@@ -53,7 +53,7 @@ DKV_FLOP = BWD_FLOP * 3.0 / 5.0
 WORKLOAD = "causal flash-attention fwd+bwd, B=4 H=12 N=4096 d=64, fp32 in/out, bf16 operands"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the tensor kernels on this exact workload, from one
 # ncu capture each (the operands, 4 x 25 MB bf16 + fp32 outputs, mostly stay in the 126 MB L2)
-NCU_DRAM_BYTES_PER_LAUNCH = {"flash_fwd_kernel": 84055808 + 19096576, "bwd_fused_kernel": 319950336 + 200664064,
+NCU_DRAM_BYTES_PER_LAUNCH = {"flash_fwd_kernel": 86776576 + 18225920, "bwd_fused_kernel": 332784384 + 209495552,
                              "bwd_dq_kernel": 106472960 + 25134592, "bwd_dkv_kernel": 108812800 + 60150016}
 NOMINAL_BF16_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
@@ -319,8 +319,10 @@ def multi_gpu_bench(h, torch, dist, la, fa, rank, world, local, steps):
         fdec.close()
     out["splitkv_fused"] = {"ms_per_step": ms_f, "aggregate_gbs": total / ms_f / 1e6, "scaling": "strong",
                             "ms_per_step_graph": ms_g, "aggregate_gbs_graph": total / ms_g / 1e6,
-                            "workload": "the same step; triples stored to every rank's exchange region over NVLink, "
-                                        "step flags, merge: one kernel after the partial-attention kernel"}
+                            "workload": "the same step as ONE kernel per rank: the CTA that finishes a (sequence, KV head) "
+                                        "group stores its triples into every other rank's exchange region over NVLink "
+                                        "({value, step} words, plain peer stores), waits (bounded) for theirs and merges; "
+                                        "no collective call per step"}
     del caches, dec, fdec
     # ---- 32768-token forward, heads over ranks
     n, heads = 32768, 8
@@ -599,20 +601,25 @@ def run_case(args):
 
 
 def run_splitkv(args):
-    """Long-context int8-KV decode (32q/4kv, ctx 131072, 8 sequences) with the
-    key axis split over the ranks: partial attention on this rank's keys, one all-gather of the
-    (m, l, acc) triples, log-sum-exp merge on every rank.  Strong scaling: the total context is fixed.
+    """Long-context int8-KV decode (32q/4kv, ctx 131072, 8 sequences) with the key axis split over the ranks
+    (strong scaling: the total context is fixed), in every form the library has, each host-launched back to
+    back and replayed from a CUDA graph of 16 steps, device time, max over ranks:
+      nccl      partial attention, all-gather of the (m, l, acc) triples, merge kernel
+      exchange  partial attention, then one kernel that stores the triples to every rank, waits and merges
+      push      the attention kernel stores the triples itself; a second kernel waits and merges
+      one       the whole step in one kernel
+    and the pieces of the first two on their own (partial kernel, all-gather, merge, exchange kernel).
     Run under torchrun for N > 1; prints one JSON line on rank 0."""
     import torch
     import torch.distributed as dist
     from mx230_b200 import llm_attention as la
     from mx230_b200.common import Handle
-    from mx230_b200.multi_gpu import SplitKvDecoder, SplitKvPlan
+    from mx230_b200.multi_gpu import SplitKvDecoder, SplitKvPlan, gather_partials
     rank, world, local = dist_env()
     torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
     nh, nkv, ctx, n_seq = 32, 4, 131072, 8
     h = Handle(local, 64 << 20)
     plan = SplitKvPlan(ctx=ctx, world=world, n_seq=n_seq, n_head=nh)
@@ -624,33 +631,60 @@ def run_splitkv(args):
         c.k.random_(-128, 128), c.v.random_(-128, 128), c.ks.uniform_(0.01, 0.03), c.vs.uniform_(0.01, 0.03)
         caches.append(c)
     q = torch.randn(n_seq, nh * 64, device="cuda")
-    dec = SplitKvDecoder(h, plan, rank, fused=bool(args.fused))
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    steps, warm = max(1, args.steps), max(3, args.warmup)
-    for i in range(warm):
-        dec.step(q, caches[i % 2], nkv, span, nh * 64)
-    if world > 1:
+    decs = {"nccl": SplitKvDecoder(h, plan, rank)}
+    for how in ("exchange", "push", "one"):
+        decs[how] = SplitKvDecoder(h, plan, rank, fused=how)
+    d0 = decs["nccl"]
+    fns = {k: (lambda i, d=d: d.step(q, caches[i % 2], nkv, span, nh * 64)) for k, d in decs.items()}
+    fns["piece_partial"] = lambda i: la.attn_decode_partial(h, d0.m, d0.l, d0.acc, q, caches[i % 2], 0, span, n_seq, nh,
+                                                            nkv, 64, span, nh * 64)
+    fns["piece_all_gather"] = lambda i: gather_partials(plan, d0.local, d0.gathered, None)
+    fns["piece_merge"] = lambda i: la.merge_partials_packed(h, d0.out, d0.gathered, world, plan.rows, 64)
+    fns["piece_exchange_merge"] = lambda i: decs["exchange"].peer.exchange_merge(decs["exchange"].out, d0.local)
+    reps = max(10, args.steps)
+
+    def max_over_ranks(us):
+        t = torch.tensor([us], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return round(float(t[0]), 2)
+
+    def timed(run, n):
         dist.barrier()
-    torch.cuda.synchronize()
-    ev[0].record()
-    for i in range(steps):
-        dec.step(q, caches[i % 2], nkv, span, nh * 64)
-    ev[1].record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([ev[0].elapsed_time(ev[1]) / steps], device="cuda")
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            run(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3
+
+    host, graph = {}, {}
+    for name, fn in fns.items():
+        for i in range(max(3, args.warmup)):
+            fn(i)
+        host[name] = max_over_ranks(timed(fn, reps) / reps)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(16):
+                fn(i)
+        for _ in range(3):
+            g.replay()
+        graph[name] = max_over_ranks(timed(lambda i: g.replay(), 10) / 160)
     h.check_status()
     total_bytes = n_seq * ctx * nkv * (128 + 16)
     if rank == 0:
-        print(json.dumps({"case": "splitkv", "fused_exchange": bool(args.fused), "n_gpus": world, "ms_per_step": float(ms), "steps": steps,
-                          "kv_bytes_total": total_bytes, "aggregate_gbs": total_bytes / float(ms) / 1e6,
-                          "scaling": "strong", "exchange_bytes_per_rank": plan.bytes_per_rank(),
+        print(json.dumps({"case": "splitkv", "n_gpus": world, "us_per_step_host_launched": host, "us_per_step_graph": graph,
+                          "kv_bytes_total": total_bytes, "aggregate_gbs_one_kernel_graph": total_bytes / graph["one"] / 1e3,
+                          "aggregate_gbs_nccl_graph": total_bytes / graph["nccl"] / 1e3, "scaling": "strong",
+                          "exchange_bytes_per_rank": plan.bytes_per_rank(),
                           "config": {"workload": "int8-KV GQA decode 32q/4kv ctx 131072 x 8 sequences, keys split over ranks"}}))
-    dec.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    for d in decs.values():
+        d.close()
+    dist.barrier()
+    dist.destroy_process_group()
     h.close()
 
 
@@ -821,7 +855,6 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--fused", type=int, default=0, help="--case splitkv: 1 = exchange + merge in one kernel over peer memory")
     ap.add_argument("--case", default=None, choices=["fwd", "bwd", "bwd_two_pass", "decode_c4", "decode_long", "splitkv", "configs", "proj"],
                     help="fwd|bwd|decode_*: profiling aid, runs one kernel family a few times and exits; "
                          "splitkv: long-context decode with keys split over the ranks (torchrun for N > 1); "

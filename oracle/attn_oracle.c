@@ -9,7 +9,7 @@
  * Parity status: the fp32 attention forward/backward follows the reference's
  * Rust CPU code and is additionally pinned on the GPU box against the
  * reference's own unmodified CUDA kernels (compiled out of tree into
- * oracle/_ref by oracle/build_ref.py).  The int8 KV quantiser has no CPU
+ * oracle/_ref by build_ref() of oracle/build.py).  The int8 KV quantiser has no CPU
  * implementation and no test vector in the reference ("parity unpinned" by
  * reference fixtures); its ground truth is the reference kernel source, and it
  * too is pinned against that kernel run on the GPU box when oracle/_ref exists.

@@ -50,7 +50,9 @@ def build_oracle(force: bool = False) -> str:
 
 def build_ref(reference_root: str | None = None, force: bool = False) -> list[str]:
     """Compile the reference's attention-path kernels to sm_100a cubins in oracle/_ref."""
-    root = reference_root or os.environ.get("MX230_REFERENCE", "/root/reference")
+    # where the reference checkout lies: the argument, $MX230_REFERENCE, else a `reference` directory beside this repository
+    root = reference_root or os.environ.get("MX230_REFERENCE") or os.path.join(
+        os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
     if not os.path.isdir(root):
         return []
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"

@@ -54,3 +54,23 @@ def test_create_without_device_fails_loudly(lib_built):
 def test_sources_are_sm100a_only():
     assert build.ARCH_FLAGS == ["-gencode", "arch=compute_100a,code=sm_100a"]
     assert len(build.sources()) >= 5
+
+
+def test_rust_extern_block_matches_the_header():
+    """include/mx230_sys.rs is generated from the header; it must be regenerated when a prototype changes."""
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "include", "gen_rust_extern.py")], capture_output=True,
+                         text=True, check=True).stdout
+    assert out == open(os.path.join(root, "include", "mx230_sys.rs")).read()
+    assert out.count("pub fn mx230_") == len(_lib.declared_functions())
+
+
+def test_splitkv_comm_rejects_bad_arguments_without_a_device(lib_built):
+    L = _lib.lib()
+    c = C.c_void_p()
+    assert L.mx230_splitkv_comm_create(None, 0, 2, 8, 64, C.byref(c)) == _lib.ERR_INVALID_ARG
+    assert L.mx230_splitkv_exchange_merge(None, None, None, None) == _lib.ERR_INVALID_ARG
+    assert L.mx230_splitkv_wait_merge(None, None, None) == _lib.ERR_INVALID_ARG
+    assert L.mx230_splitkv_comm_disconnect(None) == _lib.ERR_INVALID_ARG
+    L.mx230_splitkv_comm_destroy(None)   # a null communicator is ignored
