@@ -241,20 +241,27 @@ def prefill_bench(h, torch, la, n_tok=512, nh=14, nkv=2, reps=10):
             qkv = torch.randn(n_tok, stride, device="cuda")
             o = torch.empty(n_tok, qd, device="cuda")
             f = lambda: la.attn_prefill(h, o, qkv, c, pos0, n_tok, nh, nkv, stride, qd)
-            for _ in range(3):
-                f()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(reps):
-                f()
-            e1.record()
-            torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / reps
+            us = graph_time_us(torch, [f] * 8)   # three launches of a few microseconds each: timed from a CUDA graph
             pairs = n_tok * pos0 + n_tok * (n_tok + 1) // 2
             out[f"{'int8' if quant else 'fp32'}_kv_pos0_{pos0}"] = {
                 "us": us, "tflops": 4.0 * 64 * pairs * nh / us / 1e6, "n_tok": n_tok, "n_keys": n_keys,
-                "heads": f"{nh}q/{nkv}kv", "launches_per_call": 3}
+                "heads": f"{nh}q/{nkv}kv", "launches_per_call": 3, "timing": "CUDA graph of 8 calls, 5 replays"}
+    # the projections either side (gpu.rs:3187-3198, 3354-3365): qkv = x W + b and y = attn W + b for the same chunk
+    e = 896
+    x = torch.randn(n_tok, e, device="cuda")
+    for name, dt in (("fp32_w", torch.float32), ("fp16_w", torch.float16)):
+        w1 = (torch.randn(e, stride, device="cuda") / 30).to(dt)
+        w2 = (torch.randn(qd, e, device="cuda") / 30).to(dt)
+        b1, b2 = torch.randn(stride, device="cuda"), torch.randn(e, device="cuda")
+        qkv = torch.empty(n_tok, stride, device="cuda")
+        att = torch.randn(n_tok, qd, device="cuda")
+        y = torch.empty(n_tok, e, device="cuda")
+        la.gemm(h, qkv, x, w1, b1), la.gemm(h, y, att, w2, b2)   # workspace grown outside the capture
+        u1 = graph_time_us(torch, [lambda: la.gemm(h, qkv, x, w1, b1)] * 8)
+        u2 = graph_time_us(torch, [lambda: la.gemm(h, y, att, w2, b2)] * 8)
+        out[f"proj_{name}"] = {"qkv_us": u1, "out_us": u2, "qkv_tflops": 2.0 * n_tok * e * stride / u1 / 1e6,
+                               "out_tflops": 2.0 * n_tok * qd * e / u2 / 1e6, "shape": f"{n_tok} x {e} -> {stride} / {qd} -> {e}",
+                               "launches_per_call": 2, "timing": "CUDA graph of 8 calls, 5 replays"}
     return out
 
 

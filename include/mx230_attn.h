@@ -419,6 +419,16 @@ int mx230_attn_prefill_dp4a_paged(mx230_handle *h, void *stream, float *out, con
  * (n_slices * n_out floats, at most ceil(n_in / 16) slices). */
 int mx230_gemv(mx230_handle *h, void *stream, float *y, const float *x, const void *w, int w_fp16,
                const float *b, int n_in, int n_out, int accum);
+/* The same projections for a batch of rows (prefill): gemm(), src/gpu.rs:1291-1420, called for qkv at
+ * gpu.rs:3187-3198 and for the output projection at gpu.rs:3354-3365 (kernels gemm_f32* / gemm_half*,
+ * llm.cu:1632-1733): C[r][o] = sum_i A[r][i] w[i*n + o] + bias[o], A [m][k] and C [m][n] fp32 contiguous,
+ * w [k][n] fp32 (w_fp16 = 0) or fp16 (1), bias may be null.  Any m; k % 16 == 0 (as the reference asserts),
+ * n % 8 == 0.  Tensor cores with 16-bit operands and fp32 accumulation: fp16 weights are used as they lie, A is
+ * rounded to fp16; fp32 weights and A are each split into two bf16 terms (16 bits of mantissa) and three
+ * products are summed.  Workspace: mx230_gemm_workspace_bytes.  Int8 / int4 weight formats: not built. */
+size_t mx230_gemm_workspace_bytes(int m, int n, int k, int w_fp16);
+int mx230_gemm(mx230_handle *h, void *stream, float *C, const float *A, const void *w, int w_fp16,
+               const float *bias, int m, int n, int k);
 /* gemv_int8, llm.cu:226-316 (host gemv() Weights::Int8, gpu.rs:1200-1211): int8 weights packed as int32
  * words of four consecutive input rows, w_packed[(i/4)*n_out + o]; activations quantised inside the
  * kernel per group of act_group (4 or 8: the reference's compile-time AG) values, absmax/127, round to

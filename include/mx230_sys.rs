@@ -267,6 +267,11 @@ extern "C" {
         h: *mut Mx230Handle, stream: *mut c_void, y: *mut f32, x: *const f32, w: *const c_void, w_fp16: c_int,
         b: *const f32, n_in: c_int, n_out: c_int, accum: c_int,
     ) -> c_int;
+    pub fn mx230_gemm_workspace_bytes(m: c_int, n: c_int, k: c_int, w_fp16: c_int) -> usize;
+    pub fn mx230_gemm(
+        h: *mut Mx230Handle, stream: *mut c_void, C: *mut f32, A: *const f32, w: *const c_void, w_fp16: c_int,
+        bias: *const f32, m: c_int, n: c_int, k: c_int,
+    ) -> c_int;
     pub fn mx230_gemv_int8(
         h: *mut Mx230Handle, stream: *mut c_void, y: *mut f32, x: *const f32, w_packed: *const c_void,
         scales: *const f32, b: *const f32, n_in: c_int, n_out: c_int, accum: c_int, act_group: c_int,

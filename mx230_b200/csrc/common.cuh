@@ -144,6 +144,9 @@ struct mx230_splitkv_comm {
 int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
                          uint64_t outer, uint64_t row_stride_bytes, uint64_t outer_stride_bytes,
                          uint32_t box_rows);
+// 16-bit matrix [rows][inner] (bf16, or fp16 when `fp16`), {box_inner, box_rows, 1} boxes, 128-byte swizzle, zero fill.
+int mx230_make_tmap_2d_16bit(mx230_handle *h, CUtensorMap *out, const void *base, int fp16, uint64_t inner,
+                             uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows);
 // fp32 tensor map over [outer][rows][64] with a {32, 32, 1} box (half rows of 128 bytes) and 128-byte swizzle.
 int mx230_make_tmap_f32_half_rows(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,
                                   uint64_t outer);

@@ -341,6 +341,27 @@ int mx230_make_tmap_bf16(mx230_handle *h, CUtensorMap *out, const void *base, ui
     return MX230_OK;
 }
 
+// 16-bit (bf16 or fp16) matrix [rows][inner], rows `row_stride_bytes` apart, as a three-dimensional map with an outer
+// extent of 1 (the kernels' load helper is the 3-D form): boxes of box_inner x box_rows elements, 128-byte swizzle
+// (box_inner * 2 <= 128), zero fill outside the matrix.
+int mx230_make_tmap_2d_16bit(mx230_handle *h, CUtensorMap *out, const void *base, int fp16, uint64_t inner,
+                             uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows) {
+    MX_REQUIRE(((uintptr_t)base & 15) == 0, MX230_ERR_INVALID_ARG, "tensor map base %p is not 16-byte aligned", base);
+    MX_REQUIRE(row_stride_bytes % 16 == 0 && box_inner * 2 <= 128 && box_rows <= 256, MX230_ERR_INVALID_ARG,
+               "tensor map: row stride must be a multiple of 16 bytes and the box at most 128 bytes x 256 rows");
+    cuuint64_t dims[3] = {inner, rows, 1};
+    cuuint64_t strides[2] = {row_stride_bytes, row_stride_bytes * rows};
+    cuuint32_t box[3] = {box_inner, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = h->encode_tiled(out, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                                 const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return mx230_fail(MX230_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return MX230_OK;
+}
+
 // fp32 [outer][rows][64] seen as 128-byte half rows: boxes of 32 rows x 32 floats, 128-byte swizzle
 // (the staging layout of the fused backward's dQ reductions).
 int mx230_make_tmap_f32_half_rows(mx230_handle *h, CUtensorMap *out, const void *base, uint64_t rows,

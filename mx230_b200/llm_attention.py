@@ -364,6 +364,28 @@ def gemv(h: Handle, y, x, w, b=None, accum=False, stream=None):
                            ptr(b), n_in, n_out, int(accum)))
 
 
+def gemm(h: Handle, c, a, w, b=None, stream=None):
+    """gemm (gpu.rs:1291-1420) for the prefill-side projections: c [m][n] = a [m][k] . w [k][n] + b, `w` fp32 or
+    fp16.  Grows the handle's workspace when it is too small for the staged operands."""
+    m, k = a.shape
+    n = w.shape[1]
+    fp16 = 1 if w.dtype == torch.float16 else 0
+    h.reserve(lib().mx230_gemm_workspace_bytes(m, n, k, fp16))
+    check(lib().mx230_gemm(h._h, stream_ptr(stream), ptr(c), ptr(a), ptr(w), fp16, ptr(b), m, n, k))
+
+
+def prefill_layer_attention(h: Handle, y, x, w_qkv, b_qkv, w_proj, b_proj, qkv, attn, c: KvCache, pos0, n_tok, n_head,
+                            n_kv_head, head_dim, theta, pg: Paging | None = None, use_rope=True, stream=None):
+    """The attention half of one layer for a prefill chunk, as batch_body_from runs it (gpu.rs:3187-3365):
+    qkv = x W_qkv + b (gemm), RoPE, KV write, causal attention over the cache, y = attn W_proj + b (gemm).
+    `qkv` [n_tok][q_dim + 2 kv_dim] and `attn` [n_tok][q_dim] are the caller's scratch rows (the reference's batch_qkv
+    and batch_attn); the residual add that follows stays with the caller, as in the reference."""
+    q_dim = n_head * head_dim
+    gemm(h, qkv, x, w_qkv, b_qkv, stream)
+    prefill_step(h, attn, qkv, c, pos0, n_tok, n_head, n_kv_head, head_dim, theta, qkv.shape[1], q_dim, pg, use_rope, stream)
+    gemm(h, y, attn, w_proj, b_proj, stream)
+
+
 def gemv_int8(h: Handle, y, x, w_packed, scales, b=None, accum=False, act_group=8, stream=None):
     """gemv_int8 (llm.cu:226-316): `w_packed` int32 [n_in / 4][n_out], four consecutive input rows per word."""
     n_in, n_out = w_packed.shape[0] * 4, w_packed.shape[1]

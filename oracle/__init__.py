@@ -305,6 +305,13 @@ def gemv(x, w, b=None, y=None, accum=False):
     return out
 
 
+def gemm(a, w, b=None):
+    """The reference gemm (gpu.rs:1291-1420; kernels gemm_f32* / gemm_half*, llm.cu:1632-1733): c[r][o] =
+    sum_i a[r][i] w[i][o] + b[o], every row the sequential fp32 sum of `gemv`."""
+    a = np.ascontiguousarray(a, np.float32)
+    return np.stack([gemv(a[r], w, b) for r in range(a.shape[0])]) if a.shape[0] else np.zeros((0, np.asarray(w).shape[1]), np.float32)
+
+
 def pack_int8_weights(w8):
     """int8 [n_in][n_out] -> int32 words of four consecutive input rows, w32[(i/4)][o], byte j = row 4(i/4)+j
     (the reference's load-time repacking, llm.cu:183-188)."""

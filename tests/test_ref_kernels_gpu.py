@@ -329,6 +329,30 @@ def test_reference_gemv_kernels_equal_oracle(llm_mod):
     assert oracle.allclose_err(y.cpu().numpy(), oracle.gemv_int8(x, w32, scales, b, ag=4), RTOL, ATOL) < 1.0
 
 
+def test_reference_gemm_kernels_equal_oracle(llm_mod):
+    """gemm_f32_wide / gemm_half_wide (the prefill tier, M > 64: grid (ceil(n/128), ceil(m/128)) x 256 threads,
+    gpu.rs:1117-1123) and gemm_f32 (the 64-row tier, grid (ceil(n/64), ceil(m/64)) x (16, 16), gpu.rs:1109-1115)
+    against the oracle's gemm, the function the library's mx230_gemm is tested with."""
+    m, n, k = 200, 1152, 896
+    a = oracle.normal((m, k), 91, 0)
+    w = (oracle.normal((k, n), 92, 0) / np.sqrt(k)).astype(np.float32)
+    b = oracle.normal((n,), 93, 0)
+    want = oracle.gemm(a, w, b)
+    c = torch.zeros(m, n, device="cuda")
+    llm_mod.launch("gemm_f32_wide", ((n + 127) // 128, (m + 127) // 128), (256,), [c, dev(a), dev(w), dev(b), m, n, k])
+    torch.cuda.synchronize()
+    assert oracle.allclose_err(c.cpu().numpy(), want, RTOL, ATOL) < 1.0
+    c.zero_()
+    llm_mod.launch("gemm_f32", ((n + 63) // 64, (m + 63) // 64), (16, 16), [c, dev(a), dev(w), dev(b), m, n, k])
+    torch.cuda.synchronize()
+    assert oracle.allclose_err(c.cpu().numpy(), want, RTOL, ATOL) < 1.0
+    wh = w.astype(np.float16)
+    c.zero_()
+    llm_mod.launch("gemm_half_wide", ((n + 127) // 128, (m + 127) // 128), (256,), [c, dev(a), dev(wh), dev(b), m, n, k])
+    torch.cuda.synchronize()
+    assert oracle.allclose_err(c.cpu().numpy(), oracle.gemm(a, wh, b), RTOL, ATOL) < 1.0
+
+
 def test_library_int8_prefill_against_the_reference_int8_prefill(llm_mod, handle):
     """The reference's attn_prefill_q8 quantises q per (row, head) to int8 and scores with integer dots; the library's
     default score mode over an int8 cache reproduces that arithmetic (the codes cross the tensor cores exactly), its
