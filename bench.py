@@ -546,7 +546,7 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "per_gpu_units": f"{BH} (batch, head) units",
                        "l2": "inputs larger than L2 (4 x 50 MB fp32 operands per step)",
                        "entry_points": "mx230_attn_flash_lse + mx230_attn_bwd_preprocess + mx230_attn_bwd_flash",
-                       "options": "MX230_OPT_BWD_REUSE_STAGED = 1 (the backward reuses the forward's staged Q, K, V)",
+                       "options": "MX230_OPT_BWD_REUSE_STAGED = 1 (the backward reuses the forward's staged Q, K, V and the dO copy the Delta pre-pass leaves)",
                        "inputs": "N(0,1), library generator, seed 1000 + rank"},
             "fwd_tflops": world * FWD_FLOP / (kern["flash_fwd_kernel"]["ms_per_launch"] * 1e-3) / 1e12,
             "bwd_tflops": world * BWD_FLOP / (sum(kern[k]["ms_per_launch"] for k in kern if k.startswith("bwd_") and

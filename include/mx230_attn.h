@@ -66,8 +66,10 @@ enum {
     MX230_OPT_BWD_REUSE_STAGED = 5, /* mx230_attn_bwd_{dq,dkv,flash}: 1 = when the workspace still holds the bf16 copies
                                     of Q, K, V that mx230_attn_flash[_lse] staged for the SAME pointers and shape
                                     (no other workspace-using call in between, same stream, tensor contents
-                                    unchanged -- the caller's promise), stage only dO.  0 (default) = always
-                                    stage all four */
+                                    unchanged -- the caller's promise), stage only dO; and when
+                                    mx230_attn_bwd_preprocess ran in between for the SAME dO pointer (contents
+                                    unchanged since), it has left dO's bf16 copy there as well and nothing is
+                                    staged.  0 (default) = always stage all four */
     MX230_OPT_WAIT_LIMIT = 6,    /* bound of every device-side barrier wait, in thousands of SM cycles (default
                                     4000000 = 4e9 cycles, about 2 s); on expiry the kernel records a status and
                                     returns (mx230_check_status -> MX230_ERR_DEVICE_STATUS).  Synchronises the device */

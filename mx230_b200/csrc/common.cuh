@@ -46,6 +46,7 @@ struct mx230_handle {
         const void *q, *k, *v;
         int batch_heads, n;
         int valid;
+        const void *d_o;   // the fp32 dO whose bf16 copy the Delta pre-pass left in the fourth staging slot (null: none)
     } staged;
     long long launches;    // kernels launched through this handle
     mx230_encode_tiled_fn encode_tiled;

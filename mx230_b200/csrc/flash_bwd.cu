@@ -719,8 +719,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
     if (warp == 9) mx::tmem_dealloc(tmem, TM_COLS);
 }
 
-// Delta_i = sum_x dO[i,x] O[i,x]; 16 threads per row, one float4 each.
-__global__ void bwd_preprocess_kernel(const float *dO, const float *O, float *Delta, size_t rows) {
+// Delta_i = sum_x dO[i,x] O[i,x]; 16 threads per row, one float4 each.  With `dOb` the bf16 copy of dO that the
+// backward's tensor-core passes read is written on the way (the values are in registers here anyway).
+__global__ void bwd_preprocess_kernel(const float *dO, const float *O, float *Delta, size_t rows, __nv_bfloat16 *dOb) {
     size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t row = gid >> 4;
     int part = (int)(gid & 15);
@@ -729,6 +730,12 @@ __global__ void bwd_preprocess_kernel(const float *dO, const float *O, float *De
         float4 a = *(const float4 *)(dO + row * HD + part * 4);
         float4 b = *(const float4 *)(O + row * HD + part * 4);
         d = a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+        if (dOb) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+            uint2 w;
+            w.x = *(const uint32_t *)&lo, w.y = *(const uint32_t *)&hi;
+            *(uint2 *)(dOb + row * HD + part * 4) = w;
+        }
     }
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
@@ -885,14 +892,21 @@ int bwd_fp32(mx230_handle *h, void *stream, const float *Q, const float *K, cons
     // probabilities then sum to one over a row whatever the rounding did to a single score.
     if (h->bwd_reuse_staged && h->staged.valid && h->staged.q == Q && h->staged.k == K && h->staged.v == V &&
         h->staged.batch_heads == batch_heads && h->staged.n == n) {
-        // the forward's bf16 copies of these very tensors are still in the workspace: only dO is staged
-        rc = mx230_launch_cast(h, (cudaStream_t)stream, src + 3, dst + 3, 1, batch_heads, (size_t)n * HD,
-                               fused ? dQ : nullptr, 1.0f, nullptr);
+        // the forward's bf16 copies of these very tensors are still in the workspace: only dO is staged, and not even
+        // that when the Delta pre-pass of this dO has left its bf16 copy in the fourth slot (dQ is then cleared by a memset)
+        if (h->staged.d_o == dO) {
+            if (fused) MX_CHECK_CUDA(cudaMemsetAsync(dQ, 0, (size_t)batch_heads * n * HD * sizeof(float), (cudaStream_t)stream));
+        } else {
+            h->staged.d_o = nullptr;   // the slot is about to hold another tensor's copy
+            rc = mx230_launch_cast(h, (cudaStream_t)stream, src + 3, dst + 3, 1, batch_heads, (size_t)n * HD,
+                                   fused ? dQ : nullptr, 1.0f, nullptr);
+            if (!rc) h->staged.d_o = dO;
+        }
     } else {
         h->staged.valid = 0;
         rc = mx230_launch_cast(h, (cudaStream_t)stream, src, dst, 4, batch_heads, (size_t)n * HD, fused ? dQ : nullptr,
                                MX230_QK_LOG2_SCALE, nullptr);
-        if (!rc) h->staged = {Q, K, V, batch_heads, n, 1};
+        if (!rc) h->staged = {Q, K, V, batch_heads, n, 1, dO};
     }
     if (rc) return rc;
     return bwd_bf16(h, stream, dst[0], dst[1], dst[2], dst[3], L, Delta, dQ, dK, dV, batch_heads, n, causal,
@@ -913,8 +927,17 @@ extern "C" int mx230_attn_bwd_preprocess(mx230_handle *h, void *stream, const fl
     mx230_device_guard guard(h->device);
     size_t threads = rows * 16;
     cudaStream_t st = (cudaStream_t)stream;
+    // With the reuse option, and the forward's staged Q, K, V of this very shape still in the workspace, the backward
+    // that follows will look for dO's bf16 copy in the fourth staging slot: leave it there now.
+    __nv_bfloat16 *dOb = nullptr;
+    if (h->bwd_reuse_staged && h->staged.valid && h->staged.batch_heads == batch_heads && h->staged.n == n && h->ws &&
+        mx230_flash_workspace_bytes(batch_heads, n, 1) <= h->ws_bytes) {
+        dOb = (__nv_bfloat16 *)((char *)h->ws + 3 * mx230_flash_stage_bytes(batch_heads, n));
+        h->staged.d_o = nullptr;
+    }
     MX_LAUNCH(h, st, MX230_K_BWD_PREPROCESS,
-              (bwd_preprocess_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(dO, O, Delta, rows)));
+              (bwd_preprocess_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(dO, O, Delta, rows, dOb)));
+    if (dOb) h->staged.d_o = dO;
     return MX230_OK;
 }
 

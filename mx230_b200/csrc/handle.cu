@@ -134,6 +134,7 @@ extern "C" int mx230_reserve(mx230_handle *h, size_t bytes) {
     if (h->ws) cudaFree(h->ws);
     h->ws = nullptr;
     h->ws_bytes = 0;
+    h->staged.valid = 0;   // whatever was staged went with the old workspace
     MX_CHECK_CUDA(cudaMalloc(&h->ws, bytes));
     h->ws_bytes = bytes;
     return MX230_OK;

@@ -289,3 +289,60 @@ def test_zero_sizes_and_bad_arguments(handle):
     fa.run_flash(small, q, q, q, torch.zeros_like(q), 512, False)
     small.check_status()
     small.close()
+
+
+@pytest.mark.parametrize("two_pass", [0, 1])
+@pytest.mark.parametrize("bh,n", [(3, 700), (5, 1024)])
+def test_backward_reusing_the_forwards_staged_operands(bh, n, two_pass):
+    """MX230_OPT_BWD_REUSE_STAGED: the backward takes Q, K, V from the bf16 copies the forward left in the workspace and
+    dO from the copy the Delta pre-pass left there.  Same kernels on the same bits: dK, dV (and dQ in the two-pass form)
+    must equal the default path's bit for bit, the fused dQ to the usual tolerance; a call for other tensors in between,
+    a changed dO pointer and a workspace regrowth must all fall back to staging."""
+    from mx230_b200 import _lib
+    from mx230_b200.common import Handle
+    h = Handle(0, fa.workspace_bytes(bh, n, True))
+    try:
+        q, k, v, do = (dev(oracle.normal((bh, n, 64), 900 + n, i)) for i in range(4))
+        h.set_option(_lib.OPT_BWD_TWO_PASS, two_pass)
+
+        def step(reuse, d_o, between=None):
+            h.set_option(_lib.OPT_BWD_REUSE_STAGED, reuse)
+            o, l, delta = torch.zeros(bh, n, 64, device="cuda"), torch.zeros(bh, n, device="cuda"), torch.zeros(bh, n, device="cuda")
+            g = [torch.full((bh, n, 64), float("nan"), device="cuda") for _ in range(3)]
+            fa.run_flash_lse(h, q, k, v, o, l, n, True)
+            n0 = h.launches
+            fa.run_preprocess(h, d_o, o, delta, n)
+            if between is not None:
+                between()
+            fa.run_bwd_flash(h, q, k, v, d_o, l, delta, *g, n, True)
+            h.check_status()
+            return g, h.launches - n0
+
+        base, n_base = step(0, do)
+        got, n_reuse = step(1, do)
+        assert n_reuse == n_base - 1          # no staging launch at all
+        assert torch.equal(got[1], base[1]) and torch.equal(got[2], base[2])
+        if two_pass:
+            assert torch.equal(got[0], base[0])
+        else:
+            assert_close(got[0].cpu().numpy(), base[0].cpu().numpy(), "dQ reuse vs default", max_abs=1e-4, mean_rel=1e-5)
+        wq, wk, wv = oracle.attn_bwd(*(x.cpu().numpy() for x in (q, k, v, do)), True)
+        # (max-abs at 3e-2 as for the other thousand-token gradients: the largest of 327680 bf16-operand errors per tensor;
+        # what this test is about is the equality with the default path above)
+        for name, a, w in zip("QKV", got, (wq, wk, wv)):
+            assert_close(a.cpu().numpy(), w, f"d{name} with reuse", max_abs=3e-2)
+        # another dO tensor between the pre-pass and the backward: its copy is not the one in the workspace
+        do2 = do.clone()
+        got2, n2 = step(1, do, between=lambda: fa.run_preprocess(h, do2, torch.zeros(bh, n, 64, device="cuda"),
+                                                                torch.zeros(bh, n, device="cuda"), n))
+        assert n2 == n_base + 1 and torch.equal(got2[1], base[1]) and torch.equal(got2[2], base[2])
+        # a forward for other tensors in between: everything is staged again
+        q2 = q.clone()
+        got3, _ = step(1, do, between=lambda: fa.run_flash_lse(h, q2, k, v, torch.zeros(bh, n, 64, device="cuda"),
+                                                              torch.zeros(bh, n, device="cuda"), n, True))
+        assert torch.equal(got3[1], base[1]) and torch.equal(got3[2], base[2])
+        # the workspace regrown between forward and backward: the staged copies are gone
+        got4, _ = step(1, do, between=lambda: h.reserve(fa.workspace_bytes(bh, n, True) + (1 << 20)))
+        assert torch.equal(got4[1], base[1]) and torch.equal(got4[2], base[2])
+    finally:
+        h.close()
