@@ -128,6 +128,15 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
+def host_threads() -> int:
+    """Cores this process may run on.  Not omp_get_max_threads: torchrun exports OMP_NUM_THREADS=1 to its workers, which
+    would turn the all-cores CPU arm into a single-threaded one; the oracle takes its thread count as an argument."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -153,7 +162,7 @@ def run_reference(args):
     if rank != 0:
         return
     import oracle
-    threads = oracle.max_threads()
+    threads = host_threads()
     q, k, v, do = (oracle.normal((BH, N, D), 1234, i) for i in range(4))
 
     def step():
@@ -528,7 +537,7 @@ def run_ours(args):
                     "frac_of_nominal": kern[dom]["achieved_tflops"] / NOMINAL_BF16_TFLOPS,
                     "per_kernel": kern}
         import oracle
-        cores = oracle.max_threads()
+        cores = host_threads()
         heads = max(1, min(cores, BH))   # one head per thread: every core busy
         sec = cpu_sample(heads, cores)
         sec1 = cpu_sample(1, 1)   # what the reference itself does: one head on one thread
