@@ -1,4 +1,4 @@
-"""Prints the Rust `extern "C"` block for every prototype of mx230_attn.h (the block INTEGRATION.md shows).
+"""Prints the Rust `extern "C"` block for every prototype of mx230_attn.h.
 
     python include/gen_rust_extern.py > mx230_sys.rs
 
