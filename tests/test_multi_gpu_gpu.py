@@ -180,3 +180,83 @@ def test_two_handles_in_one_process():
     for i in (0, 2, 3):
         np.testing.assert_array_equal(outs[0][i], outs[1][i])
     assert np.abs(outs[0][1] - outs[1][1]).max() <= 1e-4
+
+
+def _absent_peer_worker(rank, world, port, ret):
+    """Failure detection without a GPU fault: after two good steps rank 1 stops taking part (a host-side decision,
+    between steps, nothing of its own in flight).  Rank 0's next step stores its triples, waits for rank 1's with a
+    short limit, and its kernel returns by itself with the status word set; the context stays usable and a fresh
+    communicator works again."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import datetime
+    import torch.distributed as dist
+    from mx230_b200 import _lib, llm_attention as la
+    from mx230_b200._lib import Mx230Error
+    from mx230_b200.common import Handle
+    from mx230_b200.multi_gpu import SplitKvDecoder, SplitKvPlan
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=60))
+    try:
+        dev = f"cuda:{rank}"
+        h = Handle(rank, 16 << 20)
+        n_seq, nh, nkv, span = 2, 8, 2, 300
+        plan = SplitKvPlan(ctx=span * world, world=world, n_seq=n_seq, n_head=nh, align=4)
+        torch.manual_seed(7 + rank)
+        c = la.KvCache(n_seq * span, nkv, 64, True, True, device=dev)
+        c.k.random_(-128, 128), c.v.random_(-128, 128), c.ks.uniform_(0.01, 0.03), c.vs.uniform_(0.01, 0.03)
+        q = torch.randn(n_seq, nh * 64, device=dev)
+        dec = SplitKvDecoder(h, plan, rank, device=dev, fused=True)
+        for _ in range(2):
+            good = dec.step(q, c, nkv, span, nh * 64).clone()
+        torch.cuda.synchronize()
+        h.check_status()
+        dist.barrier()
+        status = None
+        if rank == 0:   # rank 1 sits this step out
+            h.set_option(_lib.OPT_WAIT_LIMIT, 4000)   # 4e6 cycles, about 2 ms
+            dec.out.fill_(float("nan"))
+            dec.step(q, c, nkv, span, nh * 64)
+            try:
+                h.check_status()
+            except Mx230Error as e:
+                status = e.code
+            untouched = bool(torch.isnan(dec.out).all())
+            h.set_option(_lib.OPT_WAIT_LIMIT, 4000000)
+        dist.barrier()          # rank 1 learns on the host that the step is over
+        dec.close()             # the step counts of the two ranks no longer agree: this communicator is done
+        dec2 = SplitKvDecoder(h, plan, rank, device=dev, fused=True)
+        again = dec2.step(q, c, nkv, span, nh * 64)
+        torch.cuda.synchronize()
+        h.check_status()
+        same = bool(torch.equal(again, good))
+        dec2.close()
+        ret[rank] = (status, untouched if rank == 0 else None, same)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_absent_peer_is_detected_by_the_bounded_wait_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from mx230_b200 import _lib
+    ctxm = mp.get_context("spawn")
+    ret = ctxm.Manager().dict()
+    port = _free_port()
+    procs = [ctxm.Process(target=_absent_peer_worker, args=(r, 2, port, ret), daemon=True) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+    codes = [p.exitcode for p in procs]
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+    assert codes == [0, 0], f"rank exit codes {codes}"
+    assert ret[0][0] == _lib.ERR_DEVICE_STATUS and ret[0][1] is True   # the wait ran out, nothing was written
+    assert ret[0][2] and ret[1][2]                                      # a fresh communicator gives the same result as before
