@@ -40,22 +40,25 @@ constexpr int BN = 128;        // keys per K/V tile
 constexpr int HD = 64;
 constexpr int KV_STAGES = 4;
 constexpr int TILE_BYTES = BN * HD * 2;  // 16 KB
-constexpr int FWD_THREADS = 384;        // 3 warpgroups: softmax 0, softmax 1, {TMA, 2 MMA issuers, idle}
+constexpr int HALVES = 2;               // softmax groups per query tile: each takes half of the tile's key columns
+constexpr int SOFT_WARPS = QT * HALVES * 4;   // 16
+constexpr int FWD_THREADS = (SOFT_WARPS + 4) * 32;   // 640: four softmax warpgroups + {TMA, 2 MMA issuers, idle}
 // setmaxnreg moves registers only inside the CTA's launch-time allocation (168 per thread for 384
 // threads): what the softmax warps gain must have been released by the third warpgroup, or the
 // increase would block for ever.
 #ifndef FWD_REGS_SOFTMAX
-#define FWD_REGS_SOFTMAX 216
-#define FWD_REGS_SERVICE 72
+#define FWD_REGS_SOFTMAX 104
+#define FWD_REGS_SERVICE 64
 #endif
-static_assert(8 * FWD_REGS_SOFTMAX + 4 * FWD_REGS_SERVICE <= 12 * 168, "setmaxnreg budget exceeds the launch-time register allocation");
+static_assert(SOFT_WARPS * FWD_REGS_SOFTMAX + 4 * FWD_REGS_SERVICE <= (SOFT_WARPS + 4) * 96, "setmaxnreg budget exceeds the launch-time register allocation");
 
 // build-time knobs of the softmax loop
 #ifndef FWD_FAST
 #define FWD_FAST 1        // fixed-reference mode (no row max, no subtraction) while the sums stay in range
 #endif
 #ifndef FWD_POLY
-#define FWD_POLY 2        // of every FWD_POLY_DEN column pairs, how many take 2^x from the FMA-pipe polynomial
+#define FWD_POLY 1        // of every FWD_POLY_DEN column pairs, how many take 2^x from the FMA-pipe polynomial (with four
+                          // softmax warps per scheduler the loop is issue-bound: 1 of 4 beats 2 of 4 by 7-10 %, 0 of 4 loses 9 %)
 #endif
 #ifndef FWD_POLY_DEN
 #define FWD_POLY_DEN 4
@@ -80,7 +83,9 @@ constexpr int SMEM_Q = 0;
 constexpr int SMEM_K = SMEM_Q + Q_BUFS * QT * TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;
 constexpr int SMEM_BAR = SMEM_V + KV_STAGES * TILE_BYTES;
-constexpr int SMEM_TOTAL = SMEM_BAR + 256;
+constexpr int SMEM_XCH = SMEM_BAR + 512;   // [2 item parities][QT][2][BM] floats: row sums handed from the second half of a tile to the first
+constexpr int SMEM_XMAX = SMEM_XCH + 2 * QT * 2 * BM * 4;   // [QT][2 tile parities][HALVES][BM] floats: row-max parts of the general mode
+constexpr int SMEM_TOTAL = SMEM_XMAX + QT * 2 * HALVES * BM * 4;
 constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;  // slack for 1024-byte alignment
 
 // barrier slots (8 bytes each) inside SMEM_BAR
@@ -94,7 +99,9 @@ constexpr int BAR_S_FULL = BAR_V_EMPTY + KV_STAGES;  // [QT] MMA -> softmax: S_t
 constexpr int BAR_S_FREE = BAR_S_FULL + QT;          // [QT] softmax -> MMA: S_t copied to registers
 constexpr int BAR_P_FULL = BAR_S_FREE + QT;          // [QT] softmax -> MMA: P_t written
 constexpr int BAR_O_DONE = BAR_P_FULL + QT;          // [QT] MMA -> softmax: O_t += P_t V complete
-constexpr int N_BARS = BAR_O_DONE + QT;              // 28
+constexpr int BAR_XCH = BAR_O_DONE + QT;             // [QT] second half of tile t -> first half: its row sums are published
+constexpr int BAR_XMAX = BAR_XCH + QT;               // [QT] general mode: both halves of tile t have published their part of the row max
+constexpr int N_BARS = BAR_XMAX + QT;                // 32
 
 // tensor-memory columns: nothing aliases, so S_t(j+1) can be produced while P_t(j) is consumed
 constexpr int TM_S = 0;     // S_t at TM_S + t*128, fp32
@@ -178,7 +185,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (tid == 0) {
         for (int b = 0; b < Q_BUFS; ++b) {
             mx::mbar_init(bar(BAR_Q_FULL + b), 1);
-            mx::mbar_init(bar(BAR_Q_EMPTY + b), QT * BM / 32);  // one elected lane per softmax warp arrives
+            mx::mbar_init(bar(BAR_Q_EMPTY + b), SOFT_WARPS);  // one elected lane per softmax warp arrives
         }
         for (int s = 0; s < KV_STAGES; ++s) {
             mx::mbar_init(bar(BAR_K_FULL + s), 1);
@@ -188,14 +195,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         for (int t = 0; t < QT; ++t) {
             mx::mbar_init(bar(BAR_S_FULL + t), 1);
-            mx::mbar_init(bar(BAR_S_FREE + t), BM / 32);  // one elected lane per warp arrives
-            mx::mbar_init(bar(BAR_P_FULL + t), BM / 32);
+            mx::mbar_init(bar(BAR_S_FREE + t), HALVES * BM / 32);  // one elected lane per warp of the tile's groups arrives
+            mx::mbar_init(bar(BAR_P_FULL + t), HALVES * BM / 32);
             mx::mbar_init(bar(BAR_O_DONE + t), 1);
+            mx::mbar_init(bar(BAR_XCH + t), BM / 32);
+            mx::mbar_init(bar(BAR_XMAX + t), HALVES * BM / 32);
         }
         *abort_flag = 0;
         mx::mbar_fence_init();
     }
-    if (warp == 9) mx::tmem_alloc(mx::smem_u32((const void *)tmem_slot), TM_COLS);
+    if (warp == SOFT_WARPS + 1) mx::tmem_alloc(mx::smem_u32((const void *)tmem_slot), TM_COLS);
     mx::tc_fence_before();
     __syncthreads();
     mx::tc_fence_after();
@@ -203,9 +212,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     // register budget: the softmax warpgroups hold a 128-value score row per thread, the
     // third warpgroup (TMA, two MMA issuers, one idle warp) needs few
-    if (warp >= 8) {
+    if (warp >= SOFT_WARPS) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FWD_REGS_SERVICE));
-        if (warp == 8) {
+        if (warp == SOFT_WARPS) {
         // ------------------------- TMA producer -------------------------
         if (lane == 0) {
             mx::tma_prefetch_desc(&tmQ);
@@ -245,7 +254,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
         }
         __syncwarp();
-        } else if (warp == 9) {
+        } else if (warp == SOFT_WARPS + 1) {
         // ------------------------- MMA issuer 1: S_t = Q_t K^T ----------
         // The whole warp runs the loop and the waits; one elected lane issues.  Control flow and descriptor
         // arithmetic stay warp-uniform that way (a lone thread inside a divergent branch pays several dependent
@@ -290,7 +299,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
         }
         __syncwarp();
-        } else if (warp == 10) {
+        } else if (warp == SOFT_WARPS + 2) {
         // ------------------------- MMA issuer 2: O_t += P_t V -----------
         if (FWD_UNIFORM_ISSUE || lane == 0) {
             constexpr uint32_t IDESC_O = mx::mma_idesc_bf16(BM, HD, false, true);
@@ -333,12 +342,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
     } else {
         // ------------------------- softmax groups -----------------------
+        // Four groups: tile t = warp / 8 has two, each taking 64 of the 128 key columns of every score tile (one thread
+        // per query row and half).  Four softmax warps per scheduler instead of two hide each other's dependent-issue
+        // latencies; without a row max (the usual mode) the halves never talk to each other inside the loop, and the
+        // general mode has each half compute the full row's max redundantly rather than exchange it.
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FWD_REGS_SOFTMAX));
-        const int t = warp >> 2;             // query tile of this group
-        const int row_in_tile = tid & 127;
+        const int t = warp >> 3;             // query tile of this group
+        const int half = (warp >> 2) & 1;    // which 64 key columns of every tile
+        const int row_in_tile = (warp & 3) * 32 + lane;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tm_s = tmem + lane_off + TM_S + t * BN;
-        const uint32_t tm_p = tmem + lane_off + TM_P + t * (BN / 2);
+        const uint32_t tm_s_tile = tmem + lane_off + TM_S + t * BN;
+        const uint32_t tm_s = tm_s_tile + half * (BN / 2);
+        const uint32_t tm_p = tmem + lane_off + TM_P + t * (BN / 2) + half * (BN / 4);
         const uint32_t tm_o = tmem + lane_off + TM_O + t * HD;
         // Scores arrive in log2 units when Q was staged pre-multiplied by scale * log2(e) (c = 1), else raw (c = scale * log2(e)).
         const bool i8_scores = P.row_a != nullptr;   // scores rebuilt from integer dots: already in log2 units
@@ -346,6 +361,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float l_scale = (P.prescaled || i8_scores) ? 0.6931471805599453f : 0.125f;   // running max -> natural-log units
         bool ok = true;
         uint32_t cnt = 0;  // score tiles this group has taken so far, over all items
+        uint32_t xmc = 0;  // row-max exchanges this group has made so far (general-mode tiles only)
         int bh, q0;
         for (int it = 0; ok && fwd_item(P, it, bh, q0); ++it) {
         const int n_t = fwd_tile_iters(P, q0, t);
@@ -373,13 +389,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // the norms are those of the fp32 values; rounding to bf16 moves a norm by less than 0.4 %
             fast = nq * nk * (MX230_QK_LOG2_SCALE * MX230_QK_LOG2_SCALE) <= 80.0f * 80.0f;
         }
-        float m = fast ? 0.0f : -CUDART_INF_F, l = 0.0f;
+        float m = fast ? 0.0f : -CUDART_INF_F, l = 0.0f;   // l: this half's share of the row sum
         float l_norm = 0.0f;   // what O is divided by (fast mode: see below; general mode: l)
+        uint32_t va[32], vb[32];
         if (fast) {
-        // ---- max-free loop, software-pipelined over the row halves: the second half of a score row lands under the
-        // first half's exponentials, and the first half of the NEXT row is requested (once its barrier is seen
-        // complete, without waiting) before the last quarter of this one is exponentiated
-        uint32_t va[BN / 2], vb[BN / 2];
+        // ---- max-free loop: the group's second 32 columns land under the exponentials of the first 32
         uint64_t rs2[2] = {0ull, 0ull};
         float rs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         auto exp32 = [&](const uint32_t *src, uint32_t *pk, int key_base, bool need_mask) {
@@ -436,41 +450,31 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             bool good = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), cnt & 1, abort_flag, P.status));
             if (!good) return false;
             mx::tc_fence_after();
-            mx::tmem_ld32(tm_s, *(uint32_t(*)[32])(va));
-            mx::tmem_ld32(tm_s + 32, *(uint32_t(*)[32])(va + 32));
+            mx::tmem_ld32(tm_s, va);
             mx::tmem_wait_ld();                                       // va is in registers
-            mx::tmem_ld32(tm_s + 64, *(uint32_t(*)[32])(vb));        // lands under the first exponentials
-            mx::tmem_ld32(tm_s + 96, *(uint32_t(*)[32])(vb + 32));
+            mx::tmem_ld32(tm_s + 32, vb);                             // lands under the first exponentials
             const int key0 = j * BN;
             const bool need_mask = (key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM + P.q_off);
-            uint32_t pk01[32], pk23[16];
-            exp32(va, pk01, key0, need_mask);
-            mx::tmem_wait_ld();                                       // the whole row has left S_t
+            uint32_t pk[16];
+            exp32(va, pk, key0 + half * (BN / 2), need_mask);
+            mx::tmem_wait_ld();                                       // this group's columns have left S_t
             mx::tc_fence_before();
             __syncwarp();
             if (lane == 0) mx::mbar_arrive(bar(BAR_S_FREE + t));
-            exp32(va + 32, pk01 + 16, key0 + 32, need_mask);
             if (!FIRST) {
                 // P_t is free once the previous P V has completed: that takes several hundred cycles from the end of the
-                // previous softmax, which is why half a row is exponentiated before the first store
+                // previous softmax, which is why a quarter of the row is exponentiated before the first store
                 good = __all_sync(0xFFFFFFFFu,
                                   mx::mbar_wait_fast(bar(BAR_O_DONE + t), (cnt - 1) & 1, abort_flag, P.status));
                 if (!good) return false;
                 mx::tc_fence_after();
             }
-            mx::tmem_st16(tm_p, *(uint32_t(*)[16])(pk01));
-            mx::tmem_st16(tm_p + 16, *(uint32_t(*)[16])(pk01 + 16));
+            mx::tmem_st16(tm_p, pk);
+            if (FIRST) sum_rounded16(pk);
+            exp32(vb, pk, key0 + half * (BN / 2) + 32, need_mask);
+            mx::tmem_st16(tm_p + 16, pk);
             if (FIRST) {
-                sum_rounded16(pk01);
-                sum_rounded16(pk01 + 16);
-            }
-            exp32(vb, pk23, key0 + 64, need_mask);
-            mx::tmem_st16(tm_p + 32, pk23);
-            if (FIRST) sum_rounded16(pk23);
-            exp32(vb + 32, pk23, key0 + 96, need_mask);
-            mx::tmem_st16(tm_p + 48, pk23);
-            if (FIRST) {
-                sum_rounded16(pk23);
+                sum_rounded16(pk);
                 l_first = sum_now();
             }
             mx::tmem_wait_st();
@@ -490,53 +494,61 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         l = sum_now();
         l_norm = l - l_first + ((rb[0] + rb[1]) + (rb[2] + rb[3]));
         } else {
-        // ---- general loop: running row max, raised lazily
+        // ---- general loop: running row max, raised lazily.  Each half takes the max of its own 64 columns and the two
+        // exchange them through shared memory (one bounded barrier per tile and query tile); both then hold the same
+        // row max and take the same decisions, exponentiate their own columns and rescale their own 32 columns of O.
         float row_a = 0.0f, row_qsum = 0.0f;
         if (i8_scores && row < NQ) {
             row_a = P.row_a[(size_t)bh * NQ + row];
             row_qsum = P.row_qsum[(size_t)bh * NQ + row];
         }
+        float *xmax = (float *)(smem + SMEM_XMAX) + t * 2 * HALVES * BM;   // [2 tile parities][HALVES][BM]
         for (int j = 0; j < n_t; ++j, ++cnt) {
             ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_S_FULL + t), cnt & 1, abort_flag, P.status));
             if (!ok) break;
             mx::tc_fence_after();
-            // the whole score row into registers with one round trip, then S_t is free again
-            uint32_t v[BN];
-#pragma unroll
-            for (int cc = 0; cc < BN / 32; ++cc) mx::tmem_ld32(tm_s + cc * 32, *(uint32_t(*)[32])(v + cc * 32));
+            mx::tmem_ld32(tm_s, va);
+            mx::tmem_ld32(tm_s + 32, vb);
             mx::tmem_wait_ld();
             mx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) mx::mbar_arrive(bar(BAR_S_FREE + t));
-
-            const int key0 = j * BN;
+            if (lane == 0) mx::mbar_arrive(bar(BAR_S_FREE + t));   // this group's columns have left S_t
+            const int key0 = j * BN, col0 = half * (BN / 2);
             if (i8_scores) {
                 // the tile holds exact integer dots of int8 codes: the reference kernel's score for them
-                const float2 *cs = P.col_kskb + (size_t)(bh / P.kv_group) * P.n_k_pad + key0;
+                const float2 *cs = P.col_kskb + (size_t)(bh / P.kv_group) * P.n_k_pad + key0 + col0;
 #pragma unroll
-                for (int i = 0; i < BN; ++i) {
-                    const float2 kk = __ldg(cs + i);
-                    v[i] = __float_as_uint(row_a * fmaf(__uint_as_float(v[i]), kk.x, row_qsum * kk.y));
+                for (int i = 0; i < 32; ++i) {
+                    const float2 k0 = __ldg(cs + i), k1 = __ldg(cs + 32 + i);
+                    va[i] = __float_as_uint(row_a * fmaf(__uint_as_float(va[i]), k0.x, row_qsum * k0.y));
+                    vb[i] = __float_as_uint(row_a * fmaf(__uint_as_float(vb[i]), k1.x, row_qsum * k1.y));
                 }
             }
             if ((key0 + BN > N) || (P.causal && key0 + BN - 1 > q0 + t * BM + P.q_off)) {
 #pragma unroll
-                for (int i = 0; i < BN; ++i)
-                    if (key0 + i > last) v[i] = 0xFF800000u;  // -inf
+                for (int i = 0; i < 32; ++i) {
+                    if (key0 + col0 + i > last) va[i] = 0xFF800000u;  // -inf
+                    if (key0 + col0 + 32 + i > last) vb[i] = 0xFF800000u;
+                }
             }
             // four independent max chains (a single chain would serialise on the ALU latency)
             float mx4[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                mx4[u] = fmax3(__uint_as_float(v[u * 32]), __uint_as_float(v[u * 32 + 1]), __uint_as_float(v[u * 32 + 2]));
+            for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(__uint_as_float(va[u]), __uint_as_float(vb[u]));
 #pragma unroll
-            for (int i = 3; i + 1 < 32; i += 2)
+            for (int i = 4; i < 32; i += 4)
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    mx4[u] = fmax3(mx4[u], __uint_as_float(v[u * 32 + i]), __uint_as_float(v[u * 32 + i + 1]));
-            float mx_ = fmaxf(fmax3(mx4[0], mx4[1], mx4[2]), mx4[3]);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) mx_ = fmaxf(mx_, __uint_as_float(v[u * 32 + 31]));
+                for (int u = 0; u < 4; ++u) mx4[u] = fmax3(mx4[u], __uint_as_float(va[i + u]), __uint_as_float(vb[i + u]));
+            float mx_ = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // exchange with the other half of the row
+            float *xm = xmax + (cnt & 1) * HALVES * BM;
+            xm[half * BM + row_in_tile] = mx_;
+            __syncwarp();
+            if (lane == 0) mx::mbar_arrive(bar(BAR_XMAX + t));
+            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_XMAX + t), xmc & 1, abort_flag, P.status));
+            ++xmc;
+            if (!ok) break;
+            mx_ = fmaxf(mx_, xm[(1 - half) * BM + row_in_tile]);
             // raise the running max only when it pays (always on the first tile)
             const bool raise = (j == 0) || ((mx_ - m) * c > RESCALE_LOG2);
             const float m_new = raise ? mx_ : m;
@@ -550,30 +562,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 mx::tc_fence_after();
                 if (__any_sync(0xFFFFFFFFu, raise)) {
 #pragma unroll 1
-                    for (int cc = 0; cc < HD / 16; ++cc) {
+                    for (int cc = 0; cc < 2; ++cc) {
                         uint32_t o[16];
-                        mx::tmem_ld16(tm_o + cc * 16, o);
+                        mx::tmem_ld16(tm_o + half * 32 + cc * 16, o);
                         mx::tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        mx::tmem_st16(tm_o + cc * 16, o);
+                        mx::tmem_st16(tm_o + half * 32 + cc * 16, o);
                     }
                 }
             }
             float rs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t pk[16];
 #pragma unroll
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = mx::ex2(fmaf(__uint_as_float(v[cc * 32 + i]), c, nmc));
-                    const float p1 = mx::ex2(fmaf(__uint_as_float(v[cc * 32 + i + 1]), c, nmc));
-                    rs[i & 2] += p0;
-                    rs[(i & 2) + 1] += p1;
-                    pk[i >> 1] = mx::pack_bf16(p0, p1);
-                }
-                mx::tmem_st16(tm_p + cc * 16, pk);
+            for (int i = 0; i < 32; i += 2) {
+                const float p0 = mx::ex2(fmaf(__uint_as_float(va[i]), c, nmc));
+                const float p1 = mx::ex2(fmaf(__uint_as_float(va[i + 1]), c, nmc));
+                rs[i & 2] += p0;
+                rs[(i & 2) + 1] += p1;
+                pk[i >> 1] = mx::pack_bf16(p0, p1);
             }
+            mx::tmem_st16(tm_p, pk);
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float p0 = mx::ex2(fmaf(__uint_as_float(vb[i]), c, nmc));
+                const float p1 = mx::ex2(fmaf(__uint_as_float(vb[i + 1]), c, nmc));
+                rs[i & 2] += p0;
+                rs[(i & 2) + 1] += p1;
+                pk[i >> 1] = mx::pack_bf16(p0, p1);
+            }
+            mx::tmem_st16(tm_p + 16, pk);
             l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));
             m = m_new;
             mx::tmem_wait_st();
@@ -581,14 +599,35 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             __syncwarp();
             if (lane == 0) mx::mbar_arrive(bar(BAR_P_FULL + t));
         }
+        l_norm = l;
+        }
+        // The two halves of a row add their sums: half 1 publishes its pair and goes on to the next item, half 0 waits
+        // for it (and for the tile's last P V) and does the tile's epilogue.
+        float *xch = (float *)(smem + SMEM_XCH) + ((it & 1) * QT + t) * 2 * BM;
+        if (half == 1) {
+            // (the tile's last P V must have read this group's share of P_t before the next item's first tile overwrites it)
+            if (ok && n_t > 0)
+                ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_O_DONE + t), (cnt - 1) & 1, abort_flag, P.status));
+            if (ok) {
+                xch[row_in_tile] = l;
+                xch[BM + row_in_tile] = l_norm;
+                __syncwarp();
+                if (lane == 0) mx::mbar_arrive(bar(BAR_XCH + t));
+            }
+        } else if (ok) {
+            ok = __all_sync(0xFFFFFFFFu, mx::mbar_wait(bar(BAR_XCH + t), it & 1, abort_flag, P.status));
+            if (ok) {
+                l += xch[row_in_tile];
+                l_norm += xch[BM + row_in_tile];
+            }
         }
         // epilogue: O / l and the log-sum-exp
-        if (ok && n_t > 0) {
+        if (ok && n_t > 0 && half == 0) {
             ok = __all_sync(0xFFFFFFFFu,
                             mx::mbar_wait(bar(BAR_O_DONE + t), (cnt - 1) & 1, abort_flag, P.status));
             if (ok) {
                 mx::tc_fence_after();
-                const float inv = 1.0f / (fast ? l_norm : l);
+                const float inv = 1.0f / l_norm;
                 float *orow = P.O + (size_t)bh * P.o_head_stride + (size_t)row * P.o_row_stride;
                 if (P.tma_out) {
                     // each warp stages its 32 rows, 32 columns at a time, in a swizzled 4 KB piece of this tile's Q
@@ -596,17 +635,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     // end: 16-byte stores from lane = row registers each touch a sector of their own
                     const int wrow0 = q0 + t * BM + (warp & 3) * 32;
                     const int st_off = SMEM_Q + (qbuf * QT + t) * TILE_BYTES + (warp & 3) * 4096;
-#pragma unroll
+#pragma unroll 1
                     for (int cc = 0; cc < HD / 32; ++cc) {
-                        uint32_t o[32];
-                        mx::tmem_ld32(tm_o + cc * 32, o);
+                        mx::tmem_ld32(tm_o + cc * 32, va);
                         mx::tmem_wait_ld();
                         unsigned char *srow = smem + st_off + lane * 128;
 #pragma unroll
                         for (int cch = 0; cch < 8; ++cch)
                             *(float4 *)(srow + ((cch ^ (lane & 7)) << 4)) =
-                                make_float4(__uint_as_float(o[4 * cch]) * inv, __uint_as_float(o[4 * cch + 1]) * inv,
-                                            __uint_as_float(o[4 * cch + 2]) * inv, __uint_as_float(o[4 * cch + 3]) * inv);
+                                make_float4(__uint_as_float(va[4 * cch]) * inv, __uint_as_float(va[4 * cch + 1]) * inv,
+                                            __uint_as_float(va[4 * cch + 2]) * inv, __uint_as_float(va[4 * cch + 3]) * inv);
                         mx::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0 && wrow0 < NQ) {
@@ -617,16 +655,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         __syncwarp();
                     }
                 } else
-#pragma unroll
+#pragma unroll 1
                 for (int cc = 0; cc < HD / 32; ++cc) {
-                    uint32_t o[32];
-                    mx::tmem_ld32(tm_o + cc * 32, o);
+                    mx::tmem_ld32(tm_o + cc * 32, va);
                     mx::tmem_wait_ld();
                     if (row < NQ) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 4) {
-                            float4 o4 = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
-                                                    __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                            float4 o4 = make_float4(__uint_as_float(va[i]) * inv, __uint_as_float(va[i + 1]) * inv,
+                                                    __uint_as_float(va[i + 2]) * inv, __uint_as_float(va[i + 3]) * inv);
                             *(float4 *)(orow + cc * 32 + i) = o4;
                         }
                     }
@@ -644,7 +681,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mx::tc_fence_before();
     __syncthreads();
     mx::tc_fence_after();
-    if (warp == 9) mx::tmem_dealloc(tmem, TM_COLS);
+    if (warp == SOFT_WARPS + 1) mx::tmem_dealloc(tmem, TM_COLS);
 }
 
 // fp32 -> bf16 (round to nearest even) for up to four equally sized tensors of `heads` x `per_head4` float4s.
