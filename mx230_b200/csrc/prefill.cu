@@ -20,25 +20,51 @@ namespace {
 
 constexpr int HD = 64;
 
+// Largest value of `v` over the block (v >= 0), returned to thread 0
+__device__ __forceinline__ float block_max256(float v) {
+    __shared__ float part[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 8) {
+        v = part[threadIdx.x];
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFu, v, o));
+    }
+    return v;
+}
+
 // out[h][r][0..63] (bf16) <- qkv[r*stride + h*64 + 0..63] * 1/sqrt(64) * log2(e), so that the attention
-// kernel's scores arrive in log2 units (one rounding, from the fp32 product); 8 elements per thread
-__global__ void stage_q_kernel(__nv_bfloat16 *out, const float *qkv, int n_tok, int n_head, int stride) {
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // over n_head*n_tok*8
-    size_t total = (size_t)n_head * n_tok * 8;
-    if (idx >= total) return;
-    int c = (int)(idx & 7);
-    size_t hr = idx >> 3;
-    int r = (int)(hr % n_tok);
-    int h = (int)(hr / n_tok);
-    const float4 *src = (const float4 *)(qkv + (size_t)r * stride + h * HD + c * 8);
-    float4 a = src[0], b = src[1];
+// kernel's scores arrive in log2 units (one rounding, from the fp32 product).  Grid (MX230_NORM_PARTS, n_head): block
+// (p, h) stages the rows r = p (mod 32) of head h, eight threads per row, and leaves the largest squared norm of its
+// (unscaled) rows in norm2[h][p]: with the keys' norms that bounds every score of the head, which lets the attention
+// kernel run without a row max.
+__global__ void stage_q_kernel(__nv_bfloat16 *out, float *norm2, const float *qkv, int n_tok, int n_head, int stride) {
+    const int p = blockIdx.x, h = blockIdx.y;
+    const int c = threadIdx.x & 7, slot = threadIdx.x >> 3;
     const float sc = MX230_QK_LOG2_SCALE;
-    uint4 o;
-    o.x = mx::pack_bf16(a.x * sc, a.y * sc);
-    o.y = mx::pack_bf16(a.z * sc, a.w * sc);
-    o.z = mx::pack_bf16(b.x * sc, b.y * sc);
-    o.w = mx::pack_bf16(b.z * sc, b.w * sc);
-    *(uint4 *)(out + ((size_t)h * n_tok + r) * HD + c * 8) = o;
+    float best = 0.0f;
+    for (int r0 = p; r0 < n_tok; r0 += MX230_NORM_PARTS * 32) {
+        const int r = r0 + MX230_NORM_PARTS * slot;
+        float ss = 0.0f;
+        if (r < n_tok) {
+            const float4 *src = (const float4 *)(qkv + (size_t)r * stride + h * HD + c * 8);
+            const float4 a = src[0], b = src[1];
+            ss = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+            uint4 o;
+            o.x = mx::pack_bf16(a.x * sc, a.y * sc);
+            o.y = mx::pack_bf16(a.z * sc, a.w * sc);
+            o.z = mx::pack_bf16(b.x * sc, b.y * sc);
+            o.w = mx::pack_bf16(b.z * sc, b.w * sc);
+            *(uint4 *)(out + ((size_t)h * n_tok + r) * HD + c * 8) = o;
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);   // the row's eight threads
+        best = fmaxf(best, ss);
+    }
+    best = block_max256(best);
+    if (threadIdx.x == 0) norm2[h * MX230_NORM_PARTS + p] = best;
 }
 
 struct StageKv {
@@ -51,45 +77,55 @@ struct StageKv {
     int n_keys, n_kv_head;
 };
 
-// one thread stages 8 consecutive dims of one (key, kv head) for K and V
-__global__ void stage_kv_kernel(const StageKv P) {
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // over n_keys*n_kv_head*8
-    size_t total = (size_t)P.n_keys * P.n_kv_head * 8;
-    if (idx >= total) return;
-    int c = (int)(idx & 7);
-    size_t th = idx >> 3;
-    int h = (int)(th % P.n_kv_head);
-    int t = (int)(th / P.n_kv_head);
-    size_t row = P.bt ? (size_t)(P.bt[t / P.bs] * P.bs + t % P.bs) : (size_t)t;
-    size_t kvd = (size_t)P.n_kv_head * HD;
-    size_t dst = ((size_t)h * P.n_keys + t) * HD + c * 8;
-    float k[8], v[8];
-    if (P.kq) {
-        int2 kw = *(const int2 *)(P.kq + row * kvd + h * HD + c * 8);
-        int2 vw = *(const int2 *)(P.vq + row * kvd + h * HD + c * 8);
-        float ksc = P.ks[row * P.n_kv_head + h], vsc = P.vs[row * P.n_kv_head + h];
-        float kbe = P.kb ? P.kb[row * P.n_kv_head + h] : 0.0f, vbe = P.vb ? P.vb[row * P.n_kv_head + h] : 0.0f;
-        const int kk[2] = {kw.x, kw.y}, vv[2] = {vw.x, vw.y};
+// Grid (MX230_NORM_PARTS, n_kv_head): block (p, h) stages the keys t = p (mod 32) of K/V head h, eight threads per key (8
+// consecutive dims of K and of V each), and leaves the largest squared norm of its staged K rows in norm2[h][p].
+__global__ void stage_kv_kernel(const StageKv P, float *norm2) {
+    const int p = blockIdx.x, h = blockIdx.y;
+    const int c = threadIdx.x & 7, slot = threadIdx.x >> 3;
+    const size_t kvd = (size_t)P.n_kv_head * HD;
+    float best = 0.0f;
+    for (int t0 = p; t0 < P.n_keys; t0 += MX230_NORM_PARTS * 32) {
+        const int t = t0 + MX230_NORM_PARTS * slot;
+        float ss = 0.0f;
+        if (t < P.n_keys) {
+            const size_t row = P.bt ? (size_t)(P.bt[t / P.bs] * P.bs + t % P.bs) : (size_t)t;
+            const size_t dst = ((size_t)h * P.n_keys + t) * HD + c * 8;
+            float k[8], v[8];
+            if (P.kq) {
+                int2 kw = *(const int2 *)(P.kq + row * kvd + h * HD + c * 8);
+                int2 vw = *(const int2 *)(P.vq + row * kvd + h * HD + c * 8);
+                float ksc = P.ks[row * P.n_kv_head + h], vsc = P.vs[row * P.n_kv_head + h];
+                float kbe = P.kb ? P.kb[row * P.n_kv_head + h] : 0.0f, vbe = P.vb ? P.vb[row * P.n_kv_head + h] : 0.0f;
+                const int kk[2] = {kw.x, kw.y}, vv[2] = {vw.x, vw.y};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            // dequantise as the reference does into its V tile: code * scale + beta (llm.cu:3759-3764)
-            k[i] = (float)(int8_t)((kk[i >> 2] >> (8 * (i & 3))) & 0xFF) * ksc + kbe;
-            v[i] = (float)(int8_t)((vv[i >> 2] >> (8 * (i & 3))) & 0xFF) * vsc + vbe;
+                for (int i = 0; i < 8; ++i) {
+                    // dequantise as the reference does into its V tile: code * scale + beta (llm.cu:3759-3764)
+                    k[i] = (float)(int8_t)((kk[i >> 2] >> (8 * (i & 3))) & 0xFF) * ksc + kbe;
+                    v[i] = (float)(int8_t)((vv[i >> 2] >> (8 * (i & 3))) & 0xFF) * vsc + vbe;
+                }
+            } else {
+                const float4 *kp = (const float4 *)(P.kcache + row * kvd + h * HD + c * 8);
+                const float4 *vp = (const float4 *)(P.vcache + row * kvd + h * HD + c * 8);
+                float4 a = kp[0], b = kp[1], e = vp[0], f = vp[1];
+                k[0] = a.x, k[1] = a.y, k[2] = a.z, k[3] = a.w, k[4] = b.x, k[5] = b.y, k[6] = b.z, k[7] = b.w;
+                v[0] = e.x, v[1] = e.y, v[2] = e.z, v[3] = e.w, v[4] = f.x, v[5] = f.y, v[6] = f.z, v[7] = f.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += k[i] * k[i];
+            uint4 ko, vo;
+            ko.x = mx::pack_bf16(k[0], k[1]), ko.y = mx::pack_bf16(k[2], k[3]);
+            ko.z = mx::pack_bf16(k[4], k[5]), ko.w = mx::pack_bf16(k[6], k[7]);
+            vo.x = mx::pack_bf16(v[0], v[1]), vo.y = mx::pack_bf16(v[2], v[3]);
+            vo.z = mx::pack_bf16(v[4], v[5]), vo.w = mx::pack_bf16(v[6], v[7]);
+            *(uint4 *)(P.kout + dst) = ko;
+            *(uint4 *)(P.vout + dst) = vo;
         }
-    } else {
-        const float4 *kp = (const float4 *)(P.kcache + row * kvd + h * HD + c * 8);
-        const float4 *vp = (const float4 *)(P.vcache + row * kvd + h * HD + c * 8);
-        float4 a = kp[0], b = kp[1], e = vp[0], f = vp[1];
-        k[0] = a.x, k[1] = a.y, k[2] = a.z, k[3] = a.w, k[4] = b.x, k[5] = b.y, k[6] = b.z, k[7] = b.w;
-        v[0] = e.x, v[1] = e.y, v[2] = e.z, v[3] = e.w, v[4] = f.x, v[5] = f.y, v[6] = f.z, v[7] = f.w;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);   // the key's eight threads
+        best = fmaxf(best, ss);
     }
-    uint4 ko, vo;
-    ko.x = mx::pack_bf16(k[0], k[1]), ko.y = mx::pack_bf16(k[2], k[3]);
-    ko.z = mx::pack_bf16(k[4], k[5]), ko.w = mx::pack_bf16(k[6], k[7]);
-    vo.x = mx::pack_bf16(v[0], v[1]), vo.y = mx::pack_bf16(v[2], v[3]);
-    vo.z = mx::pack_bf16(v[4], v[5]), vo.w = mx::pack_bf16(v[6], v[7]);
-    *(uint4 *)(P.kout + dst) = ko;
-    *(uint4 *)(P.vout + dst) = vo;
+    best = block_max256(best);
+    if (threadIdx.x == 0) norm2[h * MX230_NORM_PARTS + p] = best;
 }
 
 // ---- int8 score mode (the reference kernels' own arithmetic, llm.cu:3700-3716,3737-3754,3774-3782) ----
@@ -208,7 +244,8 @@ int prefill(mx230_handle *h, void *stream, float *out, const float *qkv, const f
     size_t kbytes = align1k((size_t)n_kv_head * n_keys * HD * 2);
     size_t rbytes = align1k((size_t)n_head * n_tok * 4);
     size_t cbytes = align1k((size_t)n_kv_head * n_k_pad * 8);
-    size_t need = qbytes + 2 * kbytes + 2 * rbytes + cbytes;
+    size_t nbytes = align1k((size_t)(n_head + n_kv_head) * MX230_NORM_PARTS * 4);
+    size_t need = qbytes + 2 * kbytes + 2 * rbytes + cbytes + nbytes;
     MX_REQUIRE(h->ws && need <= h->ws_bytes, MX230_ERR_WORKSPACE,
                "%s: workspace %zu B < %zu B needed (call mx230_reserve)", who, h->ws_bytes, need);
     mx230_device_guard guard(h->device);
@@ -220,6 +257,8 @@ int prefill(mx230_handle *h, void *stream, float *out, const float *qkv, const f
     float *row_a = (float *)((char *)h->ws + qbytes + 2 * kbytes);
     float *row_qsum = (float *)((char *)row_a + rbytes);
     float2 *kskb = (float2 *)((char *)row_qsum + rbytes);
+    float *q_norm2 = (float *)((char *)kskb + cbytes);
+    float *k_norm2 = q_norm2 + (size_t)n_head * MX230_NORM_PARTS;
     StageKv S{kbuf, vbuf, kcache, vcache, kq, vq, ks, vs, kb, vb, bt, bs, n_keys, n_kv_head};
     size_t tk = (size_t)n_keys * n_kv_head * 8;
     // Which score arithmetic: over an int8 cache the handle's MX230_OPT_Q8_SCORE_MODE decides, as for decode
@@ -237,12 +276,13 @@ int prefill(mx230_handle *h, void *stream, float *out, const float *qkv, const f
                                          n_head / n_kv_head, HD, out_stride, 1, 0, nullptr, nullptr, row_a, row_qsum,
                                          (const float *)kskb);
     }
-    size_t tq = (size_t)n_head * n_tok * 8;
+    // values (fp32 cache, or an int8 cache in the exact score mode): the staging kernels also leave the row norms that
+    // let the attention kernel take its max-free path whenever the head's scores are bounded
     MX_LAUNCH(h, st, MX230_K_PREFILL,
-              (stage_q_kernel<<<(unsigned)((tq + 255) / 256), 256, 0, st>>>(qb, qkv, n_tok, n_head, qkv_stride)));
-    MX_LAUNCH(h, st, MX230_K_PREFILL, (stage_kv_kernel<<<(unsigned)((tk + 255) / 256), 256, 0, st>>>(S)));
+              (stage_q_kernel<<<dim3(MX230_NORM_PARTS, n_head), 256, 0, st>>>(qb, q_norm2, qkv, n_tok, n_head, qkv_stride)));
+    MX_LAUNCH(h, st, MX230_K_PREFILL, (stage_kv_kernel<<<dim3(MX230_NORM_PARTS, n_kv_head), 256, 0, st>>>(S, k_norm2)));
     return mx230_launch_flash_fwd_ex(h, st, qb, kbuf, vbuf, out, nullptr, n_head, n_tok, n_keys, pos0,
-                                     n_head / n_kv_head, HD, out_stride, 1, 1, nullptr, nullptr, nullptr, nullptr, nullptr);
+                                     n_head / n_kv_head, HD, out_stride, 1, 1, q_norm2, k_norm2, nullptr, nullptr, nullptr);
 }
 
 }  // namespace
@@ -251,7 +291,8 @@ extern "C" size_t mx230_prefill_workspace_bytes(int n_tok, int n_keys, int n_hea
     if (n_tok <= 0 || n_keys <= 0 || n_head <= 0 || n_kv_head <= 0) return 0;
     // staged bf16 Q, K, V, then (int8 score mode) the per-row q factors and the per-key (scale, offset) pairs
     return align1k((size_t)n_head * n_tok * HD * 2) + 2 * align1k((size_t)n_kv_head * n_keys * HD * 2) +
-           2 * align1k((size_t)n_head * n_tok * 4) + align1k((size_t)n_kv_head * ((n_keys + 127) / 128 * 128) * 8);
+           2 * align1k((size_t)n_head * n_tok * 4) + align1k((size_t)n_kv_head * ((n_keys + 127) / 128 * 128) * 8) +
+           align1k((size_t)(n_head + n_kv_head) * MX230_NORM_PARTS * 4);
 }
 
 extern "C" int mx230_attn_prefill(mx230_handle *h, void *stream, float *out, const float *qkv,

@@ -115,3 +115,32 @@ def test_prefill_step_writes_cache_then_attends(handle):
     o1 = torch.zeros(qd, device="cuda")
     la.attn_decode(handle, o1, d[pos0 + n_tok - 1], c, pos0 + n_tok - 1, nh, nkv, 64)
     assert_close(out[-1].cpu().numpy(), o1.cpu().numpy(), "prefill row vs decode")
+
+
+@pytest.mark.parametrize("scale", [1.0, 6.0])
+def test_prefill_fp32_cache_small_and_large_scores(handle, scale):
+    """The staging kernels leave the row norms of Q and K; bounded scores (scale 1) let the attention kernel run without
+    a row max, large ones (scale 6: |q . k| / 8 * log2(e) far above 80) must take the running-max path.  Both against
+    the oracle; the inputs are bf16-representable after staging so that at large scores the comparison is not about
+    the rounding of q and k."""
+    nh, nkv, pos0, n_tok = 8, 2, 40, 260
+    qd, kvd = nh * 64, nkv * 64
+    stride = qd + 2 * kvd
+    n_keys = pos0 + n_tok
+    bf = lambda x: torch.from_numpy(np.ascontiguousarray(x, np.float32)).to(torch.bfloat16).float().numpy()
+    c = np.float32(0.125 * 1.4426950408889634)
+    rows = oracle.normal((n_keys, stride), 555, 0)
+    rows[:, :qd] = bf(scale * rows[:, :qd] * c) / c     # q is staged as q * scale * log2(e)
+    rows[:, qd:] = bf(np.concatenate([scale * rows[:, qd:qd + kvd], rows[:, qd + kvd:]], axis=1))
+    rows = rows.astype(np.float32)
+    kc, vc = np.zeros((n_keys, kvd), np.float32), np.zeros((n_keys, kvd), np.float32)
+    for t in range(n_keys):
+        oracle.copy_kv_row(kc, vc, rows[t], t, qd, kvd)
+    cch = la.KvCache(n_keys, nkv)
+    cch.k.copy_(dev(kc)), cch.v.copy_(dev(vc))
+    new = np.ascontiguousarray(rows[pos0:])
+    want = oracle.prefill(new, pos0, n_tok, nh, nkv, stride, qd, kcache=kc, vcache=vc)
+    out = torch.zeros(n_tok, qd, device="cuda")
+    la.attn_prefill(handle, out, dev(new), cch, pos0, n_tok, nh, nkv, stride, qd)
+    handle.check_status()
+    assert_close(out.cpu().numpy(), want, f"prefill, score scale {scale}")
