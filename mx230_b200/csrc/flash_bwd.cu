@@ -59,6 +59,9 @@ constexpr int BWD_THREADS = 512;
 #define BWD_REGS_COMPUTE 192
 #define BWD_REGS_SERVICE 64
 #endif
+#ifndef BWD_SPLIT_LOAD
+#define BWD_SPLIT_LOAD 1   // X, Y of a tile are pulled in two 32-column pieces, the second under the first one's arithmetic (fused pass: 290 -> 281 us)
+#endif
 #ifndef BWD_POLY
 #define BWD_POLY 0         // fused pass: of every four column pairs, how many take 2^x from the FMA-pipe polynomial
 #endif
@@ -572,6 +575,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             if (!ok) break;
             mx::tc_fence_after();
             uint32_t xv[HS], yv[HS];
+#if BWD_SPLIT_LOAD
+            // the second 32 columns are requested once the first have landed and arrive under their arithmetic
+            mx::tmem_ld32(tm_row + TM_X + h * HS, *(uint32_t(*)[32])(xv));
+            mx::tmem_ld32(tm_row + TM_Y + h * HS, *(uint32_t(*)[32])(yv));
+            mx::tmem_wait_ld();
+            mx::tmem_ld32(tm_row + TM_X + h * HS + 32, *(uint32_t(*)[32])(xv + 32));
+            mx::tmem_ld32(tm_row + TM_Y + h * HS + 32, *(uint32_t(*)[32])(yv + 32));
+#else
             mx::tmem_ld32(tm_row + TM_X + h * HS, *(uint32_t(*)[32])(xv));
             mx::tmem_ld32(tm_row + TM_X + h * HS + 32, *(uint32_t(*)[32])(xv + 32));
             mx::tmem_ld32(tm_row + TM_Y + h * HS, *(uint32_t(*)[32])(yv));
@@ -580,20 +591,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
             mx::tc_fence_before();
             __syncwarp();
             if (lane == 0) mx::mbar_arrive(bar(BAR_SDP_FREE));
+#endif
 
             const int str0 = (it_beg + y) * BS + h * HS;    // first streamed row of this half
             const bool need_mask = (str0 + HS > N) ||
                                    (P.causal && (MODE == 0 ? (str0 + HS - 1 > own0) : (str0 < own0 + BT - 1)));
             const float *ld = (const float *)(smem + SM_LD + s * (2 * BS * 4)) + h * HS;
-            if (need_mask) {
+            auto mask_cols = [&](int i0, int i1) {
                 // masked scores become -inf up front (p = 0, so E = 0): the main loop stays branch-free
 #pragma unroll
-                for (int i = 0; i < HS; ++i) {
+                for (int i = i0; i < i1; ++i) {
                     const int c0 = str0 + i;
                     const bool v0 = c0 < N && (!P.causal || (MODE == 0 ? c0 <= row : c0 >= row));
                     if (!v0) xv[i] = 0xFF800000u;
                 }
-            }
+            };
+            if (need_mask) mask_cols(0, BWD_SPLIT_LOAD ? 32 : HS);
             uint32_t pe[HS / 2], pp[MODE >= 1 ? HS / 2 : 1];
             // fused pass: E goes to shared memory as bf16, this thread's key row = one 128-byte swizzled line of
             // 64 queries.  Two buffers: the MMAs of tile y-1 may still read the other one (those of y-2 are
@@ -602,6 +615,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmOwnA, const __grid_constant__ C
                                    (tid & 127) * 128;
 #pragma unroll
             for (int i = 0; i < HS; i += 2) {
+#if BWD_SPLIT_LOAD
+                if (i == 32) {   // the second half of this thread's X, Y is in registers: the MMAs may overwrite them
+                    mx::tmem_wait_ld();
+                    mx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mx::mbar_arrive(bar(BAR_SDP_FREE));
+                    if (need_mask) mask_cols(32, HS);
+                }
+#endif
                 if (MODE == 1) {
                     const float2 l2 = *(const float2 *)(ld + i), d2 = *(const float2 *)(ld + BS + i);
                     nl0 = l2.x, nl1 = l2.y, nd0 = d2.x, nd1 = d2.y;
