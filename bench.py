@@ -53,7 +53,7 @@ DKV_FLOP = BWD_FLOP * 3.0 / 5.0
 WORKLOAD = "causal flash-attention fwd+bwd, B=4 H=12 N=4096 d=64, fp32 in/out, bf16 operands"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the tensor kernels on this exact workload, from one
 # ncu capture each (the operands, 4 x 25 MB bf16 + fp32 outputs, mostly stay in the 126 MB L2)
-NCU_DRAM_BYTES_PER_LAUNCH = {"flash_fwd_kernel": 86384128 + 18874368, "bwd_fused_kernel": 331904000 + 208673792,
+NCU_DRAM_BYTES_PER_LAUNCH = {"flash_fwd_kernel": 86331904 + 18123776, "bwd_fused_kernel": 328961536 + 207100928,
                              "bwd_dq_kernel": 106472960 + 25134592, "bwd_dkv_kernel": 108812800 + 60150016}
 NOMINAL_BF16_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
