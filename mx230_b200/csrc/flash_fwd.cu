@@ -12,15 +12,19 @@
 //     that every CTA gets the same number of key tiles), and every role runs ahead into the next
 //     item on its own, so the next item's Q / K loads and first Q K^T run under the current
 //     item's last softmax and its epilogue;
-//   * warp 8 streams Q (two buffers, alternating by item) and K/V tiles (128 keys) through a
+//   * warps 0-15 are four softmax warpgroups, two per query tile (tile t = warp / 8), each taking 64 of
+//     the 128 key columns of every score tile, one thread per (query row, half): the thread pulls its
+//     columns into registers 32 at a time (the second piece lands under the first one's exponentials),
+//     which frees S_t for the next Q K^T, takes exp2 and the row sum, and writes bf16 P into its own
+//     tensor-memory columns.  Usually without a row max (see the fixed-reference mode below: the
+//     halves of a row then meet only once per item, to add their sums); otherwise the halves exchange
+//     their part of the row max through shared memory and O_t is rescaled in tensor memory only when
+//     the max grows by > 2^8;
+//   * warp 16 streams Q (two buffers, alternating by item) and K/V tiles (128 keys) through a
 //     4-stage shared-memory ring with plain per-CTA TMA tile loads (128-byte swizzle);
-//   * warp 9 issues the tcgen05.mma stream S_t = Q_t K^T into tensor memory (128 fp32 columns
-//     per tile), warp 10 the stream O_t += P_t V with P_t read from tensor memory as bf16 (a
-//     thread issues an MMA about every 60 cycles, so each stream has its own thread);
-//   * warps 0-3 / 4-7 are the softmax groups of tile 0 / 1, one thread per query row: the
-//     score row is pulled into registers in one round trip (which frees S_t for the next
-//     QK^T at once), then row max, exp2, row sum, bf16 P into its own tensor-memory
-//     columns; O_t is rescaled in tensor memory only when the row max grows by > 2^8.
+//   * warp 17 issues the tcgen05.mma stream S_t = Q_t K^T into tensor memory (128 fp32 columns
+//     per tile), warp 18 the stream O_t += P_t V with P_t read from tensor memory as bf16 (each
+//     stream has its own warp, which runs its loop warp-uniformly with one elected lane issuing).
 //   The two tiles ping-pong and S, P, O never alias, so the tensor core computes the next
 //   scores and the other tile's P V while a tile's softmax runs on the CUDA cores.
 //
@@ -43,8 +47,8 @@ constexpr int TILE_BYTES = BN * HD * 2;  // 16 KB
 constexpr int HALVES = 2;               // softmax groups per query tile: each takes half of the tile's key columns
 constexpr int SOFT_WARPS = QT * HALVES * 4;   // 16
 constexpr int FWD_THREADS = (SOFT_WARPS + 4) * 32;   // 640: four softmax warpgroups + {TMA, 2 MMA issuers, idle}
-// setmaxnreg moves registers only inside the CTA's launch-time allocation (168 per thread for 384
-// threads): what the softmax warps gain must have been released by the third warpgroup, or the
+// setmaxnreg moves registers only inside the CTA's launch-time allocation (96 per thread for 640
+// threads): what the softmax warps gain must have been released by the service warpgroup, or the
 // increase would block for ever.
 #ifndef FWD_REGS_SOFTMAX
 #define FWD_REGS_SOFTMAX 104
@@ -210,8 +214,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mx::tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    // register budget: the softmax warpgroups hold a 128-value score row per thread, the
-    // third warpgroup (TMA, two MMA issuers, one idle warp) needs few
+    // register budget: a softmax thread holds 64 score values and their packed probabilities, the
+    // service warpgroup (TMA, two MMA issuers, one idle warp) needs few
     if (warp >= SOFT_WARPS) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FWD_REGS_SERVICE));
         if (warp == SOFT_WARPS) {
