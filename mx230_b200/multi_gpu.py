@@ -143,10 +143,10 @@ class SplitKvDecoder:
         self.h, self.plan, self.rank, self.group = handle, plan, rank, group
         if fused and plan.rows % 2:
             raise ValueError("the fused exchange needs an even number of (sequence, head) rows")
-        self.peer = PeerExchange(handle, rank, plan.world, plan.rows, plan.head_dim, group) if fused else None
         self.mode = "one" if fused is True else fused
         if fused and self.mode not in ("one", "push", "exchange"):
             raise ValueError(f"unknown fused mode {fused!r}")
+        self.peer = PeerExchange(handle, rank, plan.world, plan.rows, plan.head_dim, group) if fused else None
         self.gathered = torch.zeros(plan.world, plan.floats_per_rank, dtype=torch.float32, device=device)
         # alone, the rank writes its partial straight into the gathered buffer
         self.local = self.gathered[0] if plan.world == 1 and not fused else torch.zeros(

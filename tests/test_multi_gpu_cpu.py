@@ -93,3 +93,12 @@ def test_split_kv_over_gloo_world2(ctx):
         assert len(results) == world
         for r in range(world):
             assert results[r] < 5e-6, dict(results)
+
+
+def test_split_kv_decoder_rejects_bad_fused_arguments_before_touching_the_device():
+    """An odd row count or an unknown mode is refused by the constructor itself, before any library call."""
+    from mx230_b200.multi_gpu import SplitKvDecoder, SplitKvPlan
+    with pytest.raises(ValueError):
+        SplitKvDecoder(None, SplitKvPlan(ctx=256, world=2, n_seq=1, n_head=7), 0, device="cpu", fused=True)
+    with pytest.raises(ValueError):
+        SplitKvDecoder(None, SplitKvPlan(ctx=256, world=2, n_seq=1, n_head=8), 0, device="cpu", fused="both")
