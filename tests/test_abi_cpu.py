@@ -74,3 +74,35 @@ def test_splitkv_comm_rejects_bad_arguments_without_a_device(lib_built):
     assert L.mx230_splitkv_wait_merge(None, None, None) == _lib.ERR_INVALID_ARG
     assert L.mx230_splitkv_comm_disconnect(None) == _lib.ERR_INVALID_ARG
     L.mx230_splitkv_comm_destroy(None)   # a null communicator is ignored
+
+
+def test_header_is_plain_c_and_links_against_the_library(lib_built, tmp_path):
+    """The boundary is a C ABI: the header compiles as pedantic C99 and as C++, and a C program that calls through it
+    links against the shared library and runs without a GPU (version and error-string calls only)."""
+    import shutil
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cc, cxx = shutil.which("gcc") or shutil.which("cc"), shutil.which("g++") or shutil.which("c++")
+    if cc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "abi.c"
+    src.write_text('#include <stdio.h>\n#include <string.h>\n#include "mx230_attn.h"\n'
+                   'int main(void) {\n'
+                   '    mx230_splitkv_comm *c = 0;\n'
+                   '    if (mx230_abi_version() != MX230_ABI_VERSION) return 1;\n'
+                   '    if (mx230_splitkv_comm_create(0, 0, 2, 8, 64, &c) != MX230_ERR_INVALID_ARG) return 2;\n'
+                   '    if (strlen(mx230_last_error()) == 0) return 3;\n'
+                   '    if (mx230_gemm_workspace_bytes(512, 1152, 896, 1) != 512u * 896u * 2u) return 4;\n'
+                   '    puts(mx230_status_string(MX230_ERR_WORKSPACE));\n'
+                   '    return 0;\n}\n')
+    inc = os.path.join(root, "include")
+    subprocess.run([cc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", inc, "-fsyntax-only", str(src)], check=True)
+    if cxx:
+        subprocess.run([cxx, "-std=c++11", "-Wall", "-I", inc, "-fsyntax-only", "-x", "c++", str(src)], check=True)
+    exe = tmp_path / "abi"
+    libdir = os.path.dirname(lib_built)
+    subprocess.run([cc, "-std=c99", "-I", inc, str(src), "-o", str(exe), "-L", libdir, "-lmx230_attn",
+                    "-Wl,-rpath," + libdir], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, (out.returncode, out.stdout, out.stderr)
+    assert out.stdout.strip()
