@@ -255,3 +255,37 @@ def test_prefill_rows_equal_decode_rows():
         assert np.array_equal(out[i], oracle.gqa_decode_f32(rows[8 + i], kc, vc, 8 + i, nh, nkv))
     outq = oracle.prefill(rows[8:], 8, ctx - 8, nh, nkv, stride, nh * 64, cache=cache)
     assert np.array_equal(outq[3], oracle.gqa_decode_q8(rows[11], cache, 11, nh, 0))
+
+
+def test_gemv_gemm_and_int8_gemv_against_float64():
+    """The projection restatements against an independent float64 evaluation: gemv / gemm (fp32 and fp16 weights, with
+    bias, residual accumulate) to fp32 summation accuracy, gemv_int8 against the same arithmetic written out in numpy
+    (per-group activation quantisation, integer dots, per-column scales)."""
+    rs = np.random.RandomState(5)
+    m, k, n = 5, 96, 40
+    a = oracle.normal((m, k), 61, 0)
+    w = (oracle.normal((k, n), 62, 0) / np.sqrt(k)).astype(np.float32)
+    b = oracle.normal((n,), 63, 0)
+    want = a.astype(np.float64) @ w.astype(np.float64) + b
+    assert np.abs(oracle.gemm(a, w, b) - want).max() < 1e-5
+    wh = w.astype(np.float16)
+    assert np.abs(oracle.gemm(a, wh, b) - (a.astype(np.float64) @ wh.astype(np.float64) + b)).max() < 1e-5
+    y0 = oracle.normal((n,), 64, 0)
+    assert np.abs(oracle.gemv(a[0], w, None, y0, True) - (y0 + a[0].astype(np.float64) @ w.astype(np.float64))).max() < 1e-5
+    assert oracle.gemm(np.zeros((0, k), np.float32), w, b).shape == (0, n)
+    # int8 weights: groups of `ag` activations share a scale amax / 127; y = (sum_g dot_g * xs_g) * scale[o] + b[o]
+    w8 = rs.randint(-127, 128, size=(k, n)).astype(np.int8)
+    scales = (rs.rand(n) * 0.01 + 0.001).astype(np.float32)
+    x = a[1]
+    for ag in (4, 8):
+        acc = np.zeros(n, np.float64)
+        for g0 in range(0, k, ag):
+            xg = x[g0:g0 + ag]
+            amax = np.float32(np.abs(xg).max())
+            if amax == 0:
+                continue
+            codes = np.clip(np.rint(xg * (np.float32(127.0) / amax)), -127, 127).astype(np.int64)
+            acc += (codes @ w8[g0:g0 + ag].astype(np.int64)) * np.float64(amax / np.float32(127.0))
+        want8 = acc * scales + b
+        got8 = oracle.gemv_int8(x, oracle.pack_int8_weights(w8), scales, b, ag=ag)
+        assert np.abs(got8 - want8).max() < 2e-4 * max(1.0, np.abs(want8).max()), ag
